@@ -1,0 +1,334 @@
+"""Public attention entry points, same names and arguments as the reference
+(flaxattention/core/attention.py): ``flax_attention`` (:169-218), ``flax_attention_pallas``
+(:220-312) and ``math_attention`` (:67-106).
+
+All three run the hand-written sm_100a kernels through the C ABI (``_cabi``): the flash
+forward (or the split-KV decode kernel for short query blocks), and the flash backward
+through ``torch.autograd`` where the reference uses ``jax.custom_vjp``
+(flaxattention/kernel/attention.py:166-168, :653).  Inputs are torch CUDA tensors; numpy
+arrays are copied to the current CUDA device and the result is copied back.  There is no
+CPU implementation.
+"""
+from __future__ import annotations
+
+import math
+from typing import Any, Callable, Dict, Optional, Tuple, Union
+
+import numpy as np
+import torch
+
+from . import _cabi
+from .blockmask import BlockMask, module_for, noop_mask
+
+_DTYPES = {torch.float16: _cabi.FA_F16, torch.bfloat16: _cabi.FA_BF16, torch.float32: _cabi.FA_F32}
+
+# decode path: query blocks of at most this many rows go through the split-KV kernel
+DECODE_MAX_SQ = 64
+DECODE_MIN_SKV = 512
+
+
+def _identity(score, batch, head, token_q, token_kv):
+    return score
+
+
+def _validate_sdpa_input(query, key, value):
+    if query.dtype != key.dtype or query.dtype != value.dtype:
+        raise ValueError(
+            f"Expected query, key, and value to have the same dtype, "
+            f"but got query.dtype: {query.dtype}, key.dtype: {key.dtype}, "
+            f"and value.dtype: {value.dtype} instead."
+        )
+    if query.ndim < 2 or key.ndim < 2 or value.ndim < 2:
+        raise ValueError(
+            f"Expected query, key, and value to all be  at least 2 dimensional, but got query.dim: "
+            f"{query.ndim}, key.dim: {key.ndim} and value.dim: {value.ndim} instead."
+        )
+
+
+def _validate_embed_dim(query, key, value):
+    if query.shape[-1] != key.shape[-1]:
+        raise ValueError(
+            f"Expect query and key/value to have the same embedding dimension "
+            f"but got E={query.shape[-1]} and E={key.shape[-1]}."
+        )
+    if value.shape[-1] > query.shape[-1]:
+        raise ValueError(
+            f"NYI: Currently value embedding dimension must be less than or equal to query embedding dimension. "
+            f"Got Ev={value.shape[-1]} and E={query.shape[-1]}."
+        )
+
+
+def _validate_heads(hq: int, hkv: int, enable_gqa: bool):
+    if (not enable_gqa) and hq != hkv:
+        raise ValueError(
+            f"Expect query and key/value to have the same number of heads "
+            f"but got Hq={hq} and Hkv={hkv}. "
+            f"Try setting enable_gqa=True for GQA."
+        )
+    if enable_gqa and hq % hkv != 0:
+        raise ValueError(
+            f"Expect number of query heads to be a multiple of kv heads for GQA "
+            f"but got Hq={hq} and Hkv={hkv}."
+        )
+
+
+# --------------------------------------------------------------------------------------
+# C-ABI call plumbing
+# --------------------------------------------------------------------------------------
+def _tensor(t: torch.Tensor, layout: str) -> _cabi.FaTensor:
+    """layout 'bhsd' or 'bshd'; the last dim must be contiguous."""
+    if t.stride(-1) != 1:
+        raise ValueError("the head dimension must be contiguous")
+    if layout == "bhsd":
+        return _cabi.FaTensor(t.data_ptr(), t.stride(0), t.stride(1), t.stride(2))
+    return _cabi.FaTensor(t.data_ptr(), t.stride(0), t.stride(2), t.stride(1))
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+class _Call:
+    """Everything one attention problem needs besides q/k/v: shapes, mods, tables."""
+
+    def __init__(self, query, key, value, score_mod, mask_mod, block_mask: Optional[BlockMask], scale, layout,
+                 b_offset, h_offset, options):
+        if query.device.type != "cuda":
+            raise RuntimeError("flaxattention_b200 runs on CUDA tensors only; there is no CPU path")
+        if query.dtype not in _DTYPES:
+            raise ValueError(f"unsupported dtype {query.dtype}; use float16, bfloat16 or float32")
+        self.layout = layout
+        if layout == "bhsd":
+            self.B, self.Hq, self.Sq, self.D = query.shape
+            _, self.Hkv, self.Skv, self.Dv = value.shape
+        else:
+            self.B, self.Sq, self.Hq, self.D = query.shape
+            _, self.Skv, self.Hkv, self.Dv = value.shape
+        self.dtype = query.dtype
+        self.scale = float(scale)
+        self.b_offset, self.h_offset = int(b_offset), int(h_offset)
+        self.block_mask = block_mask
+        if block_mask is not None and block_mask.kv_indices.ndim != 4:
+            raise ValueError("BlockMask tables must be 4-dimensional [B, H, nQ, nKV]")
+        self.module = module_for(score_mod, mask_mod)
+        self.options = dict(options or {})
+
+    def params(self, q, k, v, o, lse) -> _cabi.FaAttnParams:
+        p = _cabi.FaAttnParams()
+        p.dtype = _DTYPES[self.dtype]
+        p.B, p.Hq, p.Hkv, p.Sq, p.Skv, p.D, p.Dv = self.B, self.Hq, self.Hkv, self.Sq, self.Skv, self.D, self.Dv
+        p.scale = self.scale
+        p.b_offset, p.h_offset = self.b_offset, self.h_offset
+        p.q, p.k, p.v, p.o = (_tensor(t, self.layout) for t in (q, k, v, o))
+        p.lse = _ptr(lse)
+        bm = self.block_mask
+        if bm is not None:
+            t = p.tables
+            if bm.kv_num_blocks.device != q.device:
+                raise ValueError("the BlockMask tables live on a different device than the inputs")
+            t.kv_num_blocks, t.kv_indices = _ptr(bm.kv_num_blocks), _ptr(bm.kv_indices)
+            t.full_kv_num_blocks, t.full_kv_indices = _ptr(bm.full_kv_num_blocks), _ptr(bm.full_kv_indices)
+            t.q_num_blocks, t.q_indices = _ptr(bm.q_num_blocks), _ptr(bm.q_indices)
+            t.full_q_num_blocks, t.full_q_indices = _ptr(bm.full_q_num_blocks), _ptr(bm.full_q_indices)
+            t.mask_B, t.mask_H = bm.kv_indices.shape[0], bm.kv_indices.shape[1]
+            t.num_q_blocks, t.num_kv_blocks = bm.kv_indices.shape[2], bm.kv_indices.shape[3]
+            t.q_block_size, t.kv_block_size = bm.BLOCK_SIZE
+            for x in (bm.kv_num_blocks, bm.kv_indices, bm.full_kv_num_blocks, bm.full_kv_indices, bm.q_num_blocks,
+                      bm.q_indices, bm.full_q_num_blocks, bm.full_q_indices):
+                if x is not None and (x.dtype != torch.int32 or not x.is_contiguous()):
+                    raise ValueError("BlockMask tables must be contiguous int32 tensors")
+        return p
+
+    def use_decode(self) -> bool:
+        force = self.options.get("path")
+        if force == "decode":
+            return True
+        if force == "fwd":
+            return False
+        return self.Sq <= DECODE_MAX_SQ and self.Skv >= DECODE_MIN_SKV and self.dtype != torch.float32
+
+    def out_like(self, query):
+        if self.layout == "bhsd":
+            return torch.empty(self.B, self.Hq, self.Sq, self.Dv, dtype=query.dtype, device=query.device)
+        return torch.empty(self.B, self.Sq, self.Hq, self.Dv, dtype=query.dtype, device=query.device)
+
+
+def _forward(call: _Call, q, k, v):
+    L = _cabi.lib()
+    out = call.out_like(q)
+    lse = torch.empty(call.B, call.Hq, call.Sq, dtype=torch.float32, device=q.device)
+    p = call.params(q, k, v, out, lse)
+    stream = torch.cuda.current_stream(q.device).cuda_stream
+    with torch.cuda.device(q.device):
+        if call.use_decode():
+            splits = int(call.options.get("num_splits", 0))
+            if splits <= 0:
+                sms = torch.cuda.get_device_properties(q.device).multi_processor_count
+                splits = L.fa_decode_num_splits(p, sms)
+            nbytes = L.fa_decode_workspace_bytes(p, splits)
+            ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
+            _cabi.check(L.fa_decode(call.module.handle, p, splits, ws.data_ptr(), nbytes, stream))
+        else:
+            _cabi.check(L.fa_fwd(call.module.handle, p, stream))
+    return out, lse
+
+
+def _backward(call: _Call, q, k, v, out, lse, dout):
+    L = _cabi.lib()
+    if dout.stride(-1) != 1:
+        dout = dout.contiguous()
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    p = call.params(q, k, v, out, lse)
+    nbytes = L.fa_bwd_workspace_bytes(p)
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
+    stream = torch.cuda.current_stream(q.device).cuda_stream
+    with torch.cuda.device(q.device):
+        _cabi.check(L.fa_bwd(call.module.handle, p, _tensor(dout, call.layout), _tensor(dq, call.layout),
+                             _tensor(dk, call.layout), _tensor(dv, call.layout), ws.data_ptr(), nbytes, stream))
+    return dq, dk, dv
+
+
+class _AttentionFn(torch.autograd.Function):
+    """Forward saves (q, k, v, out, lse), the residuals of the reference's custom_vjp
+    (flaxattention/kernel/attention.py:335); backward returns (dq, dk, dv)."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, call: _Call):
+        out, lse = _forward(call, q, k, v)
+        ctx.call = call
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.mark_non_differentiable(lse)
+        return out, lse
+
+    @staticmethod
+    def backward(ctx, dout, _dlse):
+        q, k, v, out, lse = ctx.saved_tensors
+        dq, dk, dv = _backward(ctx.call, q, k, v, out, lse, dout)
+        return dq, dk, dv, None
+
+
+def _run(call: _Call, q, k, v):
+    if torch.is_grad_enabled() and (q.requires_grad or k.requires_grad or v.requires_grad):
+        return _AttentionFn.apply(q, k, v, call)
+    return _forward(call, q, k, v)
+
+
+def _as_cuda(x):
+    """numpy -> CUDA tensor on the current device (host-to-device copy); tensors pass through."""
+    if isinstance(x, np.ndarray):
+        if not torch.cuda.is_available():
+            raise RuntimeError("flaxattention_b200 needs a CUDA device (B200, sm_100a); there is no CPU path")
+        return torch.from_numpy(x).cuda(non_blocking=True), True
+    return x, False
+
+
+# --------------------------------------------------------------------------------------
+# public API
+# --------------------------------------------------------------------------------------
+def flax_attention(
+    query,
+    key,
+    value,
+    score_mod: Optional[Callable] = None,
+    block_mask: Optional[BlockMask] = None,
+    scale: Optional[float] = None,
+    enable_gqa: bool = False,
+    return_lse: bool = False,
+    kernel_options: Optional[Dict[str, Any]] = None,
+    *,
+    b_offset: int = 0,
+    h_offset: int = 0,
+) -> Union[torch.Tensor, Tuple[torch.Tensor, torch.Tensor]]:
+    """Attention with a fused ``score_mod`` and a BlockMask, ``[B, H, S, D]`` layout.
+
+    Returns the output in the input dtype and, with ``return_lse``, the natural-log
+    logsumexp ``[B, Hq, Sq]`` in float32 (``-inf`` for fully masked rows, whose output is 0).
+    ``kernel_options``: ``{"path": "fwd" | "decode", "num_splits": int}``.
+    ``b_offset`` / ``h_offset`` are the global indices of the first batch / head of a
+    batch x heads shard; the mods see global indices.
+    """
+    query, from_np = _as_cuda(query)
+    key, _ = _as_cuda(key)
+    value, _ = _as_cuda(value)
+    _validate_sdpa_input(query, key, value)
+    _validate_embed_dim(query, key, value)
+    if query.ndim != 4 or key.ndim != 4 or value.ndim != 4:
+        raise NotImplementedError("NYI: query, key, and value must be 4D tensors")
+    _validate_heads(query.shape[-3], key.shape[-3], enable_gqa)
+    if score_mod is None:
+        score_mod = _identity
+    if scale is None:
+        scale = 1.0 / math.sqrt(query.shape[-1])
+    mask_mod = None if block_mask is None else block_mask.mask_mod
+    call = _Call(query, key, value, score_mod, mask_mod, block_mask, scale, "bhsd", b_offset, h_offset,
+                 kernel_options)
+    out, lse = _run(call, query, key, value)
+    if from_np:
+        out, lse = out.cpu().numpy(), lse.cpu().numpy()
+    if return_lse:
+        return out, lse
+    return out
+
+
+def math_attention(query, key, value, score_mod, block_mask: Tuple, scale, kernel_options=None,
+                   score_mod_other_buffers: Tuple = (), mask_mod_other_buffers: Tuple = (), use_pallas: bool = False):
+    """Signature of the reference's ``math_attention`` (core/attention.py:67-106): takes
+    ``BlockMask.as_tuple()`` and returns ``(output, logsumexp / ln 2)``.  It runs the same
+    fused kernels as ``flax_attention``; a dense score tensor is never built."""
+    if score_mod_other_buffers or mask_mod_other_buffers:
+        raise NotImplementedError("captured buffers are not supported")
+    mask_mod = block_mask[-1]
+    bm = BlockMask(*block_mask[:8], (block_mask[8], block_mask[9]), mask_mod)
+    call = _Call(query, key, value, score_mod, mask_mod, bm, scale, "bhsd", 0, 0, kernel_options)
+    out, lse = _run(call, query, key, value)
+    return out, lse / math.log(2.0)
+
+
+def flax_attention_pallas(
+    query,
+    key,
+    value,
+    score_mod: Optional[Callable] = None,
+    mask_mod: Optional[Callable] = None,
+    block_q: int = 64,
+    block_k: int = 64,
+    sm_scale: Optional[float] = None,
+    bhln: bool = True,
+    enable_gqa: bool = False,
+    *,
+    block_mask: Optional[BlockMask] = None,
+    return_lse: bool = False,
+    b_offset: int = 0,
+    h_offset: int = 0,
+):
+    """The reference's fused-kernel entry point.  ``bhln=True`` means ``[B, H, L, N]``
+    inputs, ``False`` ``[B, L, H, N]``; either way the kernels read the tensors through
+    strides, so the transposed copies the reference makes (core/attention.py:243-246, :312)
+    do not happen.  ``block_q`` / ``block_k`` are accepted for compatibility; tile sizes are
+    chosen by the library.  Beyond the reference: GQA is implemented (the reference only
+    validates it), and an optional ``block_mask`` enables block skipping (its ``mask_mod``
+    is used when ``mask_mod`` is not given)."""
+    del block_q, block_k
+    query, from_np = _as_cuda(query)
+    key, _ = _as_cuda(key)
+    value, _ = _as_cuda(value)
+    _validate_sdpa_input(query, key, value)
+    _validate_embed_dim(query, key, value)
+    if query.ndim != 4 or key.ndim != 4 or value.ndim != 4:
+        raise NotImplementedError("NYI: query, key, and value must be 4D tensors")
+    h_axis = 1 if bhln else 2
+    _validate_heads(query.shape[h_axis], key.shape[h_axis], enable_gqa)
+    if sm_scale is None:
+        sm_scale = 1 / math.sqrt(query.shape[-1])
+    if score_mod is None:
+        score_mod = _identity
+    if mask_mod is None:
+        mask_mod = block_mask.mask_mod if block_mask is not None else noop_mask
+    call = _Call(query, key, value, score_mod, mask_mod, block_mask, sm_scale, "bhsd" if bhln else "bshd",
+                 b_offset, h_offset, None)
+    out, lse = _run(call, query, key, value)
+    if from_np:
+        out, lse = out.cpu().numpy(), lse.cpu().numpy()
+    if return_lse:
+        return out, lse
+    return out

@@ -1,0 +1,535 @@
+// Host side of the C ABI declared in include/flaxattn.h, plus the kernels that do not
+// depend on a score_mod / mask_mod (table compaction, backward preprocess, decode combine).
+//
+// Kernels that embed user mods are compiled at run time: the mod fragment is placed in
+// front of a kernel template from the kernels/ directory, compiled for sm_100a with
+// NVRTC, cached in memory per module and on disk per content hash, and loaded through the
+// context-independent library API of the CUDA runtime.
+#include <cuda_runtime.h>
+#include <nvrtc.h>
+
+#include <dlfcn.h>
+#include <sys/stat.h>
+#include <unistd.h>
+
+#include <atomic>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <fstream>
+#include <map>
+#include <mutex>
+#include <sstream>
+#include <string>
+#include <vector>
+
+#include "../../include/flaxattn.h"
+#include "kernels/fa_params.h"
+
+namespace {
+
+thread_local std::string g_err;
+int fail(int code, const std::string& msg) {
+  g_err = msg;
+  return code;
+}
+#define FA_CUDA_CHECK(expr)                                                                       \
+  do {                                                                                            \
+    cudaError_t e_ = (expr);                                                                      \
+    if (e_ != cudaSuccess)                                                                        \
+      return fail(FA_ECUDA, std::string(#expr) + ": " + cudaGetErrorName(e_) + ": " + cudaGetErrorString(e_)); \
+  } while (0)
+
+std::mutex g_mu;
+std::string g_kernel_dir, g_cache_dir;
+bool g_cache_dir_set = false;
+std::atomic<int> g_compile_count{0};
+
+// ---- small utilities -------------------------------------------------------------------
+uint64_t fnv1a(const std::string& s, uint64_t seed) {
+  uint64_t h = seed;
+  for (unsigned char c : s) {
+    h ^= c;
+    h *= 1099511628211ull;
+  }
+  return h;
+}
+std::string hash_hex(const std::string& s) {
+  char buf[40];
+  snprintf(buf, sizeof buf, "%016llx%016llx", (unsigned long long)fnv1a(s, 1469598103934665603ull),
+           (unsigned long long)fnv1a(s, 0x9e3779b97f4a7c15ull));
+  return buf;
+}
+bool read_file(const std::string& path, std::string& out) {
+  std::ifstream f(path, std::ios::binary);
+  if (!f) return false;
+  std::ostringstream ss;
+  ss << f.rdbuf();
+  out = ss.str();
+  return true;
+}
+void mkdirs(const std::string& path) {
+  std::string cur;
+  for (size_t i = 0; i < path.size(); ++i) {
+    cur.push_back(path[i]);
+    if (path[i] == '/' || i + 1 == path.size()) mkdir(cur.c_str(), 0755);
+  }
+}
+std::string kernel_dir() {
+  if (!g_kernel_dir.empty()) return g_kernel_dir;
+  if (const char* e = getenv("FLAXATTN_KERNEL_DIR")) return g_kernel_dir = e;
+  Dl_info info;
+  if (dladdr((void*)&fnv1a, &info) && info.dli_fname) {
+    std::string p = info.dli_fname;
+    size_t k = p.rfind('/');
+    const std::string base = k == std::string::npos ? std::string(".") : p.substr(0, k);
+    struct stat sb;
+    g_kernel_dir = base + "/kernels";
+    if (stat(g_kernel_dir.c_str(), &sb) != 0) g_kernel_dir = base + "/csrc/kernels";
+  } else {
+    g_kernel_dir = "kernels";
+  }
+  return g_kernel_dir;
+}
+std::string cache_dir() {
+  if (g_cache_dir_set) return g_cache_dir;
+  g_cache_dir_set = true;
+  if (const char* e = getenv("FLAXATTN_CACHE_DIR")) return g_cache_dir = e;
+  const char* home = getenv("HOME");
+  g_cache_dir = std::string(home ? home : "/tmp") + "/.cache/flaxattn_b200";
+  return g_cache_dir;
+}
+
+const char* const kTemplateFiles[] = {"fa_params.h", "fa_common.cuh", "fa_fwd.cuh", "fa_bwd.cuh",
+                                      "fa_decode.cuh", "fa_blockmask.cuh"};
+std::string g_templates_hash;
+int templates_hash(std::string& out) {
+  if (g_templates_hash.empty()) {
+    std::string all;
+    for (const char* f : kTemplateFiles) {
+      std::string s;
+      if (read_file(kernel_dir() + "/" + f, s)) all += s;
+      all += "\n--\n";
+    }
+    if (all.size() < 200) return fail(FA_ECOMPILE, "kernel templates not found in '" + kernel_dir() + "'");
+    g_templates_hash = hash_hex(all);
+  }
+  out = g_templates_hash;
+  return FA_OK;
+}
+
+// ---- run-time compilation --------------------------------------------------------------
+int nvrtc_compile(const std::string& src, const std::vector<std::string>& opts, std::string& cubin) {
+  nvrtcProgram prog;
+  nvrtcResult r = nvrtcCreateProgram(&prog, src.c_str(), "flaxattn_kernel.cu", 0, nullptr, nullptr);
+  if (r != NVRTC_SUCCESS) return fail(FA_ECOMPILE, std::string("nvrtcCreateProgram: ") + nvrtcGetErrorString(r));
+  std::vector<const char*> o;
+  for (auto& s : opts) o.push_back(s.c_str());
+  r = nvrtcCompileProgram(prog, (int)o.size(), o.data());
+  if (r != NVRTC_SUCCESS) {
+    size_t n = 0;
+    nvrtcGetProgramLogSize(prog, &n);
+    std::string log(n, '\0');
+    if (n) nvrtcGetProgramLog(prog, &log[0]);
+    nvrtcDestroyProgram(&prog);
+    return fail(FA_ECOMPILE, std::string("kernel compilation failed: ") + nvrtcGetErrorString(r) + "\n" + log);
+  }
+  size_t n = 0;
+  r = nvrtcGetCUBINSize(prog, &n);
+  if (r != NVRTC_SUCCESS || n == 0) {
+    nvrtcDestroyProgram(&prog);
+    return fail(FA_ECOMPILE, "nvrtcGetCUBINSize failed");
+  }
+  cubin.resize(n);
+  nvrtcGetCUBIN(prog, &cubin[0]);
+  nvrtcDestroyProgram(&prog);
+  g_compile_count++;
+  return FA_OK;
+}
+
+struct Kernel {
+  std::string cubin;
+  std::string entry;
+  cudaLibrary_t lib = nullptr;
+  cudaKernel_t fn = nullptr;
+  int smem = 0;
+  unsigned long long smem_set_mask = 0;  // devices on which the dynamic smem limit was raised
+};
+
+}  // namespace
+
+struct fa_module {
+  std::string mod_source;
+  std::map<std::string, Kernel*> kernels;  // key: template + defines
+};
+
+namespace {
+
+const char* const kDefaultMods =
+    "#define FA_HAS_SCORE_MOD 0\n#define FA_HAS_MASK_MOD 0\n"
+    "__device__ __forceinline__ float fa_score_mod(float s, int, int, int, int) { return s; }\n"
+    "__device__ __forceinline__ float fa_score_mod_grad(float, int, int, int, int) { return 1.0f; }\n"
+    "__device__ __forceinline__ bool fa_mask_mod(int, int, int, int) { return true; }\n";
+
+// Returns the compiled kernel `entry` of `tmpl` with the given defines (compiling if needed).
+int get_kernel(fa_module* m, const std::string& tmpl, const std::string& defines, const std::string& entry,
+               int smem, Kernel** out) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  const std::string key = tmpl + "|" + defines + "|" + entry;
+  auto it = m->kernels.find(key);
+  if (it != m->kernels.end()) {
+    *out = it->second;
+    return FA_OK;
+  }
+  std::string th;
+  if (int rc = templates_hash(th)) return rc;
+  std::string src = defines + "\n" + m->mod_source + "\n#include \"" + tmpl + "\"\n";
+  std::vector<std::string> opts = {"--gpu-architecture=sm_100a", "-std=c++17", "-lineinfo",
+                                   "-I" + kernel_dir()};
+  int major = 0, minor = 0;
+  nvrtcVersion(&major, &minor);
+  std::string h = hash_hex(src + "|" + th + "|" + std::to_string(major) + "." + std::to_string(minor));
+  std::string cubin;
+  const std::string cdir = cache_dir();
+  const std::string cpath = cdir + "/" + h + ".cubin";
+  bool from_cache = !cdir.empty() && read_file(cpath, cubin) && cubin.size() > 64;
+  if (!from_cache) {
+    if (int rc = nvrtc_compile(src, opts, cubin)) return rc;
+    if (!cdir.empty()) {
+      mkdirs(cdir);
+      const std::string tmp = cpath + ".tmp" + std::to_string((long)getpid());
+      std::ofstream f(tmp, std::ios::binary);
+      if (f) {
+        f.write(cubin.data(), (std::streamsize)cubin.size());
+        f.close();
+        rename(tmp.c_str(), cpath.c_str());
+      }
+    }
+  }
+  Kernel* k = new Kernel();
+  k->cubin.swap(cubin);
+  k->entry = entry;
+  k->smem = smem;
+  m->kernels[key] = k;
+  *out = k;
+  return FA_OK;
+}
+
+// Loads the kernel on first launch and raises its dynamic shared-memory limit on this device.
+int ready_kernel(Kernel* k) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (k->fn == nullptr) {
+    FA_CUDA_CHECK(cudaLibraryLoadData(&k->lib, k->cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0));
+    FA_CUDA_CHECK(cudaLibraryGetKernel(&k->fn, k->lib, k->entry.c_str()));
+  }
+  int dev = 0;
+  FA_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 64 && !(k->smem_set_mask >> dev & 1ull)) {
+    if (k->smem > 48 * 1024)
+      FA_CUDA_CHECK(cudaFuncSetAttribute((const void*)k->fn, cudaFuncAttributeMaxDynamicSharedMemorySize, k->smem));
+    k->smem_set_mask |= 1ull << dev;
+  }
+  return FA_OK;
+}
+
+int launch(Kernel* k, dim3 grid, dim3 block, void* params, void* stream) {
+  if (int rc = ready_kernel(k)) return rc;
+  void* args[] = {params};
+  FA_CUDA_CHECK(cudaLaunchKernel((const void*)k->fn, grid, block, args, (size_t)k->smem, (cudaStream_t)stream));
+  return FA_OK;
+}
+
+// ---- configuration ---------------------------------------------------------------------
+int esize(int dtype) { return dtype == FA_F32 ? 4 : 2; }
+int pitch(int cols, int es) { return cols * es + 16; }
+constexpr int kMaxSmem = 227 * 1024;
+
+struct FwdCfg {
+  int BM, BN, warps, smem;
+};
+int fwd_smem(int dtype, int D, int Dv, int BM, int BN) {
+  const int es = esize(dtype);
+  int s = BM * pitch(D, es) + 2 * BN * pitch(D, es) + 2 * BN * pitch(Dv, es);
+  if (dtype == FA_F32) s += BM * pitch(BN, 4);
+  return s;
+}
+bool divides_or_single(int tile, int block, int nblocks) { return nblocks <= 1 || block % tile == 0; }
+
+int pick_fwd(int dtype, int D, int Dv, int Sq, const FaTables* t, FwdCfg& c) {
+  struct Cand { int BM, BN, warps; };
+  std::vector<Cand> cands;
+  if (dtype == FA_F32) {
+    cands = {{64, 64, 4}, {64, 32, 4}, {32, 32, 2}, {16, 32, 1}, {16, 16, 1}};
+  } else {
+    if (D <= 64 && Sq > 64) cands.push_back({128, 64, 4});
+    if (D <= 128 && Sq > 64) cands.push_back({128, 64, 8});
+    cands.push_back({64, 64, 4});
+    cands.push_back({64, 32, 4});
+    cands.push_back({32, 32, 2});
+    cands.push_back({16, 32, 1});
+    cands.push_back({16, 16, 1});
+  }
+  for (auto& x : cands) {
+    if (t && t->kv_num) {
+      if (!divides_or_single(x.BM, t->QB, t->nQ) || !divides_or_single(x.BN, t->KVB, t->nKV)) continue;
+    }
+    const int s = fwd_smem(dtype, D, Dv, x.BM, x.BN);
+    if (s > kMaxSmem) continue;
+    c = {x.BM, x.BN, x.warps, s};
+    return FA_OK;
+  }
+  return fail(FA_EUNSUPPORTED, "no forward tile configuration fits this head dim / BlockMask block size "
+                               "(block sizes must be multiples of 16 unless there is a single block)");
+}
+
+std::string defs(std::initializer_list<std::pair<const char*, int>> kv) {
+  std::string s;
+  for (auto& p : kv) s += std::string("#define ") + p.first + " " + std::to_string(p.second) + "\n";
+  return s;
+}
+
+// ---- argument validation ---------------------------------------------------------------
+int check_tensor(const fa_tensor& t, const char* name, int es, bool required = true) {
+  if (t.ptr == nullptr) return required ? fail(FA_EINVAL, std::string(name) + ": null pointer") : FA_OK;
+  if (((uintptr_t)t.ptr & 15) != 0) return fail(FA_EINVAL, std::string(name) + ": pointer must be 16-byte aligned");
+  if ((t.stride_b * es) % 16 || (t.stride_h * es) % 16 || (t.stride_s * es) % 16)
+    return fail(FA_EINVAL, std::string(name) + ": byte strides must be multiples of 16");
+  return FA_OK;
+}
+FaTensor cvt(const fa_tensor& t) { return FaTensor{t.ptr, t.stride_b, t.stride_h, t.stride_s}; }
+FaTensor cvt(const fa_tensor* t) { return t ? cvt(*t) : FaTensor{nullptr, 0, 0, 0}; }
+
+int check_common(fa_module* m, const fa_attn_params* p) {
+  if (!m) return fail(FA_EINVAL, "module is null");
+  if (!p) return fail(FA_EINVAL, "params is null");
+  if (p->dtype < FA_F16 || p->dtype > FA_F32) return fail(FA_EINVAL, "unknown dtype");
+  if (p->B <= 0 || p->Hq <= 0 || p->Hkv <= 0 || p->Sq <= 0 || p->Skv <= 0)
+    return fail(FA_EINVAL, "B, Hq, Hkv, Sq, Skv must be positive");
+  if (p->Hq % p->Hkv) return fail(FA_EINVAL, "Hq must be a multiple of Hkv");
+  if (p->D <= 0 || p->D % 16 || p->Dv <= 0 || p->Dv % 16)
+    return fail(FA_EUNSUPPORTED, "head dims must be positive multiples of 16");
+  if (p->Dv > p->D) return fail(FA_EINVAL, "value head dim must not exceed the query/key head dim");
+  if (p->D > 256) return fail(FA_EUNSUPPORTED, "head dim above 256 is not supported");
+  if (p->B > 65535 || p->Hq > 65535) return fail(FA_EUNSUPPORTED, "B and Hq must not exceed 65535");
+  const int es = esize(p->dtype);
+  if (int rc = check_tensor(p->q, "q", es)) return rc;
+  if (int rc = check_tensor(p->k, "k", es)) return rc;
+  if (int rc = check_tensor(p->v, "v", es)) return rc;
+  if (int rc = check_tensor(p->o, "o", es)) return rc;
+  const fa_block_tables& t = p->tables;
+  if (t.kv_num_blocks) {
+    if (!t.kv_indices) return fail(FA_EINVAL, "kv_indices is null");
+    if ((t.full_kv_num_blocks == nullptr) != (t.full_kv_indices == nullptr))
+      return fail(FA_EINVAL, "full_kv_num_blocks and full_kv_indices must be both given or both null");
+    if (t.num_q_blocks <= 0 || t.num_kv_blocks <= 0 || t.q_block_size <= 0 || t.kv_block_size <= 0)
+      return fail(FA_EINVAL, "BlockMask grid and block sizes must be positive");
+    if (!(t.mask_B == 1 || t.mask_B == p->B) || !(t.mask_H == 1 || t.mask_H == p->Hq))
+      return fail(FA_EINVAL, "BlockMask batch/head dims must be 1 or match B/Hq");
+    if ((long long)t.num_q_blocks * t.q_block_size < p->Sq || (long long)t.num_kv_blocks * t.kv_block_size < p->Skv)
+      return fail(FA_EINVAL, "BlockMask does not cover the sequence lengths");
+  }
+  return FA_OK;
+}
+
+FaTables cvt_tables(const fa_block_tables& t) {
+  FaTables r;
+  r.kv_num = t.kv_num_blocks; r.kv_idx = t.kv_indices;
+  r.full_kv_num = t.full_kv_num_blocks; r.full_kv_idx = t.full_kv_indices;
+  r.q_num = t.q_num_blocks; r.q_idx = t.q_indices;
+  r.full_q_num = t.full_q_num_blocks; r.full_q_idx = t.full_q_indices;
+  r.mB = t.mask_B; r.mH = t.mask_H; r.nQ = t.num_q_blocks; r.nKV = t.num_kv_blocks;
+  r.QB = t.q_block_size; r.KVB = t.kv_block_size;
+  return r;
+}
+
+void fill_params(const fa_attn_params* p, FaParams& k) {
+  memset(&k, 0, sizeof k);
+  k.q = cvt(p->q); k.k = cvt(p->k); k.v = cvt(p->v); k.o = cvt(p->o);
+  k.lse = p->lse; k.status = p->status;
+  k.B = p->B; k.Hq = p->Hq; k.Hkv = p->Hkv; k.Sq = p->Sq; k.Skv = p->Skv; k.D = p->D; k.Dv = p->Dv;
+  k.b_off = p->b_offset; k.h_off = p->h_offset; k.scale = p->scale;
+  k.t = cvt_tables(p->tables);
+}
+
+// ---- kernels that do not depend on the mods --------------------------------------------
+
+// One warp per table row.  The reference orders a row by a stable descending argsort of the
+// 0/1 block grid (flaxattention/core/blockmask.py:57-64): set columns ascending, then the
+// unset columns ascending.  `transposed` builds the q-tables from the same class grid.
+__global__ void fa_tables_kernel(const signed char* __restrict__ cls, int rows_per_bh, int cols, int want,
+                                 bool transposed, int nQ, int nKV, long long n_rows,
+                                 int* __restrict__ num_out, int* __restrict__ idx_out) {
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= n_rows) return;
+  const int lane = threadIdx.x & 31;
+  const long long bh = row / rows_per_bh;
+  const int r = (int)(row - bh * rows_per_bh);
+  const signed char* g = cls + bh * (long long)nQ * nKV;
+  auto is_set = [&](int c) -> bool {
+    const signed char v = transposed ? g[(long long)c * nKV + r] : g[(long long)r * nKV + c];
+    return v == want;
+  };
+  int total = 0;
+  for (int c0 = 0; c0 < cols; c0 += 32) {
+    const int c = c0 + lane;
+    const bool s = c < cols && is_set(c);
+    total += __popc(__ballot_sync(0xffffffffu, s));
+  }
+  int n_set = 0, n_unset = 0;
+  int* out = idx_out + row * cols;
+  for (int c0 = 0; c0 < cols; c0 += 32) {
+    const int c = c0 + lane;
+    const bool in = c < cols;
+    const bool s = in && is_set(c);
+    const unsigned bs = __ballot_sync(0xffffffffu, s);
+    const unsigned bu = __ballot_sync(0xffffffffu, in && !s);
+    const unsigned lt = (1u << lane) - 1u;
+    if (s) out[n_set + __popc(bs & lt)] = c;
+    else if (in) out[total + n_unset + __popc(bu & lt)] = c;
+    n_set += __popc(bs);
+    n_unset += __popc(bu);
+  }
+  if (lane == 0) num_out[row] = total;
+}
+
+}  // namespace
+
+// ======================================================================================
+// C ABI
+// ======================================================================================
+extern "C" {
+
+const char* fa_last_error(void) { return g_err.c_str(); }
+int fa_version(void) { return 100; }
+
+int fa_set_kernel_dir(const char* path) {
+  if (!path) return fail(FA_EINVAL, "path is null");
+  std::lock_guard<std::mutex> lk(g_mu);
+  g_kernel_dir = path;
+  g_templates_hash.clear();
+  return FA_OK;
+}
+int fa_set_cache_dir(const char* path) {
+  if (!path) return fail(FA_EINVAL, "path is null");
+  std::lock_guard<std::mutex> lk(g_mu);
+  g_cache_dir = path;
+  g_cache_dir_set = true;
+  return FA_OK;
+}
+int fa_compile_count(void) { return g_compile_count.load(); }
+
+int fa_module_create(const char* mod_source, fa_module** out) {
+  if (!out) return fail(FA_EINVAL, "out is null");
+  fa_module* m = new fa_module();
+  m->mod_source = (mod_source && *mod_source) ? mod_source : kDefaultMods;
+  *out = m;
+  return FA_OK;
+}
+
+void fa_module_destroy(fa_module* m) {
+  if (!m) return;
+  for (auto& kv : m->kernels) {
+    if (kv.second->lib) cudaLibraryUnload(kv.second->lib);
+    delete kv.second;
+  }
+  delete m;
+}
+
+}  // extern "C"
+
+namespace {
+
+int get_fwd_kernel(fa_module* m, int dtype, int D, int Dv, const FwdCfg& c, Kernel** k) {
+  return get_kernel(m, "fa_fwd.cuh",
+                    defs({{"FA_DTYPE", dtype}, {"FA_D", D}, {"FA_DV", Dv}, {"FA_BM", c.BM}, {"FA_BN", c.BN},
+                          {"FA_WARPS", c.warps}}),
+                    "fa_fwd_kernel", c.smem, k);
+}
+int get_blockmask_kernel(fa_module* m, Kernel** k) {
+  return get_kernel(m, "fa_blockmask.cuh", "", "fa_blockmask_classify_kernel", 0, k);
+}
+
+}  // namespace
+
+extern "C" {
+
+int fa_module_prepare(fa_module* m, int kind, int dtype, int D, int Dv, int Sq_hint, int Skv_hint) {
+  if (!m) return fail(FA_EINVAL, "module is null");
+  (void)Skv_hint;
+  Kernel* k = nullptr;
+  switch (kind) {
+    case FA_KIND_FWD: {
+      FwdCfg c;
+      if (int rc = pick_fwd(dtype, D, Dv, Sq_hint, nullptr, c)) return rc;
+      return get_fwd_kernel(m, dtype, D, Dv, c, &k);
+    }
+    case FA_KIND_BLOCKMASK:
+      return get_blockmask_kernel(m, &k);
+    default:
+      return fail(FA_EUNSUPPORTED, "fa_module_prepare: unknown kind");
+  }
+}
+
+int fa_fwd(fa_module* m, const fa_attn_params* p, void* stream) {
+  if (int rc = check_common(m, p)) return rc;
+  FaParams kp;
+  fill_params(p, kp);
+  FwdCfg c;
+  if (int rc = pick_fwd(p->dtype, p->D, p->Dv, p->Sq, &kp.t, c)) return rc;
+  Kernel* k = nullptr;
+  if (int rc = get_fwd_kernel(m, p->dtype, p->D, p->Dv, c, &k)) return rc;
+  kp.n_q_tiles = (p->Sq + c.BM - 1) / c.BM;
+  return launch(k, dim3(kp.n_q_tiles, p->Hq, p->B), dim3(c.warps * 32), &kp, stream);
+}
+
+size_t fa_block_mask_workspace_bytes(int B, int H, int Q_LEN, int KV_LEN, int q_block, int kv_block) {
+  if (B <= 0 || H <= 0 || Q_LEN <= 0 || KV_LEN <= 0 || q_block <= 0 || kv_block <= 0) return 0;
+  const long long nQ = (Q_LEN + q_block - 1) / q_block, nKV = (KV_LEN + kv_block - 1) / kv_block;
+  return (size_t)((long long)B * H * nQ * nKV);
+}
+
+int fa_block_mask(fa_module* m, int B, int H, int Q_LEN, int KV_LEN, int q_block, int kv_block, int b_offset,
+                  int h_offset, int32_t* kv_num_blocks, int32_t* kv_indices, int32_t* full_kv_num_blocks,
+                  int32_t* full_kv_indices, int32_t* q_num_blocks, int32_t* q_indices, int32_t* full_q_num_blocks,
+                  int32_t* full_q_indices, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!m) return fail(FA_EINVAL, "module is null");
+  const size_t need = fa_block_mask_workspace_bytes(B, H, Q_LEN, KV_LEN, q_block, kv_block);
+  if (need == 0) return fail(FA_EINVAL, "B, H, Q_LEN, KV_LEN and block sizes must be positive");
+  if (!kv_num_blocks || !kv_indices) return fail(FA_EINVAL, "kv_num_blocks / kv_indices are null");
+  if ((full_kv_num_blocks == nullptr) != (full_kv_indices == nullptr))
+    return fail(FA_EINVAL, "full_kv_num_blocks and full_kv_indices must be both given or both null");
+  if ((q_num_blocks == nullptr) != (q_indices == nullptr) || (full_q_num_blocks == nullptr) != (full_q_indices == nullptr))
+    return fail(FA_EINVAL, "q tables must be given as (num, indices) pairs");
+  if (full_q_num_blocks && !full_kv_num_blocks) return fail(FA_EINVAL, "full q tables need full kv tables");
+  if (!workspace || workspace_bytes < need) return fail(FA_EWORKSPACE, "block-mask workspace too small");
+  const int nQ = (Q_LEN + q_block - 1) / q_block, nKV = (KV_LEN + kv_block - 1) / kv_block;
+  if ((long long)B * H > 65535 || nQ > 65535) return fail(FA_EUNSUPPORTED, "B*H and the q-block count must not exceed 65535");
+  Kernel* k = nullptr;
+  if (int rc = get_blockmask_kernel(m, &k)) return rc;
+  FaMaskParams mp;
+  mp.cls = (signed char*)workspace;
+  mp.B = B; mp.H = H; mp.nQ = nQ; mp.nKV = nKV; mp.QB = q_block; mp.KVB = kv_block;
+  mp.b_off = b_offset; mp.h_off = h_offset;
+  if (int rc = launch(k, dim3(nKV, nQ, B * H), dim3(256), &mp, stream)) return rc;
+
+  cudaStream_t st = (cudaStream_t)stream;
+  const int wpb = 4;
+  auto run = [&](int want, bool transposed, int32_t* num, int32_t* idx) -> int {
+    if (!num) return FA_OK;
+    const int rows = transposed ? nKV : nQ, cols = transposed ? nQ : nKV;
+    const long long n_rows = (long long)B * H * rows;
+    const unsigned blocks = (unsigned)((n_rows + wpb - 1) / wpb);
+    fa_tables_kernel<<<blocks, wpb * 32, 0, st>>>(mp.cls, rows, cols, want, transposed, nQ, nKV, n_rows, num, idx);
+    FA_CUDA_CHECK(cudaGetLastError());
+    return FA_OK;
+  };
+  // Without separate full tables every non-empty block is listed as partial.
+  if (!full_kv_num_blocks) return fail(FA_EUNSUPPORTED, "tables without separate full blocks are not implemented");
+  if (int rc = run(1, false, kv_num_blocks, kv_indices)) return rc;
+  if (int rc = run(2, false, full_kv_num_blocks, full_kv_indices)) return rc;
+  if (int rc = run(1, true, q_num_blocks, q_indices)) return rc;
+  if (int rc = run(2, true, full_q_num_blocks, full_q_indices)) return rc;
+  return FA_OK;
+}
+
+}  // extern "C"

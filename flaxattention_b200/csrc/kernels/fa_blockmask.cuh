@@ -1,0 +1,38 @@
+// Block classification for create_block_mask.  Replaces the dense-mask route of
+// flaxattention/core/blockmask.py:277-369 (create_mask -> reshape -> block sums): one CTA
+// evaluates mask_mod on the QB x KVB positions of one block and writes its class
+// (0 = no position kept, 1 = some, 2 = all) without materialising the [B,H,Q,KV] mask.
+// Positions beyond Q_LEN / KV_LEN are evaluated like any other, because the reference
+// classifies on the lengths rounded up to whole blocks (core/blockmask.py:440-444).
+// The mod fragment (fa_mask_mod, FA_HAS_MASK_MOD) is placed before this file.
+#pragma once
+#include "fa_params.h"
+
+extern "C" __global__ void __launch_bounds__(256) fa_blockmask_classify_kernel(const __grid_constant__ FaMaskParams p) {
+  const int kvb = blockIdx.x, qb = blockIdx.y;
+  const int bh = blockIdx.z;
+  const int b = bh / p.H, h = bh - b * p.H;
+  const long long total = (long long)p.QB * p.KVB;
+  int cnt = 0;
+#if FA_HAS_MASK_MOD
+  const int gb = b + p.b_off, gh = h + p.h_off;
+  const int q0 = qb * p.QB, k0 = kvb * p.KVB;
+  for (long long i = threadIdx.x; i < total; i += 256) {
+    const int qi = (int)(i / p.KVB);
+    const int kj = (int)(i - (long long)qi * p.KVB);
+    cnt += fa_mask_mod(gb, gh, q0 + qi, k0 + kj) ? 1 : 0;
+  }
+#else
+  for (long long i = threadIdx.x; i < total; i += 256) cnt += 1;
+#endif
+  __shared__ long long s_cnt;
+  if (threadIdx.x == 0) s_cnt = 0;
+  __syncthreads();
+  for (int o = 16; o > 0; o >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, o);
+  if ((threadIdx.x & 31) == 0) atomicAdd((unsigned long long*)&s_cnt, (unsigned long long)cnt);
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const long long c = s_cnt;
+    p.cls[(((long long)b * p.H + h) * p.nQ + qb) * p.nKV + kvb] = (signed char)(c == 0 ? 0 : (c == total ? 2 : 1));
+  }
+}

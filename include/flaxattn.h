@@ -1,0 +1,132 @@
+/*
+ * flaxattn.h - C ABI of the B200 (sm_100a) flash-attention library.
+ *
+ * The entry points are what a custom-call binding (jax.ffi handler, ctypes, cffi) needs
+ * in place of the Pallas launches of the reference:
+ *   fa_fwd          <- pl.pallas_call(mha_forward_kernel ...)     flaxattention/kernel/attention.py:243, :321
+ *   fa_bwd          <- _preprocess_backward + pl.pallas_call(mha_backward_kernel ...)
+ *                                                                  flaxattention/kernel/attention.py:348-366, :612-647
+ *   fa_decode       <- the Sq<16 padded forward launch             flaxattention/core/attention.py:269-273, :310-311
+ *   fa_block_mask   <- create_mask + _convert_mask_to_block_mask + _dense_to_ordered
+ *                                                                  flaxattention/core/blockmask.py:277-369, :57-64
+ *   fa_module_*     <- jax.jit tracing of score_mod / mask_mod and the Triton compile they trigger
+ *                                                                  flaxattention/core/attention.py:220-230, :281-296
+ *
+ * Conventions
+ *   - every function returns 0 on success, a negative FA_E* code otherwise; fa_last_error()
+ *     gives the message of the calling thread's last failure;
+ *   - the caller owns all device memory (inputs, outputs, workspaces); the library owns only
+ *     compiled modules; launches are asynchronous on the given stream;
+ *   - tensors are described by a base pointer and element strides for batch, head and
+ *     sequence; the head dimension is contiguous.  [B,H,S,D] and [B,S,H,D] are both
+ *     expressible, so no transposed copies are needed around a call;
+ *   - there is no CPU implementation: without a CUDA device every compute entry point
+ *     fails with FA_ECUDA.
+ */
+#ifndef FLAXATTN_H_
+#define FLAXATTN_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FA_OK 0
+#define FA_EINVAL (-1)    /* bad argument (shape, stride, alignment, null pointer) */
+#define FA_ECOMPILE (-2)  /* run-time compilation of a kernel failed; see fa_last_error */
+#define FA_ECUDA (-3)     /* a CUDA call failed */
+#define FA_EUNSUPPORTED (-4)
+#define FA_EWORKSPACE (-5) /* workspace too small */
+
+enum fa_dtype { FA_F16 = 0, FA_BF16 = 1, FA_F32 = 2 };
+
+/* kernel kinds, for fa_module_prepare */
+enum fa_kind { FA_KIND_FWD = 0, FA_KIND_BWD = 1, FA_KIND_DECODE = 2, FA_KIND_BLOCKMASK = 3 };
+
+typedef struct fa_module fa_module; /* a lowered (score_mod, mask_mod) pair and its compiled kernels */
+
+typedef struct fa_tensor {
+  void* ptr;        /* device pointer, 16-byte aligned */
+  int64_t stride_b; /* element strides; all byte strides must be multiples of 16 */
+  int64_t stride_h;
+  int64_t stride_s;
+} fa_tensor;
+
+/* BlockMask tables, the layout of flaxattention/core/blockmask.py:72-119 (int32, device).
+ * kv_num_blocks == NULL means "no block mask": every key block is visited and mask_mod,
+ * if the module has one, is applied everywhere. */
+typedef struct fa_block_tables {
+  const int32_t* kv_num_blocks;      /* [mask_B, mask_H, num_q_blocks] */
+  const int32_t* kv_indices;         /* [mask_B, mask_H, num_q_blocks, num_kv_blocks] */
+  const int32_t* full_kv_num_blocks; /* same shapes, or NULL */
+  const int32_t* full_kv_indices;
+  const int32_t* q_num_blocks;       /* [mask_B, mask_H, num_kv_blocks]; needed by fa_bwd only */
+  const int32_t* q_indices;          /* [mask_B, mask_H, num_kv_blocks, num_q_blocks] */
+  const int32_t* full_q_num_blocks;
+  const int32_t* full_q_indices;
+  int32_t mask_B, mask_H;            /* 1 = broadcast over batch / heads */
+  int32_t num_q_blocks, num_kv_blocks;
+  int32_t q_block_size, kv_block_size;
+} fa_block_tables;
+
+typedef struct fa_attn_params {
+  int32_t dtype; /* enum fa_dtype of q, k, v, o (and dout, dq, dk, dv) */
+  int32_t B, Hq, Hkv, Sq, Skv, D, Dv;
+  float scale;
+  int32_t b_offset, h_offset; /* global index of this shard's first batch / head: what the mods see */
+  fa_tensor q, k, v, o;
+  float* lse;                 /* [B,Hq,Sq] natural-log logsumexp; fwd/decode: output or NULL; bwd: input */
+  fa_block_tables tables;
+  int32_t* status;            /* optional device word; kernels OR error bits into it (0 = clean) */
+} fa_attn_params;
+
+const char* fa_last_error(void);
+int fa_version(void);
+
+/* Directory holding the kernel templates (*.cuh).  Default: "kernels" beside the library. */
+int fa_set_kernel_dir(const char* path);
+/* Directory for compiled-kernel cache files.  Default: $FLAXATTN_CACHE_DIR, else ~/.cache/flaxattn_b200.
+ * An empty string disables the on-disk cache. */
+int fa_set_cache_dir(const char* path);
+
+/* mod_source: CUDA text defining fa_score_mod, fa_score_mod_grad, fa_mask_mod and the macros
+ * FA_HAS_SCORE_MOD / FA_HAS_MASK_MOD.  NULL or "" = identity score_mod and no mask. */
+int fa_module_create(const char* mod_source, fa_module** out);
+void fa_module_destroy(fa_module* m);
+/* Compiles (or fetches from the cache) the kernels of one kind for a dtype / head-dim pair.
+ * Needs no GPU.  seq_hint selects the tile configuration the same way a later launch would. */
+int fa_module_prepare(fa_module* m, int kind, int dtype, int D, int Dv, int Sq_hint, int Skv_hint);
+/* Number of kernels compiled (not fetched from a cache) since the library was loaded. */
+int fa_compile_count(void);
+
+int fa_fwd(fa_module* m, const fa_attn_params* p, void* stream);
+
+size_t fa_bwd_workspace_bytes(const fa_attn_params* p);
+int fa_bwd(fa_module* m, const fa_attn_params* p, const fa_tensor* dout, const fa_tensor* dq,
+           const fa_tensor* dk, const fa_tensor* dv, void* workspace, size_t workspace_bytes, void* stream);
+
+/* Split-KV decode for Sq <= 64.  num_splits <= 0 lets the library choose. */
+int fa_decode_num_splits(const fa_attn_params* p, int sm_count);
+size_t fa_decode_workspace_bytes(const fa_attn_params* p, int num_splits);
+int fa_decode(fa_module* m, const fa_attn_params* p, int num_splits, void* workspace, size_t workspace_bytes,
+              void* stream);
+
+/* BlockMask construction.  Q_LEN / KV_LEN are the raw lengths; the block grid is
+ * ceil(Q_LEN/q_block) x ceil(KV_LEN/kv_block).  Output tables have the shapes listed in
+ * fa_block_tables with mask_B = B and mask_H = H.  full_* may be NULL (then blocks that are
+ * entirely kept are listed with the partial ones).  workspace: B*H*nQ*nKV bytes. */
+size_t fa_block_mask_workspace_bytes(int B, int H, int Q_LEN, int KV_LEN, int q_block, int kv_block);
+int fa_block_mask(fa_module* m, int B, int H, int Q_LEN, int KV_LEN, int q_block, int kv_block,
+                  int b_offset, int h_offset,
+                  int32_t* kv_num_blocks, int32_t* kv_indices,
+                  int32_t* full_kv_num_blocks, int32_t* full_kv_indices,
+                  int32_t* q_num_blocks, int32_t* q_indices,
+                  int32_t* full_q_num_blocks, int32_t* full_q_indices,
+                  void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLAXATTN_H_ */
