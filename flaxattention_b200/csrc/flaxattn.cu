@@ -6,6 +6,8 @@
 // NVRTC, cached in memory per module and on disk per content hash, and loaded through the
 // context-independent library API of the CUDA runtime.
 #include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
 #include <nvrtc.h>
 
 #include <dlfcn.h>
@@ -282,6 +284,53 @@ int pick_fwd(int dtype, int D, int Dv, int Sq, const FaTables* t, FwdCfg& c) {
                                "(block sizes must be multiples of 16 unless there is a single block)");
 }
 
+struct BwdCfg {
+  int tile, warps, smem_dq, smem_dkdv;
+};
+int pick_bwd(int dtype, int D, int Dv, const FaTables* t, BwdCfg& c) {
+  const int es = esize(dtype);
+  for (int warps : {4, 2, 1}) {
+    const int T = 16 * warps;
+    if (t && t->kv_num) {
+      if (!divides_or_single(T, t->QB, t->nQ) || !divides_or_single(T, t->KVB, t->nKV)) continue;
+    }
+    const int pq = pitch(D, es), pv = pitch(Dv, es);
+    const int f32x = dtype == FA_F32 ? T * pitch(T, 4) : 0;
+    const int dq = T * pq + T * pv + 2 * T * pq + 2 * T * pv + f32x;
+    const int dkdv = T * pq + T * pv + 2 * T * pq + 2 * T * pv + 2 * (2 * T * 4) + f32x;
+    if (dq > kMaxSmem || dkdv > kMaxSmem) continue;
+    c = {T, warps, dq, dkdv};
+    return FA_OK;
+  }
+  return fail(FA_EUNSUPPORTED, "no backward tile configuration fits this head dim / BlockMask block size");
+}
+
+struct DecCfg {
+  int BM, BN, stages, smem;
+};
+int pick_decode(int dtype, int D, int Dv, int Sq, const FaTables* t, DecCfg& c) {
+  if (dtype == FA_F32) return fail(FA_EUNSUPPORTED, "the decode kernel takes fp16 / bf16 inputs");
+  if (Sq > 64) return fail(FA_EUNSUPPORTED, "the decode kernel handles at most 64 query rows");
+  if (t && t->kv_num && t->nQ != 1) return fail(FA_EUNSUPPORTED, "decode needs a BlockMask with a single q block");
+  const int BM = Sq <= 16 ? 16 : (Sq <= 32 ? 32 : 64);
+  const int CG = 4 / (BM / 16);
+  for (int BN : {128, 64, 32, 16}) {
+    if (BN / CG < 16) continue;
+    if (D > 64 && BN > 64) continue;
+    if (t && t->kv_num && !divides_or_single(BN, t->KVB, t->nKV)) continue;
+    for (int stages : {3, 2}) {
+      const int pipe = stages * (BN * pitch(D, 2) + BN * pitch(Dv, 2));
+      const int mrg = CG * BM * (Dv + 4) * 4;
+      const int smem = BM * pitch(D, 2) + (pipe > mrg ? pipe : mrg);
+      if (smem > 113 * 1024 && stages == 3) continue;  // keep two CTAs per SM when possible
+      if (smem > kMaxSmem) continue;
+      c = {BM, BN, stages, smem};
+      return FA_OK;
+    }
+  }
+  return fail(FA_EUNSUPPORTED, "no decode tile configuration fits this head dim / BlockMask block size");
+}
+
 std::string defs(std::initializer_list<std::pair<const char*, int>> kv) {
   std::string s;
   for (auto& p : kv) s += std::string("#define ") + p.first + " " + std::to_string(p.second) + "\n";
@@ -392,6 +441,85 @@ __global__ void fa_tables_kernel(const signed char* __restrict__ cls, int rows_p
   if (lane == 0) num_out[row] = total;
 }
 
+
+// delta[b,h,q] = sum_d O[b,h,q,d] * dO[b,h,q,d]  (flaxattention/kernel/attention.py:338-345).
+// LPR lanes cooperate on one row; each lane reads 16-byte pieces.
+template <int DT, int LPR>
+__global__ void fa_delta_kernel(FaTensor o, FaTensor dout, float* __restrict__ delta, int Hq, int Sq, int Dv,
+                                long long n_rows) {
+  constexpr int ES = DT == FA_F32 ? 4 : 2;
+  constexpr int EPC = 16 / ES;  // elements per 16-byte chunk
+  const long long gt = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long row = gt / LPR;
+  const int sub = (int)(gt % LPR);
+  float acc = 0.f;
+  if (row < n_rows) {
+    const long long bh = row / Sq;
+    const int q = (int)(row - bh * Sq);
+    const int b = (int)(bh / Hq), h = (int)(bh - (long long)b * Hq);
+    const char* po = (const char*)o.ptr + ((long long)b * o.sb + (long long)h * o.sh + (long long)q * o.ss) * ES;
+    const char* pd = (const char*)dout.ptr + ((long long)b * dout.sb + (long long)h * dout.sh + (long long)q * dout.ss) * ES;
+    for (int c = sub; c * EPC < Dv; c += LPR) {
+      const uint4 a = *(const uint4*)(po + c * 16);
+      const uint4 d = *(const uint4*)(pd + c * 16);
+      const unsigned aw[4] = {a.x, a.y, a.z, a.w}, dw[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (DT == FA_F32) {
+          acc += __uint_as_float(aw[i]) * __uint_as_float(dw[i]);
+        } else if (DT == FA_F16) {
+          const __half2 ha = *reinterpret_cast<const __half2*>(&aw[i]);
+          const __half2 hd = *reinterpret_cast<const __half2*>(&dw[i]);
+          const float2 fa = __half22float2(ha), fd = __half22float2(hd);
+          acc += fa.x * fd.x + fa.y * fd.y;
+        } else {
+          acc += __uint_as_float(aw[i] << 16) * __uint_as_float(dw[i] << 16) +
+                 __uint_as_float(aw[i] & 0xffff0000u) * __uint_as_float(dw[i] & 0xffff0000u);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int off = LPR / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (row < n_rows && sub == 0) delta[row] = acc;
+}
+
+// Combines the per-split partial results of the decode kernel: one warp per output row.
+template <int DT>
+__global__ void fa_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                         FaTensor o, float* __restrict__ lse, int Hq, int Sq, int Dv, int ns,
+                                         long long n_rows) {
+  const long long row = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= n_rows) return;
+  const int lane = threadIdx.x & 31;
+  const long long bh = row / Sq;
+  const int q = (int)(row - bh * Sq);
+  const int b = (int)(bh / Hq), h = (int)(bh - (long long)b * Hq);
+  float mstar = -INFINITY;
+  for (int s = 0; s < ns; ++s) mstar = fmaxf(mstar, part_ml[((bh * ns + s) * Sq + q) * 2]);
+  float lstar = 0.f;
+  for (int s = 0; s < ns; ++s) {
+    const float m = part_ml[((bh * ns + s) * Sq + q) * 2];
+    const float w = m == -INFINITY ? 0.f : exp2f(m - mstar);
+    lstar += w * part_ml[((bh * ns + s) * Sq + q) * 2 + 1];
+  }
+  const float inv = lstar > 0.f ? 1.f / lstar : 0.f;
+  constexpr int ES = 2;
+  char* og = (char*)o.ptr + ((long long)b * o.sb + (long long)h * o.sh + (long long)q * o.ss) * ES;
+  for (int c = lane; c < Dv; c += 32) {
+    float acc = 0.f;
+    for (int s = 0; s < ns; ++s) {
+      const float m = part_ml[((bh * ns + s) * Sq + q) * 2];
+      const float w = m == -INFINITY ? 0.f : exp2f(m - mstar);
+      acc += w * part_o[((bh * ns + s) * Sq + q) * Dv + c];
+    }
+    acc *= inv;
+    if (DT == FA_F16) ((__half*)og)[c] = __float2half_rn(acc);
+    else ((__nv_bfloat16*)og)[c] = __float2bfloat16_rn(acc);
+  }
+  if (lane == 0 && lse != nullptr) lse[row] = lstar > 0.f ? (mstar + log2f(lstar)) * 0.6931471805599453f : -INFINITY;
+}
+
 }  // namespace
 
 // ======================================================================================
@@ -445,6 +573,18 @@ int get_fwd_kernel(fa_module* m, int dtype, int D, int Dv, const FwdCfg& c, Kern
                           {"FA_WARPS", c.warps}}),
                     "fa_fwd_kernel", c.smem, k);
 }
+int get_bwd_kernel(fa_module* m, int dtype, int D, int Dv, const BwdCfg& c, bool dq, Kernel** k) {
+  return get_kernel(m, "fa_bwd.cuh",
+                    defs({{"FA_DTYPE", dtype}, {"FA_D", D}, {"FA_DV", Dv}, {"FA_BQ", c.tile}, {"FA_BK", c.tile},
+                          {"FA_WARPS", c.warps}}),
+                    dq ? "fa_bwd_dq_kernel" : "fa_bwd_dkdv_kernel", dq ? c.smem_dq : c.smem_dkdv, k);
+}
+int get_decode_kernel(fa_module* m, int dtype, int D, int Dv, const DecCfg& c, Kernel** k) {
+  return get_kernel(m, "fa_decode.cuh",
+                    defs({{"FA_DTYPE", dtype}, {"FA_D", D}, {"FA_DV", Dv}, {"FA_BM", c.BM}, {"FA_BN", c.BN},
+                          {"FA_STAGES", c.stages}}),
+                    "fa_decode_kernel", c.smem, k);
+}
 int get_blockmask_kernel(fa_module* m, Kernel** k) {
   return get_kernel(m, "fa_blockmask.cuh", "", "fa_blockmask_classify_kernel", 0, k);
 }
@@ -463,6 +603,17 @@ int fa_module_prepare(fa_module* m, int kind, int dtype, int D, int Dv, int Sq_h
       if (int rc = pick_fwd(dtype, D, Dv, Sq_hint, nullptr, c)) return rc;
       return get_fwd_kernel(m, dtype, D, Dv, c, &k);
     }
+    case FA_KIND_BWD: {
+      BwdCfg c;
+      if (int rc = pick_bwd(dtype, D, Dv, nullptr, c)) return rc;
+      if (int rc = get_bwd_kernel(m, dtype, D, Dv, c, true, &k)) return rc;
+      return get_bwd_kernel(m, dtype, D, Dv, c, false, &k);
+    }
+    case FA_KIND_DECODE: {
+      DecCfg c;
+      if (int rc = pick_decode(dtype, D, Dv, Sq_hint, nullptr, c)) return rc;
+      return get_decode_kernel(m, dtype, D, Dv, c, &k);
+    }
     case FA_KIND_BLOCKMASK:
       return get_blockmask_kernel(m, &k);
     default:
@@ -480,6 +631,116 @@ int fa_fwd(fa_module* m, const fa_attn_params* p, void* stream) {
   if (int rc = get_fwd_kernel(m, p->dtype, p->D, p->Dv, c, &k)) return rc;
   kp.n_q_tiles = (p->Sq + c.BM - 1) / c.BM;
   return launch(k, dim3(kp.n_q_tiles, p->Hq, p->B), dim3(c.warps * 32), &kp, stream);
+}
+
+size_t fa_bwd_workspace_bytes(const fa_attn_params* p) {
+  if (!p || p->B <= 0 || p->Hq <= 0 || p->Sq <= 0) return 0;
+  return ((size_t)p->B * p->Hq * p->Sq * sizeof(float) + 255) / 256 * 256;
+}
+
+int fa_bwd(fa_module* m, const fa_attn_params* p, const fa_tensor* dout, const fa_tensor* dq, const fa_tensor* dk,
+           const fa_tensor* dv, void* workspace, size_t workspace_bytes, void* stream) {
+  if (int rc = check_common(m, p)) return rc;
+  if (!dout || !dq || !dk || !dv) return fail(FA_EINVAL, "dout, dq, dk and dv descriptors are required");
+  const int es = esize(p->dtype);
+  if (int rc = check_tensor(*dout, "dout", es)) return rc;
+  if (int rc = check_tensor(*dq, "dq", es)) return rc;
+  if (int rc = check_tensor(*dk, "dk", es)) return rc;
+  if (int rc = check_tensor(*dv, "dv", es)) return rc;
+  if (!p->lse) return fail(FA_EINVAL, "lse (forward logsumexp) is required for the backward pass");
+  if (p->tables.kv_num_blocks && !p->tables.q_num_blocks)
+    return fail(FA_EINVAL, "the backward pass needs the q tables of the BlockMask");
+  if (p->tables.kv_num_blocks && ((p->tables.full_q_num_blocks == nullptr) != (p->tables.full_kv_num_blocks == nullptr)))
+    return fail(FA_EINVAL, "full q tables and full kv tables must be given together");
+  const size_t need = fa_bwd_workspace_bytes(p);
+  if (!workspace || workspace_bytes < need) return fail(FA_EWORKSPACE, "backward workspace too small");
+  FaParams kp;
+  fill_params(p, kp);
+  kp.dout = cvt(*dout); kp.dq = cvt(*dq); kp.dk = cvt(*dk); kp.dv = cvt(*dv);
+  kp.delta = (float*)workspace;
+  BwdCfg c;
+  if (int rc = pick_bwd(p->dtype, p->D, p->Dv, &kp.t, c)) return rc;
+  Kernel *kdq = nullptr, *kdkdv = nullptr;
+  if (int rc = get_bwd_kernel(m, p->dtype, p->D, p->Dv, c, true, &kdq)) return rc;
+  if (int rc = get_bwd_kernel(m, p->dtype, p->D, p->Dv, c, false, &kdkdv)) return rc;
+  {
+    cudaStream_t st = (cudaStream_t)stream;
+    const long long n_rows = (long long)p->B * p->Hq * p->Sq;
+    const int chunks = p->Dv * es / 16;
+    const int lpr = chunks >= 8 ? 8 : (chunks >= 4 ? 4 : (chunks >= 2 ? 2 : 1));
+    const long long threads = n_rows * lpr;
+    const unsigned blocks = (unsigned)((threads + 255) / 256);
+#define FA_DELTA(DT, L) fa_delta_kernel<DT, L><<<blocks, 256, 0, st>>>(kp.o, kp.dout, kp.delta, p->Hq, p->Sq, p->Dv, n_rows)
+#define FA_DELTA_DT(L)                                      \
+  do {                                                      \
+    if (p->dtype == FA_F16) FA_DELTA(FA_F16, L);            \
+    else if (p->dtype == FA_BF16) FA_DELTA(FA_BF16, L);     \
+    else FA_DELTA(FA_F32, L);                               \
+  } while (0)
+    if (lpr == 8) FA_DELTA_DT(8);
+    else if (lpr == 4) FA_DELTA_DT(4);
+    else if (lpr == 2) FA_DELTA_DT(2);
+    else FA_DELTA_DT(1);
+#undef FA_DELTA_DT
+#undef FA_DELTA
+    FA_CUDA_CHECK(cudaGetLastError());
+  }
+  if (int rc = launch(kdkdv, dim3((p->Skv + c.tile - 1) / c.tile, p->Hkv, p->B), dim3(c.warps * 32), &kp, stream))
+    return rc;
+  return launch(kdq, dim3((p->Sq + c.tile - 1) / c.tile, p->Hq, p->B), dim3(c.warps * 32), &kp, stream);
+}
+
+int fa_decode_num_splits(const fa_attn_params* p, int sm_count) {
+  if (!p || p->B <= 0 || p->Hq <= 0 || p->Skv <= 0) return 1;
+  if (sm_count <= 0) sm_count = 148;
+  const long long bh = (long long)p->B * p->Hq;
+  const int tiles = (p->Skv + 127) / 128;
+  long long want = (4ll * sm_count + bh - 1) / bh;
+  const int cap = tiles / 4 > 1 ? tiles / 4 : 1;
+  if (want > cap) want = cap;
+  if (want < 1) want = 1;
+  if (want > 256) want = 256;
+  return (int)want;
+}
+
+size_t fa_decode_workspace_bytes(const fa_attn_params* p, int num_splits) {
+  if (!p || num_splits <= 1) return 0;
+  const size_t rows = (size_t)p->B * p->Hq * num_splits * p->Sq;
+  return (rows * p->Dv * sizeof(float) + 255) / 256 * 256 + (rows * 2 * sizeof(float) + 255) / 256 * 256;
+}
+
+int fa_decode(fa_module* m, const fa_attn_params* p, int num_splits, void* workspace, size_t workspace_bytes,
+              void* stream) {
+  if (int rc = check_common(m, p)) return rc;
+  if (num_splits <= 0) num_splits = fa_decode_num_splits(p, 0);
+  if (num_splits > 65535) return fail(FA_EINVAL, "too many splits");
+  FaParams kp;
+  fill_params(p, kp);
+  DecCfg c;
+  if (int rc = pick_decode(p->dtype, p->D, p->Dv, p->Sq, &kp.t, c)) return rc;
+  const size_t need = fa_decode_workspace_bytes(p, num_splits);
+  if (need && (!workspace || workspace_bytes < need)) return fail(FA_EWORKSPACE, "decode workspace too small");
+  if (need && ((uintptr_t)workspace & 15)) return fail(FA_EINVAL, "workspace must be 16-byte aligned");
+  Kernel* k = nullptr;
+  if (int rc = get_decode_kernel(m, p->dtype, p->D, p->Dv, c, &k)) return rc;
+  kp.num_splits = num_splits;
+  if (need) {
+    const size_t rows = (size_t)p->B * p->Hq * num_splits * p->Sq;
+    kp.part_o = (float*)workspace;
+    kp.part_ml = (float*)((char*)workspace + (rows * p->Dv * sizeof(float) + 255) / 256 * 256);
+  }
+  if (int rc = launch(k, dim3(num_splits, p->Hq, p->B), dim3(128), &kp, stream)) return rc;
+  if (num_splits > 1) {
+    const long long n_rows = (long long)p->B * p->Hq * p->Sq;
+    const unsigned blocks = (unsigned)((n_rows + 3) / 4);
+    cudaStream_t st = (cudaStream_t)stream;
+    if (p->dtype == FA_F16)
+      fa_decode_combine_kernel<FA_F16><<<blocks, 128, 0, st>>>(kp.part_o, kp.part_ml, kp.o, kp.lse, p->Hq, p->Sq, p->Dv, num_splits, n_rows);
+    else
+      fa_decode_combine_kernel<FA_BF16><<<blocks, 128, 0, st>>>(kp.part_o, kp.part_ml, kp.o, kp.lse, p->Hq, p->Sq, p->Dv, num_splits, n_rows);
+    FA_CUDA_CHECK(cudaGetLastError());
+  }
+  return FA_OK;
 }
 
 size_t fa_block_mask_workspace_bytes(int B, int H, int Q_LEN, int KV_LEN, int q_block, int kv_block) {

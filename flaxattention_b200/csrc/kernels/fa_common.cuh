@@ -114,42 +114,60 @@ __device__ __forceinline__ void fa_load_tile(fa_u32 smem, const char* gbase, lon
 }
 
 // ---- BlockMask table access ----------------------------------------------------------
-// Sequence of kv tiles one q tile has to visit: first the partial blocks (mask_mod is
-// applied), then the full blocks (mask_mod skipped).  A block of KVB tokens is cut into
-// tiles of BN tokens; tiles that start at or beyond Skv are dropped.
-struct FaKvWalk {
+// Sequence of tiles one row of the block grid has to visit: first the partial blocks
+// (mask_mod is applied), then the full blocks (mask_mod skipped).  A block of BS tokens is
+// cut into tiles of T tokens; tiles that start at or beyond the sequence length S are
+// dropped.  Used for the kv tiles of a q block (kv tables) and for the q tiles of a kv
+// block (q tables).
+struct FaWalk {
   const int* idx[2];
   int num[2];
-  int nKV, KVB, Skv, tpb;  // tpb = tiles per block
-  int total;               // number of (block, tile) slots = (num[0]+num[1]) * tpb
+  int ncols, BS, S, tpb;  // tpb = tiles per block
+  int total;              // number of (block, tile) slots = (num[0]+num[1]) * tpb
 
-  template <int BN>
-  __device__ __forceinline__ void init(const FaTables& t, int b, int h, int qblk, int Skv_) {
-    Skv = Skv_;
-    if (t.kv_num == nullptr) {
-      idx[0] = idx[1] = nullptr;
-      num[0] = 1; num[1] = 0;
-      nKV = 1; KVB = 0x40000000;
-      tpb = (Skv + BN - 1) / BN;
+  template <int T>
+  __device__ __forceinline__ void init_dense(int S_) {
+    S = S_;
+    idx[0] = idx[1] = nullptr;
+    num[0] = 1; num[1] = 0;
+    ncols = 1; BS = 0x40000000;
+    tpb = (S + T - 1) / T;
+    total = tpb;
+  }
+  template <int T>
+  __device__ __forceinline__ void init_rows(const int* num_p, const int* idx_p, const int* fnum_p, const int* fidx_p,
+                                            long long row, int ncols_, int BS_, int S_) {
+    S = S_; ncols = ncols_; BS = BS_;
+    idx[0] = idx_p + row * ncols;
+    num[0] = min(max(num_p[row], 0), ncols);
+    if (fnum_p != nullptr) {
+      idx[1] = fidx_p + row * ncols;
+      num[1] = min(max(fnum_p[row], 0), ncols);
     } else {
-      const int bm = t.mB == 1 ? 0 : b, hm = t.mH == 1 ? 0 : h;
-      const long long row = ((long long)bm * t.mH + hm) * t.nQ + qblk;
-      nKV = t.nKV; KVB = t.KVB;
-      idx[0] = t.kv_idx + row * nKV;
-      num[0] = min(max(t.kv_num[row], 0), nKV);
-      if (t.full_kv_num != nullptr) {
-        idx[1] = t.full_kv_idx + row * nKV;
-        num[1] = min(max(t.full_kv_num[row], 0), nKV);
-      } else {
-        idx[1] = nullptr; num[1] = 0;
-      }
-      const int span = min(KVB, Skv);
-      tpb = (span + BN - 1) / BN;
+      idx[1] = nullptr; num[1] = 0;
     }
+    const int span = min(BS, S);
+    tpb = (span + T - 1) / T;
     total = (num[0] + num[1]) * tpb;
   }
-  // slot -> first key of the tile (or -1 when the tile lies beyond Skv); full = skip mask_mod
-  template <int BN>
+  // kv tiles for q block `qblk` of (b, h)
+  template <int T>
+  __device__ __forceinline__ void init_kv(const FaTables& t, int b, int h, int qblk, int Skv) {
+    if (t.kv_num == nullptr) { init_dense<T>(Skv); return; }
+    const int bm = t.mB == 1 ? 0 : b, hm = t.mH == 1 ? 0 : h;
+    const long long row = ((long long)bm * t.mH + hm) * t.nQ + qblk;
+    init_rows<T>(t.kv_num, t.kv_idx, t.full_kv_num, t.full_kv_idx, row, t.nKV, t.KVB, Skv);
+  }
+  // q tiles for kv block `kvblk` of (b, h)
+  template <int T>
+  __device__ __forceinline__ void init_q(const FaTables& t, int b, int h, int kvblk, int Sq) {
+    if (t.kv_num == nullptr || t.q_num == nullptr) { init_dense<T>(Sq); return; }
+    const int bm = t.mB == 1 ? 0 : b, hm = t.mH == 1 ? 0 : h;
+    const long long row = ((long long)bm * t.mH + hm) * t.nKV + kvblk;
+    init_rows<T>(t.q_num, t.q_idx, t.full_q_num, t.full_q_idx, row, t.nQ, t.QB, Sq);
+  }
+  // slot -> first token of the tile (or -1 when the tile lies beyond S); full = skip mask_mod
+  template <int T>
   __device__ __forceinline__ int tile_start(int slot, bool& full) const {
     int bi = slot / tpb;
     const int ti = slot - bi * tpb;
@@ -157,8 +175,176 @@ struct FaKvWalk {
     if (bi >= num[0]) { bi -= num[0]; which = 1; }
     full = which == 1;
     int blk = 0;
-    if (idx[which] != nullptr) blk = min(max(idx[which][bi], 0), nKV - 1);
-    const long long n0 = (long long)blk * KVB + (long long)ti * BN;
-    return n0 < Skv ? (int)n0 : -1;
+    if (idx[which] != nullptr) blk = min(max(idx[which][bi], 0), ncols - 1);
+    const long long n0 = (long long)blk * BS + (long long)ti * T;
+    return n0 < S ? (int)n0 : -1;
+  }
+  template <int T>
+  __device__ __forceinline__ bool next(int& slot, int& start, bool& full) const {
+    while (slot < total) {
+      start = tile_start<T>(slot, full);
+      ++slot;
+      if (start >= 0) return true;
+    }
+    return false;
   }
 };
+
+// ---- warp-level tile products (one m16 row tile per warp) ----------------------------
+// Accumulator layout is that of mma.sync m16n8k16: acc[nj][0..1] = row g, cols nj*8+2t+{0,1};
+// acc[nj][2..3] = row g+8, same cols (g = lane/4, t = lane%4).
+
+// A fragments of a 16 x KD row-major tile (rows row0.. of the padded smem tile)
+template <int KD>
+__device__ __forceinline__ void fa_load_a_frags(fa_u32 (&a)[KD / 16][4], fa_u32 sA, int pitch, int row0, int lane) {
+#pragma unroll
+  for (int kk = 0; kk < KD / 16; ++kk) {
+    const int r = row0 + ((lane >> 3) & 1) * 8 + (lane & 7);
+    const int c = kk * 16 + (lane >> 4) * 8;
+    fa_ldsm_x4(sA + r * pitch + c * 2, a[kk][0], a[kk][1], a[kk][2], a[kk][3]);
+  }
+}
+// acc[16 x NN] += A[16 x KD] * B^T, B stored [NN rows][KD cols] row-major ("NT")
+template <int DT, int KD, int NN>
+__device__ __forceinline__ void fa_mma_nt(float (&acc)[NN / 8][4], const fa_u32 (&a)[KD / 16][4], fa_u32 sB, int pitchB,
+                                          int lane) {
+#pragma unroll
+  for (int kk = 0; kk < KD / 16; ++kk) {
+#pragma unroll
+    for (int nj = 0; nj < NN / 16; ++nj) {
+      fa_u32 r0, r1, r2, r3;
+      const int r = nj * 16 + (lane >> 4) * 8 + (lane & 7);
+      const int c = kk * 16 + ((lane >> 3) & 1) * 8;
+      fa_ldsm_x4(sB + r * pitchB + c * 2, r0, r1, r2, r3);
+      fa_mma16816<DT>(acc[2 * nj], a[kk], r0, r1);
+      fa_mma16816<DT>(acc[2 * nj + 1], a[kk], r2, r3);
+    }
+  }
+}
+// same, A fragments fetched from shared memory on the fly (keeps registers free)
+template <int DT, int KD, int NN>
+__device__ __forceinline__ void fa_mma_nt_smemA(float (&acc)[NN / 8][4], fa_u32 sA, int pitchA, int row0, fa_u32 sB,
+                                                int pitchB, int lane) {
+#pragma unroll
+  for (int kk = 0; kk < KD / 16; ++kk) {
+    fa_u32 a[4];
+    {
+      const int r = row0 + ((lane >> 3) & 1) * 8 + (lane & 7);
+      const int c = kk * 16 + (lane >> 4) * 8;
+      fa_ldsm_x4(sA + r * pitchA + c * 2, a[0], a[1], a[2], a[3]);
+    }
+#pragma unroll
+    for (int nj = 0; nj < NN / 16; ++nj) {
+      fa_u32 r0, r1, r2, r3;
+      const int r = nj * 16 + (lane >> 4) * 8 + (lane & 7);
+      const int c = kk * 16 + ((lane >> 3) & 1) * 8;
+      fa_ldsm_x4(sB + r * pitchB + c * 2, r0, r1, r2, r3);
+      fa_mma16816<DT>(acc[2 * nj], a, r0, r1);
+      fa_mma16816<DT>(acc[2 * nj + 1], a, r2, r3);
+    }
+  }
+}
+// out[16 x NN] += P[16 x KK] * B, P taken from an accumulator (rounded to DT), B stored
+// [KK rows][NN cols] row-major ("NN")
+template <int DT, int KK, int NN>
+__device__ __forceinline__ void fa_mma_nn(float (&out)[NN / 8][4], const float (&pacc)[KK / 8][4], fa_u32 sB, int pitchB,
+                                          int lane) {
+#pragma unroll
+  for (int kj = 0; kj < KK / 16; ++kj) {
+    fa_u32 a[4];
+    a[0] = fa_pack2<DT>(pacc[2 * kj][0], pacc[2 * kj][1]);
+    a[1] = fa_pack2<DT>(pacc[2 * kj][2], pacc[2 * kj][3]);
+    a[2] = fa_pack2<DT>(pacc[2 * kj + 1][0], pacc[2 * kj + 1][1]);
+    a[3] = fa_pack2<DT>(pacc[2 * kj + 1][2], pacc[2 * kj + 1][3]);
+#pragma unroll
+    for (int dj = 0; dj < NN / 16; ++dj) {
+      fa_u32 r0, r1, r2, r3;
+      const int r = kj * 16 + ((lane >> 3) & 1) * 8 + (lane & 7);
+      const int c = dj * 16 + (lane >> 4) * 8;
+      fa_ldsm_x4_t(sB + r * pitchB + c * 2, r0, r1, r2, r3);
+      fa_mma16816<DT>(out[2 * dj], a, r0, r1);
+      fa_mma16816<DT>(out[2 * dj + 1], a, r2, r3);
+    }
+  }
+}
+
+// fp32 counterparts on plain FMA (exact fp32 products; used when the inputs are fp32)
+template <int KD, int NN>
+__device__ __forceinline__ void fa_simt_nt(float (&acc)[NN / 8][4], const unsigned char* A, int pitchA, int row0,
+                                           const unsigned char* B, int pitchB, int lane) {
+  const int r = row0 + (lane >> 2);
+  for (int d4 = 0; d4 < KD / 4; ++d4) {
+    const float4 qa = *(const float4*)(A + r * pitchA + d4 * 16);
+    const float4 qb = *(const float4*)(A + (r + 8) * pitchA + d4 * 16);
+#pragma unroll
+    for (int nj = 0; nj < NN / 8; ++nj) {
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const int c = nj * 8 + (lane & 3) * 2 + e;
+        const float4 k4 = *(const float4*)(B + c * pitchB + d4 * 16);
+        acc[nj][e] = fmaf(qa.x, k4.x, fmaf(qa.y, k4.y, fmaf(qa.z, k4.z, fmaf(qa.w, k4.w, acc[nj][e]))));
+        acc[nj][2 + e] = fmaf(qb.x, k4.x, fmaf(qb.y, k4.y, fmaf(qb.z, k4.z, fmaf(qb.w, k4.w, acc[nj][2 + e]))));
+      }
+    }
+  }
+}
+// P (accumulator) goes through a per-warp fp32 smem tile [16+][KK] with pitch pitchP
+template <int KK, int NN>
+__device__ __forceinline__ void fa_simt_nn(float (&out)[NN / 8][4], const float (&pacc)[KK / 8][4], unsigned char* P,
+                                           int pitchP, int row0, const unsigned char* B, int pitchB, int lane) {
+  const int r = row0 + (lane >> 2);
+  __syncwarp();
+#pragma unroll
+  for (int nj = 0; nj < KK / 8; ++nj) {
+    const int c = nj * 8 + (lane & 3) * 2;
+    *(float2*)(P + r * pitchP + c * 4) = make_float2(pacc[nj][0], pacc[nj][1]);
+    *(float2*)(P + (r + 8) * pitchP + c * 4) = make_float2(pacc[nj][2], pacc[nj][3]);
+  }
+  __syncwarp();
+  for (int k = 0; k < KK; ++k) {
+    const float pa = *(const float*)(P + r * pitchP + k * 4);
+    const float pb = *(const float*)(P + (r + 8) * pitchP + k * 4);
+#pragma unroll
+    for (int dj = 0; dj < NN / 8; ++dj) {
+      const float2 vv = *(const float2*)(B + k * pitchB + (dj * 8 + (lane & 3) * 2) * 4);
+      out[dj][0] = fmaf(pa, vv.x, out[dj][0]);
+      out[dj][1] = fmaf(pa, vv.y, out[dj][1]);
+      out[dj][2] = fmaf(pb, vv.x, out[dj][2]);
+      out[dj][3] = fmaf(pb, vv.y, out[dj][3]);
+    }
+  }
+}
+
+// 4-byte cp.async (used for per-row scalars such as lse / delta); src_bytes = 0 zero-fills
+__device__ __forceinline__ void fa_cp_async4(fa_u32 dst, const void* src, int src_bytes) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(src), "r"(src_bytes) : "memory");
+}
+
+// Store a 16-row accumulator tile (scaled) into a padded smem tile in the output dtype
+template <int DT, int NN>
+__device__ __forceinline__ void fa_store_acc(unsigned char* S, int pitch, int row0, const float (&acc)[NN / 8][4],
+                                             float mul, int lane) {
+  const int r = row0 + (lane >> 2);
+#pragma unroll
+  for (int dj = 0; dj < NN / 8; ++dj) {
+    const int c = dj * 8 + (lane & 3) * 2;
+    if (DT == FA_DT_F32) {
+      *(float2*)(S + r * pitch + c * 4) = make_float2(acc[dj][0] * mul, acc[dj][1] * mul);
+      *(float2*)(S + (r + 8) * pitch + c * 4) = make_float2(acc[dj][2] * mul, acc[dj][3] * mul);
+    } else {
+      *(fa_u32*)(S + r * pitch + c * 2) = fa_pack2<DT>(acc[dj][0] * mul, acc[dj][1] * mul);
+      *(fa_u32*)(S + (r + 8) * pitch + c * 2) = fa_pack2<DT>(acc[dj][2] * mul, acc[dj][3] * mul);
+    }
+  }
+}
+// Cooperative copy of `valid_rows` rows of a padded smem tile to global memory
+template <int COLS, int ESIZE, int NT>
+__device__ __forceinline__ void fa_store_tile(char* gbase, long long row_stride_bytes, const unsigned char* S,
+                                              int valid_rows, int tid) {
+  constexpr int CPR = COLS * ESIZE / 16;
+  constexpr int PITCH = FaTile<COLS, ESIZE>::PITCH;
+  for (int i = tid; i < valid_rows * CPR; i += NT) {
+    const int r = i / CPR, c = i - r * CPR;
+    *(uint4*)(gbase + (long long)r * row_stride_bytes + c * 16) = *(const uint4*)(S + r * PITCH + c * 16);
+  }
+}

@@ -127,21 +127,14 @@ extern "C" __global__ void __launch_bounds__(fa_fwd::NT) fa_fwd_kernel(const __g
   fa_load_tile<D, ES, NT>(sQ, qg, p.q.ss * ES, BM, p.Sq - m0, tid);
   fa_cp_commit();
 
-  FaKvWalk walk;
+  FaWalk walk;
   {
     int qblk = 0;
     if (p.t.kv_num != nullptr) qblk = min(m0 / p.t.QB, p.t.nQ - 1);
-    walk.init<BN>(p.t, b, h, qblk, p.Skv);
+    walk.init_kv<BN>(p.t, b, h, qblk, p.Skv);
   }
   int slot = 0;
-  auto next_tile = [&](int& n0, bool& full) -> bool {
-    while (slot < walk.total) {
-      n0 = walk.tile_start<BN>(slot, full);
-      ++slot;
-      if (n0 >= 0) return true;
-    }
-    return false;
-  };
+  auto next_tile = [&](int& n0, bool& full) -> bool { return walk.next<BN>(slot, n0, full); };
   auto load_kv = [&](int stage, int n0) {
     fa_load_tile<D, ES, NT>(sK + stage * K_BYTES, kg + (long long)n0 * p.k.ss * ES, p.k.ss * ES, BN, p.Skv - n0, tid);
     fa_load_tile<DV, ES, NT>(sV + stage * V_BYTES, vg + (long long)n0 * p.v.ss * ES, p.v.ss * ES, BN, p.Skv - n0, tid);

@@ -1,0 +1,210 @@
+"""GPU parity of the attention forward against the CPU oracle and the stored vectors.
+Tolerances are the ones the task states: output and LSE max-abs error <= 2e-2 for
+fp16/bf16 and <= 1e-5 for fp32 (LSE: relative to its magnitude where |LSE| > 1)."""
+import math
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from _util import DTYPES, lse_err, max_abs, qkv
+from cases import ATTENTION_CASES, fullmask
+from oracle.attention_oracle import flax_attention_oracle, flax_attention_oracle_chunked
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+ATT = np.load(os.path.join(HERE, "golden", "attention_golden.npz"))
+TOL = {"f16": 2e-2, "bf16": 2e-2, "f32": 1e-5}
+
+
+def _run(q, k, v, score_mod=None, mask_mod=None, use_block_mask=True, block_size=128, path="fwd", **kw):
+    import flaxattention_b200 as fa
+
+    B, Hq, Sq, _ = q.shape
+    Skv = k.shape[2]
+    bm = None
+    if mask_mod is not None:
+        if use_block_mask:
+            bm = fa.create_block_mask(mask_mod, B, Hq, Sq, Skv, BLOCK_SIZE=block_size)
+        else:
+            # no tables: one block spanning everything, mask_mod applied everywhere
+            bm = fa.blockmask._create_empty_block_mask(q.cuda(), k.cuda())
+            bm.mask_mod = mask_mod
+    out, lse = fa.flax_attention(q.cuda(), k.cuda(), v.cuda(), score_mod=score_mod, block_mask=bm,
+                                 enable_gqa=q.shape[1] != k.shape[1], return_lse=True,
+                                 kernel_options={"path": path}, **kw)
+    torch.cuda.synchronize()
+    return out.cpu(), lse.cpu()
+
+
+def _check(out, lse, ref_out, ref_lse, tol):
+    assert not torch.isnan(out.float()).any()
+    assert max_abs(out, ref_out) <= tol
+    err, same = lse_err(lse, ref_lse)
+    assert same, "-inf pattern of the LSE differs"
+    fin = torch.isfinite(ref_lse)
+    scale = max(1.0, ref_lse[fin].abs().max().item()) if fin.any() else 1.0
+    assert err <= tol * scale
+
+
+@pytest.mark.parametrize("name", sorted(ATTENTION_CASES))
+def test_fp32_matches_golden_and_oracle(name):
+    B, Hq, Hkv, Sq, Skv, D, score_mod, mask_mod = ATTENTION_CASES[name]
+    stride = int(ATT[f"{name}.shape"][6])
+    q, k, v = qkv(B, Hq, Hkv, Sq, Skv, D)
+    out, lse = _run(q, k, v, score_mod, mask_mod)
+    ref_out, ref_lse = flax_attention_oracle(q, k, v, score_mod, mask_mod)
+    _check(out, lse, ref_out, ref_lse, 1e-5)
+    assert max_abs(out[:, :, ::stride], torch.from_numpy(ATT[f"{name}.out"])) <= 1e-5
+
+
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+@pytest.mark.parametrize("name", sorted(ATTENTION_CASES))
+def test_half_precision_matches_oracle(name, dt):
+    B, Hq, Hkv, Sq, Skv, D, score_mod, mask_mod = ATTENTION_CASES[name]
+    q, k, v = qkv(B, Hq, Hkv, Sq, Skv, D, dtype=DTYPES[dt])
+    out, lse = _run(q, k, v, score_mod, mask_mod)
+    ref_out, ref_lse = flax_attention_oracle(q, k, v, score_mod, mask_mod)
+    _check(out, lse, ref_out, ref_lse, TOL[dt])
+
+
+SHAPES = [
+    # B, Hq, Hkv, Sq, Skv, D, Dv, dtype, score, mask, block_size
+    (1, 2, 2, 128, 128, 16, 16, "f16", None, None, 128),
+    (1, 2, 2, 384, 384, 32, 32, "bf16", "alibi", "causal", 128),
+    (2, 4, 4, 512, 512, 64, 64, "f16", "checker", None, 128),
+    (1, 2, 2, 1024, 1024, 128, 128, "bf16", None, "sink", 128),
+    (1, 2, 2, 1024, 1024, 128, 64, "f16", "alibi", "window", 64),
+    (1, 4, 2, 200, 333, 64, 64, "bf16", "alibi", "causal", 128),
+    (1, 2, 1, 1, 777, 64, 64, "f16", "alibi", None, 128),
+    (1, 2, 2, 16, 1000, 64, 64, "bf16", None, "offset", 128),
+    (1, 1, 1, 640, 640, 256, 256, "f16", None, "causal", 128),
+    (1, 2, 2, 300, 300, 96, 48, "f32", "checker", "causal", 128),
+    (1, 1, 1, 256, 256, 128, 128, "f32", "alibi", "sink", 128),
+]
+
+
+def _mods(score, mask, Hq, Sq, Skv):
+    from flaxattention_b200.masks import (causal_mask, generate_attention_sink, generate_causal_offset,
+                                          generate_sliding_window)
+    from flaxattention_b200.mods import checkerboard, generate_alibi_bias
+
+    s = {None: None, "alibi": generate_alibi_bias(Hq), "checker": checkerboard}[score]
+    m = {None: None, "causal": causal_mask, "sink": generate_attention_sink(200, 4),
+         "window": generate_sliding_window(100), "offset": generate_causal_offset(Skv - Sq)}[mask]
+    return s, m
+
+
+@pytest.mark.parametrize("case", SHAPES, ids=lambda c: "-".join(map(str, c)))
+def test_shape_sweep(case):
+    B, Hq, Hkv, Sq, Skv, D, Dv, dt, score, mask, bs = case
+    s, m = _mods(score, mask, Hq, Sq, Skv)
+    q, k, v = qkv(B, Hq, Hkv, Sq, Skv, D, Dv, dtype=DTYPES[dt])
+    out, lse = _run(q, k, v, s, m, block_size=bs)
+    ref_out, ref_lse = flax_attention_oracle(q, k, v, s, m)
+    _check(out, lse, ref_out, ref_lse, TOL[dt])
+
+
+def test_mask_without_tables_equals_mask_with_tables():
+    from flaxattention_b200.masks import generate_attention_sink
+
+    m = generate_attention_sink(100, 4)
+    q, k, v = qkv(1, 2, 2, 512, 512, 64, dtype=torch.float16)
+    o1, l1 = _run(q, k, v, None, m, use_block_mask=True)
+    o2, l2 = _run(q, k, v, None, m, use_block_mask=False)
+    assert max_abs(o1, o2) <= 2e-3 and max_abs(l1, l2) <= 1e-4
+
+
+def test_fully_masked_gives_zero_output():
+    # tests/attention_test.py:65-129 (test_fully_masked, test_pallas_fully_masked)
+    import flaxattention_b200 as fa
+
+    q, k, v = qkv(4, 8, 8, 64, 64, 32)
+    out, lse = _run(q, k, v, None, fullmask)
+    assert torch.count_nonzero(out) == 0 and bool(torch.isneginf(lse).all())
+    out2 = fa.flax_attention_pallas(q.cuda(), k.cuda(), v.cuda(), mask_mod=fullmask).cpu()
+    assert torch.count_nonzero(out2) == 0
+
+
+def test_pallas_entry_point_layouts():
+    """flax_attention_pallas: bhln=True is [B,H,L,N]; bhln=False is [B,L,H,N]; both read
+    through strides and must agree with flax_attention (examples/example.py:86)."""
+    import flaxattention_b200 as fa
+    from flaxattention_b200.blockmask import and_masks
+    from flaxattention_b200.masks import causal_mask, generate_sliding_window
+    from flaxattention_b200.mods import generate_alibi_bias
+
+    alibi = generate_alibi_bias(4)
+    merged = and_masks(causal_mask, generate_sliding_window(10))
+    q, k, v = (t.cuda() for t in qkv(2, 4, 4, 128, 128, 32, dtype=torch.float16))
+    bm = fa.create_block_mask(merged, 2, 4, 128, 128)
+    a = fa.flax_attention(q, k, v, score_mod=alibi, block_mask=bm)
+    b = fa.flax_attention_pallas(q, k, v, score_mod=alibi, mask_mod=merged)
+    c = fa.flax_attention_pallas(q.transpose(1, 2).contiguous(), k.transpose(1, 2).contiguous(),
+                                 v.transpose(1, 2).contiguous(), score_mod=alibi, mask_mod=merged, bhln=False)
+    assert c.shape == (2, 128, 4, 32)
+    assert max_abs(a, b) <= 2e-3 and max_abs(a, c.transpose(1, 2)) <= 2e-3
+    ref, _ = flax_attention_oracle(q.cpu(), k.cpu(), v.cpu(), alibi, merged)
+    assert max_abs(a.cpu(), ref) <= 2e-2
+
+
+def test_math_attention_signature():
+    import flaxattention_b200 as fa
+    from flaxattention_b200.masks import causal_mask
+
+    q, k, v = (t.cuda() for t in qkv(1, 2, 2, 256, 256, 64, dtype=torch.bfloat16))
+    bm = fa.create_block_mask(causal_mask, 1, 2, 256, 256)
+    out, lse2 = fa.math_attention(q, k, v, fa.attention._identity, bm.as_tuple(), 0.125)
+    ref, ref_lse = flax_attention_oracle(q.cpu(), k.cpu(), v.cpu(), None, causal_mask, 0.125)
+    assert max_abs(out.cpu(), ref) <= 2e-2
+    assert max_abs(lse2.cpu() * math.log(2.0), ref_lse) <= 2e-2
+
+
+def test_numpy_inputs_round_trip_through_the_device():
+    import flaxattention_b200 as fa
+
+    q, k, v = qkv(1, 2, 2, 64, 64, 32)
+    out = fa.flax_attention(q.numpy(), k.numpy(), v.numpy())
+    assert isinstance(out, np.ndarray)
+    ref, _ = flax_attention_oracle(q, k, v)
+    assert max_abs(torch.from_numpy(out), ref) <= 1e-5
+
+
+def test_shard_offsets_reproduce_the_global_result():
+    """A batch x heads shard computed with b_offset / h_offset equals the slice of the full
+    problem (the mods see global indices)."""
+    import flaxattention_b200 as fa
+    from cases import head_dependent
+    from flaxattention_b200.mods import generate_alibi_bias
+
+    alibi = generate_alibi_bias(4)
+    q, k, v = (t.cuda() for t in qkv(4, 4, 4, 256, 256, 64, dtype=torch.float16))
+    bm = fa.create_block_mask(head_dependent, 4, 4, 256, 256)
+    full = fa.flax_attention(q, k, v, score_mod=alibi, block_mask=bm)
+    sl = (slice(2, 4), slice(1, 3))
+    part = fa.flax_attention(q[sl].contiguous(), k[sl].contiguous(), v[sl].contiguous(), score_mod=alibi,
+                             block_mask=bm.shard(*sl), b_offset=2, h_offset=1)
+    assert torch.equal(part, full[sl])
+
+
+def test_benchmark_shape_properties():
+    """Full-size configuration (B8 H8 S2048 D64 fp16, checkerboard): the dense oracle is run
+    on a slice of heads; the rest is covered by properties: softmax rows are convex weights
+    (constant V gives constant output), and the result does not depend on how the batch is
+    split."""
+    import flaxattention_b200 as fa
+    from flaxattention_b200.mods import checkerboard
+
+    q, k, v = qkv(8, 8, 8, 2048, 2048, 64, dtype=torch.float16)
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    out, lse = fa.flax_attention(qc, kc, vc, score_mod=checkerboard, return_lse=True)
+    ref, ref_lse = flax_attention_oracle_chunked(q[:1, :2], k[:1, :2], v[:1, :2], checkerboard, None, chunk_bh=1)
+    assert max_abs(out[:1, :2].cpu(), ref) <= 2e-2
+    assert max_abs(lse[:1, :2].cpu(), ref_lse) <= 2e-2
+    ones = torch.ones_like(vc)
+    assert max_abs(fa.flax_attention(qc, kc, ones, score_mod=checkerboard).cpu(), ones.cpu()) <= 2e-3
+    half = fa.flax_attention(qc[4:], kc[4:], vc[4:], score_mod=checkerboard, b_offset=4)
+    assert torch.equal(half, out[4:])
+    again = fa.flax_attention(qc, kc, vc, score_mod=checkerboard)
+    assert torch.equal(again, out), "the forward must be deterministic"

@@ -1,0 +1,148 @@
+"""Tracer / lowering tests (CPU): the expression graph recorded from a mod must evaluate
+to what the Python mod itself returns on numpy arrays, the symbolic derivative must match
+a finite difference, and the generated CUDA text must compile for sm_100a."""
+import numpy as np
+import pytest
+
+from flaxattention_b200 import _cabi, fnp, modtrace
+from flaxattention_b200.blockmask import and_masks, or_masks, noop_mask
+from flaxattention_b200.masks import (causal_mask, generate_attention_sink, generate_causal_offset,
+                                      generate_sliding_window)
+from flaxattention_b200.mods import checkerboard, generate_alibi_bias
+
+
+def _grid(B=2, H=3, Q=17, KV=19):
+    b = np.arange(B, dtype=np.int32).reshape(B, 1, 1, 1)
+    h = np.arange(H, dtype=np.int32).reshape(1, H, 1, 1)
+    q = np.arange(Q, dtype=np.int32).reshape(1, 1, Q, 1)
+    kv = np.arange(KV, dtype=np.int32).reshape(1, 1, 1, KV)
+    s = np.random.default_rng(0).standard_normal((B, H, Q, KV)).astype(np.float32)
+    return s, b, h, q, kv
+
+
+def tanh_softcap(score, b, h, q, kv):
+    return 30.0 * fnp.tanh(score / 30.0)
+
+
+def rel_bias(score, b, h, q, kv):
+    return score + fnp.abs(q - kv) * -0.25 + fnp.where(kv % 3 == 0, 1.0, 0.0) * (b + 1)
+
+
+def floor_mix(score, b, h, q, kv):
+    return score * fnp.exp2(-((q // 4) - (kv // 4)) / 8.0) + fnp.minimum(score, 0.5) - fnp.maximum(score, -0.5)
+
+
+def neg_mod(score, b, h, q, kv):
+    return fnp.where((q - kv) % -3 == -1, score * score, fnp.sigmoid(score))
+
+
+SCORE_MODS = [generate_alibi_bias(8), checkerboard, tanh_softcap, rel_bias, floor_mix, neg_mod]
+MASK_MODS = [causal_mask, generate_sliding_window(5), generate_attention_sink(6, 2), generate_causal_offset(3),
+             and_masks(causal_mask, lambda b, h, q, kv: (kv + h) % 2 == 0),
+             or_masks(lambda b, h, q, kv: kv < 2, lambda b, h, q, kv: ~(q < kv) & (b == 1)), noop_mask]
+
+
+@pytest.mark.parametrize("fn", SCORE_MODS)
+def test_score_mod_graph_matches_python(fn):
+    s, b, h, q, kv = _grid()
+    tm = modtrace.trace_score_mod(fn)
+    got = modtrace.evaluate(tm, s, b, h, q, kv)
+    want = np.asarray(fn(s, b, h, q, kv), dtype=np.float32)
+    np.testing.assert_allclose(np.broadcast_to(got, want.shape), want, rtol=2e-6, atol=2e-6)
+
+
+@pytest.mark.parametrize("fn", MASK_MODS)
+def test_mask_mod_graph_matches_python(fn):
+    s, b, h, q, kv = _grid()
+    tm = modtrace.trace_mask_mod(fn)
+    got = np.broadcast_to(modtrace.evaluate(tm, None, b, h, q, kv), s.shape)
+    want = np.broadcast_to(np.asarray(fn(b, h, q, kv)).astype(bool), s.shape)
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.parametrize("fn", SCORE_MODS)
+def test_symbolic_derivative(fn):
+    s, b, h, q, kv = _grid()
+    s = s.astype(np.float64)
+    tm = modtrace.trace_score_mod(fn)
+    g = modtrace.evaluate(modtrace.derivative(tm), s.astype(np.float32), b, h, q, kv)
+    eps = 1e-3
+    f = lambda x: np.asarray(fn(x, b, h, q, kv), dtype=np.float64)  # noqa: E731
+    fd = (f(s + eps) - f(s - eps)) / (2 * eps)
+    # exclude the kinks of min/max
+    ok = (np.abs(np.abs(s) - 0.5) > 2 * eps)
+    np.testing.assert_allclose(np.broadcast_to(g, fd.shape)[ok], fd[ok], rtol=2e-3, atol=2e-3)
+
+
+def test_python_mod_semantics():
+    def m(score, b, h, q, kv):
+        return fnp.where(((q - kv) % 4 == 3) & ((q - kv) // 4 == -1), 1.0, 0.0)
+
+    s, b, h, q, kv = _grid()
+    got = modtrace.evaluate(modtrace.trace_score_mod(m), s, b, h, q, kv)
+    d = (q - kv)
+    want = ((np.remainder(d, 4) == 3) & (np.floor_divide(d, 4) == -1)).astype(np.float32)
+    assert np.array_equal(np.broadcast_to(got, want.shape), np.broadcast_to(want, want.shape))
+
+
+def test_score_mod_as_mask():
+    def neginf_future(score, b, h, q, kv):
+        return fnp.where(q >= kv, score, -fnp.inf)
+
+    s, b, h, q, kv = _grid()
+    tm = modtrace.trace_mask_mod(neginf_future)
+    got = np.broadcast_to(modtrace.evaluate(tm, None, b, h, q, kv), s.shape)
+    assert np.array_equal(got, np.broadcast_to(q >= kv, s.shape))
+
+
+def test_numpy_and_torch_function_interop():
+    import torch
+
+    def m_np(score, b, h, q, kv):
+        return np.where(np.greater_equal(q, kv), np.exp2(score), np.tanh(score))
+
+    def m_torch(score, b, h, q, kv):
+        return torch.where(q >= kv, torch.exp2(score), torch.tanh(score))
+
+    a = modtrace.to_cuda(modtrace.trace_score_mod(m_np), "f")
+    c = modtrace.to_cuda(modtrace.trace_score_mod(m_torch), "f")
+    assert a == c
+
+
+def test_data_dependent_branch_is_rejected():
+    def bad(score, b, h, q, kv):
+        return score if q >= kv else -score
+
+    with pytest.raises(TypeError):
+        modtrace.trace_score_mod(bad)
+
+
+def test_identity_and_noop_are_elided():
+    ms = modtrace.lower_mods(lambda s, b, h, q, kv: s, noop_mask)
+    assert "FA_HAS_SCORE_MOD 0" in ms.source and "FA_HAS_MASK_MOD 0" in ms.source
+    ms2 = modtrace.lower_mods(checkerboard, causal_mask)
+    assert ms2.key != ms.key and "FA_HAS_SCORE_MOD 1" in ms2.source
+
+
+def test_lowered_mods_compile_for_sm100a(tmp_path):
+    """Run-time compilation needs no GPU; every kernel kind must build with a real mod."""
+    L = _cabi.lib()
+    L.fa_set_cache_dir(str(tmp_path).encode())
+    try:
+        ms = modtrace.lower_mods(floor_mix, generate_attention_sink(64, 4))
+        m = _cabi.Module(ms.source)
+        before = L.fa_compile_count()
+        m.prepare(_cabi.KIND_BLOCKMASK, 0, 64, 64)
+        m.prepare(_cabi.KIND_FWD, _cabi.FA_BF16, 64, 64)
+        assert L.fa_compile_count() == before + 2
+        # a second module with the same source hits the on-disk cache
+        m2 = _cabi.Module(ms.source)
+        m2.prepare(_cabi.KIND_FWD, _cabi.FA_BF16, 64, 64)
+        assert L.fa_compile_count() == before + 2
+        bad = _cabi.Module("#define FA_HAS_SCORE_MOD 1\n#define FA_HAS_MASK_MOD 0\nthis is not CUDA\n")
+        with pytest.raises(_cabi.FlaxAttnError) as ei:
+            bad.prepare(_cabi.KIND_FWD, _cabi.FA_F16, 64, 64)
+        assert ei.value.code == -2
+    finally:
+        import os
+        L.fa_set_cache_dir(os.path.join(os.path.dirname(_cabi.LIB_PATH), "_kernel_cache").encode())
