@@ -14,6 +14,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(_HERE, "libflaxattn.so")
 
 FA_F16, FA_BF16, FA_F32 = 0, 1, 2
+FLAG_ROUND_SCORES = 1
 KIND_FWD, KIND_BWD, KIND_DECODE, KIND_BLOCKMASK = 0, 1, 2, 3
 
 
@@ -43,6 +44,7 @@ class FaAttnParams(C.Structure):
         ("q", FaTensor), ("k", FaTensor), ("v", FaTensor), ("o", FaTensor),
         ("lse", C.c_void_p),
         ("tables", FaBlockTables),
+        ("flags", C.c_int32),
         ("status", C.c_void_p),
     ]
 

@@ -92,7 +92,7 @@ class _Call:
     """Everything one attention problem needs besides q/k/v: shapes, mods, tables."""
 
     def __init__(self, query, key, value, score_mod, mask_mod, block_mask: Optional[BlockMask], scale, layout,
-                 b_offset, h_offset, options):
+                 b_offset, h_offset, options, round_scores=False):
         if query.device.type != "cuda":
             raise RuntimeError("flaxattention_b200 runs on CUDA tensors only; there is no CPU path")
         if query.dtype not in _DTYPES:
@@ -112,6 +112,7 @@ class _Call:
             raise ValueError("BlockMask tables must be 4-dimensional [B, H, nQ, nKV]")
         self.module = module_for(score_mod, mask_mod)
         self.options = dict(options or {})
+        self.round_scores = bool(self.options.get("round_scores", round_scores))
 
     def params(self, q, k, v, o, lse) -> _cabi.FaAttnParams:
         p = _cabi.FaAttnParams()
@@ -121,6 +122,7 @@ class _Call:
         p.b_offset, p.h_offset = self.b_offset, self.h_offset
         p.q, p.k, p.v, p.o = (_tensor(t, self.layout) for t in (q, k, v, o))
         p.lse = _ptr(lse)
+        p.flags = _cabi.FLAG_ROUND_SCORES if self.round_scores else 0
         bm = self.block_mask
         if bm is not None:
             t = p.tables
@@ -243,7 +245,10 @@ def flax_attention(
 
     Returns the output in the input dtype and, with ``return_lse``, the natural-log
     logsumexp ``[B, Hq, Sq]`` in float32 (``-inf`` for fully masked rows, whose output is 0).
-    ``kernel_options``: ``{"path": "fwd" | "decode", "num_splits": int}``.
+    ``kernel_options``: ``{"path": "fwd" | "decode", "num_splits": int, "round_scores": bool}``.
+    For fp16 / bf16 inputs the scores are rounded to the input dtype before the scale, as in
+    the reference's dense path (``jnp.matmul`` in the input dtype, core/attention.py:27);
+    ``round_scores=False`` keeps the fp32 product like ``flax_attention_pallas`` does.
     ``b_offset`` / ``h_offset`` are the global indices of the first batch / head of a
     batch x heads shard; the mods see global indices.
     """
@@ -261,7 +266,7 @@ def flax_attention(
         scale = 1.0 / math.sqrt(query.shape[-1])
     mask_mod = None if block_mask is None else block_mask.mask_mod
     call = _Call(query, key, value, score_mod, mask_mod, block_mask, scale, "bhsd", b_offset, h_offset,
-                 kernel_options)
+                 kernel_options, round_scores=True)
     out, lse = _run(call, query, key, value)
     if from_np:
         out, lse = out.cpu().numpy(), lse.cpu().numpy()
@@ -279,7 +284,7 @@ def math_attention(query, key, value, score_mod, block_mask: Tuple, scale, kerne
         raise NotImplementedError("captured buffers are not supported")
     mask_mod = block_mask[-1]
     bm = BlockMask(*block_mask[:8], (block_mask[8], block_mask[9]), mask_mod)
-    call = _Call(query, key, value, score_mod, mask_mod, bm, scale, "bhsd", 0, 0, kernel_options)
+    call = _Call(query, key, value, score_mod, mask_mod, bm, scale, "bhsd", 0, 0, kernel_options, round_scores=True)
     out, lse = _run(call, query, key, value)
     return out, lse / math.log(2.0)
 

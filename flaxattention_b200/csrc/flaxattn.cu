@@ -567,22 +567,24 @@ void fa_module_destroy(fa_module* m) {
 
 namespace {
 
-int get_fwd_kernel(fa_module* m, int dtype, int D, int Dv, const FwdCfg& c, Kernel** k) {
+int round_flag(int dtype, int flags) { return (dtype != FA_F32 && (flags & FA_FLAG_ROUND_SCORES)) ? 1 : 0; }
+
+int get_fwd_kernel(fa_module* m, int dtype, int D, int Dv, int flags, const FwdCfg& c, Kernel** k) {
   return get_kernel(m, "fa_fwd.cuh",
                     defs({{"FA_DTYPE", dtype}, {"FA_D", D}, {"FA_DV", Dv}, {"FA_BM", c.BM}, {"FA_BN", c.BN},
-                          {"FA_WARPS", c.warps}}),
+                          {"FA_WARPS", c.warps}, {"FA_ROUND_SCORES", round_flag(dtype, flags)}}),
                     "fa_fwd_kernel", c.smem, k);
 }
-int get_bwd_kernel(fa_module* m, int dtype, int D, int Dv, const BwdCfg& c, bool dq, Kernel** k) {
+int get_bwd_kernel(fa_module* m, int dtype, int D, int Dv, int flags, const BwdCfg& c, bool dq, Kernel** k) {
   return get_kernel(m, "fa_bwd.cuh",
                     defs({{"FA_DTYPE", dtype}, {"FA_D", D}, {"FA_DV", Dv}, {"FA_BQ", c.tile}, {"FA_BK", c.tile},
-                          {"FA_WARPS", c.warps}}),
+                          {"FA_WARPS", c.warps}, {"FA_ROUND_SCORES", round_flag(dtype, flags)}}),
                     dq ? "fa_bwd_dq_kernel" : "fa_bwd_dkdv_kernel", dq ? c.smem_dq : c.smem_dkdv, k);
 }
-int get_decode_kernel(fa_module* m, int dtype, int D, int Dv, const DecCfg& c, Kernel** k) {
+int get_decode_kernel(fa_module* m, int dtype, int D, int Dv, int flags, const DecCfg& c, Kernel** k) {
   return get_kernel(m, "fa_decode.cuh",
                     defs({{"FA_DTYPE", dtype}, {"FA_D", D}, {"FA_DV", Dv}, {"FA_BM", c.BM}, {"FA_BN", c.BN},
-                          {"FA_STAGES", c.stages}}),
+                          {"FA_STAGES", c.stages}, {"FA_ROUND_SCORES", round_flag(dtype, flags)}}),
                     "fa_decode_kernel", c.smem, k);
 }
 int get_blockmask_kernel(fa_module* m, Kernel** k) {
@@ -601,18 +603,18 @@ int fa_module_prepare(fa_module* m, int kind, int dtype, int D, int Dv, int Sq_h
     case FA_KIND_FWD: {
       FwdCfg c;
       if (int rc = pick_fwd(dtype, D, Dv, Sq_hint, nullptr, c)) return rc;
-      return get_fwd_kernel(m, dtype, D, Dv, c, &k);
+      return get_fwd_kernel(m, dtype, D, Dv, 0, c, &k);
     }
     case FA_KIND_BWD: {
       BwdCfg c;
       if (int rc = pick_bwd(dtype, D, Dv, nullptr, c)) return rc;
-      if (int rc = get_bwd_kernel(m, dtype, D, Dv, c, true, &k)) return rc;
-      return get_bwd_kernel(m, dtype, D, Dv, c, false, &k);
+      if (int rc = get_bwd_kernel(m, dtype, D, Dv, 0, c, true, &k)) return rc;
+      return get_bwd_kernel(m, dtype, D, Dv, 0, c, false, &k);
     }
     case FA_KIND_DECODE: {
       DecCfg c;
       if (int rc = pick_decode(dtype, D, Dv, Sq_hint, nullptr, c)) return rc;
-      return get_decode_kernel(m, dtype, D, Dv, c, &k);
+      return get_decode_kernel(m, dtype, D, Dv, 0, c, &k);
     }
     case FA_KIND_BLOCKMASK:
       return get_blockmask_kernel(m, &k);
@@ -628,7 +630,7 @@ int fa_fwd(fa_module* m, const fa_attn_params* p, void* stream) {
   FwdCfg c;
   if (int rc = pick_fwd(p->dtype, p->D, p->Dv, p->Sq, &kp.t, c)) return rc;
   Kernel* k = nullptr;
-  if (int rc = get_fwd_kernel(m, p->dtype, p->D, p->Dv, c, &k)) return rc;
+  if (int rc = get_fwd_kernel(m, p->dtype, p->D, p->Dv, p->flags, c, &k)) return rc;
   kp.n_q_tiles = (p->Sq + c.BM - 1) / c.BM;
   return launch(k, dim3(kp.n_q_tiles, p->Hq, p->B), dim3(c.warps * 32), &kp, stream);
 }
@@ -661,8 +663,8 @@ int fa_bwd(fa_module* m, const fa_attn_params* p, const fa_tensor* dout, const f
   BwdCfg c;
   if (int rc = pick_bwd(p->dtype, p->D, p->Dv, &kp.t, c)) return rc;
   Kernel *kdq = nullptr, *kdkdv = nullptr;
-  if (int rc = get_bwd_kernel(m, p->dtype, p->D, p->Dv, c, true, &kdq)) return rc;
-  if (int rc = get_bwd_kernel(m, p->dtype, p->D, p->Dv, c, false, &kdkdv)) return rc;
+  if (int rc = get_bwd_kernel(m, p->dtype, p->D, p->Dv, p->flags, c, true, &kdq)) return rc;
+  if (int rc = get_bwd_kernel(m, p->dtype, p->D, p->Dv, p->flags, c, false, &kdkdv)) return rc;
   {
     cudaStream_t st = (cudaStream_t)stream;
     const long long n_rows = (long long)p->B * p->Hq * p->Sq;
@@ -722,7 +724,7 @@ int fa_decode(fa_module* m, const fa_attn_params* p, int num_splits, void* works
   if (need && (!workspace || workspace_bytes < need)) return fail(FA_EWORKSPACE, "decode workspace too small");
   if (need && ((uintptr_t)workspace & 15)) return fail(FA_EINVAL, "workspace must be 16-byte aligned");
   Kernel* k = nullptr;
-  if (int rc = get_decode_kernel(m, p->dtype, p->D, p->Dv, c, &k)) return rc;
+  if (int rc = get_decode_kernel(m, p->dtype, p->D, p->Dv, p->flags, c, &k)) return rc;
   kp.num_splits = num_splits;
   if (need) {
     const size_t rows = (size_t)p->B * p->Hq * num_splits * p->Sq;

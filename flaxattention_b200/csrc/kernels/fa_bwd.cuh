@@ -157,6 +157,7 @@ extern "C" __global__ void __launch_bounds__(fa_bwd::NT) fa_bwd_dq_kernel(const 
       fa_mma_nt_smemA<DT, DV, BK>(dp, sdO, PV, warp * 16, sV + vo, PV, lane);
     }
 
+    fa_round_acc<DT, BK / 8>(s);
     const bool ragged = n0c + BK > p.Skv;
 #pragma unroll
     for (int j = 0; j < BK / 8; ++j) {
@@ -297,6 +298,7 @@ extern "C" __global__ void __launch_bounds__(fa_bwd::NT) fa_bwd_dkdv_kernel(cons
         fa_mma_nt_smemA<DT, DV, BQ>(dp, sV, PV, warp * 16, sdO + doo, PV, lane);
       }
 
+      fa_round_acc<DT, BQ / 8>(s);
       const float* rl = (const float*)(Rs + stage * ROWS_BYTES);
       const bool ragged = m0c + BQ > p.Sq;
 #pragma unroll

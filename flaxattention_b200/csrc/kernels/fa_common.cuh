@@ -54,6 +54,43 @@ __device__ __forceinline__ float fa_to_float(fa_u16 v) {
   }
 }
 
+// Rounds two fp32 scores to the input dtype and back.  The reference's dense path computes
+// Q.K^T in the input dtype before casting to fp32 (flaxattention/core/attention.py:27);
+// kernels built with FA_ROUND_SCORES reproduce that rounding, the others keep the fp32
+// product the way the reference's fused kernel does (flaxattention/kernel/attention.py:82).
+template <int DT>
+__device__ __forceinline__ void fa_round2(float& a, float& b) {
+  if (DT == FA_DT_F16) {
+    fa_u32 r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+    fa_u16 lo, hi;
+    asm("mov.b32 {%0, %1}, %2;" : "=h"(lo), "=h"(hi) : "r"(r));
+    asm("cvt.f32.f16 %0, %1;" : "=f"(a) : "h"(lo));
+    asm("cvt.f32.f16 %0, %1;" : "=f"(b) : "h"(hi));
+  } else if (DT == FA_DT_BF16) {
+    fa_u32 r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(b), "f"(a));
+    a = __uint_as_float(r << 16);
+    b = __uint_as_float(r & 0xffff0000u);
+  }
+}
+#ifndef FA_ROUND_SCORES
+#define FA_ROUND_SCORES 0
+#endif
+// applies the rounding to a whole accumulator tile
+template <int DT, int N>
+__device__ __forceinline__ void fa_round_acc(float (&acc)[N][4]) {
+#if FA_ROUND_SCORES
+  if (DT != FA_DT_F32) {
+#pragma unroll
+    for (int j = 0; j < N; ++j) {
+      fa_round2<DT>(acc[j][0], acc[j][1]);
+      fa_round2<DT>(acc[j][2], acc[j][3]);
+    }
+  }
+#endif
+}
+
 // ---- cp.async ------------------------------------------------------------------------
 // 16-byte global->shared copy; src_bytes = 0 zero-fills the destination.
 __device__ __forceinline__ void fa_cp_async16(fa_u32 dst, const void* src, int src_bytes) {

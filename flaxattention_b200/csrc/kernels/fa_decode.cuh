@@ -126,6 +126,7 @@ extern "C" __global__ void __launch_bounds__(fa_dec::NT) fa_decode_kernel(const 
     for (int j = 0; j < WN / 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.f;
     fa_mma_nt<DT, D, WN>(s, qf, sK + cur * K_BYTES + cg * WN * PQ, PQ, lane);
 
+    fa_round_acc<DT, WN / 8>(s);
     const bool ragged = n0 + WN > p.Skv;
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {

@@ -231,6 +231,8 @@ extern "C" __global__ void __launch_bounds__(fa_fwd::NT) fa_fwd_kernel(const __g
     }
 #endif
 
+#pragma unroll
+    for (int wm = 0; wm < WM; ++wm) fa_round_acc<DT, BN / 8>(s[wm]);
     if (fullc) softmax_tile<false>(s, o, st, p, gb, gh, row_base, n0c, lane);
     else softmax_tile<true>(s, o, st, p, gb, gh, row_base, n0c, lane);
 

@@ -40,6 +40,11 @@ extern "C" {
 #define FA_EUNSUPPORTED (-4)
 #define FA_EWORKSPACE (-5) /* workspace too small */
 
+/* Round Q.K^T to the input dtype before the scale, as the reference's dense path does
+ * (flaxattention/core/attention.py:27).  Without it the fp32 product is kept, as in the
+ * reference's fused kernel (flaxattention/kernel/attention.py:82).  No effect for FA_F32. */
+#define FA_FLAG_ROUND_SCORES 1
+
 enum fa_dtype { FA_F16 = 0, FA_BF16 = 1, FA_F32 = 2 };
 
 /* kernel kinds, for fa_module_prepare */
@@ -79,6 +84,7 @@ typedef struct fa_attn_params {
   fa_tensor q, k, v, o;
   float* lse;                 /* [B,Hq,Sq] natural-log logsumexp; fwd/decode: output or NULL; bwd: input */
   fa_block_tables tables;
+  int32_t flags;              /* FA_FLAG_* */
   int32_t* status;            /* optional device word; kernels OR error bits into it (0 = clean) */
 } fa_attn_params;
 
