@@ -1,0 +1,368 @@
+"""Benchmark of the attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
+
+One "step" is one pass of the hot path over one batch: the flash forward and the flash
+backward (dQ, dK, dV of output.sum()) of the workload.  The default workload is the
+configuration the headline metric is quoted on: B=8, H=8, Sq=Skv=2048, D=64, fp16,
+checkerboard score_mod, no mask (examples/benchmark.py of the reference).  Inputs are
+synthetic N(0,1) tensors from fixed seeds (K: 0, Q: 1, V: 2).
+
+Scaling is weak: under torchrun every rank processes its own batch of 8 with the global
+batch offset 8 * rank passed to the kernels, and there is no data-path collective.
+
+The single JSON line carries the contract keys plus:
+  roofline      the dominant kernel against the measured bf16 tensor peak
+  kernels       per-kernel device time and achieved TFLOP/s
+  fwd / decode  forward-only TFLOP/s and split-KV decode GB/s (N=1)
+  cpu_baseline  the CPU oracle (a port of the reference's dense path) timed on this box's
+                host cores on a bounded sample
+  e2e           the same step through the public API with pinned host buffers: host->device
+                copies of q, k, v and device->host copies of out, dq, dk, dv inside the timing
+`--impl reference` times the CPU oracle alone (the reference itself needs JAX, which is not
+installed); it is the one place besides cpu_baseline where bench.py runs code from oracle/.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import statistics
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+import torch  # noqa: E402
+
+WORKLOADS = {
+    # name: B, H, Sq, Skv, D, dtype, score_mod, mask, block
+    "cfg2": dict(B=8, H=8, Sq=2048, Skv=2048, D=64, dtype="f16", score="checkerboard", mask=None),
+    "cfg3": dict(B=8, H=8, Sq=2048, Skv=2048, D=64, dtype="bf16", score="alibi", mask="causal"),
+    "cfg4": dict(B=4, H=16, Sq=8192, Skv=8192, D=128, dtype="bf16", score=None, mask="sink"),
+}
+DECODE = dict(B=32, H=8, Skv=16384, D=64, dtype="f16")
+DT = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from ncu captures (profiles/); None = not captured
+NCU_TRAFFIC = {"fa_fwd_kernel": None, "fa_bwd_dkdv_kernel": None, "fa_bwd_dq_kernel": None}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return dict(tflops=p["bf16_tflops"], tflops_sustained=p["bf16_tflops_sustained"], hbm=p["hbm_gbs"],
+                    source="measured")
+    return dict(tflops=1590.0, tflops_sustained=1400.0, hbm=6650.0, source="fallback")
+
+
+def mods_for(w):
+    from flaxattention_b200.masks import causal_mask, generate_attention_sink
+    from flaxattention_b200.mods import checkerboard, generate_alibi_bias
+
+    score = {None: None, "checkerboard": checkerboard, "alibi": generate_alibi_bias(w["H"])}[w["score"]]
+    mask = {None: None, "causal": causal_mask, "sink": generate_attention_sink(1024, 4)}[w["mask"]]
+    return score, mask
+
+
+def host_inputs(w, b_offset, pinned):
+    """Seeded N(0,1) tensors; batch entry b of the global problem is generated on its own,
+    so a shard does not depend on the number of ranks."""
+    out = []
+    for seed, S in ((1, w["Sq"]), (0, w["Skv"]), (2, w["Skv"])):
+        t = torch.empty(w["B"], w["H"], S, w["D"], dtype=DT[w["dtype"]])
+        for b in range(w["B"]):
+            g = np.random.Generator(np.random.Philox(key=[seed, b_offset + b]))
+            t[b] = torch.from_numpy(g.standard_normal((w["H"], S, w["D"]), dtype=np.float32)).to(t.dtype)
+        out.append(t.pin_memory() if pinned else t)
+    return out
+
+
+class ClockSampler:
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-i", str(index),
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            pass
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            text, _ = self.proc.communicate(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+            text, _ = self.proc.communicate()
+        sm, mx, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in text.strip().splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def cpu_oracle_step(w, sample_b, score, mask):
+    """One forward + backward of the CPU oracle on `sample_b` batch entries; returns seconds."""
+    from oracle.attention_oracle import attention_grads_oracle
+
+    ws = dict(w, B=sample_b)
+    q, k, v = host_inputs(ws, 0, pinned=False)
+    dout = torch.ones(sample_b, w["H"], w["Sq"], w["D"])
+    t0 = time.perf_counter()
+    attention_grads_oracle(q, k, v, dout, score, mask)
+    return time.perf_counter() - t0
+
+
+def flops_fwd(w):
+    return 4.0 * w["B"] * w["H"] * w["Sq"] * w["Skv"] * w["D"]
+
+
+def run_reference(args, w, rank, world):
+    """CPU arm: the oracle port of the reference's dense path on all host threads."""
+    if rank != 0:
+        return
+    score, mask = mods_for(w)
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    sample_b = 1
+    for _ in range(args.warmup):
+        cpu_oracle_step(w, sample_b, score, mask)
+    ts = [cpu_oracle_step(w, sample_b, score, mask) for _ in range(args.steps)]
+    sec = sum(ts) / len(ts)
+    fl = 3.5 * flops_fwd(dict(w, B=sample_b))
+    val = fl / sec / 1e12
+    sample = f"B={sample_b} of {w['B']} batch entries per step, all heads, fwd+bwd, fp32 dense oracle (torch CPU)"
+    line = {
+        "impl": "reference", "metric": "fwd+bwd attention TFLOP/s (dense-equivalent)", "value": val,
+        "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": sec * 1e3, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f32", "data": "synthetic",
+        "config": {"workload": args.workload, **{k: w[k] for k in ("B", "H", "Sq", "Skv", "D")},
+                   "score_mod": w["score"], "mask": w["mask"], "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+        "note": "the reference needs JAX, which is not installed; this is the CPU oracle port of its dense path",
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
+    ap.add_argument("--no-extras", action="store_true", help="skip forward-only, decode, per-kernel and CPU legs")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    w = WORKLOADS[args.workload]
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, w, rank, world)
+        return
+
+    import flaxattention_b200 as fa
+    from flaxattention_b200 import _cabi
+    from flaxattention_b200 import attention as A
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=dev)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    score, mask = mods_for(w)
+    b_off = w["B"] * rank
+    hq, hk, hv = host_inputs(w, b_off, pinned=True)
+    q, k, v = hq.to(dev), hk.to(dev), hv.to(dev)
+    bm = None
+    if mask is not None:
+        bm = fa.create_block_mask(mask, w["B"], w["H"], w["Sq"], w["Skv"], b_offset=b_off)
+    dout = torch.ones(w["B"], w["H"], w["Sq"], w["D"], dtype=q.dtype, device=dev)
+    flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def flush_l2():
+        flush_buf.fill_(1)
+
+    mask_mod = None if bm is None else bm.mask_mod
+
+    def make_call(flags=0):
+        return A._Call(q, k, v, score, mask_mod, bm, 1.0 / math.sqrt(w["D"]), "bhsd", b_off, 0, {"flags": flags})
+
+    call = make_call()
+
+    def step_kernels():
+        out, lse = A._forward(call, q, k, v)
+        return A._backward(call, q, k, v, out, lse, dout)
+
+    def timed(fn, steps, warmup):
+        for _ in range(warmup):
+            fn()
+        barrier()
+        evs = []
+        for _ in range(steps):
+            flush_l2()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            evs.append((e0, e1))
+        barrier()
+        return sum(a.elapsed_time(b) for a, b in evs) / steps  # ms per step
+
+    # ---- headline: fwd + bwd, inputs resident in HBM -----------------------------------
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    ms = timed(step_kernels, args.steps, args.warmup)
+    clocks = sampler.stop() if sampler else None
+    if world > 1:
+        t = torch.tensor([ms], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = t.item()
+    fl_fwd = flops_fwd(w)
+    value = 3.5 * fl_fwd * world / (ms * 1e-3) / 1e12
+
+    # ---- e2e: public API, pinned host buffers, copies inside the timing -----------------
+    ho = [torch.empty_like(hq).pin_memory() for _ in range(4)]
+
+    def step_e2e():
+        qd = hq.to(dev, non_blocking=True).requires_grad_(True)
+        kd = hk.to(dev, non_blocking=True).requires_grad_(True)
+        vd = hv.to(dev, non_blocking=True).requires_grad_(True)
+        out = fa.flax_attention_pallas(qd, kd, vd, score_mod=score, mask_mod=mask_mod, block_mask=bm, b_offset=b_off)
+        out.backward(dout)
+        ho[0].copy_(out.detach(), non_blocking=True)
+        ho[1].copy_(qd.grad, non_blocking=True)
+        ho[2].copy_(kd.grad, non_blocking=True)
+        ho[3].copy_(vd.grad, non_blocking=True)
+
+    ms_e2e = timed(step_e2e, max(3, args.steps // 2), 3)
+    if world > 1:
+        t = torch.tensor([ms_e2e], device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms_e2e = t.item()
+    nbytes = hq.numel() * hq.element_size()
+    e2e = {"value": 3.5 * fl_fwd * world / (ms_e2e * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+           "h2d_bytes_per_step": 3 * nbytes, "d2h_bytes_per_step": 4 * nbytes}
+
+    line = {
+        "metric": "fwd+bwd attention TFLOP/s (dense-equivalent)", "value": value, "unit": "TFLOP/s",
+        "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": w["dtype"], "data": "synthetic",
+        "config": {"workload": args.workload, **{k_: w[k_] for k_ in ("B", "H", "Sq", "Skv", "D")},
+                   "score_mod": w["score"], "mask": w["mask"], "global_batch": w["B"] * world,
+                   "parallelism": f"batch x heads shards, {world} rank(s), no collective",
+                   "l2": "flushed between timed steps (256 MiB write)", "flops": "3.5 * 4*B*H*Sq*Skv*D per step"},
+        "e2e": e2e, "gpu_launches": 4 * args.steps, "clocks": clocks,
+    }
+
+    # ---- per-kernel timing, roofline, forward-only, decode, CPU baseline (rank 0, N=1 legs) ----
+    pk = peaks()
+    if not args.no_extras:
+        steps_k = max(5, args.steps // 2)
+        out, lse = A._forward(call, q, k, v)
+        t_fwd = timed(lambda: A._forward(call, q, k, v), steps_k, 3)
+        only = {
+            "fa_bwd_dkdv_kernel": _cabi.FLAG_BWD_SKIP_DELTA | _cabi.FLAG_BWD_SKIP_DQ,
+            "fa_bwd_dq_kernel": _cabi.FLAG_BWD_SKIP_DELTA | _cabi.FLAG_BWD_SKIP_DKDV,
+            "fa_delta_kernel": _cabi.FLAG_BWD_SKIP_DKDV | _cabi.FLAG_BWD_SKIP_DQ,
+        }
+        A._backward(call, q, k, v, out, lse, dout)  # delta is in place for the partial runs
+        unit = fl_fwd / 4.0  # one S x S x D product = 2*B*H*Sq*Skv*D
+        alg = {"fa_fwd_kernel": 2 * unit, "fa_bwd_dkdv_kernel": 4 * unit, "fa_bwd_dq_kernel": 1 * unit,
+               "fa_delta_kernel": 0.0}
+        kernels = {"fa_fwd_kernel": {"ms": t_fwd}}
+        for name, flags in only.items():
+            c2 = make_call(flags)
+            kernels[name] = {"ms": timed(lambda c2=c2: A._backward(c2, q, k, v, out, lse, dout), steps_k, 3)}
+        for name, d in kernels.items():
+            d["algorithmic_tflops"] = alg[name] / (d["ms"] * 1e-3) / 1e12 if alg[name] else None
+        dom = max((n for n in kernels if alg[n]), key=lambda n: kernels[n]["ms"])
+        ach = kernels[dom]["algorithmic_tflops"]
+        line["kernels"] = kernels
+        line["roofline"] = {"bound": "tensor", "kernel": dom, "achieved": ach, "peak": pk["tflops"], "unit": "TFLOP/s",
+                            "frac": ach / pk["tflops"], "peak_source": pk["source"] + " (bf16 cuBLAS burst)",
+                            "frac_of_nominal_2250": ach / 2250.0, "traffic": NCU_TRAFFIC.get(dom)}
+        line["fwd"] = {"ms": t_fwd, "tflops": fl_fwd / (t_fwd * 1e-3) / 1e12,
+                       "frac_of_measured_peak": fl_fwd / (t_fwd * 1e-3) / 1e12 / pk["tflops"]}
+        if bm is not None:
+            blocks = bm.computed_blocks() * (w["B"] // bm.kv_indices.shape[0]) * (w["H"] // bm.kv_indices.shape[1])
+            comp = 4.0 * w["D"] * bm.BLOCK_SIZE[0] * bm.BLOCK_SIZE[1] * blocks
+            line["computed_blocks"] = {"fwd_tflops": comp / (t_fwd * 1e-3) / 1e12,
+                                       "fwd_bwd_tflops": 3.5 * comp * world / (ms * 1e-3) / 1e12,
+                                       "sparsity_pct": bm.sparsity()}
+        if world == 1:
+            line["decode"] = bench_decode(fa, dev, timed, pk)
+            if rank == 0:
+                cores = os.cpu_count() or 1
+                torch.set_num_threads(cores)
+                sb = 1
+                cpu_oracle_step(w, sb, score, mask)
+                ts = [cpu_oracle_step(w, sb, score, mask) for _ in range(5)]
+                sec = sum(ts) / len(ts)
+                line["cpu_baseline"] = {
+                    "value": 3.5 * flops_fwd(dict(w, B=sb)) / sec / 1e12, "unit": "TFLOP/s", "cores": cores,
+                    "kind": "port",
+                    "sample": f"B={sb} of {w['B']} batch entries, all heads, fwd+bwd, 5 repetitions, fp32 dense oracle"}
+    if rank == 0:
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def bench_decode(fa, dev, timed, pk):
+    from flaxattention_b200.masks import generate_causal_offset
+    from flaxattention_b200.mods import generate_alibi_bias
+
+    d = DECODE
+    res = {}
+    kk = torch.randn(d["B"], d["H"], d["Skv"], d["D"], device=dev, dtype=DT[d["dtype"]])
+    vv = torch.randn_like(kk)
+    alibi = generate_alibi_bias(d["H"])
+    for sq in (1, 16, 64):
+        qq = torch.randn(d["B"], d["H"], sq, d["D"], device=dev, dtype=kk.dtype)
+        bm = fa.create_block_mask(generate_causal_offset(d["Skv"] - sq), d["B"], d["H"], sq, d["Skv"])
+        fn = lambda: fa.flax_attention_pallas(qq, kk, vv, score_mod=alibi, block_mask=bm)  # noqa: E731
+        ms = timed(fn, 20, 3)
+        nbytes = 2 * kk.numel() * 2 + 2 * qq.numel() * 2
+        res[f"sq{sq}"] = {"ms": ms, "gbs": nbytes / (ms * 1e-3) / 1e9, "frac_of_measured_hbm": nbytes / (ms * 1e-3) / 1e9 / pk["hbm"]}
+    return res
+
+
+if __name__ == "__main__":
+    main()

@@ -122,7 +122,7 @@ class _Call:
         p.b_offset, p.h_offset = self.b_offset, self.h_offset
         p.q, p.k, p.v, p.o = (_tensor(t, self.layout) for t in (q, k, v, o))
         p.lse = _ptr(lse)
-        p.flags = _cabi.FLAG_ROUND_SCORES if self.round_scores else 0
+        p.flags = (_cabi.FLAG_ROUND_SCORES if self.round_scores else 0) | int(self.options.get("flags", 0))
         bm = self.block_mask
         if bm is not None:
             t = p.tables

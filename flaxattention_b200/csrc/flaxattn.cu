@@ -346,7 +346,6 @@ int check_tensor(const fa_tensor& t, const char* name, int es, bool required = t
   return FA_OK;
 }
 FaTensor cvt(const fa_tensor& t) { return FaTensor{t.ptr, t.stride_b, t.stride_h, t.stride_s}; }
-FaTensor cvt(const fa_tensor* t) { return t ? cvt(*t) : FaTensor{nullptr, 0, 0, 0}; }
 
 int check_common(fa_module* m, const fa_attn_params* p) {
   if (!m) return fail(FA_EINVAL, "module is null");
@@ -665,7 +664,7 @@ int fa_bwd(fa_module* m, const fa_attn_params* p, const fa_tensor* dout, const f
   Kernel *kdq = nullptr, *kdkdv = nullptr;
   if (int rc = get_bwd_kernel(m, p->dtype, p->D, p->Dv, p->flags, c, true, &kdq)) return rc;
   if (int rc = get_bwd_kernel(m, p->dtype, p->D, p->Dv, p->flags, c, false, &kdkdv)) return rc;
-  {
+  if (!(p->flags & FA_FLAG_BWD_SKIP_DELTA)) {
     cudaStream_t st = (cudaStream_t)stream;
     const long long n_rows = (long long)p->B * p->Hq * p->Sq;
     const int chunks = p->Dv * es / 16;
@@ -687,8 +686,10 @@ int fa_bwd(fa_module* m, const fa_attn_params* p, const fa_tensor* dout, const f
 #undef FA_DELTA
     FA_CUDA_CHECK(cudaGetLastError());
   }
-  if (int rc = launch(kdkdv, dim3((p->Skv + c.tile - 1) / c.tile, p->Hkv, p->B), dim3(c.warps * 32), &kp, stream))
-    return rc;
+  if (!(p->flags & FA_FLAG_BWD_SKIP_DKDV))
+    if (int rc = launch(kdkdv, dim3((p->Skv + c.tile - 1) / c.tile, p->Hkv, p->B), dim3(c.warps * 32), &kp, stream))
+      return rc;
+  if (p->flags & FA_FLAG_BWD_SKIP_DQ) return FA_OK;
   return launch(kdq, dim3((p->Sq + c.tile - 1) / c.tile, p->Hq, p->B), dim3(c.warps * 32), &kp, stream);
 }
 

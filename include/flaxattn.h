@@ -44,6 +44,11 @@ extern "C" {
  * (flaxattention/core/attention.py:27).  Without it the fp32 product is kept, as in the
  * reference's fused kernel (flaxattention/kernel/attention.py:82).  No effect for FA_F32. */
 #define FA_FLAG_ROUND_SCORES 1
+/* Measurement aids for fa_bwd: leave out one of its three kernels (the results of a call
+ * that sets any of them are incomplete). */
+#define FA_FLAG_BWD_SKIP_DELTA 2
+#define FA_FLAG_BWD_SKIP_DKDV 4
+#define FA_FLAG_BWD_SKIP_DQ 8
 
 enum fa_dtype { FA_F16 = 0, FA_BF16 = 1, FA_F32 = 2 };
 
