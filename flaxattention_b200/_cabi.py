@@ -63,7 +63,7 @@ EXPORTS = [
     "fa_last_error", "fa_version", "fa_set_kernel_dir", "fa_set_cache_dir", "fa_module_create",
     "fa_module_destroy", "fa_module_prepare", "fa_compile_count", "fa_fwd", "fa_bwd_workspace_bytes",
     "fa_bwd", "fa_decode_num_splits", "fa_decode_workspace_bytes", "fa_decode",
-    "fa_block_mask_workspace_bytes", "fa_block_mask",
+    "fa_block_mask_workspace_bytes", "fa_block_mask", "fa_decode_static_capacity", "fa_decode_static",
 ]
 
 
@@ -98,6 +98,9 @@ def lib() -> C.CDLL:
         L.fa_decode_workspace_bytes.restype = C.c_size_t
         L.fa_decode_workspace_bytes.argtypes = [C.POINTER(FaAttnParams), C.c_int]
         L.fa_decode.argtypes = [C.c_void_p, C.POINTER(FaAttnParams), C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]
+    if hasattr(L, "fa_decode_static"):
+        L.fa_decode_static_capacity.restype = C.c_size_t
+        L.fa_decode_static.argtypes = [C.c_void_p, C.POINTER(FaAttnParams), C.c_int, C.c_void_p]
     L.fa_set_kernel_dir(os.path.join(_HERE, "csrc", "kernels").encode())
     cache = os.environ.get("FLAXATTN_CACHE_DIR")
     if cache is None:

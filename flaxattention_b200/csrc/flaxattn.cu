@@ -28,6 +28,10 @@
 #include "../../include/flaxattn.h"
 #include "kernels/fa_params.h"
 
+#ifndef FA_STATIC_SCRATCH_BYTES
+#define FA_STATIC_SCRATCH_BYTES (16u << 20)
+#endif
+
 namespace {
 
 thread_local std::string g_err;
@@ -794,6 +798,57 @@ int fa_block_mask(fa_module* m, int B, int H, int Q_LEN, int KV_LEN, int q_block
   if (int rc = run(1, true, q_num_blocks, q_indices)) return rc;
   if (int rc = run(2, true, full_q_num_blocks, full_q_indices)) return rc;
   return FA_OK;
+}
+
+}  // extern "C"
+
+// ======================================================================================
+// Decode without any allocation by the caller or the library
+// ======================================================================================
+namespace {
+
+// Scratch for the split-KV partial results of fa_decode_static.  It is part of the loaded
+// library image: every GPU that loads the library holds these bytes until the process exits.
+constexpr size_t kStaticScratchBytes = (size_t)FA_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+std::mutex g_static_mu;
+void* g_static_ptr[64] = {nullptr};
+
+// In host code `g_static_scratch` is only a handle for the symbol, not a device address; the
+// address a kernel can use has to be asked for, once per device, with that device current.
+int static_scratch(void** out) {
+  int dev = 0;
+  FA_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(FA_EUNSUPPORTED, "device ordinal above 63");
+  std::lock_guard<std::mutex> lk(g_static_mu);
+  if (g_static_ptr[dev] == nullptr) {
+    void* ptr = nullptr;
+    FA_CUDA_CHECK(cudaGetSymbolAddress(&ptr, g_static_scratch));
+    if (ptr == nullptr) return fail(FA_ECUDA, "cudaGetSymbolAddress returned a null address");
+    g_static_ptr[dev] = ptr;
+  }
+  *out = g_static_ptr[dev];
+  return FA_OK;
+}
+
+}  // namespace
+
+extern "C" {
+
+size_t fa_decode_static_capacity(void) { return kStaticScratchBytes; }
+
+int fa_decode_static(fa_module* m, const fa_attn_params* p, int num_splits, void* stream) {
+  if (!p) return fail(FA_EINVAL, "params is null");
+  if (num_splits <= 0) num_splits = fa_decode_num_splits(p, 0);
+  const size_t need = fa_decode_workspace_bytes(p, num_splits);
+  if (need > kStaticScratchBytes)
+    return fail(FA_EWORKSPACE, "fa_decode_static: this problem needs " + std::to_string(need) +
+                                   " bytes of split-KV scratch, the built-in scratch holds " +
+                                   std::to_string(kStaticScratchBytes) + "; use fewer splits or fa_decode");
+  void* ws = nullptr;
+  if (int rc = static_scratch(&ws)) return rc;
+  return fa_decode(m, p, num_splits, ws, kStaticScratchBytes, stream);
 }
 
 }  // extern "C"

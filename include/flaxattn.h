@@ -124,6 +124,30 @@ size_t fa_decode_workspace_bytes(const fa_attn_params* p, int num_splits);
 int fa_decode(fa_module* m, const fa_attn_params* p, int num_splits, void* workspace, size_t workspace_bytes,
               void* stream);
 
+/* fa_decode for callers that cannot allocate device memory.  (No counterpart in the reference.)
+ *
+ * Some hosts of this library may not call cudaMalloc around a decode step: a custom-call
+ * handler that is handed only the buffers its framework planned, a serving loop whose memory
+ * pool is fixed at start-up, code that runs while a stream is being captured.  For them the
+ * split-KV scratch lives inside the library, in a device array of
+ * fa_decode_static_capacity() bytes (16 MiB) that every GPU which loads the library keeps
+ * until the process exits.  The caller passes only inputs and outputs; the call itself
+ * allocates nothing and frees nothing.
+ *
+ * Same arguments and results as fa_decode (num_splits <= 0 lets the library choose).  A
+ * problem whose scratch (fa_decode_workspace_bytes) exceeds the capacity is refused with
+ * FA_EWORKSPACE and a message that names both sizes.
+ *
+ * First call on a device: the library looks up the device address of its scratch array
+ * (with that device current) and, if this module's decode kernel has not run on the device
+ * yet, compiles and loads it.  Make that first call before any stream capture begins.
+ *
+ * All calls share the one array.  The kernels overwrite every scratch word they later read,
+ * so nothing has to be cleared between calls, but two fa_decode_static calls that can
+ * overlap on the same GPU (different streams, no ordering) race on it: serialise them. */
+size_t fa_decode_static_capacity(void);
+int fa_decode_static(fa_module* m, const fa_attn_params* p, int num_splits, void* stream);
+
 /* BlockMask construction.  Q_LEN / KV_LEN are the raw lengths; the block grid is
  * ceil(Q_LEN/q_block) x ceil(KV_LEN/kv_block).  Output tables have the shapes listed in
  * fa_block_tables with mask_B = B and mask_H = H.  full_* may be NULL (then blocks that are
