@@ -178,6 +178,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-extras", action="store_true", help="skip forward-only, decode, per-kernel and CPU legs")
+    ap.add_argument("--profile", default=None, choices=["fwd", "bwd", "decode"],
+                    help="small case for a profiler: a few launches of one kernel family, no JSON line")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     w = WORKLOADS[args.workload]
@@ -188,6 +190,9 @@ def main():
 
     if args.impl == "reference":
         run_reference(args, w, rank, world)
+        return
+    if args.profile:
+        run_profile_case(args, w)
         return
 
     import flaxattention_b200 as fa
@@ -343,6 +348,40 @@ def main():
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+
+
+def run_profile_case(args, w):
+    """A few launches of one kernel family on a reduced batch, for ncu (a capture replays every
+    launch many times, so the case is kept small).  fwd / bwd: the workload with B=2;
+    decode: B=8, H=8, Skv=16384, Sq=1 (K+V = 268 MB, larger than L2)."""
+    import flaxattention_b200 as fa
+    from flaxattention_b200 import attention as A
+    from flaxattention_b200.masks import generate_causal_offset
+    from flaxattention_b200.mods import generate_alibi_bias
+
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    if args.profile == "decode":
+        d = dict(DECODE, B=8)
+        kk = torch.randn(d["B"], d["H"], d["Skv"], d["D"], device=dev, dtype=DT[d["dtype"]])
+        vv = torch.randn_like(kk)
+        qq = torch.randn(d["B"], d["H"], 1, d["D"], device=dev, dtype=kk.dtype)
+        bm = fa.create_block_mask(generate_causal_offset(d["Skv"] - 1), d["B"], d["H"], 1, d["Skv"])
+        for _ in range(4):
+            fa.flax_attention_pallas(qq, kk, vv, score_mod=generate_alibi_bias(d["H"]), block_mask=bm)
+        torch.cuda.synchronize()
+        return
+    ws = dict(w, B=2)
+    score, mask = mods_for(ws)
+    q, k, v = (t.to(dev) for t in host_inputs(ws, 0, pinned=False))
+    bm = fa.create_block_mask(mask, ws["B"], ws["H"], ws["Sq"], ws["Skv"]) if mask is not None else None
+    call = A._Call(q, k, v, score, None if bm is None else bm.mask_mod, bm, 1.0 / math.sqrt(ws["D"]), "bhsd", 0, 0, None)
+    dout = torch.ones(ws["B"], ws["H"], ws["Sq"], ws["D"], dtype=q.dtype, device=dev)
+    for _ in range(4):
+        out, lse = A._forward(call, q, k, v)
+        if args.profile == "bwd":
+            A._backward(call, q, k, v, out, lse, dout)
+    torch.cuda.synchronize()
 
 
 def bench_decode(fa, dev, timed, pk):
