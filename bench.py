@@ -43,6 +43,7 @@ import torch  # noqa: E402
 WORKLOADS = {
     # name: B, H, Sq, Skv, D, dtype, score_mod, mask, block
     "cfg2": dict(B=8, H=8, Sq=2048, Skv=2048, D=64, dtype="f16", score="checkerboard", mask=None),
+    "cfg2_nomod": dict(B=8, H=8, Sq=2048, Skv=2048, D=64, dtype="f16", score=None, mask=None),
     "cfg3": dict(B=8, H=8, Sq=2048, Skv=2048, D=64, dtype="bf16", score="alibi", mask="causal"),
     "cfg4": dict(B=4, H=16, Sq=8192, Skv=8192, D=128, dtype="bf16", score=None, mask="sink"),
 }

@@ -16,6 +16,7 @@ LIB_PATH = os.path.join(_HERE, "libflaxattn.so")
 FA_F16, FA_BF16, FA_F32 = 0, 1, 2
 FLAG_ROUND_SCORES = 1
 FLAG_BWD_SKIP_DELTA, FLAG_BWD_SKIP_DKDV, FLAG_BWD_SKIP_DQ = 2, 4, 8
+FLAG_GENERAL_KERNELS = 16
 KIND_FWD, KIND_BWD, KIND_DECODE, KIND_BLOCKMASK = 0, 1, 2, 3
 
 

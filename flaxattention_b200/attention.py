@@ -123,6 +123,11 @@ class _Call:
         p.q, p.k, p.v, p.o = (_tensor(t, self.layout) for t in (q, k, v, o))
         p.lse = _ptr(lse)
         p.flags = (_cabi.FLAG_ROUND_SCORES if self.round_scores else 0) | int(self.options.get("flags", 0))
+        if self.options.get("kernels") == "general":
+            p.flags |= _cabi.FLAG_GENERAL_KERNELS
+        st = self.options.get("status")  # optional int32 CUDA tensor the kernels OR error bits into
+        if st is not None:
+            p.status = st.data_ptr()
         bm = self.block_mask
         if bm is not None:
             t = p.tables

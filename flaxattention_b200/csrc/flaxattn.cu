@@ -6,6 +6,7 @@
 // NVRTC, cached in memory per module and on disk per content hash, and loaded through the
 // context-independent library API of the CUDA runtime.
 #include <cuda_runtime.h>
+#include <cuda.h>
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 #include <nvrtc.h>
@@ -107,7 +108,7 @@ std::string cache_dir() {
 }
 
 const char* const kTemplateFiles[] = {"fa_params.h", "fa_common.cuh", "fa_fwd.cuh", "fa_bwd.cuh",
-                                      "fa_decode.cuh", "fa_blockmask.cuh"};
+                                      "fa_decode.cuh", "fa_blockmask.cuh", "fa_sm100.cuh", "fa_fwd_tc.cuh"};
 std::string g_templates_hash;
 int templates_hash(std::string& out) {
   if (g_templates_hash.empty()) {
@@ -590,6 +591,91 @@ int get_decode_kernel(fa_module* m, int dtype, int D, int Dv, int flags, const D
                           {"FA_STAGES", c.stages}, {"FA_ROUND_SCORES", round_flag(dtype, flags)}}),
                     "fa_decode_kernel", c.smem, k);
 }
+// ---- tcgen05 forward: TMA tensor maps and dispatch -----------------------------------------
+struct alignas(64) FaTensorMapHost {
+  unsigned long long v[16];
+};
+static_assert(sizeof(FaTensorMapHost) == sizeof(CUtensorMap), "tensor map size");
+struct FaTcParamsHost {
+  FaParams p;
+  FaTensorMapHost tq, tk, tv;
+};
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn g_encode_tiled = nullptr;
+
+int encode_fn(EncodeTiledFn* out) {
+  std::lock_guard<std::mutex> lk(g_mu);
+  if (!g_encode_tiled) {
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    FA_CUDA_CHECK(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+    if (!fn || q != cudaDriverEntryPointSuccess) return fail(FA_ECUDA, "cuTensorMapEncodeTiled is not available");
+    g_encode_tiled = (EncodeTiledFn)fn;
+  }
+  *out = g_encode_tiled;
+  return FA_OK;
+}
+
+// 4-d map (D, S, H, B) over a [.., S, D]-strided tensor; box = 64 elements x 128 rows, 128-byte swizzle
+int make_map(FaTensorMapHost* out, int dtype, const fa_tensor& t, int D, int S, int H, int B) {
+  EncodeTiledFn enc = nullptr;
+  if (int rc = encode_fn(&enc)) return rc;
+  const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)H, (cuuint64_t)B};
+  const cuuint64_t strides[3] = {(cuuint64_t)t.stride_s * 2, (cuuint64_t)t.stride_h * 2, (cuuint64_t)t.stride_b * 2};
+  const cuuint32_t box[4] = {64, 128, 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc((CUtensorMap*)out, dtype == FA_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
+                   t.ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(FA_ECUDA, "cuTensorMapEncodeTiled failed with code " + std::to_string((int)r));
+  return FA_OK;
+}
+
+// Shapes the tcgen05 forward kernel covers; everything else runs on the general kernel.
+bool tc_fwd_eligible(const fa_attn_params* p) {
+  if (p->flags & FA_FLAG_GENERAL_KERNELS) return false;
+  if (p->dtype == FA_F32) return false;
+  if (p->D != p->Dv || !(p->D == 64 || p->D == 128)) return false;
+  if (p->Sq < 128 || p->Skv > 32768) return false;
+  const fa_block_tables& t = p->tables;
+  if (t.kv_num_blocks) {
+    if (!(t.num_q_blocks == 1 || t.q_block_size % 128 == 0)) return false;
+    if (!(t.num_kv_blocks == 1 || t.kv_block_size % 128 == 0)) return false;
+  }
+  // byte strides above the row must stay below 2^40 (tensor-map limit); rows are 16-byte aligned already
+  return true;
+}
+
+int get_fwd_tc_kernel(fa_module* m, int dtype, int D, int flags, Kernel** k) {
+  const int atoms = D / 64, nstage = D == 64 ? 3 : 2;
+  const int smem = 2 * atoms * 16384 + 2 * nstage * atoms * 16384 + (1 + 4 * nstage + 6) * 8 + 16 + 256 * 2 + 256 * 2 +
+                   2 * 256 + 1024;
+  std::string d = defs({{"FA_DTYPE", dtype}, {"FA_D", D}, {"FA_ROUND_SCORES", round_flag(dtype, flags)}});
+  if (const char* e = getenv("FLAXATTN_TC_DEFS")) {  // tuning aid: extra "NAME=VALUE,NAME=VALUE" defines
+    std::string t = e, item;
+    std::stringstream ss(t);
+    while (std::getline(ss, item, ',')) {
+      const size_t eq = item.find('=');
+      if (eq != std::string::npos) d += "#define " + item.substr(0, eq) + " " + item.substr(eq + 1) + "\n";
+    }
+  }
+  return get_kernel(m, "fa_fwd_tc.cuh", d, "fa_fwd_tc_kernel", smem, k);
+}
+
+int launch_fwd_tc(fa_module* m, const fa_attn_params* p, const FaParams& kp, void* stream) {
+  Kernel* k = nullptr;
+  if (int rc = get_fwd_tc_kernel(m, p->dtype, p->D, p->flags, &k)) return rc;
+  FaTcParamsHost tp;
+  tp.p = kp;
+  if (int rc = make_map(&tp.tq, p->dtype, p->q, p->D, p->Sq, p->Hq, p->B)) return rc;
+  if (int rc = make_map(&tp.tk, p->dtype, p->k, p->D, p->Skv, p->Hkv, p->B)) return rc;
+  if (int rc = make_map(&tp.tv, p->dtype, p->v, p->Dv, p->Skv, p->Hkv, p->B)) return rc;
+  return launch(k, dim3((p->Sq + 255) / 256, p->Hq, p->B), dim3(384), &tp, stream);
+}
+
 int get_blockmask_kernel(fa_module* m, Kernel** k) {
   return get_kernel(m, "fa_blockmask.cuh", "", "fa_blockmask_classify_kernel", 0, k);
 }
@@ -606,6 +692,8 @@ int fa_module_prepare(fa_module* m, int kind, int dtype, int D, int Dv, int Sq_h
     case FA_KIND_FWD: {
       FwdCfg c;
       if (int rc = pick_fwd(dtype, D, Dv, Sq_hint, nullptr, c)) return rc;
+      if (dtype != FA_F32 && D == Dv && (D == 64 || D == 128) && Sq_hint >= 128)
+        if (int rc = get_fwd_tc_kernel(m, dtype, D, 0, &k)) return rc;
       return get_fwd_kernel(m, dtype, D, Dv, 0, c, &k);
     }
     case FA_KIND_BWD: {
@@ -630,6 +718,7 @@ int fa_fwd(fa_module* m, const fa_attn_params* p, void* stream) {
   if (int rc = check_common(m, p)) return rc;
   FaParams kp;
   fill_params(p, kp);
+  if (tc_fwd_eligible(p)) return launch_fwd_tc(m, p, kp, stream);
   FwdCfg c;
   if (int rc = pick_fwd(p->dtype, p->D, p->Dv, p->Sq, &kp.t, c)) return rc;
   Kernel* k = nullptr;

@@ -1,0 +1,507 @@
+// Flash-attention forward for sm_100a on the 5th-generation tensor cores:
+//   S = Q K^T and O += P V are tcgen05.mma instructions with accumulators in TMEM,
+//   Q / K / V tiles arrive by TMA (128-byte swizzle) through an mbarrier ring,
+//   the softmax runs thread-per-row on data read with tcgen05.ld, and P goes back to TMEM
+//   (16-bit, aliasing S) to be the A operand of the second product.
+// Same math and BlockMask walk as fa_fwd.cuh (see there for the reference citations); this
+// kernel covers fp16 / bf16, D = Dv in {64, 128}, block sizes that are multiples of 128.
+//
+// One CTA owns two 128-row query tiles of one (batch, head) and streams 128-row K/V tiles
+// past both.  Warp roles (12 warps = 3 warpgroups):
+//   warps 0-3  softmax warpgroup of query tile 0      warps 4-7  of query tile 1
+//   warp 8     TMA producer (one lane)
+//   warp 9     MMA issuer (one lane); also allocates / frees TMEM       warps 10-11 idle
+// Registers are moved from the third warpgroup to the two softmax warpgroups (setmaxnreg),
+// which hold a whole 128-column score row per thread.
+// While one warpgroup does the softmax of its tile, the tensor core works on the other
+// tile: the issue order per kv step j is  PV0(j), S0(j+1), PV1(j), S1(j+1).
+// The running maximum is only raised when it grew by more than 2^8 (the stale maximum is
+// exact as long as it is used consistently), so rescaling O in TMEM is rare.
+//
+// Every mbarrier wait is bounded; on expiry the CTA raises FA_STATUS_WAIT_TIMEOUT in the
+// status word, all roles leave their loops, TMEM is freed and the kernel returns.
+//
+// Compile-time parameters (macros): FA_DTYPE (0 fp16, 1 bf16), FA_D (64 or 128).
+#pragma once
+#include "fa_sm100.cuh"
+
+struct FaTcParams {
+  FaParams p;
+  FaTensorMap tq, tk, tv;  // 4-d maps (D, S, H, B), box 64 x 128 x 1 x 1, 128-byte swizzle
+};
+
+namespace fa_tc {
+
+constexpr int DT = FA_DTYPE;
+constexpr int D = FA_D;
+constexpr int BM = 128, BN = 128;
+constexpr int ATOMS = D / 64;            // 64-element (128-byte) column groups per row
+constexpr int ATOM_BYTES = 128 * 128;    // 128 rows x 128 bytes
+constexpr int NSTAGE = D == 64 ? 3 : 2;
+constexpr int Q_BYTES = 2 * ATOMS * ATOM_BYTES;
+constexpr int KV_STAGE = ATOMS * ATOM_BYTES;
+constexpr int MAXT = 256;                // kv tiles per row of the block grid (Skv <= 32768)
+constexpr int NBARS = 1 + 4 * NSTAGE + 6;
+constexpr int OFF_K = Q_BYTES;
+constexpr int OFF_V = OFF_K + NSTAGE * KV_STAGE;
+constexpr int OFF_BAR = OFF_V + NSTAGE * KV_STAGE;
+constexpr int OFF_MISC = OFF_BAR + NBARS * 8;       // tmem base, abort flag, nsteps, pad
+constexpr int OFF_SCHED = OFF_MISC + 16;            // short tile[MAXT]
+constexpr int OFF_MODE = OFF_SCHED + MAXT * 2;      // uchar mode[MAXT][2]
+constexpr int OFF_CLS = OFF_MODE + MAXT * 2;        // uchar cls[2][MAXT]
+constexpr int SMEM_BYTES = OFF_CLS + 2 * MAXT + 1024;  // + slack for the 1024-byte alignment
+constexpr int TMEM_COLS = 512;
+constexpr int COL_S = 0, COL_O = 256;
+#ifndef FA_TC_HALF_EXP
+#define FA_TC_HALF_EXP 0
+#endif
+#ifndef FA_TC_SETMAXNREG
+#define FA_TC_SETMAXNREG 0
+#endif
+constexpr int NT = 384;
+constexpr int WARP_PRODUCER = 8, WARP_MMA = 9;
+constexpr int REGS_SOFTMAX = 200, REGS_OTHER = 112;
+constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
+
+static_assert(D == 64 || D == 128, "head dim 64 or 128");
+static_assert(DT == FA_DT_F16 || DT == FA_DT_BF16, "16-bit inputs");
+
+__device__ __forceinline__ fa_u32 bar_addr(fa_u32 sbase, int i) { return sbase + OFF_BAR + i * 8; }
+constexpr int BAR_Q = 0;
+constexpr int BAR_KFULL = 1, BAR_KEMPTY = 1 + NSTAGE, BAR_VFULL = 1 + 2 * NSTAGE, BAR_VEMPTY = 1 + 3 * NSTAGE;
+constexpr int BAR_S = 1 + 4 * NSTAGE, BAR_P = BAR_S + 2, BAR_O = BAR_S + 4;
+
+// Pass-1 work on one 32-column chunk of a score row (columns C0 .. C0+31 of the kv tile that
+// starts at key n0).  C0 is a template parameter and n0 a multiple of 128, so the low bits of
+// every key index are compile-time constants inside the mods.
+struct RowMax {
+  float a, b, c, d;
+};
+template <int C0>
+__device__ __forceinline__ void pass1_chunk(float (&v)[32], RowMax& mx, bool plain, bool ragged, int mode, int n0,
+                                            int qi, int gb, int gh, float scale, float sc2, int Skv) {
+  if (plain) {
+#pragma unroll
+    for (int e = 0; e < 32; e += 8) {
+      mx.a = fa_max3(mx.a, v[e], v[e + 1]);
+      mx.b = fa_max3(mx.b, v[e + 2], v[e + 3]);
+      mx.c = fa_max3(mx.c, v[e + 4], v[e + 5]);
+      mx.d = fa_max3(mx.d, v[e + 6], v[e + 7]);
+    }
+    return;
+  }
+#pragma unroll
+  for (int e = 0; e < 32; e += 2) {
+    float x0 = v[e], x1 = v[e + 1];
+    const int kv0 = n0 | (C0 + e);
+    const int kv1 = n0 | (C0 + e + 1);
+#if FA_ROUND_SCORES
+    fa_round2<DT>(x0, x1);
+#endif
+#if FA_HAS_SCORE_MOD && defined(FA_SCORE_AFFINE)
+    x0 = fmaf(x0, fa_score_mul(0.f, gb, gh, qi, kv0) * sc2, fa_score_add(0.f, gb, gh, qi, kv0) * FA_LOG2E);
+    x1 = fmaf(x1, fa_score_mul(0.f, gb, gh, qi, kv1) * sc2, fa_score_add(0.f, gb, gh, qi, kv1) * FA_LOG2E);
+#elif FA_HAS_SCORE_MOD
+    x0 = fa_score_mod(x0 * scale, gb, gh, qi, kv0) * FA_LOG2E;
+    x1 = fa_score_mod(x1 * scale, gb, gh, qi, kv1) * FA_LOG2E;
+#else
+    x0 *= sc2;
+    x1 *= sc2;
+#endif
+    bool k0 = true, k1 = true;
+#if FA_HAS_MASK_MOD
+    if (mode == 1) {
+      k0 = fa_mask_mod(gb, gh, qi, kv0);
+      k1 = fa_mask_mod(gb, gh, qi, kv1);
+    }
+#endif
+    if (ragged) {
+      k0 = k0 && (kv0 < Skv);
+      k1 = k1 && (kv1 < Skv);
+    }
+    x0 = k0 ? x0 : FA_NEG_INF;
+    x1 = k1 ? x1 : FA_NEG_INF;
+    v[e] = x0;
+    v[e + 1] = x1;
+    if ((e & 6) == 0) mx.a = fa_max3(mx.a, x0, x1);
+    else if ((e & 6) == 2) mx.b = fa_max3(mx.b, x0, x1);
+    else if ((e & 6) == 4) mx.c = fa_max3(mx.c, x0, x1);
+    else mx.d = fa_max3(mx.d, x0, x1);
+  }
+}
+
+// Pass-2 work on one chunk: p = 2^(x * cmul - m), packed to 16 bits, and the row-sum chains.
+__device__ __forceinline__ void pass2_chunk(const float (&v)[32], fa_u32 (&pk)[16], fa_u64 cmul, fa_u64 negm,
+                                            fa_u64& sum_a, fa_u64& sum_b) {
+#pragma unroll
+  for (int e = 0; e < 16; ++e) {
+    float a0, a1;
+    fa_f2_unpack(fa_fma2(fa_f2(v[2 * e], v[2 * e + 1]), cmul, negm), a0, a1);
+#if FA_TC_HALF_EXP
+    pk[e] = fa_ex2_h2<DT>(fa_pack2<DT>(a0, a1));
+    const fa_u64 pf = fa_h2_to_f2<DT>(pk[e]);
+#else
+    const float p0 = fa_ex2(a0), p1 = fa_ex2(a1);
+    pk[e] = fa_pack2<DT>(p0, p1);
+    const fa_u64 pf = fa_f2(p0, p1);
+#endif
+    if (e & 1) sum_b = fa_add2(sum_b, pf);
+    else sum_a = fa_add2(sum_a, pf);
+  }
+}
+
+}  // namespace fa_tc
+
+extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(const __grid_constant__ FaTcParams P) {
+  using namespace fa_tc;
+  const FaParams& p = P.p;
+  extern __shared__ unsigned char smem_raw[];
+  const fa_u32 raw = fa_smem_u32(smem_raw);
+  const fa_u32 sb = (raw + 1023u) & ~1023u;  // shared-window address of the aligned base
+  unsigned char* sm = smem_raw + (sb - raw);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int pair = gridDim.x - 1 - blockIdx.x;
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int m0 = pair * 2 * BM;
+  const int hk = h / (p.Hq / p.Hkv);
+  const int gb = b + p.b_off, gh = h + p.h_off;
+
+  volatile int* misc = (volatile int*)(sm + OFF_MISC);  // [0] tmem base, [1] abort, [2] nsteps
+  short* sched_tile = (short*)(sm + OFF_SCHED);
+  unsigned char* sched_mode = sm + OFF_MODE;
+  unsigned char* cls = sm + OFF_CLS;
+
+  // ---- set-up: barriers, TMEM, kv schedule ---------------------------------------------
+  if (tid == 0) {
+    fa_mbar_init(bar_addr(sb, BAR_Q), 1);
+    for (int s = 0; s < NSTAGE; ++s) {
+      fa_mbar_init(bar_addr(sb, BAR_KFULL + s), 1);
+      fa_mbar_init(bar_addr(sb, BAR_KEMPTY + s), 1);
+      fa_mbar_init(bar_addr(sb, BAR_VFULL + s), 1);
+      fa_mbar_init(bar_addr(sb, BAR_VEMPTY + s), 1);
+    }
+    for (int i = 0; i < 2; ++i) {
+      fa_mbar_init(bar_addr(sb, BAR_S + i), 1);
+      fa_mbar_init(bar_addr(sb, BAR_P + i), 128);
+      fa_mbar_init(bar_addr(sb, BAR_O + i), 1);
+    }
+    fa_mbar_init_fence();
+    misc[1] = 0;
+    misc[2] = 0;
+  }
+  const int ntiles = min((p.Skv + BN - 1) / BN, MAXT);
+  for (int i = tid; i < 2 * MAXT; i += NT) cls[i] = 0;
+  if (warp == WARP_MMA) fa_tmem_alloc(sb + OFF_MISC, TMEM_COLS);
+  __syncthreads();
+  // class of every kv tile for both query tiles: 0 skip, 1 apply mask_mod, 2 full
+  for (int i = 0; i < 2; ++i) {
+    const int mi = m0 + i * BM;
+    if (mi >= p.Sq) continue;
+    if (p.t.kv_num == nullptr) {
+      for (int t = tid; t < ntiles; t += NT) cls[i * MAXT + t] = FA_HAS_MASK_MOD ? 1 : 2;
+    } else {
+      const int bm = p.t.mB == 1 ? 0 : b, hm = p.t.mH == 1 ? 0 : h;
+      const int qblk = min(mi / p.t.QB, p.t.nQ - 1);
+      const long long row = ((long long)bm * p.t.mH + hm) * p.t.nQ + qblk;
+      const int tpb = p.t.nKV == 1 ? ntiles : p.t.KVB / BN;
+      for (int which = 0; which < 2; ++which) {
+        const int* nump = which ? p.t.full_kv_num : p.t.kv_num;
+        const int* idxp = which ? p.t.full_kv_idx : p.t.kv_idx;
+        if (nump == nullptr) continue;
+        const int num = min(max(nump[row], 0), p.t.nKV);
+        for (int e = tid; e < num * tpb; e += NT) {
+          const int bi = e / tpb, ti = e - bi * tpb;
+          const int blk = min(max(idxp[row * p.t.nKV + bi], 0), p.t.nKV - 1);
+          const int t = blk * tpb + ti;
+          if (t < ntiles) cls[i * MAXT + t] = (unsigned char)(which ? 2 : 1);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  if (tid == 0) {
+    int n = 0;
+    for (int t = 0; t < ntiles; ++t) {
+      const unsigned char c0 = cls[t], c1 = cls[MAXT + t];
+      if (c0 | c1) {
+        sched_tile[n] = (short)t;
+        sched_mode[2 * n] = c0;
+        sched_mode[2 * n + 1] = c1;
+        ++n;
+      }
+    }
+    misc[2] = n;
+  }
+  fa_tc_fence_before();
+  __syncthreads();
+  fa_tc_fence_after();
+  const fa_u32 tmem = (fa_u32)misc[0];
+  const int nsteps = misc[2];
+  volatile int* abort_flag = misc + 1;
+
+#if FA_TC_SETMAXNREG
+  if (warp >= 8) {
+    fa_setmaxnreg_dec<REGS_OTHER>();
+  } else {
+    fa_setmaxnreg_inc<REGS_SOFTMAX>();
+  }
+#endif
+  if (warp == WARP_PRODUCER) {
+    // ================================ TMA producer =======================================
+    if (lane == 0) {
+      fa_tma_prefetch_desc(&P.tq);
+      fa_tma_prefetch_desc(&P.tk);
+      fa_tma_prefetch_desc(&P.tv);
+      fa_mbar_expect_tx(bar_addr(sb, BAR_Q), Q_BYTES);
+      for (int i = 0; i < 2; ++i)
+        for (int a = 0; a < ATOMS; ++a)
+          fa_tma_load_4d(sb + (i * ATOMS + a) * ATOM_BYTES, &P.tq, bar_addr(sb, BAR_Q), a * 64, m0 + i * BM, h, b);
+      bool ok = true;
+      for (int j = 0; j < nsteps && ok; ++j) {
+        const int s = j % NSTAGE;
+        const fa_u32 ph = (fa_u32)((j / NSTAGE) & 1);
+        const int n0 = (int)sched_tile[j] * BN;
+        if (j >= NSTAGE) ok = fa_mbar_wait(bar_addr(sb, BAR_KEMPTY + s), ph ^ 1u, abort_flag);
+        if (!ok) break;
+        fa_mbar_expect_tx(bar_addr(sb, BAR_KFULL + s), KV_STAGE);
+        for (int a = 0; a < ATOMS; ++a)
+          fa_tma_load_4d(sb + OFF_K + s * KV_STAGE + a * ATOM_BYTES, &P.tk, bar_addr(sb, BAR_KFULL + s), a * 64, n0, hk, b);
+        if (j >= NSTAGE) ok = fa_mbar_wait(bar_addr(sb, BAR_VEMPTY + s), ph ^ 1u, abort_flag);
+        if (!ok) break;
+        fa_mbar_expect_tx(bar_addr(sb, BAR_VFULL + s), KV_STAGE);
+        for (int a = 0; a < ATOMS; ++a)
+          fa_tma_load_4d(sb + OFF_V + s * KV_STAGE + a * ATOM_BYTES, &P.tv, bar_addr(sb, BAR_VFULL + s), a * 64, n0, hk, b);
+      }
+    }
+  } else if (warp == WARP_MMA) {
+    // ================================ MMA issuer =========================================
+    if (lane == 0) {
+      constexpr fa_u32 IDESC_S = fa_idesc(DT, BM, BN, 0, 0);
+      constexpr fa_u32 IDESC_O = fa_idesc(DT, BM, D, 0, 1);
+      bool ok = nsteps == 0 || fa_mbar_wait(bar_addr(sb, BAR_Q), 0, abort_flag);
+      fa_u32 cnt[2] = {0, 0};  // active steps seen so far per query tile
+      // S_i = Q_i K^T for step j into TMEM columns COL_S + 128 i
+      auto issue_s = [&](int i, int j) {
+        const int s = j % NSTAGE;
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+          const fa_u32 koff = (kk / 4) * ATOM_BYTES + (kk % 4) * 32;
+          const fa_u64 da = fa_smem_desc_sw128(sb + i * ATOMS * ATOM_BYTES + koff, 16);
+          const fa_u64 db = fa_smem_desc_sw128(sb + OFF_K + s * KV_STAGE + koff, 16);
+          fa_mma_ss(tmem + COL_S + i * BN, da, db, IDESC_S, kk > 0);
+        }
+        fa_mma_commit(bar_addr(sb, BAR_S + i));
+      };
+      // O_i += P_i V for step j (P_i: 16-bit, in the first 64 columns of S_i)
+      auto issue_pv = [&](int i, int j, bool first) {
+        const int s = j % NSTAGE;
+#pragma unroll
+        for (int kk = 0; kk < BN / 16; ++kk) {
+          const fa_u64 db = fa_smem_desc_sw128(sb + OFF_V + s * KV_STAGE + kk * 2048, ATOM_BYTES);
+          fa_mma_ts(tmem + COL_O + i * D, tmem + COL_S + i * BN + kk * 8, db, IDESC_O, (!first) || kk > 0);
+        }
+        fa_mma_commit(bar_addr(sb, BAR_O + i));
+      };
+      if (ok && nsteps > 0) {
+        ok = fa_mbar_wait(bar_addr(sb, BAR_KFULL + 0), 0, abort_flag);
+        if (ok) {
+          fa_tc_fence_after();
+          if (sched_mode[0]) issue_s(0, 0);
+          if (sched_mode[1]) issue_s(1, 0);
+          fa_mma_commit(bar_addr(sb, BAR_KEMPTY + 0));
+        }
+      }
+      for (int j = 0; j < nsteps && ok; ++j) {
+        const int s = j % NSTAGE;
+        const fa_u32 ph = (fa_u32)((j / NSTAGE) & 1);
+        const bool more = j + 1 < nsteps;
+        const int s1 = (j + 1) % NSTAGE;
+        const fa_u32 ph1 = (fa_u32)(((j + 1) / NSTAGE) & 1);
+        bool k_ready = false;
+        ok = fa_mbar_wait(bar_addr(sb, BAR_VFULL + s), ph, abort_flag);
+        for (int i = 0; i < 2 && ok; ++i) {
+          if (sched_mode[2 * j + i]) {
+            ok = fa_mbar_wait(bar_addr(sb, BAR_P + i), cnt[i] & 1u, abort_flag);
+            if (!ok) break;
+            fa_tc_fence_after();
+            issue_pv(i, j, cnt[i] == 0);
+            ++cnt[i];
+          }
+          if (i == 1) fa_mma_commit(bar_addr(sb, BAR_VEMPTY + s));
+          if (more && sched_mode[2 * (j + 1) + i]) {
+            if (!k_ready) {
+              ok = fa_mbar_wait(bar_addr(sb, BAR_KFULL + s1), ph1, abort_flag);
+              if (!ok) break;
+              fa_tc_fence_after();
+              k_ready = true;
+            }
+            issue_s(i, j + 1);
+          }
+          if (i == 1 && more) fa_mma_commit(bar_addr(sb, BAR_KEMPTY + s1));
+        }
+      }
+    }
+  } else if (warp < 8) {
+    // ================================ softmax warpgroups ==================================
+    const int i = warp >> 2;                       // query tile of this warpgroup
+    const int lane_base = (warp & 3) * 32;         // TMEM lanes this warp may touch
+    const int r = lane_base + lane;                // row inside the tile
+    const int qi = m0 + i * BM + r;                // query index
+    const fa_u32 t_s = tmem + ((fa_u32)lane_base << 16) + COL_S + i * BN;
+    const fa_u32 t_o = tmem + ((fa_u32)lane_base << 16) + COL_O + i * D;
+    float m_ref = FA_NEG_INF, l = 0.f;
+    fa_u32 cnt = 0;
+    bool ok = true;
+    const float sc2 = p.scale * FA_LOG2E;
+    for (int j = 0; j < nsteps && ok; ++j) {
+      const int mode = sched_mode[2 * j + i];
+      if (mode == 0) continue;
+      const int n0 = (int)sched_tile[j] * BN;
+      ok = fa_mbar_wait_warp(bar_addr(sb, BAR_S + i), cnt & 1u, abort_flag);
+      if (!ok) break;
+      fa_tc_fence_after();
+      const bool ragged = n0 + BN > p.Skv;
+#if FA_HAS_SCORE_MOD || FA_HAS_MASK_MOD || FA_ROUND_SCORES
+      const bool plain = false;
+#else
+      const bool plain = !ragged && sc2 > 0.f;
+#endif
+      // ---- pass 1: row maximum.  The plain path (no mods, full tile) takes it over the raw
+      // scores; otherwise the scores are scaled / modded / masked, converted to log2 units
+      // and written back to TMEM in place, so that pass 2 can read them again.  An affine
+      // score_mod (A * score + B) costs one FMA: A and B absorb the scale and log2(e).
+      RowMax rm = {FA_NEG_INF, FA_NEG_INF, FA_NEG_INF, FA_NEG_INF};
+      {
+        float va[32], vb[32];
+#define FA_P1(V, C0)                                                                                   \
+  pass1_chunk<C0>(V, rm, plain, ragged, mode, n0, qi, gb, gh, p.scale, sc2, p.Skv);                     \
+  if (!plain) fa_tmem_st32(t_s + C0, V);
+        fa_tmem_ld32(t_s, va);
+        fa_tmem_wait_ld();
+        fa_tmem_ld32(t_s + 32, vb);
+        FA_P1(va, 0)
+        fa_tmem_wait_ld();
+        fa_tmem_ld32(t_s + 64, va);
+        FA_P1(vb, 32)
+        fa_tmem_wait_ld();
+        fa_tmem_ld32(t_s + 96, vb);
+        FA_P1(va, 64)
+        fa_tmem_wait_ld();
+        FA_P1(vb, 96)
+#undef FA_P1
+        if (!plain) fa_tmem_wait_st();
+      }
+      float mx = fmaxf(fmaxf(rm.a, rm.b), fmaxf(rm.c, rm.d));
+      if (plain) mx *= sc2;
+      // running maximum, raised lazily
+      const float m_new = fmaxf(m_ref, mx);
+      bool need = false;
+      float corr = 1.f;
+      if (m_ref == FA_NEG_INF) {
+        m_ref = m_new;  // nothing accumulated yet for this row
+      } else if (m_new - m_ref > RESCALE_THRESHOLD) {
+        need = true;
+        corr = fa_ex2(m_ref - m_new);
+        m_ref = m_new;
+        l *= corr;
+      }
+      if (cnt > 0 && __any_sync(0xffffffffu, need)) {
+        // O_i of the previous steps has to be complete before it is rescaled in place
+        ok = fa_mbar_wait_warp(bar_addr(sb, BAR_O + i), (cnt - 1) & 1u, abort_flag);
+        if (!ok) break;
+        fa_tc_fence_after();
+#pragma unroll 1
+        for (int c = 0; c < D / 16; ++c) {
+          float o[16];
+          fa_tmem_ld16(t_o + c * 16, o);
+          fa_tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 16; ++e) o[e] *= corr;
+          fa_tmem_st16f(t_o + c * 16, o);
+        }
+      }
+      // ---- pass 2: p = 2^(x * cmul - m) and the row sum; P goes to TMEM as 16-bit pairs.
+      // P chunk c (16 columns) overwrites score columns that have already been read.
+      // With FA_TC_HALF_EXP the exponent is rounded to the 16-bit input type first and one SFU
+      // operation yields both values of a pair already in the format the second product needs;
+      // the row sum is then taken over exactly the values that product sees.
+      const float m_use = (m_ref == FA_NEG_INF) ? 0.f : m_ref;
+      const fa_u64 negm = fa_f2(-m_use, -m_use);
+      const float cm = plain ? sc2 : 1.f;
+      const fa_u64 cmul = fa_f2(cm, cm);
+      fa_u64 sum_a = fa_f2(0.f, 0.f), sum_b = fa_f2(0.f, 0.f);
+      {
+        float va[32], vb[32];
+        fa_u32 pk[16];
+        fa_tmem_ld32(t_s, va);
+        fa_tmem_wait_ld();
+        fa_tmem_ld32(t_s + 32, vb);
+        pass2_chunk(va, pk, cmul, negm, sum_a, sum_b);
+        fa_tmem_st16(t_s, pk);
+        fa_tmem_wait_ld();
+        fa_tmem_ld32(t_s + 64, va);
+        pass2_chunk(vb, pk, cmul, negm, sum_a, sum_b);
+        fa_tmem_st16(t_s + 16, pk);
+        fa_tmem_wait_ld();
+        fa_tmem_ld32(t_s + 96, vb);
+        pass2_chunk(va, pk, cmul, negm, sum_a, sum_b);
+        fa_tmem_st16(t_s + 32, pk);
+        fa_tmem_wait_ld();
+        pass2_chunk(vb, pk, cmul, negm, sum_a, sum_b);
+        fa_tmem_st16(t_s + 48, pk);
+      }
+      float sum;
+      {
+        float s0, s1;
+        fa_f2_unpack(fa_add2(sum_a, sum_b), s0, s1);
+        sum = s0 + s1;
+      }
+      l += sum;
+      fa_tmem_wait_st();
+      fa_tc_fence_before();
+      fa_mbar_arrive(bar_addr(sb, BAR_P + i));
+      ++cnt;
+    }
+    // ---- epilogue: O / l and the logsumexp of this thread's row ---------------------------
+    if (ok && cnt > 0) ok = fa_mbar_wait_warp(bar_addr(sb, BAR_O + i), (cnt - 1) & 1u, abort_flag);
+    if (ok) {
+      fa_tc_fence_after();
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      char* og = (char*)p.o.ptr + ((long long)b * p.o.sb + (long long)h * p.o.sh + (long long)qi * p.o.ss) * 2;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        float o[32];
+        if (cnt > 0) {
+          fa_tmem_ld32(t_o + c * 32, o);
+          fa_tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[e] = 0.f;
+        }
+        if (qi < p.Sq) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 8) {
+            uint4 w;
+            w.x = fa_pack2<DT>(o[e] * inv, o[e + 1] * inv);
+            w.y = fa_pack2<DT>(o[e + 2] * inv, o[e + 3] * inv);
+            w.z = fa_pack2<DT>(o[e + 4] * inv, o[e + 5] * inv);
+            w.w = fa_pack2<DT>(o[e + 6] * inv, o[e + 7] * inv);
+            *(uint4*)(og + (c * 32 + e) * 2) = w;
+          }
+        }
+      }
+      if (p.lse != nullptr && qi < p.Sq)
+        p.lse[((long long)b * p.Hq + h) * p.Sq + qi] = l > 0.f ? (m_ref + fa_lg2(l)) * FA_LN2 : FA_NEG_INF;
+    }
+  }
+
+  // ---- teardown ----------------------------------------------------------------------------
+  fa_tc_fence_before();
+  __syncthreads();
+  if (warp == WARP_MMA) {
+    fa_tc_fence_after();
+    fa_tmem_dealloc(tmem, TMEM_COLS);
+  }
+  if (tid == 0 && *abort_flag != 0 && p.status != nullptr) atomicOr(p.status, FA_STATUS_WAIT_TIMEOUT);
+}

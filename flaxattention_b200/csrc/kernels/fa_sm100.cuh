@@ -1,0 +1,254 @@
+// Blackwell (sm_100a) primitives used by the tcgen05 attention kernels: mbarriers with
+// bounded waits, TMA tile loads, TMEM allocation / load / store, tcgen05.mma descriptors.
+// Self-contained (no CUDA headers), like fa_common.cuh.
+#pragma once
+#include "fa_common.cuh"
+
+// 128-byte opaque tensor map (same size and alignment as the driver's CUtensorMap)
+struct __align__(64) FaTensorMap {
+  unsigned long long v[16];
+};
+
+// status bits a kernel ORs into FaParams::status
+#define FA_STATUS_WAIT_TIMEOUT 1
+
+// ---- mbarrier --------------------------------------------------------------------------
+__device__ __forceinline__ void fa_mbar_init(fa_u32 bar, fa_u32 count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void fa_mbar_init_fence() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void fa_mbar_arrive(fa_u32 bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void fa_mbar_expect_tx(fa_u32 bar, fa_u32 bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool fa_mbar_try(fa_u32 bar, fa_u32 parity) {
+  fa_u32 ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+__device__ __forceinline__ fa_u64 fa_globaltimer() {
+  fa_u64 t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+// Bounded wait: gives up after ~2 s, or as soon as another thread of the CTA has given up
+// (*abort != 0).  Returns false on failure; the caller then leaves its loop and the kernel
+// tears down normally (no trap, the context stays usable, the host sees the status word).
+#define FA_WAIT_LIMIT_NS 2000000000ull
+__device__ __forceinline__ bool fa_mbar_wait(fa_u32 bar, fa_u32 parity, volatile int* abort_flag) {
+  if (fa_mbar_try(bar, parity)) return true;
+  const fa_u64 t0 = fa_globaltimer();
+  while (true) {
+    if (fa_mbar_try(bar, parity)) return true;
+    if (*abort_flag != 0) return false;
+    if (fa_globaltimer() - t0 > FA_WAIT_LIMIT_NS) {
+      *abort_flag = 1;
+      return false;
+    }
+  }
+}
+
+// warp-uniform variant: every lane waits, the warp agrees on the outcome (needed before
+// warp-collective tcgen05 instructions)
+__device__ __forceinline__ bool fa_mbar_wait_warp(fa_u32 bar, fa_u32 parity, volatile int* abort_flag) {
+  const bool ok = fa_mbar_wait(bar, parity, abort_flag);
+  return __all_sync(0xffffffffu, ok);
+}
+
+// ---- TMA -------------------------------------------------------------------------------
+// 4-d tile load (coordinates innermost first), completion counted in bytes on `bar`
+__device__ __forceinline__ void fa_tma_load_4d(fa_u32 dst, const FaTensorMap* map, fa_u32 bar, int c0, int c1, int c2,
+                                               int c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ void fa_tma_prefetch_desc(const FaTensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+// ---- TMEM ------------------------------------------------------------------------------
+// warp-collective; writes the base address of `ncols` (power of two >= 32) columns to smem
+__device__ __forceinline__ void fa_tmem_alloc(fa_u32 smem_dst, fa_u32 ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst), "r"(ncols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void fa_tmem_dealloc(fa_u32 taddr, fa_u32 ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void fa_tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fa_tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fa_tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void fa_tmem_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+// each lane reads 32 consecutive 32-bit columns of its own TMEM lane (warp w may only touch
+// lanes 32*(w%4) .. +31; taddr = base | lane_base << 16 | column)
+__device__ __forceinline__ void fa_tmem_ld32(fa_u32 taddr, float (&v)[32]) {
+  fa_u32 r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void fa_tmem_st32(fa_u32 taddr, const float (&v)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+        "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+        "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+        "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])),
+        "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])),
+        "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])),
+        "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])),
+        "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])),
+        "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+}
+// 16 packed words (32 sixteen-bit values) per lane
+__device__ __forceinline__ void fa_tmem_st16(fa_u32 taddr, const fa_u32 (&v)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+      : "memory");
+}
+
+// ---- tcgen05.mma -----------------------------------------------------------------------
+// Shared-memory matrix descriptor, 128-byte swizzle, 16-bit elements.  Both canonical forms
+// used here have 8-row groups 1024 bytes apart (SBO); LBO is the distance between
+// 64-element chunks of the MN dimension for MN-major operands (unused for K-major).
+__device__ __forceinline__ fa_u64 fa_smem_desc_sw128(fa_u32 saddr, fa_u32 lbo_bytes) {
+  fa_u64 d = 0;
+  d |= (fa_u64)((saddr & 0x3FFFFu) >> 4);
+  d |= (fa_u64)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (fa_u64)((1024u >> 4) & 0x3FFFu) << 32;
+  d |= 1ull << 46;  // descriptor version of sm_100
+  d |= 2ull << 61;  // SWIZZLE_128B
+  return d;
+}
+// instruction descriptor: fp32 accumulate, A and B of type DT (0 = f16, 1 = bf16)
+__device__ __forceinline__ constexpr fa_u32 fa_idesc(int dt, int M, int N, int a_mn_major, int b_mn_major) {
+  return (1u << 4) | ((fa_u32)dt << 7) | ((fa_u32)dt << 10) | ((fa_u32)a_mn_major << 15) | ((fa_u32)b_mn_major << 16) |
+         ((fa_u32)(N >> 3) << 17) | ((fa_u32)(M >> 4) << 24);
+}
+// D[tmem] (+)= A[smem] * B[smem]
+__device__ __forceinline__ void fa_mma_ss(fa_u32 d_tmem, fa_u64 a_desc, fa_u64 b_desc, fa_u32 idesc, fa_u32 accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// D[tmem] (+)= A[tmem] * B[smem]
+__device__ __forceinline__ void fa_mma_ts(fa_u32 d_tmem, fa_u32 a_tmem, fa_u64 b_desc, fa_u32 idesc, fa_u32 accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// arrive on `bar` once every tcgen05.mma issued so far by this thread has completed
+__device__ __forceinline__ void fa_mma_commit(fa_u32 bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// ---- packed fp32 pairs and other sm_100 ALU forms -----------------------------------------
+__device__ __forceinline__ fa_u64 fa_f2(float lo, float hi) {
+  fa_u64 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void fa_f2_unpack(fa_u64 v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ fa_u64 fa_mul2(fa_u64 a, fa_u64 b) {
+  fa_u64 r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ fa_u64 fa_add2(fa_u64 a, fa_u64 b) {
+  fa_u64 r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ fa_u64 fa_fma2(fa_u64 a, fa_u64 b, fa_u64 c) {
+  fa_u64 r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+// max of three; written as nested fmaxf so that the compiler may pick the three-input form
+__device__ __forceinline__ float fa_max3(float a, float b, float c) { return fmaxf(fmaxf(a, b), c); }
+// register re-allocation between warpgroups (all four warps of a warpgroup must execute it)
+template <int N>
+__device__ __forceinline__ void fa_setmaxnreg_inc() {
+  asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N));
+}
+template <int N>
+__device__ __forceinline__ void fa_setmaxnreg_dec() {
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N));
+}
+// 16 columns per lane
+__device__ __forceinline__ void fa_tmem_ld16(fa_u32 taddr, float (&v)[16]) {
+  fa_u32 r[16];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+__device__ __forceinline__ void fa_tmem_st16f(fa_u32 taddr, const float (&v)[16]) {
+  fa_u32 r[16];
+#pragma unroll
+  for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(v[i]);
+  fa_tmem_st16(taddr, r);
+}
+
+// exp2 of two 16-bit values at once (one SFU operation for the pair); DT selects f16 / bf16
+template <int DT>
+__device__ __forceinline__ fa_u32 fa_ex2_h2(fa_u32 x) {
+  fa_u32 r;
+  if (DT == FA_DT_F16) asm("ex2.approx.f16x2 %0, %1;" : "=r"(r) : "r"(x));
+  else asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(r) : "r"(x));
+  return r;
+}
+// widen a packed 16-bit pair to a packed fp32 pair
+template <int DT>
+__device__ __forceinline__ fa_u64 fa_h2_to_f2(fa_u32 x) {
+  if (DT == FA_DT_F16) {
+    fa_u16 lo, hi;
+    float a, b;
+    asm("mov.b32 {%0, %1}, %2;" : "=h"(lo), "=h"(hi) : "r"(x));
+    asm("cvt.f32.f16 %0, %1;" : "=f"(a) : "h"(lo));
+    asm("cvt.f32.f16 %0, %1;" : "=f"(b) : "h"(hi));
+    return fa_f2(a, b);
+  } else {
+    return fa_f2(__uint_as_float(x << 16), __uint_as_float(x & 0xffff0000u));
+  }
+}

@@ -110,6 +110,77 @@ def _is_const(e: Expr, v=None) -> bool:
 # --------------------------------------------------------------------------------------
 # typed constructors
 # --------------------------------------------------------------------------------------
+def _is_bit(e: Expr) -> bool:
+    """True when the int32 expression can only be 0 or 1."""
+    if e.dtype != I32:
+        return False
+    if e.op == "const":
+        return e.value in (0, 1)
+    if e.op == "and":
+        return _is_const(e.args[0], 1) or _is_const(e.args[1], 1) or (_is_bit(e.args[0]) and _is_bit(e.args[1]))
+    if e.op in ("or", "xor"):
+        return _is_bit(e.args[0]) and _is_bit(e.args[1])
+    if e.op == "cast_i32":
+        return e.args[0].dtype == B1
+    return False
+
+
+def _parity(e: Expr) -> Expr:
+    """e & 1 with the mask pushed through +, -, negation: the low bit of a sum is the xor of
+    the low bits.  This separates the q and kv contributions of expressions like
+    (kv - q) % 2, so that a kernel can evaluate the kv part per column at compile time."""
+    if e.op == "const":
+        return _B.const(e.value & 1, I32)
+    if e.op in ("add", "sub") and e.dtype == I32:
+        a, b = _parity(e.args[0]), _parity(e.args[1])
+        if _is_const(a, 0):
+            return b
+        if _is_const(b, 0):
+            return a
+        if a.op == "const" and b.op == "const":
+            return _B.const(a.value ^ b.value, I32)
+        return _B._mk("xor", I32, (a, b))
+    if e.op == "neg" and e.dtype == I32:
+        return _parity(e.args[0])
+    if _is_bit(e):
+        return e
+    return _B._mk("and", I32, (e, _B.const(1, I32)))
+
+
+_UNARY_OPS = ("neg", "not", "abs", "isneginf", "isinf", "isnan", "sign") + _UNARY_F
+_BINARY_OPS = ("add", "sub", "mul", "div", "floordiv", "rem", "pow", "min", "max", "and", "or", "xor", "shl", "shr",
+               "lt", "le", "gt", "ge", "eq", "ne")
+
+
+def _rebuild(e: Expr, args) -> Expr:
+    if e.op in _UNARY_OPS:
+        return unary(e.op, args[0])
+    if e.op in _BINARY_OPS:
+        return binary(e.op, args[0], args[1])
+    if e.op == "select":
+        return select(args[0], args[1], args[2])
+    if e.op.startswith("cast_"):
+        return cast(args[0], e.dtype)
+    raise NotImplementedError(e.op)
+
+
+def _assume(e: Expr, cond: Expr, value: bool, memo=None) -> Expr:
+    """e with the boolean node `cond` replaced by a constant, re-simplified."""
+    if memo is None:
+        memo = {}
+    if e is cond:
+        return _B.const(value, B1)
+    if not e.args:
+        return e
+    got = memo.get(id(e))
+    if got is not None:
+        return got
+    new_args = tuple(_assume(a, cond, value, memo) for a in e.args)
+    r = e if all(x is y for x, y in zip(new_args, e.args)) else _rebuild(e, new_args)
+    memo[id(e)] = r
+    return r
+
+
 def cast(e: Expr, dtype: str) -> Expr:
     if e.dtype == dtype:
         return e
@@ -138,6 +209,11 @@ def binary(op: str, a: Expr, b: Expr) -> Expr:
         a, b, t = _promote(a, b)
         if t == F32:
             raise TypeError(f"bitwise '{op}' is not defined for float operands")
+        if t == I32 and op == "and":
+            if _is_const(b, 1) and a.op in ("add", "sub", "neg", "const"):
+                return _parity(a)
+            if _is_const(a, 1) and b.op in ("add", "sub", "neg", "const"):
+                return _parity(b)
         if t == B1:
             if op == "and":
                 if _is_const(a):
@@ -154,6 +230,17 @@ def binary(op: str, a: Expr, b: Expr) -> Expr:
         a, b, t = _promote(a, b)
         if t == B1:
             a, b = cast(a, I32), cast(b, I32)
+        if op in ("eq", "ne") and t == I32:
+            if a.op == "const" and b.op != "const":
+                a, b = b, a
+            if b.op == "const" and _is_bit(a) and a.op != "const":
+                # a is 0 or 1: every test against a constant is `a == 0`, its negation, or constant
+                is_zero = _B._mk("eq", B1, (a, _B.const(0, I32)))
+                if b.value not in (0, 1):
+                    return _B.const(op == "ne", B1)
+                if (op == "eq") == (b.value == 0):
+                    return is_zero
+                return unary("not", is_zero)
         return _B._mk(op, B1, (a, b))
     if op in ("shl", "shr"):
         a, b = cast(a, I32), cast(b, I32)
@@ -184,6 +271,14 @@ def binary(op: str, a: Expr, b: Expr) -> Expr:
     elif op == "div":
         if _is_const(b, 1):
             return a
+    if t == I32 and op in ("rem", "floordiv") and b.op == "const" and b.value > 0 and (b.value & (b.value - 1)) == 0:
+        # Python semantics for a positive power-of-two divisor are exactly the two's-complement
+        # mask / arithmetic shift: x % 2^k == x & (2^k - 1), x // 2^k == x >> k
+        if b.value == 1:
+            return _B.const(0, I32) if op == "rem" else a
+        if op == "rem":
+            return binary("and", a, _B.const(b.value - 1, I32))
+        return _B._mk("shr", I32, (a, _B.const(b.value.bit_length() - 1, I32)))
     if a.op == "const" and b.op == "const":
         folded = _fold_binary(op, a.value, b.value, t)
         if folded is not None:
@@ -240,6 +335,8 @@ def unary(op: str, a: Expr) -> Expr:
             raise TypeError("'~' is not defined for float operands")
         if a.op == "const" and a.dtype == B1:
             return _B.const(not a.value, B1)
+        if a.op == "not" and a.dtype == B1:
+            return a.args[0]
         return _B._mk("not", a.dtype, (a,))
     if op == "abs":
         if a.dtype == B1:
@@ -264,6 +361,12 @@ def select(c: Expr, a: Expr, b: Expr) -> Expr:
     a, b, t = _promote(a, b)
     if c.op == "const":
         return a if c.value else b
+    if c.op == "not":
+        c, a, b = c.args[0], b, a
+    # inside the arms the condition is known
+    a = _assume(a, c, True)
+    b = _assume(b, c, False)
+    a, b, t = _promote(a, b)
     if a is b:
         return a
     return _B._mk("select", t, (c, a, b))
@@ -764,6 +867,66 @@ def derivative(mod: TracedMod) -> TracedMod:
 
 
 # --------------------------------------------------------------------------------------
+# affine decomposition:  score_mod(score, ...) == A(b,h,q,kv) * score + B(b,h,q,kv)
+# --------------------------------------------------------------------------------------
+def affine_parts(mod: TracedMod):
+    """Returns (A, B) as index-only TracedMods when the score_mod is affine in the score
+    (bias-type and scaling-type mods: ALiBi, relative biases, checkerboard ...), else None.
+    Kernels use it to fold the softmax scale and the log2(e) factor into one FMA per score;
+    A is also the derivative with respect to the score."""
+    if mod.kind != "score":
+        return None
+    dep: Dict[int, bool] = {}
+    memo: Dict[int, Optional[Tuple[Expr, Expr]]] = {}
+    zero, one = _B.const(0.0, F32), _B.const(1.0, F32)
+    fail = object()
+
+    def go(e: Expr):
+        if not _depends_on_score(e, dep):
+            return (zero, cast(e, F32)) if e.dtype != B1 else None
+        got = memo.get(id(e), fail)
+        if got is not fail:
+            return got
+        op, a = e.op, e.args
+        r = None
+        if op == "score":
+            r = (one, zero)
+        elif op in ("add", "sub"):
+            x, y = go(a[0]), go(a[1])
+            if x and y:
+                r = (binary(op, x[0], y[0]), binary(op, x[1], y[1]))
+        elif op == "neg":
+            x = go(a[0])
+            if x:
+                r = (unary("neg", x[0]), unary("neg", x[1]))
+        elif op == "mul":
+            for u, v in ((a[0], a[1]), (a[1], a[0])):
+                if not _depends_on_score(v, dep):
+                    x = go(u)
+                    if x:
+                        k = cast(v, F32)
+                        r = (binary("mul", x[0], k), binary("mul", x[1], k))
+                    break
+        elif op == "div":
+            if not _depends_on_score(a[1], dep):
+                x = go(a[0])
+                if x:
+                    r = (binary("div", x[0], a[1]), binary("div", x[1], a[1]))
+        elif op == "select":
+            if not _depends_on_score(a[0], dep):
+                x, y = go(a[1]), go(a[2])
+                if x and y:
+                    r = (select(a[0], x[0], y[0]), select(a[0], x[1], y[1]))
+        memo[id(e)] = r
+        return r
+
+    res = go(mod.root)
+    if res is None:
+        return None
+    return TracedMod("score", cast(res[0], F32)), TracedMod("score", cast(res[1], F32))
+
+
+# --------------------------------------------------------------------------------------
 # back ends
 # --------------------------------------------------------------------------------------
 def _topo(root: Expr) -> List[Expr]:
@@ -1022,10 +1185,17 @@ class ModSet:
         parts = [_PRELUDE]
         parts.append(f"#define FA_HAS_SCORE_MOD {1 if self.score is not None else 0}\n")
         parts.append(f"#define FA_HAS_MASK_MOD {1 if self.mask is not None else 0}\n")
+        self.affine = None
         if self.score is not None:
             self.grad = derivative(self.score)
             parts.append(to_cuda(self.score, "fa_score_mod"))
             parts.append(to_cuda(self.grad, "fa_score_mod_grad"))
+            self.affine = affine_parts(self.score)
+            if self.affine is not None:
+                # score_mod(s) == fa_score_mul(...) * s + fa_score_add(...); both ignore `score`
+                parts.append("#define FA_SCORE_AFFINE 1\n")
+                parts.append(to_cuda(self.affine[0], "fa_score_mul"))
+                parts.append(to_cuda(self.affine[1], "fa_score_add"))
         else:
             self.grad = None
             parts.append(

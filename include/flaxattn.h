@@ -49,6 +49,8 @@ extern "C" {
 #define FA_FLAG_BWD_SKIP_DELTA 2
 #define FA_FLAG_BWD_SKIP_DKDV 4
 #define FA_FLAG_BWD_SKIP_DQ 8
+/* Use the general (mma.sync) kernels even where a tcgen05 kernel covers the shape. */
+#define FA_FLAG_GENERAL_KERNELS 16
 
 enum fa_dtype { FA_F16 = 0, FA_BF16 = 1, FA_F32 = 2 };
 

@@ -106,6 +106,43 @@ def test_shape_sweep(case):
     _check(out, lse, ref_out, ref_lse, TOL[dt])
 
 
+TC_SHAPES = [
+    # shapes the tcgen05 forward covers: B, Hq, Hkv, Sq, Skv, D, dtype, score, mask
+    (1, 2, 2, 256, 256, 64, "f16", None, None),
+    (2, 2, 2, 512, 512, 64, "bf16", "checker", None),
+    (1, 4, 4, 1024, 1024, 64, "f16", "alibi", "causal"),
+    (1, 2, 2, 2048, 2048, 128, "bf16", None, "sink"),
+    (1, 2, 2, 300, 333, 64, "f16", "alibi", "causal"),
+    (1, 4, 2, 512, 768, 64, "f16", None, "window"),
+    (1, 2, 2, 128, 640, 128, "f16", "checker", None),
+    (1, 2, 2, 384, 2048, 64, "bf16", "alibi", "offset"),
+]
+
+
+@pytest.mark.parametrize("case", TC_SHAPES, ids=lambda c: "-".join(map(str, c)))
+def test_tcgen05_and_general_kernels_agree_with_the_oracle(case):
+    """Same problem through the tcgen05 kernel (default for these shapes) and through the
+    general kernel: both within tolerance of the oracle, and close to each other.  The status
+    word of the tcgen05 kernel (bounded mbarrier waits) must stay 0."""
+    import flaxattention_b200 as fa
+
+    B, Hq, Hkv, Sq, Skv, D, dt, score, mask = case
+    s, m = _mods(score, mask, Hq, Sq, Skv)
+    q, k, v = qkv(B, Hq, Hkv, Sq, Skv, D, dtype=DTYPES[dt])
+    ref_out, ref_lse = flax_attention_oracle(q, k, v, s, m)
+    bm = fa.create_block_mask(m, B, Hq, Sq, Skv) if m is not None else None
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    outs = []
+    for opts in ({"path": "fwd", "status": status}, {"path": "fwd", "kernels": "general"}):
+        out, lse = fa.flax_attention(q.cuda(), k.cuda(), v.cuda(), score_mod=s, block_mask=bm, return_lse=True,
+                                     enable_gqa=Hq != Hkv, kernel_options=opts)
+        torch.cuda.synchronize()
+        _check(out.cpu(), lse.cpu(), ref_out, ref_lse, TOL[dt])
+        outs.append(out.cpu())
+    assert int(status.item()) == 0
+    assert max_abs(outs[0], outs[1]) <= (8e-3 if dt == "f16" else 3.2e-2)
+
+
 def test_mask_without_tables_equals_mask_with_tables():
     from flaxattention_b200.masks import generate_attention_sink
 

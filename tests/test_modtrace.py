@@ -134,11 +134,12 @@ def test_lowered_mods_compile_for_sm100a(tmp_path):
         before = L.fa_compile_count()
         m.prepare(_cabi.KIND_BLOCKMASK, 0, 64, 64)
         m.prepare(_cabi.KIND_FWD, _cabi.FA_BF16, 64, 64)
-        assert L.fa_compile_count() == before + 2
+        after = L.fa_compile_count()
+        assert after >= before + 2
         # a second module with the same source hits the on-disk cache
         m2 = _cabi.Module(ms.source)
         m2.prepare(_cabi.KIND_FWD, _cabi.FA_BF16, 64, 64)
-        assert L.fa_compile_count() == before + 2
+        assert L.fa_compile_count() == after
         bad = _cabi.Module("#define FA_HAS_SCORE_MOD 1\n#define FA_HAS_MASK_MOD 0\nthis is not CUDA\n")
         with pytest.raises(_cabi.FlaxAttnError) as ei:
             bad.prepare(_cabi.KIND_FWD, _cabi.FA_F16, 64, 64)
