@@ -108,7 +108,7 @@ std::string cache_dir() {
 }
 
 const char* const kTemplateFiles[] = {"fa_params.h", "fa_common.cuh", "fa_fwd.cuh", "fa_bwd.cuh",
-                                      "fa_decode.cuh", "fa_blockmask.cuh", "fa_sm100.cuh", "fa_fwd_tc.cuh"};
+                                      "fa_decode.cuh", "fa_blockmask.cuh", "fa_sm100.cuh", "fa_fwd_tc.cuh", "fa_bwd_tc.cuh"};
 std::string g_templates_hash;
 int templates_hash(std::string& out) {
   if (g_templates_hash.empty()) {
@@ -488,6 +488,33 @@ __global__ void fa_delta_kernel(FaTensor o, FaTensor dout, float* __restrict__ d
   if (row < n_rows && sub == 0) delta[row] = acc;
 }
 
+// dq = scale * dq_acc for the tcgen05 backward: the fp32 accumulation buffer is
+// [B, Hq, sq_pad, 64] with the sixteen 16-byte chunks of a row stored at position k ^ (q & 15).
+template <int DT>
+__global__ void fa_dq_convert_kernel(const float* __restrict__ acc, FaTensor dq, int Hq, int Sq, int sq_pad, float scale,
+                                     long long n_chunks) {
+  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // one 8-element output chunk each
+  if (i >= n_chunks) return;
+  const int k8 = (int)(i & 7);
+  const long long row = i >> 3;
+  const long long bh = row / Sq;
+  const int q = (int)(row - bh * Sq);
+  const int b = (int)(bh / Hq), h = (int)(bh - (long long)b * Hq);
+  const float* src = acc + (bh * sq_pad + q) * 64;
+  const float4 lo = *(const float4*)(src + (((2 * k8) ^ (q & 15)) * 4));
+  const float4 hi = *(const float4*)(src + (((2 * k8 + 1) ^ (q & 15)) * 4));
+  char* dst = (char*)dq.ptr + ((long long)b * dq.sb + (long long)h * dq.sh + (long long)q * dq.ss) * 2 + k8 * 16;
+  if (DT == FA_F16) {
+    __half2 o[4] = {__floats2half2_rn(lo.x * scale, lo.y * scale), __floats2half2_rn(lo.z * scale, lo.w * scale),
+                    __floats2half2_rn(hi.x * scale, hi.y * scale), __floats2half2_rn(hi.z * scale, hi.w * scale)};
+    *(uint4*)dst = *reinterpret_cast<uint4*>(o);
+  } else {
+    __nv_bfloat162 o[4] = {__floats2bfloat162_rn(lo.x * scale, lo.y * scale), __floats2bfloat162_rn(lo.z * scale, lo.w * scale),
+                           __floats2bfloat162_rn(hi.x * scale, hi.y * scale), __floats2bfloat162_rn(hi.z * scale, hi.w * scale)};
+    *(uint4*)dst = *reinterpret_cast<uint4*>(o);
+  }
+}
+
 // Combines the per-split partial results of the decode kernel: one warp per output row.
 template <int DT>
 __global__ void fa_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
@@ -591,6 +618,20 @@ int get_decode_kernel(fa_module* m, int dtype, int D, int Dv, int flags, const D
                           {"FA_STAGES", c.stages}, {"FA_ROUND_SCORES", round_flag(dtype, flags)}}),
                     "fa_decode_kernel", c.smem, k);
 }
+// tuning aid: extra "NAME=VALUE,NAME=VALUE" defines for the tcgen05 kernels from $FLAXATTN_TC_DEFS
+std::string extra_defines() {
+  std::string d;
+  if (const char* e = getenv("FLAXATTN_TC_DEFS")) {
+    std::string t = e, item;
+    std::stringstream ss(t);
+    while (std::getline(ss, item, ',')) {
+      const size_t eq = item.find('=');
+      if (eq != std::string::npos) d += "#define " + item.substr(0, eq) + " " + item.substr(eq + 1) + "\n";
+    }
+  }
+  return d;
+}
+
 // ---- tcgen05 forward: TMA tensor maps and dispatch -----------------------------------------
 struct alignas(64) FaTensorMapHost {
   unsigned long long v[16];
@@ -654,14 +695,7 @@ int get_fwd_tc_kernel(fa_module* m, int dtype, int D, int flags, Kernel** k) {
   const int smem = 2 * atoms * 16384 + 2 * nstage * atoms * 16384 + (1 + 4 * nstage + 6) * 8 + 16 + 256 * 2 + 256 * 2 +
                    2 * 256 + 1024;
   std::string d = defs({{"FA_DTYPE", dtype}, {"FA_D", D}, {"FA_ROUND_SCORES", round_flag(dtype, flags)}});
-  if (const char* e = getenv("FLAXATTN_TC_DEFS")) {  // tuning aid: extra "NAME=VALUE,NAME=VALUE" defines
-    std::string t = e, item;
-    std::stringstream ss(t);
-    while (std::getline(ss, item, ',')) {
-      const size_t eq = item.find('=');
-      if (eq != std::string::npos) d += "#define " + item.substr(0, eq) + " " + item.substr(eq + 1) + "\n";
-    }
-  }
+  d += extra_defines();
   return get_kernel(m, "fa_fwd_tc.cuh", d, "fa_fwd_tc_kernel", smem, k);
 }
 
@@ -674,6 +708,40 @@ int launch_fwd_tc(fa_module* m, const fa_attn_params* p, const FaParams& kp, voi
   if (int rc = make_map(&tp.tk, p->dtype, p->k, p->D, p->Skv, p->Hkv, p->B)) return rc;
   if (int rc = make_map(&tp.tv, p->dtype, p->v, p->Dv, p->Skv, p->Hkv, p->B)) return rc;
   return launch(k, dim3((p->Sq + 255) / 256, p->Hq, p->B), dim3(384), &tp, stream);
+}
+
+// ---- tcgen05 backward ----------------------------------------------------------------------
+struct FaBwdTcParamsHost {
+  FaParams p;
+  FaTensorMapHost tq, tk, tv, tdo;
+  float* dq_acc;
+};
+
+bool tc_bwd_eligible(const fa_attn_params* p) {
+  if (p->flags & FA_FLAG_GENERAL_KERNELS) return false;
+  if (p->dtype == FA_F32) return false;
+  if (p->D != 64 || p->Dv != 64) return false;
+  if (p->Sq < 128 || p->Skv < 128) return false;
+  const int n_qtiles = (p->Sq + 127) / 128;
+  if (n_qtiles > 256 || (long long)n_qtiles * (p->Hq / p->Hkv) > 512) return false;
+  const fa_block_tables& t = p->tables;
+  if (t.kv_num_blocks) {
+    if (!(t.num_q_blocks == 1 || t.q_block_size % 128 == 0)) return false;
+    if (!(t.num_kv_blocks == 1 || t.kv_block_size % 128 == 0)) return false;
+  }
+  return true;
+}
+size_t delta_bytes(const fa_attn_params* p) { return ((size_t)p->B * p->Hq * p->Sq * sizeof(float) + 255) / 256 * 256; }
+size_t dq_acc_bytes(const fa_attn_params* p) {
+  const size_t sq_pad = (size_t)((p->Sq + 127) / 128) * 128;
+  return (size_t)p->B * p->Hq * sq_pad * 64 * sizeof(float);
+}
+
+int get_bwd_tc_kernel(fa_module* m, int dtype, int flags, Kernel** k) {
+  const int nstage = 3;
+  const int smem = (2 + 2 * nstage) * 16384 + 2 * 16384 + 128 * 64 * 4 + nstage * 2 * 128 * 4 + (1 + 2 * nstage + 7) * 8 + 16 + 512 * 4 + 256 + 1024;
+  std::string d = defs({{"FA_DTYPE", dtype}, {"FA_ROUND_SCORES", round_flag(dtype, flags)}}) + extra_defines();
+  return get_kernel(m, "fa_bwd_tc.cuh", d, "fa_bwd_tc_kernel", smem, k);
 }
 
 int get_blockmask_kernel(fa_module* m, Kernel** k) {
@@ -699,6 +767,8 @@ int fa_module_prepare(fa_module* m, int kind, int dtype, int D, int Dv, int Sq_h
     case FA_KIND_BWD: {
       BwdCfg c;
       if (int rc = pick_bwd(dtype, D, Dv, nullptr, c)) return rc;
+      if (dtype != FA_F32 && D == 64 && Dv == 64 && Sq_hint >= 128)
+        if (int rc = get_bwd_tc_kernel(m, dtype, 0, &k)) return rc;
       if (int rc = get_bwd_kernel(m, dtype, D, Dv, 0, c, true, &k)) return rc;
       return get_bwd_kernel(m, dtype, D, Dv, 0, c, false, &k);
     }
@@ -729,7 +799,9 @@ int fa_fwd(fa_module* m, const fa_attn_params* p, void* stream) {
 
 size_t fa_bwd_workspace_bytes(const fa_attn_params* p) {
   if (!p || p->B <= 0 || p->Hq <= 0 || p->Sq <= 0) return 0;
-  return ((size_t)p->B * p->Hq * p->Sq * sizeof(float) + 255) / 256 * 256;
+  size_t n = delta_bytes(p);
+  if (p->Hkv > 0 && p->Hq % p->Hkv == 0 && tc_bwd_eligible(p)) n += dq_acc_bytes(p);
+  return n;
 }
 
 int fa_bwd(fa_module* m, const fa_attn_params* p, const fa_tensor* dout, const fa_tensor* dq, const fa_tensor* dk,
@@ -752,11 +824,16 @@ int fa_bwd(fa_module* m, const fa_attn_params* p, const fa_tensor* dout, const f
   fill_params(p, kp);
   kp.dout = cvt(*dout); kp.dq = cvt(*dq); kp.dk = cvt(*dk); kp.dv = cvt(*dv);
   kp.delta = (float*)workspace;
-  BwdCfg c;
-  if (int rc = pick_bwd(p->dtype, p->D, p->Dv, &kp.t, c)) return rc;
-  Kernel *kdq = nullptr, *kdkdv = nullptr;
-  if (int rc = get_bwd_kernel(m, p->dtype, p->D, p->Dv, p->flags, c, true, &kdq)) return rc;
-  if (int rc = get_bwd_kernel(m, p->dtype, p->D, p->Dv, p->flags, c, false, &kdkdv)) return rc;
+  const bool use_tc = tc_bwd_eligible(p);
+  BwdCfg c{};
+  Kernel *kdq = nullptr, *kdkdv = nullptr, *ktc = nullptr;
+  if (use_tc) {
+    if (int rc = get_bwd_tc_kernel(m, p->dtype, p->flags, &ktc)) return rc;
+  } else {
+    if (int rc = pick_bwd(p->dtype, p->D, p->Dv, &kp.t, c)) return rc;
+    if (int rc = get_bwd_kernel(m, p->dtype, p->D, p->Dv, p->flags, c, true, &kdq)) return rc;
+    if (int rc = get_bwd_kernel(m, p->dtype, p->D, p->Dv, p->flags, c, false, &kdkdv)) return rc;
+  }
   if (!(p->flags & FA_FLAG_BWD_SKIP_DELTA)) {
     cudaStream_t st = (cudaStream_t)stream;
     const long long n_rows = (long long)p->B * p->Hq * p->Sq;
@@ -778,6 +855,33 @@ int fa_bwd(fa_module* m, const fa_attn_params* p, const fa_tensor* dout, const f
 #undef FA_DELTA_DT
 #undef FA_DELTA
     FA_CUDA_CHECK(cudaGetLastError());
+  }
+  if (use_tc) {
+    // single-pass kernel: dK, dV directly, dQ through the fp32 accumulation buffer
+    cudaStream_t st = (cudaStream_t)stream;
+    float* dq_acc = (float*)((char*)workspace + delta_bytes(p));
+    if (!(p->flags & FA_FLAG_BWD_SKIP_DKDV)) {
+      FA_CUDA_CHECK(cudaMemsetAsync(dq_acc, 0, dq_acc_bytes(p), st));
+      FaBwdTcParamsHost tp;
+      tp.p = kp;
+      tp.dq_acc = dq_acc;
+      if (int rc = make_map(&tp.tq, p->dtype, p->q, p->D, p->Sq, p->Hq, p->B)) return rc;
+      if (int rc = make_map(&tp.tk, p->dtype, p->k, p->D, p->Skv, p->Hkv, p->B)) return rc;
+      if (int rc = make_map(&tp.tv, p->dtype, p->v, p->Dv, p->Skv, p->Hkv, p->B)) return rc;
+      if (int rc = make_map(&tp.tdo, p->dtype, *dout, p->Dv, p->Sq, p->Hq, p->B)) return rc;
+      if (int rc = launch(ktc, dim3((p->Skv + 127) / 128, p->Hkv, p->B), dim3(512), &tp, stream)) return rc;
+    }
+    if (!(p->flags & FA_FLAG_BWD_SKIP_DQ)) {
+      const int sq_pad = (p->Sq + 127) / 128 * 128;
+      const long long n_chunks = (long long)p->B * p->Hq * p->Sq * 8;
+      const unsigned blocks = (unsigned)((n_chunks + 255) / 256);
+      if (p->dtype == FA_F16)
+        fa_dq_convert_kernel<FA_F16><<<blocks, 256, 0, st>>>(dq_acc, kp.dq, p->Hq, p->Sq, sq_pad, p->scale, n_chunks);
+      else
+        fa_dq_convert_kernel<FA_BF16><<<blocks, 256, 0, st>>>(dq_acc, kp.dq, p->Hq, p->Sq, sq_pad, p->scale, n_chunks);
+      FA_CUDA_CHECK(cudaGetLastError());
+    }
+    return FA_OK;
   }
   if (!(p->flags & FA_FLAG_BWD_SKIP_DKDV))
     if (int rc = launch(kdkdv, dim3((p->Skv + c.tile - 1) / c.tile, p->Hkv, p->B), dim3(c.warps * 32), &kp, stream))

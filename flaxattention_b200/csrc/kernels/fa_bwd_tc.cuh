@@ -1,0 +1,531 @@
+// Flash-attention backward for sm_100a on the 5th-generation tensor cores (fp16 / bf16,
+// D = Dv = 64).  One kernel computes dK, dV and dQ in a single pass over the (kv tile, q tile)
+// pairs the BlockMask lists: five tcgen05.mma products per pair and one exponential per
+// score, where the two-scan reference kernel (flaxattention/kernel/attention.py:423-553) and
+// fa_bwd.cuh need seven products and two exponentials.
+//
+// One CTA owns a 128-row kv tile of one (batch, kv head) and walks the q tiles of the query
+// heads that share it.  Everything is kept transposed so that the accumulators dK and dV
+// have kv rows (TMEM lanes) and P^T can be fed to the tensor core straight from TMEM:
+//   1. S^T  = K Q^T                      (TMEM, 128 kv x 128 q, fp32)
+//   2. dP^T = V dO^T                     (TMEM)
+//      p = 2^(x - lse), ds = p (dp - delta) score_mod'      thread (kv row, 64 q columns)
+//      P^T -> TMEM (16 bit),  dS^T -> shared memory (16 bit, [kv][q], 128-byte swizzle)
+//   3. dV += P^T dO                      (A from TMEM)
+//   4. dK += dS^T Q                      (A = dS^T from smem, K-major)
+//   5. dQ  = dS K                        (A = the same dS^T tile read MN-major, B = K)
+// dQ of a pair leaves TMEM through a staging tile and one bulk reduce-add into an fp32
+// accumulation buffer (summation order over kv tiles is not fixed; a small kernel scales and
+// converts it afterwards).  dK and dV are written once at the end.
+//
+// Warp roles (16 warps): 0-3 and 4-7 compute (q columns 0-63 / 64-127 of the pair tile),
+// 8-11 dQ drain, 12 TMA producer + lse/delta staging, 13 MMA issuer + TMEM owner.
+// S^T/dP^T of pair n+1 are issued as soon as the compute warps hold pair n in registers, so
+// the tensor core runs ahead of the element-wise work.
+//
+// TMEM (512 columns): S^T 0-127, dP^T 128-255, P^T 256-319, dV 320-383, dK 384-447, dQ 448-511.
+// Every mbarrier wait is bounded (see fa_sm100.cuh).
+//
+// Compile-time parameters (macros): FA_DTYPE (0 fp16, 1 bf16); D = Dv = 64.
+#pragma once
+#include "fa_sm100.cuh"
+
+struct FaBwdTcParams {
+  FaParams p;
+  FaTensorMap tq, tk, tv, tdo;  // 4-d maps (D, S, H, B), box 64 x 128 x 1 x 1, 128-byte swizzle
+  float* dq_acc;                // [B, Hq, ceil(Sq/128)*128, 64] fp32, 16-byte chunks of a row permuted
+};
+
+// Optional phase timing (tuning aid): with FA_TC_TRACE the status buffer must hold at least
+// 64 ints; slot k accumulates the SM cycles CTA (0,0,0) spent in phase k.
+#ifndef FA_TC_TRACE
+#define FA_TC_TRACE 0
+#endif
+#if FA_TC_TRACE
+#define FA_TRACE_DECL long long trace_t0 = clock64();
+#define FA_TRACE(slot)                                                                        \
+  do {                                                                                        \
+    const long long t1_ = clock64();                                                          \
+    if (trace_on) atomicAdd(p.status + (slot), (int)(t1_ - trace_t0));                        \
+    trace_t0 = t1_;                                                                           \
+  } while (0)
+#else
+#define FA_TRACE_DECL
+#define FA_TRACE(slot)
+#endif
+
+namespace fa_btc {
+
+constexpr int DT = FA_DTYPE;
+constexpr int D = 64;
+constexpr int BT = 128;                  // tile edge (kv rows and q columns)
+constexpr int ATOM_BYTES = 128 * 128;    // 128 rows x 128 bytes
+constexpr int NSTAGE = 3;
+constexpr int MAXP = 512;                // (head, q tile) pairs per CTA
+constexpr int NT = 512;
+constexpr int WARP_PRODUCER = 12, WARP_MMA = 13;
+constexpr int REGS_COMPUTE = 200, REGS_OTHER = 56;
+
+// shared memory map (from a 1024-byte aligned base)
+constexpr int OFF_K = 0;
+constexpr int OFF_V = OFF_K + ATOM_BYTES;
+constexpr int OFF_Q = OFF_V + ATOM_BYTES;                   // NSTAGE tiles
+constexpr int OFF_DO = OFF_Q + NSTAGE * ATOM_BYTES;         // NSTAGE tiles
+constexpr int OFF_DS = OFF_DO + NSTAGE * ATOM_BYTES;        // dS^T: two atoms (q 0-63, q 64-127)
+constexpr int OFF_DQ = OFF_DS + 2 * ATOM_BYTES;             // fp32 staging 128 x 64
+constexpr int OFF_ROW = OFF_DQ + 128 * 64 * 4;              // NSTAGE x (nlse2[128], ndelta[128]) floats
+constexpr int OFF_BAR = OFF_ROW + NSTAGE * 2 * 128 * 4;
+constexpr int NBARS = 1 + 2 * NSTAGE + 7;
+constexpr int OFF_MISC = OFF_BAR + NBARS * 8;               // tmem base, abort, npairs, pad
+constexpr int OFF_PAIR = OFF_MISC + 16;                     // int pair[MAXP]: tile | mode << 16 | g << 20
+constexpr int OFF_CLS = OFF_PAIR + MAXP * 4;                // uchar cls[256]
+constexpr int SMEM_BYTES = OFF_CLS + 256 + 1024;
+constexpr int TMEM_COLS = 512;
+constexpr int COL_S = 0, COL_DP = 128, COL_P = 256, COL_DV = 320, COL_DK = 384, COL_DQ = 448;
+
+constexpr int BAR_KV = 0;
+constexpr int BAR_QFULL = 1, BAR_QEMPTY = 1 + NSTAGE;
+constexpr int BAR_SFULL = 1 + 2 * NSTAGE;   // S^T and dP^T of a pair are in TMEM
+constexpr int BAR_SFREE = BAR_SFULL + 1;    // compute warps hold them in registers (256 arrivals)
+constexpr int BAR_PREADY = BAR_SFULL + 2;   // P^T in TMEM and dS^T in smem (256 arrivals)
+constexpr int BAR_PFREE = BAR_SFULL + 3;    // products 3-5 of the pair are complete
+constexpr int BAR_DQFULL = BAR_SFULL + 4;   // dQ of the pair is in TMEM
+constexpr int BAR_DQFREE = BAR_SFULL + 5;   // drain warps hold it in registers (128 arrivals)
+constexpr int BAR_FINAL = BAR_SFULL + 6;
+
+__device__ __forceinline__ fa_u32 bar_addr(fa_u32 sb, int i) { return sb + OFF_BAR + i * 8; }
+
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
+}
+__device__ __forceinline__ void bulk_reduce_add_f32(float* gdst, fa_u32 ssrc, fa_u32 bytes) {
+  asm volatile("cp.reduce.async.bulk.global.shared::cta.bulk_group.add.f32 [%0], [%1], %2;" ::"l"(gdst), "r"(ssrc), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+__device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+
+// Element-wise work of one thread on a 32-column chunk: scores s and dp (fp32, raw) for kv row
+// `kv` and q columns q0 .. q0+31 -> packed P^T and dS^T (16 bit).  C0 (chunk offset inside the
+// 128-column tile) is a template parameter and q0 a multiple of 128 plus C0, so the low bits of
+// the q index are compile-time constants inside the mods.
+template <int C0>
+__device__ __forceinline__ void chunk(const float (&s)[32], const float (&dp)[32], const float* nlse2, const float* ndelta,
+                                      fa_u32 (&pp)[16], fa_u32 (&ds)[16], int mode, int m0, int kv, int gb, int gh,
+                                      float scale, float sc2) {
+#pragma unroll
+  for (int e = 0; e < 32; e += 4) {
+    const float4 nl = *(const float4*)(nlse2 + C0 + e);
+    const float4 nd = *(const float4*)(ndelta + C0 + e);
+    float pv[4], dv[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int qi = m0 | (C0 + e + u);
+      const float nlu = u == 0 ? nl.x : (u == 1 ? nl.y : (u == 2 ? nl.z : nl.w));
+      const float ndu = u == 0 ? nd.x : (u == 1 ? nd.y : (u == 2 ? nd.z : nd.w));
+      float x = s[e + u];
+      float g = 1.f;
+#if FA_ROUND_SCORES
+      {
+        float dummy = 0.f;
+        fa_round2<DT>(x, dummy);
+      }
+#endif
+#if FA_HAS_SCORE_MOD && defined(FA_SCORE_AFFINE)
+      g = fa_score_mul(0.f, gb, gh, qi, kv);
+      x = fmaf(x, g * sc2, fa_score_add(0.f, gb, gh, qi, kv) * FA_LOG2E + nlu);
+#elif FA_HAS_SCORE_MOD
+      g = fa_score_mod_grad(x * scale, gb, gh, qi, kv);
+      x = fa_score_mod(x * scale, gb, gh, qi, kv) * FA_LOG2E + nlu;
+#else
+      x = fmaf(x, sc2, nlu);
+#endif
+      float pr = fa_ex2(x);
+#if FA_HAS_MASK_MOD
+      if (mode == 1) pr = fa_mask_mod(gb, gh, qi, kv) ? pr : 0.f;
+#endif
+      pv[u] = pr;
+      dv[u] = pr * (dp[e + u] + ndu) * g;
+    }
+    pp[e / 2] = fa_pack2<DT>(pv[0], pv[1]);
+    pp[e / 2 + 1] = fa_pack2<DT>(pv[2], pv[3]);
+    ds[e / 2] = fa_pack2<DT>(dv[0], dv[1]);
+    ds[e / 2 + 1] = fa_pack2<DT>(dv[2], dv[3]);
+  }
+}
+
+}  // namespace fa_btc
+
+extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(const __grid_constant__ FaBwdTcParams P) {
+  using namespace fa_btc;
+  const FaParams& p = P.p;
+  extern __shared__ unsigned char smem_raw[];
+  const fa_u32 raw = fa_smem_u32(smem_raw);
+  const fa_u32 sb = (raw + 1023u) & ~1023u;
+  unsigned char* sm = smem_raw + (sb - raw);
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int kt = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int n0 = kt * BT;
+  const int G = p.Hq / p.Hkv;
+  const int gb = b + p.b_off;
+  const int n_qtiles = (p.Sq + BT - 1) / BT;
+  const int sq_pad = n_qtiles * BT;
+
+#if FA_TC_TRACE
+  const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && p.status != nullptr;
+#endif
+  volatile int* misc = (volatile int*)(sm + OFF_MISC);  // [0] tmem base, [1] abort, [2] npairs
+  int* pairs = (int*)(sm + OFF_PAIR);
+  unsigned char* cls = sm + OFF_CLS;
+
+  // ---- set-up --------------------------------------------------------------------------------
+  if (tid == 0) {
+    fa_mbar_init(bar_addr(sb, BAR_KV), 1);
+    for (int s = 0; s < NSTAGE; ++s) {
+      fa_mbar_init(bar_addr(sb, BAR_QFULL + s), 1);
+      fa_mbar_init(bar_addr(sb, BAR_QEMPTY + s), 1);
+    }
+    fa_mbar_init(bar_addr(sb, BAR_SFULL), 1);
+    fa_mbar_init(bar_addr(sb, BAR_SFREE), 256);
+    fa_mbar_init(bar_addr(sb, BAR_PREADY), 256);
+    fa_mbar_init(bar_addr(sb, BAR_PFREE), 1);
+    fa_mbar_init(bar_addr(sb, BAR_DQFULL), 1);
+    fa_mbar_init(bar_addr(sb, BAR_DQFREE), 128);
+    fa_mbar_init(bar_addr(sb, BAR_FINAL), 1);
+    fa_mbar_init_fence();
+    misc[1] = 0;
+    misc[2] = 0;
+  }
+  if (warp == WARP_MMA) fa_tmem_alloc(sb + OFF_MISC, TMEM_COLS);
+  // (head, q tile) pairs of this kv tile: per head, classify the q tiles (0 skip, 1 mask, 2 full)
+  int npairs = 0;  // meaningful in thread 0 only
+  for (int g = 0; g < G; ++g) {
+    const int h = hk * G + g;
+    __syncthreads();
+    for (int t = tid; t < 256; t += NT) cls[t] = 0;
+    __syncthreads();
+    if (p.t.kv_num == nullptr || p.t.q_num == nullptr) {
+      for (int t = tid; t < min(n_qtiles, 256); t += NT) cls[t] = FA_HAS_MASK_MOD ? 1 : 2;
+    } else {
+      const int bm = p.t.mB == 1 ? 0 : b, hm = p.t.mH == 1 ? 0 : h;
+      const int kvblk = min(n0 / p.t.KVB, p.t.nKV - 1);
+      const long long row = ((long long)bm * p.t.mH + hm) * p.t.nKV + kvblk;
+      const int tpb = p.t.nQ == 1 ? n_qtiles : p.t.QB / BT;
+      for (int which = 0; which < 2; ++which) {
+        const int* nump = which ? p.t.full_q_num : p.t.q_num;
+        const int* idxp = which ? p.t.full_q_idx : p.t.q_idx;
+        if (nump == nullptr) continue;
+        const int num = min(max(nump[row], 0), p.t.nQ);
+        for (int e = tid; e < num * tpb; e += NT) {
+          const int bi = e / tpb, ti = e - bi * tpb;
+          const int blk = min(max(idxp[row * p.t.nQ + bi], 0), p.t.nQ - 1);
+          const int t = blk * tpb + ti;
+          if (t < min(n_qtiles, 256)) cls[t] = (unsigned char)(which ? 2 : 1);
+        }
+      }
+    }
+    __syncthreads();
+    if (tid == 0) {
+      for (int t = 0; t < min(n_qtiles, 256) && npairs < MAXP; ++t)
+        if (cls[t]) pairs[npairs++] = t | ((int)cls[t] << 16) | (g << 20);
+    }
+  }
+  if (tid == 0) misc[2] = npairs;
+  fa_tc_fence_before();
+  __syncthreads();
+  fa_tc_fence_after();
+  const fa_u32 tmem = (fa_u32)misc[0];
+  npairs = misc[2];
+  volatile int* abort_flag = misc + 1;
+
+  if (warp >= 8) fa_setmaxnreg_dec<REGS_OTHER>();
+
+  if (warp == WARP_PRODUCER) {
+    // ================================ producer ================================================
+    if (lane == 0) {
+      fa_tma_prefetch_desc(&P.tq);
+      fa_tma_prefetch_desc(&P.tk);
+      fa_tma_prefetch_desc(&P.tv);
+      fa_tma_prefetch_desc(&P.tdo);
+      if (npairs > 0) {
+        fa_mbar_expect_tx(bar_addr(sb, BAR_KV), 2 * ATOM_BYTES);
+        fa_tma_load_4d(sb + OFF_K, &P.tk, bar_addr(sb, BAR_KV), 0, n0, hk, b);
+        fa_tma_load_4d(sb + OFF_V, &P.tv, bar_addr(sb, BAR_KV), 0, n0, hk, b);
+      }
+    }
+    bool ok = true;
+    for (int n = 0; n < npairs && ok; ++n) {
+      const int s = n % NSTAGE;
+      const fa_u32 ph = (fa_u32)((n / NSTAGE) & 1);
+      const int pr = pairs[n];
+      const int m0 = (pr & 0xffff) * BT, h = hk * G + (pr >> 20);
+      if (n >= NSTAGE) ok = fa_mbar_wait_warp(bar_addr(sb, BAR_QEMPTY + s), ph ^ 1u, abort_flag);
+      if (!ok) break;
+      // per-row scalars of the q tile: -lse * log2(e) (or -inf where the row has no mass or lies
+      // beyond Sq, which makes p = 0 there) and -delta
+      float* rowp = (float*)(sm + OFF_ROW + s * 2 * 128 * 4);
+      const long long rbase = ((long long)b * p.Hq + h) * p.Sq;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int q = m0 + lane * 4 + u;
+        float nl = FA_NEG_INF, nd = 0.f;
+        if (q < p.Sq) {
+          const float lse = p.lse[rbase + q];
+          nl = (lse == FA_NEG_INF) ? FA_NEG_INF : -lse * FA_LOG2E;
+          nd = -p.delta[rbase + q];
+        }
+        rowp[lane * 4 + u] = nl;
+        rowp[128 + lane * 4 + u] = nd;
+      }
+      __syncwarp();
+      if (lane == 0) {
+        fa_mbar_expect_tx(bar_addr(sb, BAR_QFULL + s), 2 * ATOM_BYTES);
+        fa_tma_load_4d(sb + OFF_Q + s * ATOM_BYTES, &P.tq, bar_addr(sb, BAR_QFULL + s), 0, m0, h, b);
+        fa_tma_load_4d(sb + OFF_DO + s * ATOM_BYTES, &P.tdo, bar_addr(sb, BAR_QFULL + s), 0, m0, h, b);
+      }
+    }
+  } else if (warp == WARP_MMA) {
+    // ================================ MMA issuer ==============================================
+    if (lane == 0 && npairs > 0) {
+      constexpr fa_u32 IDESC_KK = fa_idesc(DT, 128, 128, 0, 0);  // A, B K-major, N = 128
+      constexpr fa_u32 IDESC_TN = fa_idesc(DT, 128, D, 0, 1);    // A K-major (TMEM or smem), B MN-major, N = 64
+      constexpr fa_u32 IDESC_NN = fa_idesc(DT, 128, D, 1, 1);    // A, B MN-major
+      bool ok = fa_mbar_wait(bar_addr(sb, BAR_KV), 0, abort_flag);
+      // descriptors: the high word (stride, version, swizzle) is fixed; the low word holds the
+      // start address and the MN-chunk distance (16-byte units) and is stepped with one add
+      constexpr fa_u32 HI = fa_desc_hi_sw128();
+      const fa_u32 loK_k = fa_desc_lo(sb + OFF_K, 16), loV_k = fa_desc_lo(sb + OFF_V, 16);
+      const fa_u32 loK_mn = fa_desc_lo(sb + OFF_K, ATOM_BYTES);
+      const fa_u32 loDS_k = fa_desc_lo(sb + OFF_DS, 16), loDS_mn = fa_desc_lo(sb + OFF_DS, ATOM_BYTES);
+      auto issue_s_dp = [&](int n) {
+        const int s = n % NSTAGE;
+        const fa_u32 loQ = fa_desc_lo(sb + OFF_Q + s * ATOM_BYTES, 16), loDO = fa_desc_lo(sb + OFF_DO + s * ATOM_BYTES, 16);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          fa_mma_ss(tmem + COL_S, fa_desc_make(loK_k + kk * 2, HI), fa_desc_make(loQ + kk * 2, HI), IDESC_KK, kk > 0);
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk)
+          fa_mma_ss(tmem + COL_DP, fa_desc_make(loV_k + kk * 2, HI), fa_desc_make(loDO + kk * 2, HI), IDESC_KK, kk > 0);
+        fa_mma_commit(bar_addr(sb, BAR_SFULL));
+      };
+      if (ok) ok = fa_mbar_wait(bar_addr(sb, BAR_QFULL + 0), 0, abort_flag);
+      if (ok) {
+        fa_tc_fence_after();
+        issue_s_dp(0);
+      }
+      FA_TRACE_DECL
+      for (int n = 0; n < npairs && ok; ++n) {
+        const int s = n % NSTAGE;
+        if (n + 1 < npairs) {
+          const int s1 = (n + 1) % NSTAGE;
+          ok = fa_mbar_wait(bar_addr(sb, BAR_QFULL + s1), (fa_u32)(((n + 1) / NSTAGE) & 1), abort_flag);
+          FA_TRACE(1);   // MMA: wait for Q/dO of the next pair
+          if (ok) ok = fa_mbar_wait(bar_addr(sb, BAR_SFREE), (fa_u32)(n & 1), abort_flag);
+          FA_TRACE(2);   // MMA: wait for S^T/dP^T to be read
+          if (!ok) break;
+          fa_tc_fence_after();
+          issue_s_dp(n + 1);
+          FA_TRACE(3);   // MMA: issue products 1-2
+        }
+        ok = fa_mbar_wait(bar_addr(sb, BAR_PREADY), (fa_u32)(n & 1), abort_flag);
+        FA_TRACE(4);     // MMA: wait for P^T / dS^T
+        if (ok && n > 0) ok = fa_mbar_wait(bar_addr(sb, BAR_DQFREE), (fa_u32)((n - 1) & 1), abort_flag);
+        FA_TRACE(5);     // MMA: wait for the dQ drain
+        if (!ok) break;
+        fa_tc_fence_after();
+        {
+          const fa_u32 loQ_mn = fa_desc_lo(sb + OFF_Q + s * ATOM_BYTES, ATOM_BYTES);
+          const fa_u32 loDO_mn = fa_desc_lo(sb + OFF_DO + s * ATOM_BYTES, ATOM_BYTES);
+          const fa_u32 acc = n > 0;
+          // 3. dV += P^T dO      (K = 128 q values, 8 steps of 16 rows = 2048 bytes; A from TMEM)
+#pragma unroll
+          for (int kk = 0; kk < BT / 16; ++kk)
+            fa_mma_ts(tmem + COL_DV, tmem + COL_P + kk * 8, fa_desc_make(loDO_mn + kk * 128, HI), IDESC_TN, acc | (kk > 0));
+          FA_TRACE(7);   // MMA: issue product 3
+          // 4. dK += dS^T Q     (A = dS^T K-major: k-step kk is 32 bytes into atom kk / 4)
+#pragma unroll
+          for (int kk = 0; kk < BT / 16; ++kk)
+            fa_mma_ss(tmem + COL_DK, fa_desc_make(loDS_k + (kk >> 2) * (ATOM_BYTES >> 4) + (kk & 3) * 2, HI),
+                      fa_desc_make(loQ_mn + kk * 128, HI), IDESC_TN, acc | (kk > 0));
+          FA_TRACE(8);   // MMA: issue product 4
+          // 5. dQ = dS K        (A = dS^T read MN-major: M chunks of 64 q one atom apart; K = 128 kv rows)
+#pragma unroll
+          for (int kk = 0; kk < BT / 16; ++kk)
+            fa_mma_ss(tmem + COL_DQ, fa_desc_make(loDS_mn + kk * 128, HI), fa_desc_make(loK_mn + kk * 128, HI), IDESC_NN, kk > 0);
+        }
+        fa_mma_commit(bar_addr(sb, BAR_PFREE));
+        fa_mma_commit(bar_addr(sb, BAR_DQFULL));
+        fa_mma_commit(bar_addr(sb, BAR_QEMPTY + s));
+        if (n + 1 == npairs) fa_mma_commit(bar_addr(sb, BAR_FINAL));
+        FA_TRACE(6);     // MMA: issue products 3-5
+      }
+    }
+  } else if (warp < 8) {
+    // ================================ compute warps ============================================
+    fa_setmaxnreg_inc<REGS_COMPUTE>();
+    const int half = warp >> 2;               // q columns 64*half .. +63 of the pair tile
+    const int lane_base = (warp & 3) * 32;
+    const int r = lane_base + lane;           // kv row of this thread
+    const int kv = n0 + r;
+    const bool row_ok = kv < p.Skv;
+    const fa_u32 t_row = tmem + ((fa_u32)lane_base << 16);
+    const float sc2 = p.scale * FA_LOG2E;
+    bool ok = true;
+#if FA_TC_TRACE
+#endif
+    FA_TRACE_DECL
+    for (int n = 0; n < npairs && ok; ++n) {
+      const int s = n % NSTAGE;
+      const int pr = pairs[n];
+      const int m0 = (pr & 0xffff) * BT, mode = (pr >> 16) & 0xf, gh = hk * G + (pr >> 20) + p.h_off;
+      ok = fa_mbar_wait_warp(bar_addr(sb, BAR_SFULL), (fa_u32)(n & 1), abort_flag);
+      if (warp == 0) { FA_TRACE(10); }  // compute: wait for S^T/dP^T
+      if (ok) ok = fa_mbar_wait_warp(bar_addr(sb, BAR_QFULL + s), (fa_u32)((n / NSTAGE) & 1), abort_flag);
+      if (!ok) break;
+      fa_tc_fence_after();
+      float sa[32], sb2[32], da[32], db[32];
+      fa_tmem_ld32(t_row + COL_S + half * 64, sa);
+      fa_tmem_ld32(t_row + COL_S + half * 64 + 32, sb2);
+      fa_tmem_ld32(t_row + COL_DP + half * 64, da);
+      fa_tmem_ld32(t_row + COL_DP + half * 64 + 32, db);
+      fa_tmem_wait_ld();
+      fa_tc_fence_before();
+      fa_mbar_arrive(bar_addr(sb, BAR_SFREE));
+      if (warp == 0) { FA_TRACE(11); }  // compute: TMEM loads
+
+      const float* rowp = (const float*)(sm + OFF_ROW + s * 2 * 128 * 4);
+      fa_u32 pp0[16], pp1[16], ds0[16], ds1[16];
+      if (row_ok) {
+        if (half == 0) {
+          chunk<0>(sa, da, rowp, rowp + 128, pp0, ds0, mode, m0, kv, gb, gh, p.scale, sc2);
+          chunk<32>(sb2, db, rowp, rowp + 128, pp1, ds1, mode, m0, kv, gb, gh, p.scale, sc2);
+        } else {
+          chunk<64>(sa, da, rowp, rowp + 128, pp0, ds0, mode, m0, kv, gb, gh, p.scale, sc2);
+          chunk<96>(sb2, db, rowp, rowp + 128, pp1, ds1, mode, m0, kv, gb, gh, p.scale, sc2);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 16; ++e) pp0[e] = pp1[e] = ds0[e] = ds1[e] = 0u;
+      }
+      if (warp == 0) { FA_TRACE(12); }  // compute: element-wise math
+      // products 3-5 of the previous pair must be done with P^T and dS^T
+      if (n > 0) {
+        ok = fa_mbar_wait_warp(bar_addr(sb, BAR_PFREE), (fa_u32)((n - 1) & 1), abort_flag);
+        if (!ok) break;
+        fa_tc_fence_after();
+      }
+      if (warp == 0) { FA_TRACE(13); }  // compute: wait for products 3-5 of the previous pair
+      fa_tmem_st16(t_row + COL_P + half * 32, pp0);
+      fa_tmem_st16(t_row + COL_P + half * 32 + 16, pp1);
+      {
+        unsigned char* dsrow = sm + OFF_DS + half * ATOM_BYTES + r * 128;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint4 w;
+          w.x = ds0[4 * c]; w.y = ds0[4 * c + 1]; w.z = ds0[4 * c + 2]; w.w = ds0[4 * c + 3];
+          *(uint4*)(dsrow + ((c ^ (r & 7)) * 16)) = w;
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint4 w;
+          w.x = ds1[4 * c]; w.y = ds1[4 * c + 1]; w.z = ds1[4 * c + 2]; w.w = ds1[4 * c + 3];
+          *(uint4*)(dsrow + (((c + 4) ^ (r & 7)) * 16)) = w;
+        }
+      }
+      fa_tmem_wait_st();
+      fence_proxy_async();
+      fa_tc_fence_before();
+      fa_mbar_arrive(bar_addr(sb, BAR_PREADY));
+      if (warp == 0) { FA_TRACE(14); }  // compute: stores of P^T / dS^T
+    }
+    // ---- epilogue: dK (scaled) by warps 0-3, dV by warps 4-7 ----------------------------------
+    if (ok && npairs > 0) ok = fa_mbar_wait_warp(bar_addr(sb, BAR_FINAL), 0, abort_flag);
+    if (ok) {
+      fa_tc_fence_after();
+      const FaTensor& dst = half == 0 ? p.dk : p.dv;
+      const float mul = half == 0 ? p.scale : 1.f;
+      char* og = (char*)dst.ptr + ((long long)b * dst.sb + (long long)hk * dst.sh + (long long)kv * dst.ss) * 2;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        float o[32];
+        if (npairs > 0) {
+          fa_tmem_ld32(t_row + (half == 0 ? COL_DK : COL_DV) + c * 32, o);
+          fa_tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[e] = 0.f;
+        }
+        if (row_ok) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 8) {
+            uint4 w;
+            w.x = fa_pack2<DT>(o[e] * mul, o[e + 1] * mul);
+            w.y = fa_pack2<DT>(o[e + 2] * mul, o[e + 3] * mul);
+            w.z = fa_pack2<DT>(o[e + 4] * mul, o[e + 5] * mul);
+            w.w = fa_pack2<DT>(o[e + 6] * mul, o[e + 7] * mul);
+            *(uint4*)(og + (c * 32 + e) * 2) = w;
+          }
+        }
+      }
+    }
+  } else if (warp < 12) {
+    // ================================ dQ drain warps ===========================================
+    const int lane_base = (warp & 3) * 32;
+    const int r = lane_base + lane;  // q row inside the pair tile
+    const fa_u32 t_dq = tmem + ((fa_u32)lane_base << 16) + COL_DQ;
+    const int dtid = tid - 256;
+    bool ok = true;
+    FA_TRACE_DECL
+    for (int n = 0; n < npairs && ok; ++n) {
+      const int pr = pairs[n];
+      const int qt = pr & 0xffff, h = hk * G + (pr >> 20);
+      ok = fa_mbar_wait_warp(bar_addr(sb, BAR_DQFULL), (fa_u32)(n & 1), abort_flag);
+      if (warp == 8) { FA_TRACE(20); }  // drain: wait for dQ
+      if (!ok) break;
+      fa_tc_fence_after();
+      // the previous bulk reduce must have finished reading the staging tile
+      if (dtid == 0) bulk_wait_read0();
+      named_bar_sync(1, 128);
+      if (warp == 8) { FA_TRACE(21); }  // drain: wait for the previous bulk reduce
+      // 16-byte chunk k of row r goes to position k ^ (r & 15): spreads the rows of a warp over
+      // the banks; the accumulation buffer in global memory uses the same permutation
+      unsigned char* strow = sm + OFF_DQ + r * 256;
+      {
+        float a[32];
+        fa_tmem_ld32(t_dq, a);
+        fa_tmem_wait_ld();
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          *(float4*)(strow + ((k ^ (r & 15)) * 16)) = make_float4(a[4 * k], a[4 * k + 1], a[4 * k + 2], a[4 * k + 3]);
+        fa_tmem_ld32(t_dq + 32, a);
+        fa_tmem_wait_ld();
+        fa_tc_fence_before();
+        fa_mbar_arrive(bar_addr(sb, BAR_DQFREE));
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          *(float4*)(strow + (((k + 8) ^ (r & 15)) * 16)) = make_float4(a[4 * k], a[4 * k + 1], a[4 * k + 2], a[4 * k + 3]);
+      }
+      fence_proxy_async();
+      named_bar_sync(1, 128);
+      if (dtid == 0) {
+        float* gdst = P.dq_acc + (((long long)b * p.Hq + h) * sq_pad + (long long)qt * BT) * D;
+        bulk_reduce_add_f32(gdst, sb + OFF_DQ, 128 * 64 * 4);
+        bulk_commit();
+      }
+      if (warp == 8) { FA_TRACE(22); }  // drain: TMEM -> staging -> reduce issue
+    }
+    if (dtid == 0) bulk_wait0();
+  }
+
+  // ---- teardown ------------------------------------------------------------------------------
+  fa_tc_fence_before();
+  __syncthreads();
+  if (warp == WARP_MMA) {
+    fa_tc_fence_after();
+    fa_tmem_dealloc(tmem, TMEM_COLS);
+  }
+  if (tid == 0 && *abort_flag != 0 && p.status != nullptr) atomicOr(p.status, FA_STATUS_WAIT_TIMEOUT);
+}

@@ -281,26 +281,28 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
       constexpr fa_u32 IDESC_O = fa_idesc(DT, BM, D, 0, 1);
       bool ok = nsteps == 0 || fa_mbar_wait(bar_addr(sb, BAR_Q), 0, abort_flag);
       fa_u32 cnt[2] = {0, 0};  // active steps seen so far per query tile
+      // Descriptors: constant high word; the low word (start address and MN-chunk distance in
+      // 16-byte units) is stepped with one add per k-step.
+      constexpr fa_u32 HI = fa_desc_hi_sw128();
       // S_i = Q_i K^T for step j into TMEM columns COL_S + 128 i
       auto issue_s = [&](int i, int j) {
         const int s = j % NSTAGE;
+        const fa_u32 loQ = fa_desc_lo(sb + i * ATOMS * ATOM_BYTES, 16), loK = fa_desc_lo(sb + OFF_K + s * KV_STAGE, 16);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
-          const fa_u32 koff = (kk / 4) * ATOM_BYTES + (kk % 4) * 32;
-          const fa_u64 da = fa_smem_desc_sw128(sb + i * ATOMS * ATOM_BYTES + koff, 16);
-          const fa_u64 db = fa_smem_desc_sw128(sb + OFF_K + s * KV_STAGE + koff, 16);
-          fa_mma_ss(tmem + COL_S + i * BN, da, db, IDESC_S, kk > 0);
+          const fa_u32 koff = ((kk / 4) * ATOM_BYTES + (kk % 4) * 32) >> 4;
+          fa_mma_ss(tmem + COL_S + i * BN, fa_desc_make(loQ + koff, HI), fa_desc_make(loK + koff, HI), IDESC_S, kk > 0);
         }
         fa_mma_commit(bar_addr(sb, BAR_S + i));
       };
       // O_i += P_i V for step j (P_i: 16-bit, in the first 64 columns of S_i)
       auto issue_pv = [&](int i, int j, bool first) {
         const int s = j % NSTAGE;
+        const fa_u32 loV = fa_desc_lo(sb + OFF_V + s * KV_STAGE, ATOM_BYTES);
+        const fa_u32 acc = !first;
 #pragma unroll
-        for (int kk = 0; kk < BN / 16; ++kk) {
-          const fa_u64 db = fa_smem_desc_sw128(sb + OFF_V + s * KV_STAGE + kk * 2048, ATOM_BYTES);
-          fa_mma_ts(tmem + COL_O + i * D, tmem + COL_S + i * BN + kk * 8, db, IDESC_O, (!first) || kk > 0);
-        }
+        for (int kk = 0; kk < BN / 16; ++kk)
+          fa_mma_ts(tmem + COL_O + i * D, tmem + COL_S + i * BN + kk * 8, fa_desc_make(loV + kk * 128, HI), IDESC_O, acc | (kk > 0));
         fa_mma_commit(bar_addr(sb, BAR_O + i));
       };
       if (ok && nsteps > 0) {

@@ -147,6 +147,19 @@ __device__ __forceinline__ fa_u64 fa_smem_desc_sw128(fa_u32 saddr, fa_u32 lbo_by
   d |= 2ull << 61;  // SWIZZLE_128B
   return d;
 }
+// The same descriptor split in two words, so that an issue loop can step the start address
+// with one 32-bit add: high word = stride / version / swizzle (constant), low word = start
+// address and MN-chunk distance, both in 16-byte units.  Stepping by `bytes` adds bytes >> 4.
+__device__ __forceinline__ constexpr fa_u32 fa_desc_hi_sw128() { return (1024u >> 4) | (1u << 14) | (2u << 29); }
+__device__ __forceinline__ fa_u32 fa_desc_lo(fa_u32 saddr, fa_u32 lbo_bytes) {
+  return ((saddr & 0x3FFFFu) >> 4) | (((lbo_bytes >> 4) & 0x3FFFu) << 16);
+}
+__device__ __forceinline__ fa_u64 fa_desc_make(fa_u32 lo, fa_u32 hi) {
+  fa_u64 d;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(d) : "r"(lo), "r"(hi));
+  return d;
+}
+
 // instruction descriptor: fp32 accumulate, A and B of type DT (0 = f16, 1 = bf16)
 __device__ __forceinline__ constexpr fa_u32 fa_idesc(int dt, int M, int N, int a_mn_major, int b_mn_major) {
   return (1u << 4) | ((fa_u32)dt << 7) | ((fa_u32)dt << 10) | ((fa_u32)a_mn_major << 15) | ((fa_u32)b_mn_major << 16) |

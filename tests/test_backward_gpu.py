@@ -74,6 +74,46 @@ def test_gradients_match_fp32_reference(case):
         assert rel_err(got, ref) <= GTOL[dt], f"{name}: {rel_err(got, ref)}"
 
 
+TC_CASES = [
+    # shapes the single-pass tcgen05 backward covers (D = 64): B, Hq, Hkv, Sq, Skv, dtype, score, mask
+    (1, 1, 1, 128, 128, "f16", None, None),
+    (2, 2, 2, 512, 512, "bf16", "checker", None),
+    (1, 4, 4, 1024, 1024, "f16", "alibi", "causal"),
+    (1, 2, 2, 300, 333, "f16", "alibi", "causal"),
+    (1, 4, 2, 512, 768, "f16", "softcap", "window"),
+    (1, 2, 2, 2048, 2048, "bf16", None, "sink"),
+]
+
+
+@pytest.mark.parametrize("case", TC_CASES, ids=lambda c: "-".join(map(str, c)))
+def test_tcgen05_and_general_backward_agree_with_the_reference(case):
+    import flaxattention_b200 as fa
+
+    B, Hq, Hkv, Sq, Skv, dt, score, mask = case
+    s, m = _mods(score, mask, Hq, Sq, Skv)
+    q, k, v = qkv(B, Hq, Hkv, Sq, Skv, 64, dtype=DTYPES[dt])
+    g = np.random.Generator(np.random.Philox(11))
+    dout = torch.from_numpy(g.standard_normal((B, Hq, Sq, 64), dtype=np.float32)).to(DTYPES[dt])
+    _, _, rq, rk, rv = attention_grads_oracle(q, k, v, dout, s, m)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    res = []
+    for opts in ({"status": status}, {"kernels": "general"}):
+        bm = fa.create_block_mask(m, B, Hq, Sq, Skv) if m is not None else None
+        qc, kc, vc = (t.cuda().requires_grad_(True) for t in (q, k, v))
+        out = fa.flax_attention(qc, kc, vc, score_mod=s, block_mask=bm, enable_gqa=Hq != Hkv,
+                                kernel_options=dict(opts, path="fwd"))
+        out.backward(dout.cuda())
+        torch.cuda.synchronize()
+        got = (qc.grad.cpu(), kc.grad.cpu(), vc.grad.cpu())
+        for name, x, r in zip(("dq", "dk", "dv"), got, (rq, rk, rv)):
+            assert not torch.isnan(x.float()).any(), name
+            assert rel_err(x, r) <= GTOL[dt], f"{name}: {rel_err(x, r)}"
+        res.append(got)
+    assert int(status.item()) == 0
+    for a, b in zip(*res):
+        assert rel_err(a, b) <= (4e-3 if dt == "f16" else 3e-2)
+
+
 @pytest.mark.parametrize("name", ["grads_nomod", "grads_decode"])
 def test_gradients_match_stored_sdpa_vectors(name):
     # tests/attention_test.py:385-477: dQ of output.sum() against torch autograd
@@ -129,4 +169,7 @@ def test_benchmark_shape_backward_properties():
     b = (dk.double() * k.double()).sum(dim=(2, 3))
     assert ((a - b).abs() / (a.abs() + b.abs() + 1.0)).max().item() <= 5e-2
     out2, dq2, dk2, dv2 = _grads(q, k, v, dout, checkerboard, None)
-    assert torch.equal(dq, dq2) and torch.equal(dk, dk2) and torch.equal(dv, dv2)
+    # dK and dV accumulate in a fixed order; dQ is summed over kv tiles by reduce-adds whose
+    # order is not fixed, so it is reproducible only to fp32 summation noise
+    assert torch.equal(dk, dk2) and torch.equal(dv, dv2)
+    assert rel_err(dq2, dq) <= 1e-3
