@@ -51,7 +51,8 @@ DECODE = dict(B=32, H=8, Skv=16384, D=64, dtype="f16")
 DT = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from ncu captures (profiles/); None = not captured
-NCU_TRAFFIC = {"fa_fwd_kernel": None, "fa_bwd_dkdv_kernel": None, "fa_bwd_dq_kernel": None}
+NCU_TRAFFIC = {"fa_fwd_tc_kernel": None, "fa_bwd_tc_kernel": None, "fa_fwd_kernel": None, "fa_bwd_dkdv_kernel": None,
+               "fa_bwd_dq_kernel": None}
 
 
 def peaks():
@@ -86,43 +87,60 @@ def host_inputs(w, b_offset, pinned):
 
 
 class ClockSampler:
-    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """Samples SM clock and throttle reasons of one GPU from a background thread through NVML
+    while the timed region runs (reading only; nothing is set)."""
 
-    def __init__(self, index):
-        self.proc = None
+    def __init__(self, index, period_s=0.002):
+        import threading
+
+        self.samples, self.reasons, self.max_mhz, self.err = [], set(), None, None
+        self._stop = threading.Event()
+        self._thread = None
         try:
-            self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-i", str(index),
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
-        except OSError:
-            pass
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = float(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception as e:  # pragma: no cover - depends on the box
+            self.err = f"NVML unavailable: {e}"
+            return
+        self._period = period_s
+        self._thread = threading.Thread(target=self._run, daemon=True)
+        self._thread.start()
+
+    def _run(self):
+        nv = self._nv
+        bits = {
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+        }
+        get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or getattr(
+            nv, "nvmlDeviceGetCurrentClocksThrottleReasons")
+        while not self._stop.is_set():
+            try:
+                self.samples.append(float(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                r = int(get_reasons(self._h))
+                for name, bit in bits.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception as e:  # pragma: no cover
+                self.err = str(e)
+                break
+            self._stop.wait(self._period)
 
     def stop(self):
-        if self.proc is None:
-            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
-        self.proc.terminate()
-        try:
-            text, _ = self.proc.communicate(timeout=5)
-        except subprocess.TimeoutExpired:
-            self.proc.kill()
-            text, _ = self.proc.communicate()
-        sm, mx, reasons = [], [], set()
-        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
-        for line in text.strip().splitlines():
-            parts = [x.strip() for x in line.split(",")]
-            if len(parts) < 6:
-                continue
-            try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
-            except ValueError:
-                continue
-            for n, v in zip(names, parts[2:6]):
-                if v.lower().startswith("active"):
-                    reasons.add(n)
-        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
-                "samples": len(sm), "reasons": sorted(reasons)}
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join(timeout=2)
+        out = {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
+               "samples": len(self.samples), "reasons": sorted(self.reasons)}
+        if self.err:
+            out["note"] = self.err
+        return out
 
 
 def cpu_oracle_step(w, sample_b, score, mask):
@@ -174,7 +192,7 @@ def run_reference(args, w, rank, world):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
@@ -303,16 +321,22 @@ def main():
         steps_k = max(5, args.steps // 2)
         out, lse = A._forward(call, q, k, v)
         t_fwd = timed(lambda: A._forward(call, q, k, v), steps_k, 3)
+        # this workload runs the tcgen05 kernels: the forward, and a single-pass backward made
+        # of fa_delta_kernel, fa_bwd_tc_kernel (preceded by the memset of the dQ accumulator)
+        # and fa_dq_convert_kernel; the FA_FLAG_BWD_SKIP_* aids isolate them
+        tc = w["D"] == 64 and w["dtype"] != "f32"
+        fwd_name = "fa_fwd_tc_kernel" if tc else "fa_fwd_kernel"
+        main_name, post_name = ("fa_bwd_tc_kernel", "fa_dq_convert_kernel") if tc else ("fa_bwd_dkdv_kernel", "fa_bwd_dq_kernel")
         only = {
-            "fa_bwd_dkdv_kernel": _cabi.FLAG_BWD_SKIP_DELTA | _cabi.FLAG_BWD_SKIP_DQ,
-            "fa_bwd_dq_kernel": _cabi.FLAG_BWD_SKIP_DELTA | _cabi.FLAG_BWD_SKIP_DKDV,
+            main_name: _cabi.FLAG_BWD_SKIP_DELTA | _cabi.FLAG_BWD_SKIP_DQ,
+            post_name: _cabi.FLAG_BWD_SKIP_DELTA | _cabi.FLAG_BWD_SKIP_DKDV,
             "fa_delta_kernel": _cabi.FLAG_BWD_SKIP_DKDV | _cabi.FLAG_BWD_SKIP_DQ,
         }
         A._backward(call, q, k, v, out, lse, dout)  # delta is in place for the partial runs
         unit = fl_fwd / 4.0  # one S x S x D product = 2*B*H*Sq*Skv*D
-        alg = {"fa_fwd_kernel": 2 * unit, "fa_bwd_dkdv_kernel": 4 * unit, "fa_bwd_dq_kernel": 1 * unit,
+        alg = {fwd_name: 2 * unit, main_name: (5 if tc else 4) * unit, post_name: (0 if tc else 1) * unit,
                "fa_delta_kernel": 0.0}
-        kernels = {"fa_fwd_kernel": {"ms": t_fwd}}
+        kernels = {fwd_name: {"ms": t_fwd}}
         for name, flags in only.items():
             c2 = make_call(flags)
             kernels[name] = {"ms": timed(lambda c2=c2: A._backward(c2, q, k, v, out, lse, dout), steps_k, 3)}
