@@ -51,7 +51,8 @@ DECODE = dict(B=32, H=8, Skv=16384, D=64, dtype="f16")
 DT = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from ncu captures (profiles/); None = not captured
-NCU_TRAFFIC = {"fa_fwd_tc_kernel": None, "fa_bwd_tc_kernel": None, "fa_fwd_kernel": None, "fa_bwd_dkdv_kernel": None,
+# (captured on the B=2 profile case and scaled by 4 to the B=8 workload: traffic grows with the batch)
+NCU_TRAFFIC = {"fa_fwd_tc_kernel": 4 * 12.91e6, "fa_bwd_tc_kernel": 4 * 25.49e6, "fa_fwd_kernel": None, "fa_bwd_dkdv_kernel": None,
                "fa_bwd_dq_kernel": None}
 
 
