@@ -488,6 +488,59 @@ __global__ void fa_delta_kernel(FaTensor o, FaTensor dout, float* __restrict__ d
   if (row < n_rows && sub == 0) delta[row] = acc;
 }
 
+// Per-row scalars of the tcgen05 backward, padded to whole 128-row tiles so that a q tile's
+// values are one aligned 512-byte run: nlse2 = -lse * log2(e) (-inf for rows without mass or
+// beyond Sq, which makes p = 0 there) and ndelta = -sum_d O * dO (0 beyond Sq).
+template <int DT, int LPR>
+__global__ void fa_bwd_prep_kernel(FaTensor o, FaTensor dout, const float* __restrict__ lse, float* __restrict__ nlse2,
+                                   float* __restrict__ ndelta, int Hq, int Sq, int sq_pad, int Dv, long long n_rows_pad) {
+  constexpr int EPC = 8;
+  const long long gt = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long row = gt / LPR;
+  const int sub = (int)(gt % LPR);
+  float acc = 0.f;
+  bool valid = false;
+  long long bh = 0;
+  int q = 0;
+  if (row < n_rows_pad) {
+    bh = row / sq_pad;
+    q = (int)(row - bh * sq_pad);
+    valid = q < Sq;
+  }
+  if (valid) {
+    const int b = (int)(bh / Hq), h = (int)(bh - (long long)b * Hq);
+    const char* po = (const char*)o.ptr + ((long long)b * o.sb + (long long)h * o.sh + (long long)q * o.ss) * 2;
+    const char* pd = (const char*)dout.ptr + ((long long)b * dout.sb + (long long)h * dout.sh + (long long)q * dout.ss) * 2;
+    for (int c = sub; c * EPC < Dv; c += LPR) {
+      const uint4 a = *(const uint4*)(po + c * 16);
+      const uint4 d = *(const uint4*)(pd + c * 16);
+      const unsigned aw[4] = {a.x, a.y, a.z, a.w}, dw[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        if (DT == FA_F16) {
+          const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&aw[i]));
+          const float2 fd = __half22float2(*reinterpret_cast<const __half2*>(&dw[i]));
+          acc += fa.x * fd.x + fa.y * fd.y;
+        } else {
+          acc += __uint_as_float(aw[i] << 16) * __uint_as_float(dw[i] << 16) +
+                 __uint_as_float(aw[i] & 0xffff0000u) * __uint_as_float(dw[i] & 0xffff0000u);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int off = LPR / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (row < n_rows_pad && sub == 0) {
+    float nl = -INFINITY;
+    if (valid) {
+      const float l = lse[bh * Sq + q];
+      nl = (l == -INFINITY) ? -INFINITY : -l * 1.4426950408889634f;
+    }
+    nlse2[row] = nl;
+    ndelta[row] = valid ? -acc : 0.f;
+  }
+}
+
 // dq = scale * dq_acc for the tcgen05 backward: the fp32 accumulation buffer is
 // [B, Hq, sq_pad, 64] with the sixteen 16-byte chunks of a row stored at position k ^ (q & 15).
 template <int DT>
@@ -692,7 +745,7 @@ bool tc_fwd_eligible(const fa_attn_params* p) {
 
 int get_fwd_tc_kernel(fa_module* m, int dtype, int D, int flags, Kernel** k) {
   const int atoms = D / 64, nstage = D == 64 ? 3 : 2;
-  const int smem = 2 * atoms * 16384 + 2 * nstage * atoms * 16384 + (1 + 4 * nstage + 6) * 8 + 16 + 256 * 2 + 256 * 2 +
+  const int smem = 2 * atoms * 16384 + 2 * nstage * atoms * 16384 + (1 + 4 * nstage + 12) * 8 + 16 + 256 * 2 + 256 * 2 +
                    2 * 256 + 1024;
   std::string d = defs({{"FA_DTYPE", dtype}, {"FA_D", D}, {"FA_ROUND_SCORES", round_flag(dtype, flags)}});
   d += extra_defines();
@@ -715,6 +768,8 @@ struct FaBwdTcParamsHost {
   FaParams p;
   FaTensorMapHost tq, tk, tv, tdo;
   float* dq_acc;
+  const float* nlse2;
+  const float* ndelta;
 };
 
 bool tc_bwd_eligible(const fa_attn_params* p) {
@@ -732,6 +787,10 @@ bool tc_bwd_eligible(const fa_attn_params* p) {
   return true;
 }
 size_t delta_bytes(const fa_attn_params* p) { return ((size_t)p->B * p->Hq * p->Sq * sizeof(float) + 255) / 256 * 256; }
+size_t rows_pad_bytes(const fa_attn_params* p) {
+  const size_t sq_pad = (size_t)((p->Sq + 127) / 128) * 128;
+  return ((size_t)p->B * p->Hq * sq_pad * sizeof(float) + 255) / 256 * 256;
+}
 size_t dq_acc_bytes(const fa_attn_params* p) {
   const size_t sq_pad = (size_t)((p->Sq + 127) / 128) * 128;
   return (size_t)p->B * p->Hq * sq_pad * 64 * sizeof(float);
@@ -799,9 +858,8 @@ int fa_fwd(fa_module* m, const fa_attn_params* p, void* stream) {
 
 size_t fa_bwd_workspace_bytes(const fa_attn_params* p) {
   if (!p || p->B <= 0 || p->Hq <= 0 || p->Sq <= 0) return 0;
-  size_t n = delta_bytes(p);
-  if (p->Hkv > 0 && p->Hq % p->Hkv == 0 && tc_bwd_eligible(p)) n += dq_acc_bytes(p);
-  return n;
+  if (p->Hkv > 0 && p->Hq % p->Hkv == 0 && tc_bwd_eligible(p)) return 2 * rows_pad_bytes(p) + dq_acc_bytes(p);
+  return delta_bytes(p);
 }
 
 int fa_bwd(fa_module* m, const fa_attn_params* p, const fa_tensor* dout, const fa_tensor* dq, const fa_tensor* dk,
@@ -834,6 +892,46 @@ int fa_bwd(fa_module* m, const fa_attn_params* p, const fa_tensor* dout, const f
     if (int rc = get_bwd_kernel(m, p->dtype, p->D, p->Dv, p->flags, c, true, &kdq)) return rc;
     if (int rc = get_bwd_kernel(m, p->dtype, p->D, p->Dv, p->flags, c, false, &kdkdv)) return rc;
   }
+  if (use_tc) {
+    // workspace: nlse2 | ndelta (padded rows) | dq accumulator
+    cudaStream_t st = (cudaStream_t)stream;
+    float* nlse2 = (float*)workspace;
+    float* ndelta = (float*)((char*)workspace + rows_pad_bytes(p));
+    float* dq_acc = (float*)((char*)workspace + 2 * rows_pad_bytes(p));
+    const int sq_pad = (p->Sq + 127) / 128 * 128;
+    if (!(p->flags & FA_FLAG_BWD_SKIP_DELTA)) {
+      const long long n_rows_pad = (long long)p->B * p->Hq * sq_pad;
+      const unsigned blocks = (unsigned)((n_rows_pad * 8 + 255) / 256);
+      if (p->dtype == FA_F16)
+        fa_bwd_prep_kernel<FA_F16, 8><<<blocks, 256, 0, st>>>(kp.o, kp.dout, p->lse, nlse2, ndelta, p->Hq, p->Sq, sq_pad, p->Dv, n_rows_pad);
+      else
+        fa_bwd_prep_kernel<FA_BF16, 8><<<blocks, 256, 0, st>>>(kp.o, kp.dout, p->lse, nlse2, ndelta, p->Hq, p->Sq, sq_pad, p->Dv, n_rows_pad);
+      FA_CUDA_CHECK(cudaGetLastError());
+    }
+    if (!(p->flags & FA_FLAG_BWD_SKIP_DKDV)) {
+      FA_CUDA_CHECK(cudaMemsetAsync(dq_acc, 0, dq_acc_bytes(p), st));
+      FaBwdTcParamsHost tp;
+      tp.p = kp;
+      tp.dq_acc = dq_acc;
+      tp.nlse2 = nlse2;
+      tp.ndelta = ndelta;
+      if (int rc = make_map(&tp.tq, p->dtype, p->q, p->D, p->Sq, p->Hq, p->B)) return rc;
+      if (int rc = make_map(&tp.tk, p->dtype, p->k, p->D, p->Skv, p->Hkv, p->B)) return rc;
+      if (int rc = make_map(&tp.tv, p->dtype, p->v, p->Dv, p->Skv, p->Hkv, p->B)) return rc;
+      if (int rc = make_map(&tp.tdo, p->dtype, *dout, p->Dv, p->Sq, p->Hq, p->B)) return rc;
+      if (int rc = launch(ktc, dim3((p->Skv + 127) / 128, p->Hkv, p->B), dim3(512), &tp, stream)) return rc;
+    }
+    if (!(p->flags & FA_FLAG_BWD_SKIP_DQ)) {
+      const long long n_chunks = (long long)p->B * p->Hq * p->Sq * 8;
+      const unsigned blocks = (unsigned)((n_chunks + 255) / 256);
+      if (p->dtype == FA_F16)
+        fa_dq_convert_kernel<FA_F16><<<blocks, 256, 0, st>>>(dq_acc, kp.dq, p->Hq, p->Sq, sq_pad, p->scale, n_chunks);
+      else
+        fa_dq_convert_kernel<FA_BF16><<<blocks, 256, 0, st>>>(dq_acc, kp.dq, p->Hq, p->Sq, sq_pad, p->scale, n_chunks);
+      FA_CUDA_CHECK(cudaGetLastError());
+    }
+    return FA_OK;
+  }
   if (!(p->flags & FA_FLAG_BWD_SKIP_DELTA)) {
     cudaStream_t st = (cudaStream_t)stream;
     const long long n_rows = (long long)p->B * p->Hq * p->Sq;
@@ -855,33 +953,6 @@ int fa_bwd(fa_module* m, const fa_attn_params* p, const fa_tensor* dout, const f
 #undef FA_DELTA_DT
 #undef FA_DELTA
     FA_CUDA_CHECK(cudaGetLastError());
-  }
-  if (use_tc) {
-    // single-pass kernel: dK, dV directly, dQ through the fp32 accumulation buffer
-    cudaStream_t st = (cudaStream_t)stream;
-    float* dq_acc = (float*)((char*)workspace + delta_bytes(p));
-    if (!(p->flags & FA_FLAG_BWD_SKIP_DKDV)) {
-      FA_CUDA_CHECK(cudaMemsetAsync(dq_acc, 0, dq_acc_bytes(p), st));
-      FaBwdTcParamsHost tp;
-      tp.p = kp;
-      tp.dq_acc = dq_acc;
-      if (int rc = make_map(&tp.tq, p->dtype, p->q, p->D, p->Sq, p->Hq, p->B)) return rc;
-      if (int rc = make_map(&tp.tk, p->dtype, p->k, p->D, p->Skv, p->Hkv, p->B)) return rc;
-      if (int rc = make_map(&tp.tv, p->dtype, p->v, p->Dv, p->Skv, p->Hkv, p->B)) return rc;
-      if (int rc = make_map(&tp.tdo, p->dtype, *dout, p->Dv, p->Sq, p->Hq, p->B)) return rc;
-      if (int rc = launch(ktc, dim3((p->Skv + 127) / 128, p->Hkv, p->B), dim3(512), &tp, stream)) return rc;
-    }
-    if (!(p->flags & FA_FLAG_BWD_SKIP_DQ)) {
-      const int sq_pad = (p->Sq + 127) / 128 * 128;
-      const long long n_chunks = (long long)p->B * p->Hq * p->Sq * 8;
-      const unsigned blocks = (unsigned)((n_chunks + 255) / 256);
-      if (p->dtype == FA_F16)
-        fa_dq_convert_kernel<FA_F16><<<blocks, 256, 0, st>>>(dq_acc, kp.dq, p->Hq, p->Sq, sq_pad, p->scale, n_chunks);
-      else
-        fa_dq_convert_kernel<FA_BF16><<<blocks, 256, 0, st>>>(dq_acc, kp.dq, p->Hq, p->Sq, sq_pad, p->scale, n_chunks);
-      FA_CUDA_CHECK(cudaGetLastError());
-    }
-    return FA_OK;
   }
   if (!(p->flags & FA_FLAG_BWD_SKIP_DKDV))
     if (int rc = launch(kdkdv, dim3((p->Skv + c.tile - 1) / c.tile, p->Hkv, p->B), dim3(c.warps * 32), &kp, stream))

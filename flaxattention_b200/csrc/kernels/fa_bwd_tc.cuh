@@ -34,10 +34,17 @@ struct FaBwdTcParams {
   FaParams p;
   FaTensorMap tq, tk, tv, tdo;  // 4-d maps (D, S, H, B), box 64 x 128 x 1 x 1, 128-byte swizzle
   float* dq_acc;                // [B, Hq, ceil(Sq/128)*128, 64] fp32, 16-byte chunks of a row permuted
+  const float* nlse2;           // [B, Hq, ceil(Sq/128)*128]: -lse * log2(e); -inf for rows without mass / beyond Sq
+  const float* ndelta;          // same shape: -rowsum(O * dO); 0 beyond Sq
 };
 
 // Optional phase timing (tuning aid): with FA_TC_TRACE the status buffer must hold at least
 // 64 ints; slot k accumulates the SM cycles CTA (0,0,0) spent in phase k.
+// experiments (wrong results, timing only): bit 0 drain skips staging+reduce, bit 1 compute skips
+// the dS^T smem stores, bit 2 compute skips the math, bit 3 compute skips the TMEM loads
+#ifndef FA_TC_EXP
+#define FA_TC_EXP 0
+#endif
 #ifndef FA_TC_TRACE
 #define FA_TC_TRACE 0
 #endif
@@ -256,35 +263,23 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
         fa_tma_load_4d(sb + OFF_V, &P.tv, bar_addr(sb, BAR_KV), 0, n0, hk, b);
       }
     }
-    bool ok = true;
-    for (int n = 0; n < npairs && ok; ++n) {
-      const int s = n % NSTAGE;
-      const fa_u32 ph = (fa_u32)((n / NSTAGE) & 1);
-      const int pr = pairs[n];
-      const int m0 = (pr & 0xffff) * BT, h = hk * G + (pr >> 20);
-      if (n >= NSTAGE) ok = fa_mbar_wait_warp(bar_addr(sb, BAR_QEMPTY + s), ph ^ 1u, abort_flag);
-      if (!ok) break;
-      // per-row scalars of the q tile: -lse * log2(e) (or -inf where the row has no mass or lies
-      // beyond Sq, which makes p = 0 there) and -delta
-      float* rowp = (float*)(sm + OFF_ROW + s * 2 * 128 * 4);
-      const long long rbase = ((long long)b * p.Hq + h) * p.Sq;
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        const int q = m0 + lane * 4 + u;
-        float nl = FA_NEG_INF, nd = 0.f;
-        if (q < p.Sq) {
-          const float lse = p.lse[rbase + q];
-          nl = (lse == FA_NEG_INF) ? FA_NEG_INF : -lse * FA_LOG2E;
-          nd = -p.delta[rbase + q];
-        }
-        rowp[lane * 4 + u] = nl;
-        rowp[128 + lane * 4 + u] = nd;
-      }
-      __syncwarp();
-      if (lane == 0) {
-        fa_mbar_expect_tx(bar_addr(sb, BAR_QFULL + s), 2 * ATOM_BYTES);
-        fa_tma_load_4d(sb + OFF_Q + s * ATOM_BYTES, &P.tq, bar_addr(sb, BAR_QFULL + s), 0, m0, h, b);
-        fa_tma_load_4d(sb + OFF_DO + s * ATOM_BYTES, &P.tdo, bar_addr(sb, BAR_QFULL + s), 0, m0, h, b);
+    if (lane == 0) {
+      bool ok = true;
+      for (int n = 0; n < npairs && ok; ++n) {
+        const int s = n % NSTAGE;
+        const fa_u32 ph = (fa_u32)((n / NSTAGE) & 1);
+        const int pr = pairs[n];
+        const int m0 = (pr & 0xffff) * BT, h = hk * G + (pr >> 20);
+        if (n >= NSTAGE) ok = fa_mbar_wait(bar_addr(sb, BAR_QEMPTY + s), ph ^ 1u, abort_flag);
+        if (!ok) break;
+        // Q and dO tiles plus the per-row scalars of the q tile (prepared by fa_bwd_prep_kernel)
+        const long long rbase = ((long long)b * p.Hq + h) * sq_pad + m0;
+        const fa_u32 full = bar_addr(sb, BAR_QFULL + s);
+        fa_mbar_expect_tx(full, 2 * ATOM_BYTES + 2 * 128 * 4);
+        fa_tma_load_4d(sb + OFF_Q + s * ATOM_BYTES, &P.tq, full, 0, m0, h, b);
+        fa_tma_load_4d(sb + OFF_DO + s * ATOM_BYTES, &P.tdo, full, 0, m0, h, b);
+        fa_bulk_load(sb + OFF_ROW + s * 2 * 128 * 4, P.nlse2 + rbase, 128 * 4, full);
+        fa_bulk_load(sb + OFF_ROW + s * 2 * 128 * 4 + 128 * 4, P.ndelta + rbase, 128 * 4, full);
       }
     }
   } else if (warp == WARP_MMA) {
@@ -387,18 +382,23 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
       if (!ok) break;
       fa_tc_fence_after();
       float sa[32], sb2[32], da[32], db[32];
-      fa_tmem_ld32(t_row + COL_S + half * 64, sa);
-      fa_tmem_ld32(t_row + COL_S + half * 64 + 32, sb2);
-      fa_tmem_ld32(t_row + COL_DP + half * 64, da);
-      fa_tmem_ld32(t_row + COL_DP + half * 64 + 32, db);
-      fa_tmem_wait_ld();
+      if (FA_TC_EXP & 8) {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) sa[e] = sb2[e] = da[e] = db[e] = 0.f;
+      } else {
+        fa_tmem_ld32(t_row + COL_S + half * 64, sa);
+        fa_tmem_ld32(t_row + COL_S + half * 64 + 32, sb2);
+        fa_tmem_ld32(t_row + COL_DP + half * 64, da);
+        fa_tmem_ld32(t_row + COL_DP + half * 64 + 32, db);
+        fa_tmem_wait_ld();
+      }
       fa_tc_fence_before();
       fa_mbar_arrive(bar_addr(sb, BAR_SFREE));
       if (warp == 0) { FA_TRACE(11); }  // compute: TMEM loads
 
       const float* rowp = (const float*)(sm + OFF_ROW + s * 2 * 128 * 4);
       fa_u32 pp0[16], pp1[16], ds0[16], ds1[16];
-      if (row_ok) {
+      if (row_ok && !(FA_TC_EXP & 4)) {
         if (half == 0) {
           chunk<0>(sa, da, rowp, rowp + 128, pp0, ds0, mode, m0, kv, gb, gh, p.scale, sc2);
           chunk<32>(sb2, db, rowp, rowp + 128, pp1, ds1, mode, m0, kv, gb, gh, p.scale, sc2);
@@ -420,7 +420,7 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
       if (warp == 0) { FA_TRACE(13); }  // compute: wait for products 3-5 of the previous pair
       fa_tmem_st16(t_row + COL_P + half * 32, pp0);
       fa_tmem_st16(t_row + COL_P + half * 32 + 16, pp1);
-      {
+      if (!(FA_TC_EXP & 2)) {
         unsigned char* dsrow = sm + OFF_DS + half * ATOM_BYTES + r * 128;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -493,6 +493,14 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
       // 16-byte chunk k of row r goes to position k ^ (r & 15): spreads the rows of a warp over
       // the banks; the accumulation buffer in global memory uses the same permutation
       unsigned char* strow = sm + OFF_DQ + r * 256;
+      if (FA_TC_EXP & 1) {
+        float a[32];
+        fa_tmem_ld32(t_dq, a);
+        fa_tmem_wait_ld();
+        fa_tc_fence_before();
+        fa_mbar_arrive(bar_addr(sb, BAR_DQFREE));
+        continue;
+      }
       {
         float a[32];
         fa_tmem_ld32(t_dq, a);

@@ -128,8 +128,15 @@ extern "C" __global__ void __launch_bounds__(fa_dec::NT) fa_decode_kernel(const 
 
     fa_round_acc<DT, WN / 8>(s);
     const bool ragged = n0 + WN > p.Skv;
+    const float sc2 = p.scale * FA_LOG2E;
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
+      // rows 8..15 of a row group hold no query when Sq <= 8 (+ 16 rg): nothing to do for them
+      if (rg * 16 + hh * 8 >= p.Sq) {
+#pragma unroll
+        for (int j = 0; j < WN / 8; ++j) s[j][hh * 2] = s[j][hh * 2 + 1] = 0.f;
+        continue;
+      }
       const int qi = rg * 16 + hh * 8 + (lane >> 2);
       float mx = FA_NEG_INF;
 #pragma unroll
@@ -137,16 +144,21 @@ extern "C" __global__ void __launch_bounds__(fa_dec::NT) fa_decode_kernel(const 
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const int kv = n0 + j * 8 + (lane & 3) * 2 + e;
-          float x = s[j][hh * 2 + e] * p.scale;
-#if FA_HAS_SCORE_MOD
-          x = fa_score_mod(x, gb, gh, qi, kv);
+          float x = s[j][hh * 2 + e];
+#if FA_HAS_SCORE_MOD && defined(FA_SCORE_AFFINE)
+          // affine score_mod: scale and log2(e) folded into one FMA
+          x = fmaf(x, fa_score_mul(0.f, gb, gh, qi, kv) * sc2, fa_score_add(0.f, gb, gh, qi, kv) * FA_LOG2E);
+#elif FA_HAS_SCORE_MOD
+          x = fa_score_mod(x * p.scale, gb, gh, qi, kv) * FA_LOG2E;
+#else
+          x *= sc2;
 #endif
           bool keep = true;
 #if FA_HAS_MASK_MOD
           if (!full) keep = fa_mask_mod(gb, gh, qi, kv);
 #endif
           if (ragged) keep = keep && (kv < p.Skv);
-          x = keep ? x * FA_LOG2E : FA_NEG_INF;
+          x = keep ? x : FA_NEG_INF;
           s[j][hh * 2 + e] = x;
           mx = fmaxf(mx, x);
         }

@@ -41,7 +41,7 @@ constexpr int NSTAGE = D == 64 ? 3 : 2;
 constexpr int Q_BYTES = 2 * ATOMS * ATOM_BYTES;
 constexpr int KV_STAGE = ATOMS * ATOM_BYTES;
 constexpr int MAXT = 256;                // kv tiles per row of the block grid (Skv <= 32768)
-constexpr int NBARS = 1 + 4 * NSTAGE + 6;
+constexpr int NBARS = 1 + 4 * NSTAGE + 12;
 constexpr int OFF_K = Q_BYTES;
 constexpr int OFF_V = OFF_K + NSTAGE * KV_STAGE;
 constexpr int OFF_BAR = OFF_V + NSTAGE * KV_STAGE;
@@ -52,6 +52,28 @@ constexpr int OFF_CLS = OFF_MODE + MAXT * 2;        // uchar cls[2][MAXT]
 constexpr int SMEM_BYTES = OFF_CLS + 2 * MAXT + 1024;  // + slack for the 1024-byte alignment
 constexpr int TMEM_COLS = 512;
 constexpr int COL_S = 0, COL_O = 256;
+// With D = 64 there is TMEM left for P next to S (columns 384..511): S of the next kv step can
+// then be produced while the softmax of the current step is still writing P.  With D = 128 the
+// 512 columns are taken by S and O, and P overwrites the S columns it was computed from.
+constexpr bool SEP_P = D == 64;
+constexpr int COL_P = 384;
+// Optional phase timing (tuning aid): with FA_TC_TRACE the status buffer must hold at least
+// 64 ints; slot k accumulates the SM cycles CTA (0,0,0) spent in phase k.
+#ifndef FA_TC_TRACE
+#define FA_TC_TRACE 0
+#endif
+#if FA_TC_TRACE
+#define FA_TRACE_DECL long long trace_t0 = clock64();
+#define FA_TRACE(slot)                                                                        \
+  do {                                                                                        \
+    const long long t1_ = clock64();                                                          \
+    if (trace_on) atomicAdd(p.status + (slot), (int)(t1_ - trace_t0));                        \
+    trace_t0 = t1_;                                                                           \
+  } while (0)
+#else
+#define FA_TRACE_DECL
+#define FA_TRACE(slot)
+#endif
 #ifndef FA_TC_HALF_EXP
 #define FA_TC_HALF_EXP 0
 #endif
@@ -69,7 +91,17 @@ static_assert(DT == FA_DT_F16 || DT == FA_DT_BF16, "16-bit inputs");
 __device__ __forceinline__ fa_u32 bar_addr(fa_u32 sbase, int i) { return sbase + OFF_BAR + i * 8; }
 constexpr int BAR_Q = 0;
 constexpr int BAR_KFULL = 1, BAR_KEMPTY = 1 + NSTAGE, BAR_VFULL = 1 + 2 * NSTAGE, BAR_VEMPTY = 1 + 3 * NSTAGE;
-constexpr int BAR_S = 1 + 4 * NSTAGE, BAR_P = BAR_S + 2, BAR_O = BAR_S + 4;
+constexpr int BAR_S = 1 + 4 * NSTAGE, BAR_P = BAR_S + 2, BAR_O = BAR_S + 4, BAR_SFREE = BAR_S + 6;
+// With separate P columns S is produced and released in two 64-column halves, so that the
+// first half of the next step is already being computed while the second is still being read.
+constexpr int BAR_S2 = BAR_S + 8, BAR_SFREE2 = BAR_S + 10;
+#ifndef FA_TC_AFFINE_RECOMP
+#define FA_TC_AFFINE_RECOMP 0  // measured slower than writing the modified scores back to TMEM
+#endif
+#ifndef FA_TC_SPLIT_S
+#define FA_TC_SPLIT_S 0  // measured slower on B200: twice the S instructions load the MMA issuer
+#endif
+constexpr bool SPLIT_S = SEP_P && FA_TC_SPLIT_S;
 
 // Pass-1 work on one 32-column chunk of a score row (columns C0 .. C0+31 of the kv tile that
 // starts at key n0).  C0 is a template parameter and n0 a multiple of 128, so the low bits of
@@ -78,7 +110,7 @@ struct RowMax {
   float a, b, c, d;
 };
 template <int C0>
-__device__ __forceinline__ void pass1_chunk(float (&v)[32], RowMax& mx, bool plain, bool ragged, int mode, int n0,
+__device__ __forceinline__ void pass1_chunk(float (&v)[32], RowMax& mx, bool plain, bool recomp, bool ragged, int mode, int n0,
                                             int qi, int gb, int gh, float scale, float sc2, int Skv) {
   if (plain) {
 #pragma unroll
@@ -121,13 +153,35 @@ __device__ __forceinline__ void pass1_chunk(float (&v)[32], RowMax& mx, bool pla
     }
     x0 = k0 ? x0 : FA_NEG_INF;
     x1 = k1 ? x1 : FA_NEG_INF;
-    v[e] = x0;
-    v[e + 1] = x1;
+    if (!recomp) {
+      v[e] = x0;
+      v[e + 1] = x1;
+    }
     if ((e & 6) == 0) mx.a = fa_max3(mx.a, x0, x1);
     else if ((e & 6) == 2) mx.b = fa_max3(mx.b, x0, x1);
     else if ((e & 6) == 4) mx.c = fa_max3(mx.c, x0, x1);
     else mx.d = fa_max3(mx.d, x0, x1);
   }
+}
+
+// Pass-2 work on one chunk for a cheap affine score_mod on an unmasked tile: the raw scores are
+// still in TMEM, the exponent is A * s + (B - m) with A and B evaluated again.
+template <int C0>
+__device__ __forceinline__ void pass2_chunk_affine(const float (&v)[32], fa_u32 (&pk)[16], float negm, fa_u64& sum_a,
+                                                   fa_u64& sum_b, int n0, int qi, int gb, int gh, float sc2) {
+#if FA_HAS_SCORE_MOD && defined(FA_SCORE_AFFINE)
+#pragma unroll
+  for (int e = 0; e < 16; ++e) {
+    const int kv0 = n0 | (C0 + 2 * e), kv1 = n0 | (C0 + 2 * e + 1);
+    const float a0 = fmaf(v[2 * e], fa_score_mul(0.f, gb, gh, qi, kv0) * sc2, fa_score_add(0.f, gb, gh, qi, kv0) * FA_LOG2E + negm);
+    const float a1 = fmaf(v[2 * e + 1], fa_score_mul(0.f, gb, gh, qi, kv1) * sc2, fa_score_add(0.f, gb, gh, qi, kv1) * FA_LOG2E + negm);
+    const float p0 = fa_ex2(a0), p1 = fa_ex2(a1);
+    pk[e] = fa_pack2<DT>(p0, p1);
+    const fa_u64 pf = fa_f2(p0, p1);
+    if (e & 1) sum_b = fa_add2(sum_b, pf);
+    else sum_a = fa_add2(sum_a, pf);
+  }
+#endif
 }
 
 // Pass-2 work on one chunk: p = 2^(x * cmul - m), packed to 16 bits, and the row-sum chains.
@@ -167,6 +221,9 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
   const int hk = h / (p.Hq / p.Hkv);
   const int gb = b + p.b_off, gh = h + p.h_off;
 
+#if FA_TC_TRACE
+  const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && p.status != nullptr;
+#endif
   volatile int* misc = (volatile int*)(sm + OFF_MISC);  // [0] tmem base, [1] abort, [2] nsteps
   short* sched_tile = (short*)(sm + OFF_SCHED);
   unsigned char* sched_mode = sm + OFF_MODE;
@@ -185,6 +242,9 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
       fa_mbar_init(bar_addr(sb, BAR_S + i), 1);
       fa_mbar_init(bar_addr(sb, BAR_P + i), 128);
       fa_mbar_init(bar_addr(sb, BAR_O + i), 1);
+      fa_mbar_init(bar_addr(sb, BAR_SFREE + i), 128);
+      fa_mbar_init(bar_addr(sb, BAR_S2 + i), 1);
+      fa_mbar_init(bar_addr(sb, BAR_SFREE2 + i), 128);
     }
     fa_mbar_init_fence();
     misc[1] = 0;
@@ -280,20 +340,25 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
       constexpr fa_u32 IDESC_S = fa_idesc(DT, BM, BN, 0, 0);
       constexpr fa_u32 IDESC_O = fa_idesc(DT, BM, D, 0, 1);
       bool ok = nsteps == 0 || fa_mbar_wait(bar_addr(sb, BAR_Q), 0, abort_flag);
-      fa_u32 cnt[2] = {0, 0};  // active steps seen so far per query tile
+      fa_u32 cnt[2] = {0, 0};  // PV products issued so far per query tile
+      fa_u32 nsi[2] = {0, 0};  // S products issued so far per query tile
       // Descriptors: constant high word; the low word (start address and MN-chunk distance in
       // 16-byte units) is stepped with one add per k-step.
       constexpr fa_u32 HI = fa_desc_hi_sw128();
       // S_i = Q_i K^T for step j into TMEM columns COL_S + 128 i
-      auto issue_s = [&](int i, int j) {
+      // (with SEP_P: one 64-column half, `half` = 0 / 1; otherwise all 128 columns)
+      constexpr fa_u32 IDESC_S64 = fa_idesc(DT, BM, 64, 0, 0);
+      auto issue_s = [&](int i, int j, int half) {
         const int s = j % NSTAGE;
-        const fa_u32 loQ = fa_desc_lo(sb + i * ATOMS * ATOM_BYTES, 16), loK = fa_desc_lo(sb + OFF_K + s * KV_STAGE, 16);
+        const fa_u32 loQ = fa_desc_lo(sb + i * ATOMS * ATOM_BYTES, 16);
+        const fa_u32 loK = fa_desc_lo(sb + OFF_K + s * KV_STAGE + (SPLIT_S ? half * 64 * 128 : 0), 16);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const fa_u32 koff = ((kk / 4) * ATOM_BYTES + (kk % 4) * 32) >> 4;
-          fa_mma_ss(tmem + COL_S + i * BN, fa_desc_make(loQ + koff, HI), fa_desc_make(loK + koff, HI), IDESC_S, kk > 0);
+          fa_mma_ss(tmem + COL_S + i * BN + (SPLIT_S ? half * 64 : 0), fa_desc_make(loQ + koff, HI), fa_desc_make(loK + koff, HI),
+                    SPLIT_S ? IDESC_S64 : IDESC_S, kk > 0);
         }
-        fa_mma_commit(bar_addr(sb, BAR_S + i));
+        fa_mma_commit(bar_addr(sb, (half ? BAR_S2 : BAR_S) + i));
       };
       // O_i += P_i V for step j (P_i: 16-bit, in the first 64 columns of S_i)
       auto issue_pv = [&](int i, int j, bool first) {
@@ -302,18 +367,23 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
         const fa_u32 acc = !first;
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk)
-          fa_mma_ts(tmem + COL_O + i * D, tmem + COL_S + i * BN + kk * 8, fa_desc_make(loV + kk * 128, HI), IDESC_O, acc | (kk > 0));
+          fa_mma_ts(tmem + COL_O + i * D, tmem + (SEP_P ? COL_P + i * 64 : COL_S + i * BN) + kk * 8, fa_desc_make(loV + kk * 128, HI), IDESC_O, acc | (kk > 0));
         fa_mma_commit(bar_addr(sb, BAR_O + i));
       };
       if (ok && nsteps > 0) {
         ok = fa_mbar_wait(bar_addr(sb, BAR_KFULL + 0), 0, abort_flag);
         if (ok) {
           fa_tc_fence_after();
-          if (sched_mode[0]) issue_s(0, 0);
-          if (sched_mode[1]) issue_s(1, 0);
+          for (int i = 0; i < 2; ++i)
+            if (sched_mode[i]) {
+              issue_s(i, 0, 0);
+              if (SPLIT_S) issue_s(i, 0, 1);
+              ++nsi[i];
+            }
           fa_mma_commit(bar_addr(sb, BAR_KEMPTY + 0));
         }
       }
+      FA_TRACE_DECL
       for (int j = 0; j < nsteps && ok; ++j) {
         const int s = j % NSTAGE;
         const fa_u32 ph = (fa_u32)((j / NSTAGE) & 1);
@@ -322,24 +392,49 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
         const fa_u32 ph1 = (fa_u32)(((j + 1) / NSTAGE) & 1);
         bool k_ready = false;
         ok = fa_mbar_wait(bar_addr(sb, BAR_VFULL + s), ph, abort_flag);
+        FA_TRACE(1);  // MMA: wait V
         for (int i = 0; i < 2 && ok; ++i) {
+          const bool next_s = more && sched_mode[2 * (j + 1) + i];
+          auto do_s = [&]() {
+            if (!k_ready) {
+              ok = fa_mbar_wait(bar_addr(sb, BAR_KFULL + s1), ph1, abort_flag);
+              if (!ok) return;
+              fa_tc_fence_after();
+              k_ready = true;
+              FA_TRACE(4);  // MMA: wait K
+            }
+            if (SEP_P) {
+              // each half as soon as the softmax warps have read the previous one (without
+              // SPLIT_S: the whole tile once its second half has been read)
+              for (int half = SPLIT_S ? 0 : 1; half < 2; ++half) {
+                if (nsi[i] > 0) {
+                  ok = fa_mbar_wait(bar_addr(sb, (half ? BAR_SFREE2 : BAR_SFREE) + i), (nsi[i] - 1) & 1u, abort_flag);
+                  if (!ok) return;
+                  fa_tc_fence_after();
+                  FA_TRACE(6);  // MMA: wait S read
+                }
+                issue_s(i, j + 1, SPLIT_S ? half : 0);
+              }
+            } else {
+              issue_s(i, j + 1, 0);
+            }
+            ++nsi[i];
+            FA_TRACE(5);  // MMA: issue S
+          };
+          if (SEP_P && next_s) do_s();  // S of the next step does not have to wait for P
+          if (!ok) break;
           if (sched_mode[2 * j + i]) {
             ok = fa_mbar_wait(bar_addr(sb, BAR_P + i), cnt[i] & 1u, abort_flag);
+            FA_TRACE(2);  // MMA: wait P
             if (!ok) break;
             fa_tc_fence_after();
             issue_pv(i, j, cnt[i] == 0);
             ++cnt[i];
+            FA_TRACE(3);  // MMA: issue PV
           }
           if (i == 1) fa_mma_commit(bar_addr(sb, BAR_VEMPTY + s));
-          if (more && sched_mode[2 * (j + 1) + i]) {
-            if (!k_ready) {
-              ok = fa_mbar_wait(bar_addr(sb, BAR_KFULL + s1), ph1, abort_flag);
-              if (!ok) break;
-              fa_tc_fence_after();
-              k_ready = true;
-            }
-            issue_s(i, j + 1);
-          }
+          if (!SEP_P && next_s) do_s();
+          if (!ok) break;
           if (i == 1 && more) fa_mma_commit(bar_addr(sb, BAR_KEMPTY + s1));
         }
       }
@@ -352,15 +447,18 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
     const int qi = m0 + i * BM + r;                // query index
     const fa_u32 t_s = tmem + ((fa_u32)lane_base << 16) + COL_S + i * BN;
     const fa_u32 t_o = tmem + ((fa_u32)lane_base << 16) + COL_O + i * D;
+    const fa_u32 t_p = SEP_P ? tmem + ((fa_u32)lane_base << 16) + COL_P + i * 64 : t_s;
     float m_ref = FA_NEG_INF, l = 0.f;
     fa_u32 cnt = 0;
     bool ok = true;
     const float sc2 = p.scale * FA_LOG2E;
+    FA_TRACE_DECL
     for (int j = 0; j < nsteps && ok; ++j) {
       const int mode = sched_mode[2 * j + i];
       if (mode == 0) continue;
       const int n0 = (int)sched_tile[j] * BN;
       ok = fa_mbar_wait_warp(bar_addr(sb, BAR_S + i), cnt & 1u, abort_flag);
+      if (warp == 0) { FA_TRACE(10); }  // softmax: wait S
       if (!ok) break;
       fa_tc_fence_after();
       const bool ragged = n0 + BN > p.Skv;
@@ -368,6 +466,11 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
       const bool plain = false;
 #else
       const bool plain = !ragged && sc2 > 0.f;
+#endif
+#if FA_TC_AFFINE_RECOMP && FA_HAS_SCORE_MOD && defined(FA_SCORE_AFFINE_CHEAP) && !FA_ROUND_SCORES
+      const bool recomp = !ragged && !(FA_HAS_MASK_MOD && mode == 1);
+#else
+      const bool recomp = false;
 #endif
       // ---- pass 1: row maximum.  The plain path (no mods, full tile) takes it over the raw
       // scores; otherwise the scores are scaled / modded / masked, converted to log2 units
@@ -377,13 +480,17 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
       {
         float va[32], vb[32];
 #define FA_P1(V, C0)                                                                                   \
-  pass1_chunk<C0>(V, rm, plain, ragged, mode, n0, qi, gb, gh, p.scale, sc2, p.Skv);                     \
-  if (!plain) fa_tmem_st32(t_s + C0, V);
+  pass1_chunk<C0>(V, rm, plain, recomp, ragged, mode, n0, qi, gb, gh, p.scale, sc2, p.Skv);             \
+  if (!plain && !recomp) fa_tmem_st32(t_s + C0, V);
         fa_tmem_ld32(t_s, va);
         fa_tmem_wait_ld();
         fa_tmem_ld32(t_s + 32, vb);
         FA_P1(va, 0)
         fa_tmem_wait_ld();
+        if (SPLIT_S) {
+          ok = fa_mbar_wait_warp(bar_addr(sb, BAR_S2 + i), cnt & 1u, abort_flag);
+          fa_tc_fence_after();
+        }
         fa_tmem_ld32(t_s + 64, va);
         FA_P1(vb, 32)
         fa_tmem_wait_ld();
@@ -392,8 +499,9 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
         fa_tmem_wait_ld();
         FA_P1(vb, 96)
 #undef FA_P1
-        if (!plain) fa_tmem_wait_st();
+        if (!plain && !recomp) fa_tmem_wait_st();
       }
+      if (warp == 0) { FA_TRACE(11); }  // softmax: pass 1
       float mx = fmaxf(fmaxf(rm.a, rm.b), fmaxf(rm.c, rm.d));
       if (plain) mx *= sc2;
       // running maximum, raised lazily
@@ -433,25 +541,45 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
       const float cm = plain ? sc2 : 1.f;
       const fa_u64 cmul = fa_f2(cm, cm);
       fa_u64 sum_a = fa_f2(0.f, 0.f), sum_b = fa_f2(0.f, 0.f);
+      if (SEP_P && cnt > 0) {
+        // P has its own columns: the previous PV product must be done reading them
+        ok = fa_mbar_wait_warp(bar_addr(sb, BAR_O + i), (cnt - 1) & 1u, abort_flag);
+        if (!ok) break;
+        fa_tc_fence_after();
+      }
       {
         float va[32], vb[32];
         fa_u32 pk[16];
         fa_tmem_ld32(t_s, va);
         fa_tmem_wait_ld();
         fa_tmem_ld32(t_s + 32, vb);
-        pass2_chunk(va, pk, cmul, negm, sum_a, sum_b);
-        fa_tmem_st16(t_s, pk);
+#define FA_P2(V, C0)                                                                           \
+  if (recomp) pass2_chunk_affine<C0>(V, pk, -m_use, sum_a, sum_b, n0, qi, gb, gh, sc2);         \
+  else pass2_chunk(V, pk, cmul, negm, sum_a, sum_b);
+        FA_P2(va, 0)
+        fa_tmem_st16(t_p, pk);
         fa_tmem_wait_ld();
+        if (SPLIT_S) {
+          // columns 0..63 of this step's scores are in registers
+          fa_tc_fence_before();
+          fa_mbar_arrive(bar_addr(sb, BAR_SFREE + i));
+        }
         fa_tmem_ld32(t_s + 64, va);
-        pass2_chunk(vb, pk, cmul, negm, sum_a, sum_b);
-        fa_tmem_st16(t_s + 16, pk);
+        FA_P2(vb, 32)
+        fa_tmem_st16(t_p + 16, pk);
         fa_tmem_wait_ld();
         fa_tmem_ld32(t_s + 96, vb);
-        pass2_chunk(va, pk, cmul, negm, sum_a, sum_b);
-        fa_tmem_st16(t_s + 32, pk);
+        FA_P2(va, 64)
+        fa_tmem_st16(t_p + 32, pk);
         fa_tmem_wait_ld();
-        pass2_chunk(vb, pk, cmul, negm, sum_a, sum_b);
-        fa_tmem_st16(t_s + 48, pk);
+        if (SEP_P) {
+          // every score of this step is in registers: columns 64..127 may be overwritten too
+          fa_tc_fence_before();
+          fa_mbar_arrive(bar_addr(sb, BAR_SFREE2 + i));
+        }
+        FA_P2(vb, 96)
+        fa_tmem_st16(t_p + 48, pk);
+#undef FA_P2
       }
       float sum;
       {
@@ -464,6 +592,7 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
       fa_tc_fence_before();
       fa_mbar_arrive(bar_addr(sb, BAR_P + i));
       ++cnt;
+      if (warp == 0) { FA_TRACE(12); }  // softmax: pass 2 + stores
     }
     // ---- epilogue: O / l and the logsumexp of this thread's row ---------------------------
     if (ok && cnt > 0) ok = fa_mbar_wait_warp(bar_addr(sb, BAR_O + i), (cnt - 1) & 1u, abort_flag);

@@ -43,23 +43,36 @@ __device__ __forceinline__ fa_u64 fa_globaltimer() {
 // (*abort != 0).  Returns false on failure; the caller then leaves its loop and the kernel
 // tears down normally (no trap, the context stays usable, the host sees the status word).
 #define FA_WAIT_LIMIT_NS 2000000000ull
-__device__ __forceinline__ bool fa_mbar_wait(fa_u32 bar, fa_u32 parity, volatile int* abort_flag) {
+#ifndef FA_WAIT_SLEEP_NS
+#define FA_WAIT_SLEEP_NS 40
+#endif
+// SLEEP: back off between polls so that waiting warps leave the issue slots of their scheduler
+// to the warps that have work (the MMA issuer polls without sleeping).
+template <bool SLEEP>
+__device__ __forceinline__ bool fa_mbar_wait_t(fa_u32 bar, fa_u32 parity, volatile int* abort_flag) {
   if (fa_mbar_try(bar, parity)) return true;
-  const fa_u64 t0 = fa_globaltimer();
-  while (true) {
+  fa_u64 t0 = 0;
+  for (fa_u32 it = 0;; ++it) {
     if (fa_mbar_try(bar, parity)) return true;
-    if (*abort_flag != 0) return false;
-    if (fa_globaltimer() - t0 > FA_WAIT_LIMIT_NS) {
-      *abort_flag = 1;
-      return false;
+    if (SLEEP) __nanosleep(FA_WAIT_SLEEP_NS);
+    if ((it & 63u) == 63u) {  // the expensive checks only now and then
+      if (*abort_flag != 0) return false;
+      const fa_u64 t = fa_globaltimer();
+      if (t0 == 0) t0 = t;
+      if (t - t0 > FA_WAIT_LIMIT_NS) {
+        *abort_flag = 1;
+        return false;
+      }
     }
   }
 }
-
+__device__ __forceinline__ bool fa_mbar_wait(fa_u32 bar, fa_u32 parity, volatile int* abort_flag) {
+  return fa_mbar_wait_t<false>(bar, parity, abort_flag);
+}
 // warp-uniform variant: every lane waits, the warp agrees on the outcome (needed before
 // warp-collective tcgen05 instructions)
 __device__ __forceinline__ bool fa_mbar_wait_warp(fa_u32 bar, fa_u32 parity, volatile int* abort_flag) {
-  const bool ok = fa_mbar_wait(bar, parity, abort_flag);
+  const bool ok = fa_mbar_wait_t<true>(bar, parity, abort_flag);
   return __all_sync(0xffffffffu, ok);
 }
 
@@ -71,6 +84,11 @@ __device__ __forceinline__ void fa_tma_load_4d(fa_u32 dst, const FaTensorMap* ma
       "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
       ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
+}
+// 1-d bulk copy global -> shared (16-byte aligned addresses, size a multiple of 16)
+__device__ __forceinline__ void fa_bulk_load(fa_u32 dst, const void* src, fa_u32 bytes, fa_u32 bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
 __device__ __forceinline__ void fa_tma_prefetch_desc(const FaTensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");

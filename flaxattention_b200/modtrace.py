@@ -1194,6 +1194,11 @@ class ModSet:
             if self.affine is not None:
                 # score_mod(s) == fa_score_mul(...) * s + fa_score_add(...); both ignore `score`
                 parts.append("#define FA_SCORE_AFFINE 1\n")
+                n_ops = sum(1 for t in self.affine for e in _topo(t.root) if e.args)
+                if n_ops <= 10:
+                    # cheap enough to evaluate twice (row maximum pass and exponent pass) instead of
+                    # writing the modified scores back between the passes
+                    parts.append("#define FA_SCORE_AFFINE_CHEAP 1\n")
                 parts.append(to_cuda(self.affine[0], "fa_score_mul"))
                 parts.append(to_cuda(self.affine[1], "fa_score_add"))
         else:
