@@ -19,7 +19,8 @@
 // converts it afterwards).  dK and dV are written once at the end.
 //
 // Warp roles (16 warps): 0-3 and 4-7 compute (q columns 0-63 / 64-127 of the pair tile),
-// 8-11 dQ drain, 12 TMA producer + lse/delta staging, 13 MMA issuer + TMEM owner.
+// 8-11 dQ drain, 12 TMA producer, 13 MMA issuer A (products 1-2, TMEM owner), 14 MMA issuer B
+// (products 3-5).
 // S^T/dP^T of pair n+1 are issued as soon as the compute warps hold pair n in registers, so
 // the tensor core runs ahead of the element-wise work.
 //
@@ -70,7 +71,7 @@ constexpr int ATOM_BYTES = 128 * 128;    // 128 rows x 128 bytes
 constexpr int NSTAGE = 3;
 constexpr int MAXP = 512;                // (head, q tile) pairs per CTA
 constexpr int NT = 512;
-constexpr int WARP_PRODUCER = 12, WARP_MMA = 13;
+constexpr int WARP_PRODUCER = 12, WARP_MMA = 13, WARP_MMA_B = 14;
 constexpr int REGS_COMPUTE = 200, REGS_OTHER = 56;
 
 // shared memory map (from a 1024-byte aligned base)
@@ -193,7 +194,7 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
     fa_mbar_init(bar_addr(sb, BAR_KV), 1);
     for (int s = 0; s < NSTAGE; ++s) {
       fa_mbar_init(bar_addr(sb, BAR_QFULL + s), 1);
-      fa_mbar_init(bar_addr(sb, BAR_QEMPTY + s), 1);
+      fa_mbar_init(bar_addr(sb, BAR_QEMPTY + s), 2);  // one arrival from each MMA issuer
     }
     fa_mbar_init(bar_addr(sb, BAR_SFULL), 1);
     fa_mbar_init(bar_addr(sb, BAR_SFREE), 256);
@@ -283,20 +284,23 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
       }
     }
   } else if (warp == WARP_MMA) {
-    // ================================ MMA issuer ==============================================
+    // ================================ MMA issuer A: products 1-2 ===============================
+    // (two issuing warps, so that the waits of one overlap the issue of the other; warp A also
+    //  owns the TMEM allocation)
     if (lane == 0 && npairs > 0) {
       constexpr fa_u32 IDESC_KK = fa_idesc(DT, 128, 128, 0, 0);  // A, B K-major, N = 128
-      constexpr fa_u32 IDESC_TN = fa_idesc(DT, 128, D, 0, 1);    // A K-major (TMEM or smem), B MN-major, N = 64
-      constexpr fa_u32 IDESC_NN = fa_idesc(DT, 128, D, 1, 1);    // A, B MN-major
-      bool ok = fa_mbar_wait(bar_addr(sb, BAR_KV), 0, abort_flag);
-      // descriptors: the high word (stride, version, swizzle) is fixed; the low word holds the
-      // start address and the MN-chunk distance (16-byte units) and is stepped with one add
       constexpr fa_u32 HI = fa_desc_hi_sw128();
       const fa_u32 loK_k = fa_desc_lo(sb + OFF_K, 16), loV_k = fa_desc_lo(sb + OFF_V, 16);
-      const fa_u32 loK_mn = fa_desc_lo(sb + OFF_K, ATOM_BYTES);
-      const fa_u32 loDS_k = fa_desc_lo(sb + OFF_DS, 16), loDS_mn = fa_desc_lo(sb + OFF_DS, ATOM_BYTES);
-      auto issue_s_dp = [&](int n) {
+      bool ok = fa_mbar_wait(bar_addr(sb, BAR_KV), 0, abort_flag);
+      FA_TRACE_DECL
+      for (int n = 0; n < npairs && ok; ++n) {
         const int s = n % NSTAGE;
+        ok = fa_mbar_wait(bar_addr(sb, BAR_QFULL + s), (fa_u32)((n / NSTAGE) & 1), abort_flag);
+        FA_TRACE(1);   // MMA A: wait for Q/dO
+        if (ok && n > 0) ok = fa_mbar_wait(bar_addr(sb, BAR_SFREE), (fa_u32)((n - 1) & 1), abort_flag);
+        FA_TRACE(2);   // MMA A: wait for S^T/dP^T of the previous pair to be read
+        if (!ok) break;
+        fa_tc_fence_after();
         const fa_u32 loQ = fa_desc_lo(sb + OFF_Q + s * ATOM_BYTES, 16), loDO = fa_desc_lo(sb + OFF_DO + s * ATOM_BYTES, 16);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
@@ -305,30 +309,26 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
         for (int kk = 0; kk < D / 16; ++kk)
           fa_mma_ss(tmem + COL_DP, fa_desc_make(loV_k + kk * 2, HI), fa_desc_make(loDO + kk * 2, HI), IDESC_KK, kk > 0);
         fa_mma_commit(bar_addr(sb, BAR_SFULL));
-      };
-      if (ok) ok = fa_mbar_wait(bar_addr(sb, BAR_QFULL + 0), 0, abort_flag);
-      if (ok) {
-        fa_tc_fence_after();
-        issue_s_dp(0);
+        fa_mma_commit(bar_addr(sb, BAR_QEMPTY + s));  // first of the two arrivals that free the stage
+        FA_TRACE(3);   // MMA A: issue products 1-2
       }
+    }
+  } else if (warp == WARP_MMA_B) {
+    // ================================ MMA issuer B: products 3-5 ===============================
+    if (lane == 0 && npairs > 0) {
+      constexpr fa_u32 IDESC_TN = fa_idesc(DT, 128, D, 0, 1);    // A K-major (TMEM or smem), B MN-major, N = 64
+      constexpr fa_u32 IDESC_NN = fa_idesc(DT, 128, D, 1, 1);    // A, B MN-major
+      constexpr fa_u32 HI = fa_desc_hi_sw128();
+      const fa_u32 loK_mn = fa_desc_lo(sb + OFF_K, ATOM_BYTES);
+      const fa_u32 loDS_k = fa_desc_lo(sb + OFF_DS, 16), loDS_mn = fa_desc_lo(sb + OFF_DS, ATOM_BYTES);
+      bool ok = fa_mbar_wait(bar_addr(sb, BAR_KV), 0, abort_flag);
       FA_TRACE_DECL
       for (int n = 0; n < npairs && ok; ++n) {
         const int s = n % NSTAGE;
-        if (n + 1 < npairs) {
-          const int s1 = (n + 1) % NSTAGE;
-          ok = fa_mbar_wait(bar_addr(sb, BAR_QFULL + s1), (fa_u32)(((n + 1) / NSTAGE) & 1), abort_flag);
-          FA_TRACE(1);   // MMA: wait for Q/dO of the next pair
-          if (ok) ok = fa_mbar_wait(bar_addr(sb, BAR_SFREE), (fa_u32)(n & 1), abort_flag);
-          FA_TRACE(2);   // MMA: wait for S^T/dP^T to be read
-          if (!ok) break;
-          fa_tc_fence_after();
-          issue_s_dp(n + 1);
-          FA_TRACE(3);   // MMA: issue products 1-2
-        }
         ok = fa_mbar_wait(bar_addr(sb, BAR_PREADY), (fa_u32)(n & 1), abort_flag);
-        FA_TRACE(4);     // MMA: wait for P^T / dS^T
+        FA_TRACE(4);     // MMA B: wait for P^T / dS^T
         if (ok && n > 0) ok = fa_mbar_wait(bar_addr(sb, BAR_DQFREE), (fa_u32)((n - 1) & 1), abort_flag);
-        FA_TRACE(5);     // MMA: wait for the dQ drain
+        FA_TRACE(5);     // MMA B: wait for the dQ drain
         if (!ok) break;
         fa_tc_fence_after();
         {
@@ -339,13 +339,13 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
 #pragma unroll
           for (int kk = 0; kk < BT / 16; ++kk)
             fa_mma_ts(tmem + COL_DV, tmem + COL_P + kk * 8, fa_desc_make(loDO_mn + kk * 128, HI), IDESC_TN, acc | (kk > 0));
-          FA_TRACE(7);   // MMA: issue product 3
+          FA_TRACE(7);   // MMA B: issue product 3
           // 4. dK += dS^T Q     (A = dS^T K-major: k-step kk is 32 bytes into atom kk / 4)
 #pragma unroll
           for (int kk = 0; kk < BT / 16; ++kk)
             fa_mma_ss(tmem + COL_DK, fa_desc_make(loDS_k + (kk >> 2) * (ATOM_BYTES >> 4) + (kk & 3) * 2, HI),
                       fa_desc_make(loQ_mn + kk * 128, HI), IDESC_TN, acc | (kk > 0));
-          FA_TRACE(8);   // MMA: issue product 4
+          FA_TRACE(8);   // MMA B: issue product 4
           // 5. dQ = dS K        (A = dS^T read MN-major: M chunks of 64 q one atom apart; K = 128 kv rows)
 #pragma unroll
           for (int kk = 0; kk < BT / 16; ++kk)
@@ -353,9 +353,9 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
         }
         fa_mma_commit(bar_addr(sb, BAR_PFREE));
         fa_mma_commit(bar_addr(sb, BAR_DQFULL));
-        fa_mma_commit(bar_addr(sb, BAR_QEMPTY + s));
+        fa_mma_commit(bar_addr(sb, BAR_QEMPTY + s));  // second arrival: the stage is free
         if (n + 1 == npairs) fa_mma_commit(bar_addr(sb, BAR_FINAL));
-        FA_TRACE(6);     // MMA: issue products 3-5
+        FA_TRACE(6);     // MMA B: issue product 5 + commits
       }
     }
   } else if (warp < 8) {

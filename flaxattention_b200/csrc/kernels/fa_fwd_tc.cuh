@@ -81,7 +81,7 @@ constexpr int COL_P = 384;
 #define FA_TC_SETMAXNREG 0
 #endif
 constexpr int NT = 384;
-constexpr int WARP_PRODUCER = 8, WARP_MMA = 9;
+constexpr int WARP_PRODUCER = 8, WARP_MMA = 9, WARP_MMA_B = 10;
 constexpr int REGS_SOFTMAX = 200, REGS_OTHER = 112;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
 
@@ -332,6 +332,69 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
         fa_mbar_expect_tx(bar_addr(sb, BAR_VFULL + s), KV_STAGE);
         for (int a = 0; a < ATOMS; ++a)
           fa_tma_load_4d(sb + OFF_V + s * KV_STAGE + a * ATOM_BYTES, &P.tv, bar_addr(sb, BAR_VFULL + s), a * 64, n0, hk, b);
+      }
+    }
+  } else if (SEP_P && (warp == WARP_MMA || warp == WARP_MMA_B)) {
+    // ============ two MMA issuers (D = 64): warp A issues the S products, warp B the PV products ====
+    // With P in its own TMEM columns the two streams only meet through the softmax warps, so each
+    // issuer waits on its own barriers and the waits of one overlap the issue of the other.
+    if (lane == 0 && nsteps > 0) {
+      constexpr fa_u32 HI = fa_desc_hi_sw128();
+      if (warp == WARP_MMA) {
+        constexpr fa_u32 IDESC_S = fa_idesc(DT, BM, BN, 0, 0);
+        bool ok = fa_mbar_wait(bar_addr(sb, BAR_Q), 0, abort_flag);
+        fa_u32 nsi[2] = {0, 0};
+        FA_TRACE_DECL
+        for (int j = 0; j < nsteps && ok; ++j) {
+          const int s = j % NSTAGE;
+          ok = fa_mbar_wait(bar_addr(sb, BAR_KFULL + s), (fa_u32)((j / NSTAGE) & 1), abort_flag);
+          FA_TRACE(4);  // MMA A: wait K
+          for (int i = 0; i < 2 && ok; ++i) {
+            if (!sched_mode[2 * j + i]) continue;
+            if (nsi[i] > 0) {
+              ok = fa_mbar_wait(bar_addr(sb, BAR_SFREE2 + i), (nsi[i] - 1) & 1u, abort_flag);
+              FA_TRACE(6);  // MMA A: wait for the previous S of the tile to be read
+              if (!ok) break;
+            }
+            fa_tc_fence_after();
+            const fa_u32 loQ = fa_desc_lo(sb + i * ATOMS * ATOM_BYTES, 16), loK = fa_desc_lo(sb + OFF_K + s * KV_STAGE, 16);
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+              const fa_u32 koff = ((kk / 4) * ATOM_BYTES + (kk % 4) * 32) >> 4;
+              fa_mma_ss(tmem + COL_S + i * BN, fa_desc_make(loQ + koff, HI), fa_desc_make(loK + koff, HI), IDESC_S, kk > 0);
+            }
+            fa_mma_commit(bar_addr(sb, BAR_S + i));
+            ++nsi[i];
+            FA_TRACE(5);  // MMA A: issue S
+          }
+          fa_mma_commit(bar_addr(sb, BAR_KEMPTY + s));
+        }
+      } else {
+        constexpr fa_u32 IDESC_O = fa_idesc(DT, BM, D, 0, 1);
+        bool ok = true;
+        fa_u32 cnt[2] = {0, 0};
+        FA_TRACE_DECL
+        for (int j = 0; j < nsteps && ok; ++j) {
+          const int s = j % NSTAGE;
+          ok = fa_mbar_wait(bar_addr(sb, BAR_VFULL + s), (fa_u32)((j / NSTAGE) & 1), abort_flag);
+          FA_TRACE(1);  // MMA B: wait V
+          for (int i = 0; i < 2 && ok; ++i) {
+            if (!sched_mode[2 * j + i]) continue;
+            ok = fa_mbar_wait(bar_addr(sb, BAR_P + i), cnt[i] & 1u, abort_flag);
+            FA_TRACE(2);  // MMA B: wait P
+            if (!ok) break;
+            fa_tc_fence_after();
+            const fa_u32 loV = fa_desc_lo(sb + OFF_V + s * KV_STAGE, ATOM_BYTES);
+            const fa_u32 acc = cnt[i] > 0;
+#pragma unroll
+            for (int kk = 0; kk < BN / 16; ++kk)
+              fa_mma_ts(tmem + COL_O + i * D, tmem + COL_P + i * 64 + kk * 8, fa_desc_make(loV + kk * 128, HI), IDESC_O, acc | (kk > 0));
+            fa_mma_commit(bar_addr(sb, BAR_O + i));
+            ++cnt[i];
+            FA_TRACE(3);  // MMA B: issue PV
+          }
+          fa_mma_commit(bar_addr(sb, BAR_VEMPTY + s));
+        }
       }
     }
   } else if (warp == WARP_MMA) {
