@@ -143,7 +143,7 @@ __device__ __forceinline__ void chunk(const float (&s)[32], const float (&dp)[32
 #endif
 #if FA_HAS_SCORE_MOD && defined(FA_SCORE_AFFINE)
       g = fa_score_mul(0.f, gb, gh, qi, kv);
-      x = fmaf(x, g * sc2, fa_score_add(0.f, gb, gh, qi, kv) * FA_LOG2E + nlu);
+      x = fmaf(x, g * sc2, fa_score_add2(0.f, gb, gh, qi, kv) + nlu);
 #elif FA_HAS_SCORE_MOD
       g = fa_score_mod_grad(x * scale, gb, gh, qi, kv);
       x = fa_score_mod(x * scale, gb, gh, qi, kv) * FA_LOG2E + nlu;

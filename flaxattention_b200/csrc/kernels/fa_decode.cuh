@@ -147,7 +147,7 @@ extern "C" __global__ void __launch_bounds__(fa_dec::NT) fa_decode_kernel(const 
           float x = s[j][hh * 2 + e];
 #if FA_HAS_SCORE_MOD && defined(FA_SCORE_AFFINE)
           // affine score_mod: scale and log2(e) folded into one FMA
-          x = fmaf(x, fa_score_mul(0.f, gb, gh, qi, kv) * sc2, fa_score_add(0.f, gb, gh, qi, kv) * FA_LOG2E);
+          x = fmaf(x, fa_score_mul(0.f, gb, gh, qi, kv) * sc2, fa_score_add2(0.f, gb, gh, qi, kv));
 #elif FA_HAS_SCORE_MOD
           x = fa_score_mod(x * p.scale, gb, gh, qi, kv) * FA_LOG2E;
 #else

@@ -131,8 +131,8 @@ __device__ __forceinline__ void pass1_chunk(float (&v)[32], RowMax& mx, bool pla
     fa_round2<DT>(x0, x1);
 #endif
 #if FA_HAS_SCORE_MOD && defined(FA_SCORE_AFFINE)
-    x0 = fmaf(x0, fa_score_mul(0.f, gb, gh, qi, kv0) * sc2, fa_score_add(0.f, gb, gh, qi, kv0) * FA_LOG2E);
-    x1 = fmaf(x1, fa_score_mul(0.f, gb, gh, qi, kv1) * sc2, fa_score_add(0.f, gb, gh, qi, kv1) * FA_LOG2E);
+    x0 = fmaf(x0, fa_score_mul(0.f, gb, gh, qi, kv0) * sc2, fa_score_add2(0.f, gb, gh, qi, kv0));
+    x1 = fmaf(x1, fa_score_mul(0.f, gb, gh, qi, kv1) * sc2, fa_score_add2(0.f, gb, gh, qi, kv1));
 #elif FA_HAS_SCORE_MOD
     x0 = fa_score_mod(x0 * scale, gb, gh, qi, kv0) * FA_LOG2E;
     x1 = fa_score_mod(x1 * scale, gb, gh, qi, kv1) * FA_LOG2E;
@@ -173,8 +173,8 @@ __device__ __forceinline__ void pass2_chunk_affine(const float (&v)[32], fa_u32 
 #pragma unroll
   for (int e = 0; e < 16; ++e) {
     const int kv0 = n0 | (C0 + 2 * e), kv1 = n0 | (C0 + 2 * e + 1);
-    const float a0 = fmaf(v[2 * e], fa_score_mul(0.f, gb, gh, qi, kv0) * sc2, fa_score_add(0.f, gb, gh, qi, kv0) * FA_LOG2E + negm);
-    const float a1 = fmaf(v[2 * e + 1], fa_score_mul(0.f, gb, gh, qi, kv1) * sc2, fa_score_add(0.f, gb, gh, qi, kv1) * FA_LOG2E + negm);
+    const float a0 = fmaf(v[2 * e], fa_score_mul(0.f, gb, gh, qi, kv0) * sc2, fa_score_add2(0.f, gb, gh, qi, kv0) + negm);
+    const float a1 = fmaf(v[2 * e + 1], fa_score_mul(0.f, gb, gh, qi, kv1) * sc2, fa_score_add2(0.f, gb, gh, qi, kv1) + negm);
     const float p0 = fa_ex2(a0), p1 = fa_ex2(a1);
     pk[e] = fa_pack2<DT>(p0, p1);
     const fa_u64 pf = fa_f2(p0, p1);

@@ -101,6 +101,16 @@ def _wrap_i32(v: int) -> int:
 _B = _Builder()
 
 
+def _depends_on_leaves(e: Expr, leaves, memo=None) -> bool:
+    if memo is None:
+        memo = {}
+    r = memo.get(id(e))
+    if r is None:
+        r = e.op in leaves or any(_depends_on_leaves(a, leaves, memo) for a in e.args)
+        memo[id(e)] = r
+    return r
+
+
 def _is_const(e: Expr, v=None) -> bool:
     if e.op != "const":
         return False
@@ -262,6 +272,14 @@ def binary(op: str, a: Expr, b: Expr) -> Expr:
         if _is_const(b, 0):
             return a
     elif op == "mul":
+        if t == F32:
+            # (x * y) * c -> x * (y * c) when y does not vary along a score row (no score, no kv):
+            # the kernels can then hoist y * c out of their per-element loops
+            for u, c in ((a, b), (b, a)):
+                if c.op == "const" and u.op == "mul" and u.dtype == F32:
+                    for x, y in ((u.args[0], u.args[1]), (u.args[1], u.args[0])):
+                        if y.op != "const" and not _depends_on_leaves(y, ("score", "kv")) and _depends_on_leaves(x, ("score", "kv")):
+                            return binary("mul", x, binary("mul", y, c))
         if _is_const(a, 1):
             return b
         if _is_const(b, 1):
@@ -948,6 +966,50 @@ def _topo(root: Expr) -> List[Expr]:
     return order
 
 
+import os as _os
+
+_MAGIC_I2F = _os.environ.get("FLAXATTN_MAGIC_I2F", "0") == "1"
+_IDX_BOUND = 1 << 21  # q, kv, b, h are taken to lie in [0, 2^21): sequences of up to 2M tokens
+
+
+def _int_range(e: Expr, memo: Dict[int, Optional[Tuple[int, int]]]) -> Optional[Tuple[int, int]]:
+    """Conservative value range of an int32 expression, or None when unknown."""
+    got = memo.get(id(e), 0)
+    if got != 0:
+        return got
+    r = None
+    if e.dtype == I32:
+        if e.op == "const":
+            r = (e.value, e.value)
+        elif e.op in ("q", "kv", "b", "h"):
+            r = (0, _IDX_BOUND - 1)
+        elif e.op in ("add", "sub"):
+            a, b = _int_range(e.args[0], memo), _int_range(e.args[1], memo)
+            if a and b:
+                r = (a[0] + b[0], a[1] + b[1]) if e.op == "add" else (a[0] - b[1], a[1] - b[0])
+        elif e.op == "neg":
+            a = _int_range(e.args[0], memo)
+            if a:
+                r = (-a[1], -a[0])
+        elif e.op == "and" and (_is_bit(e) or (e.args[1].op == "const" and e.args[1].value >= 0)):
+            r = (0, 1) if _is_bit(e) else (0, e.args[1].value)
+        elif e.op in ("xor", "or") and _is_bit(e):
+            r = (0, 1)
+        elif e.op == "cast_i32" and e.args[0].dtype == B1:
+            r = (0, 1)
+        elif e.op in ("min", "max"):
+            a, b = _int_range(e.args[0], memo), _int_range(e.args[1], memo)
+            if a and b:
+                f = min if e.op == "min" else max
+                r = (f(a[0], b[0]), f(a[1], b[1]))
+        elif e.op == "abs":
+            a = _int_range(e.args[0], memo)
+            if a:
+                r = (0, max(abs(a[0]), abs(a[1])))
+    memo[id(e)] = r
+    return r
+
+
 _CTYPE = {I32: "int", F32: "float", B1: "bool"}
 
 
@@ -978,6 +1040,7 @@ def to_cuda(mod: TracedMod, name: str) -> str:
     derivative), ``bool name(int b, int h, int q, int kv)`` for a mask mod."""
     lines: List[str] = []
     names: Dict[int, str] = {}
+    ranges: Dict[int, Optional[Tuple[int, int]]] = {}
     n = 0
     for e in _topo(mod.root):
         if e.op in _LEAVES:
@@ -1045,7 +1108,17 @@ def to_cuda(mod: TracedMod, name: str) -> str:
         elif op == "select":
             rhs = f"({a[0]} ? {a[1]} : {a[2]})"
         elif op == "cast_f32":
-            rhs = f"(float)({a[0]})" if e.args[0].dtype == I32 else f"({a[0]} ? 1.0f : 0.0f)"
+            if e.args[0].dtype == I32:
+                rg = _int_range(e.args[0], ranges)
+                if _MAGIC_I2F and rg is not None and -(1 << 22) < rg[0] and rg[1] < (1 << 22):
+                    # exact int -> float for |x| < 2^22 with an integer add and a float subtract
+                    # (1.5 * 2^23 has the integer x in its low mantissa bits): keeps the
+                    # conversion off the special-function unit the softmax exponentials need
+                    rhs = f"(__int_as_float(0x4B400000 + {a[0]}) - 12582912.0f)"
+                else:
+                    rhs = f"(float)({a[0]})"
+            else:
+                rhs = f"({a[0]} ? 1.0f : 0.0f)"
         elif op == "cast_i32":
             rhs = f"(int)({a[0]})" if e.args[0].dtype == F32 else f"({a[0]} ? 1 : 0)"
         elif op == "cast_b1":
@@ -1201,6 +1274,9 @@ class ModSet:
                     parts.append("#define FA_SCORE_AFFINE_CHEAP 1\n")
                 parts.append(to_cuda(self.affine[0], "fa_score_mul"))
                 parts.append(to_cuda(self.affine[1], "fa_score_add"))
+                # B already multiplied by log2(e), with the constant folded into row-invariant factors
+                b2 = TracedMod("score", binary("mul", self.affine[1].root, _B.const(math.log2(math.e), F32)))
+                parts.append(to_cuda(b2, "fa_score_add2"))
         else:
             self.grad = None
             parts.append(
