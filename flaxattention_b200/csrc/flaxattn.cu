@@ -541,8 +541,9 @@ __global__ void fa_bwd_prep_kernel(FaTensor o, FaTensor dout, const float* __res
   }
 }
 
-// dq = scale * dq_acc for the tcgen05 backward: the fp32 accumulation buffer is
-// [B, Hq, sq_pad, 64] with the sixteen 16-byte chunks of a row stored at position k ^ (q & 15).
+// dq = scale * dq_acc for the tcgen05 backward.  The fp32 accumulation buffer holds, per
+// (b, h, 128-row q tile), two [128 rows][32 columns] blocks (columns 0-31, then 32-63), and the
+// eight 16-byte chunks of a block row r sit at position k ^ (r & 7).
 template <int DT>
 __global__ void fa_dq_convert_kernel(const float* __restrict__ acc, FaTensor dq, int Hq, int Sq, int sq_pad, float scale,
                                      long long n_chunks) {
@@ -553,9 +554,10 @@ __global__ void fa_dq_convert_kernel(const float* __restrict__ acc, FaTensor dq,
   const long long bh = row / Sq;
   const int q = (int)(row - bh * Sq);
   const int b = (int)(bh / Hq), h = (int)(bh - (long long)b * Hq);
-  const float* src = acc + (bh * sq_pad + q) * 64;
-  const float4 lo = *(const float4*)(src + (((2 * k8) ^ (q & 15)) * 4));
-  const float4 hi = *(const float4*)(src + (((2 * k8 + 1) ^ (q & 15)) * 4));
+  const int r = q & 127, c = 2 * (k8 & 3);
+  const float* src = acc + (bh * sq_pad + (q - r)) * 64 + (k8 >> 2) * (128 * 32) + r * 32;
+  const float4 lo = *(const float4*)(src + ((c ^ (r & 7)) * 4));
+  const float4 hi = *(const float4*)(src + (((c + 1) ^ (r & 7)) * 4));
   char* dst = (char*)dq.ptr + ((long long)b * dq.sb + (long long)h * dq.sh + (long long)q * dq.ss) * 2 + k8 * 16;
   if (DT == FA_F16) {
     __half2 o[4] = {__floats2half2_rn(lo.x * scale, lo.y * scale), __floats2half2_rn(lo.z * scale, lo.w * scale),
@@ -734,6 +736,7 @@ bool tc_fwd_eligible(const fa_attn_params* p) {
   if (p->dtype == FA_F32) return false;
   if (p->D != p->Dv || !(p->D == 64 || p->D == 128)) return false;
   if (p->Sq < 128 || p->Skv > 32768) return false;
+  if (!(p->scale > 0.f)) return false;  // the kernel takes row maxima over unscaled scores
   const fa_block_tables& t = p->tables;
   if (t.kv_num_blocks) {
     if (!(t.num_q_blocks == 1 || t.q_block_size % 128 == 0)) return false;
@@ -745,7 +748,7 @@ bool tc_fwd_eligible(const fa_attn_params* p) {
 
 int get_fwd_tc_kernel(fa_module* m, int dtype, int D, int flags, Kernel** k) {
   const int atoms = D / 64, nstage = D == 64 ? 3 : 2;
-  const int smem = 2 * atoms * 16384 + 2 * nstage * atoms * 16384 + (1 + 4 * nstage + 12) * 8 + 16 + 256 * 2 + 256 * 2 +
+  const int smem = 2 * atoms * 16384 + 2 * nstage * atoms * 16384 + (1 + 4 * nstage + 8) * 8 + 16 + 256 * 2 + 256 * 2 +
                    2 * 256 + 1024;
   std::string d = defs({{"FA_DTYPE", dtype}, {"FA_D", D}, {"FA_ROUND_SCORES", round_flag(dtype, flags)}});
   d += extra_defines();
@@ -760,7 +763,10 @@ int launch_fwd_tc(fa_module* m, const fa_attn_params* p, const FaParams& kp, voi
   if (int rc = make_map(&tp.tq, p->dtype, p->q, p->D, p->Sq, p->Hq, p->B)) return rc;
   if (int rc = make_map(&tp.tk, p->dtype, p->k, p->D, p->Skv, p->Hkv, p->B)) return rc;
   if (int rc = make_map(&tp.tv, p->dtype, p->v, p->Dv, p->Skv, p->Hkv, p->B)) return rc;
-  return launch(k, dim3((p->Sq + 255) / 256, p->Hq, p->B), dim3(384), &tp, stream);
+  // Heads vary fastest and the query tile pair slowest (the kernel walks the pairs from the last one
+  // down), so that under a causal mask the CTAs with the most kv tiles are dispatched first for
+  // all heads: longest-first order keeps the tail of the grid short.
+  return launch(k, dim3(p->Hq, p->B, (p->Sq + 255) / 256), dim3(384), &tp, stream);
 }
 
 // ---- tcgen05 backward ----------------------------------------------------------------------
@@ -797,8 +803,9 @@ size_t dq_acc_bytes(const fa_attn_params* p) {
 }
 
 int get_bwd_tc_kernel(fa_module* m, int dtype, int flags, Kernel** k) {
-  const int nstage = 3;
-  const int smem = (2 + 2 * nstage) * 16384 + 2 * 16384 + 128 * 64 * 4 + nstage * 2 * 128 * 4 + (1 + 2 * nstage + 7) * 8 + 16 + 512 * 4 + 256 + 1024;
+  // must match the shared-memory map of fa_bwd_tc.cuh (fa_btc::SMEM_BYTES)
+  const int nstage = 4;
+  const int smem = (2 + 2 * nstage) * 16384 + 2 * 16384 + 128 * 32 * 4 + nstage * 2 * 128 * 4 + (1 + 3 * nstage + 7) * 8 + 16 + 512 * 4 + 256 + 1024;
   std::string d = defs({{"FA_DTYPE", dtype}, {"FA_ROUND_SCORES", round_flag(dtype, flags)}}) + extra_defines();
   return get_kernel(m, "fa_bwd_tc.cuh", d, "fa_bwd_tc_kernel", smem, k);
 }
@@ -919,7 +926,8 @@ int fa_bwd(fa_module* m, const fa_attn_params* p, const fa_tensor* dout, const f
       if (int rc = make_map(&tp.tk, p->dtype, p->k, p->D, p->Skv, p->Hkv, p->B)) return rc;
       if (int rc = make_map(&tp.tv, p->dtype, p->v, p->Dv, p->Skv, p->Hkv, p->B)) return rc;
       if (int rc = make_map(&tp.tdo, p->dtype, *dout, p->Dv, p->Sq, p->Hq, p->B)) return rc;
-      if (int rc = launch(ktc, dim3((p->Skv + 127) / 128, p->Hkv, p->B), dim3(512), &tp, stream)) return rc;
+      // heads fastest, kv tile slowest: under a causal mask the first kv tiles meet the most q tiles
+      if (int rc = launch(ktc, dim3(p->Hkv, p->B, (p->Skv + 127) / 128), dim3(512), &tp, stream)) return rc;
     }
     if (!(p->flags & FA_FLAG_BWD_SKIP_DQ)) {
       const long long n_chunks = (long long)p->B * p->Hq * p->Sq * 8;

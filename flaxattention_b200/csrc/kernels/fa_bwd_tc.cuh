@@ -14,7 +14,7 @@
 //   3. dV += P^T dO                      (A from TMEM)
 //   4. dK += dS^T Q                      (A = dS^T from smem, K-major)
 //   5. dQ  = dS K                        (A = the same dS^T tile read MN-major, B = K)
-// dQ of a pair leaves TMEM through a staging tile and one bulk reduce-add into an fp32
+// dQ of a pair leaves TMEM through a staging buffer and two bulk reduce-adds into an fp32
 // accumulation buffer (summation order over kv tiles is not fixed; a small kernel scales and
 // converts it afterwards).  dK and dV are written once at the end.
 //
@@ -34,7 +34,7 @@
 struct FaBwdTcParams {
   FaParams p;
   FaTensorMap tq, tk, tv, tdo;  // 4-d maps (D, S, H, B), box 64 x 128 x 1 x 1, 128-byte swizzle
-  float* dq_acc;                // [B, Hq, ceil(Sq/128)*128, 64] fp32, 16-byte chunks of a row permuted
+  float* dq_acc;                // per (b, h, q tile): two [128 rows][32 columns] fp32 blocks, 16-byte chunks of a row permuted
   const float* nlse2;           // [B, Hq, ceil(Sq/128)*128]: -lse * log2(e); -inf for rows without mass / beyond Sq
   const float* ndelta;          // same shape: -rowsum(O * dO); 0 beyond Sq
 };
@@ -61,6 +61,16 @@ struct FaBwdTcParams {
 #define FA_TRACE_DECL
 #define FA_TRACE(slot)
 #endif
+// FA_TC_TRACE == 2 additionally records the SM clock at each phase boundary of pairs 6..8 of
+// CTA (0,0,0) in status[64 + 32 * (pair - 6) + slot] (the status buffer must hold 160 ints).
+#if FA_TC_TRACE == 2
+#define FA_STAMP(slot)                                                                        \
+  do {                                                                                        \
+    if (trace_on && n >= 6 && n < 9) p.status[64 + (n - 6) * 32 + (slot)] = (int)clock64();   \
+  } while (0)
+#else
+#define FA_STAMP(slot)
+#endif
 
 namespace fa_btc {
 
@@ -68,7 +78,7 @@ constexpr int DT = FA_DTYPE;
 constexpr int D = 64;
 constexpr int BT = 128;                  // tile edge (kv rows and q columns)
 constexpr int ATOM_BYTES = 128 * 128;    // 128 rows x 128 bytes
-constexpr int NSTAGE = 3;
+constexpr int NSTAGE = 4;
 constexpr int MAXP = 512;                // (head, q tile) pairs per CTA
 constexpr int NT = 512;
 constexpr int WARP_PRODUCER = 12, WARP_MMA = 13, WARP_MMA_B = 14;
@@ -80,10 +90,11 @@ constexpr int OFF_V = OFF_K + ATOM_BYTES;
 constexpr int OFF_Q = OFF_V + ATOM_BYTES;                   // NSTAGE tiles
 constexpr int OFF_DO = OFF_Q + NSTAGE * ATOM_BYTES;         // NSTAGE tiles
 constexpr int OFF_DS = OFF_DO + NSTAGE * ATOM_BYTES;        // dS^T: two atoms (q 0-63, q 64-127)
-constexpr int OFF_DQ = OFF_DS + 2 * ATOM_BYTES;             // fp32 staging 128 x 64
-constexpr int OFF_ROW = OFF_DQ + 128 * 64 * 4;              // NSTAGE x (nlse2[128], ndelta[128]) floats
+constexpr int OFF_DQ = OFF_DS + 2 * ATOM_BYTES;             // fp32 staging 128 x 32 (half of the dQ tile at a time)
+constexpr int DQ_HALF_BYTES = 128 * 32 * 4;
+constexpr int OFF_ROW = OFF_DQ + DQ_HALF_BYTES;             // NSTAGE x (nlse2[128], ndelta[128]) floats
 constexpr int OFF_BAR = OFF_ROW + NSTAGE * 2 * 128 * 4;
-constexpr int NBARS = 1 + 2 * NSTAGE + 7;
+constexpr int NBARS = 1 + 3 * NSTAGE + 7;
 constexpr int OFF_MISC = OFF_BAR + NBARS * 8;               // tmem base, abort, npairs, pad
 constexpr int OFF_PAIR = OFF_MISC + 16;                     // int pair[MAXP]: tile | mode << 16 | g << 20
 constexpr int OFF_CLS = OFF_PAIR + MAXP * 4;                // uchar cls[256]
@@ -92,8 +103,10 @@ constexpr int TMEM_COLS = 512;
 constexpr int COL_S = 0, COL_DP = 128, COL_P = 256, COL_DV = 320, COL_DK = 384, COL_DQ = 448;
 
 constexpr int BAR_KV = 0;
-constexpr int BAR_QFULL = 1, BAR_QEMPTY = 1 + NSTAGE;
-constexpr int BAR_SFULL = 1 + 2 * NSTAGE;   // S^T and dP^T of a pair are in TMEM
+// A stage's Q tile (with the row scalars) and dO tile are released separately: dO is last read by
+// product 3, Q by product 4, and the sooner a slot is free the further ahead the producer runs.
+constexpr int BAR_QFULL = 1, BAR_QEMPTY = 1 + NSTAGE, BAR_DOEMPTY = 1 + 2 * NSTAGE;
+constexpr int BAR_SFULL = 1 + 3 * NSTAGE;   // S^T and dP^T of a pair are in TMEM
 constexpr int BAR_SFREE = BAR_SFULL + 1;    // compute warps hold them in registers (256 arrivals)
 constexpr int BAR_PREADY = BAR_SFULL + 2;   // P^T in TMEM and dS^T in smem (256 arrivals)
 constexpr int BAR_PFREE = BAR_SFULL + 3;    // products 3-5 of the pair are complete
@@ -175,7 +188,7 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
   unsigned char* sm = smem_raw + (sb - raw);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int kt = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int kt = blockIdx.z, hk = blockIdx.x, b = blockIdx.y;  // grid: (kv heads, batch, kv tiles)
   const int n0 = kt * BT;
   const int G = p.Hq / p.Hkv;
   const int gb = b + p.b_off;
@@ -195,6 +208,7 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
     for (int s = 0; s < NSTAGE; ++s) {
       fa_mbar_init(bar_addr(sb, BAR_QFULL + s), 1);
       fa_mbar_init(bar_addr(sb, BAR_QEMPTY + s), 2);  // one arrival from each MMA issuer
+      fa_mbar_init(bar_addr(sb, BAR_DOEMPTY + s), 2);
     }
     fa_mbar_init(bar_addr(sb, BAR_SFULL), 1);
     fa_mbar_init(bar_addr(sb, BAR_SFREE), 256);
@@ -271,14 +285,17 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
         const fa_u32 ph = (fa_u32)((n / NSTAGE) & 1);
         const int pr = pairs[n];
         const int m0 = (pr & 0xffff) * BT, h = hk * G + (pr >> 20);
-        if (n >= NSTAGE) ok = fa_mbar_wait(bar_addr(sb, BAR_QEMPTY + s), ph ^ 1u, abort_flag);
+        if (n >= NSTAGE) ok = fa_mbar_wait(bar_addr(sb, BAR_DOEMPTY + s), ph ^ 1u, abort_flag);
         if (!ok) break;
-        // Q and dO tiles plus the per-row scalars of the q tile (prepared by fa_bwd_prep_kernel)
+        // Q and dO tiles plus the per-row scalars of the q tile (prepared by fa_bwd_prep_kernel);
+        // one transaction count covers all four copies
         const long long rbase = ((long long)b * p.Hq + h) * sq_pad + m0;
         const fa_u32 full = bar_addr(sb, BAR_QFULL + s);
         fa_mbar_expect_tx(full, 2 * ATOM_BYTES + 2 * 128 * 4);
-        fa_tma_load_4d(sb + OFF_Q + s * ATOM_BYTES, &P.tq, full, 0, m0, h, b);
         fa_tma_load_4d(sb + OFF_DO + s * ATOM_BYTES, &P.tdo, full, 0, m0, h, b);
+        if (n >= NSTAGE) ok = fa_mbar_wait(bar_addr(sb, BAR_QEMPTY + s), ph ^ 1u, abort_flag);
+        if (!ok) break;
+        fa_tma_load_4d(sb + OFF_Q + s * ATOM_BYTES, &P.tq, full, 0, m0, h, b);
         fa_bulk_load(sb + OFF_ROW + s * 2 * 128 * 4, P.nlse2 + rbase, 128 * 4, full);
         fa_bulk_load(sb + OFF_ROW + s * 2 * 128 * 4 + 128 * 4, P.ndelta + rbase, 128 * 4, full);
       }
@@ -296,9 +313,9 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
       for (int n = 0; n < npairs && ok; ++n) {
         const int s = n % NSTAGE;
         ok = fa_mbar_wait(bar_addr(sb, BAR_QFULL + s), (fa_u32)((n / NSTAGE) & 1), abort_flag);
-        FA_TRACE(1);   // MMA A: wait for Q/dO
+        FA_TRACE(1); FA_STAMP(1);   // MMA A: wait for Q/dO
         if (ok && n > 0) ok = fa_mbar_wait(bar_addr(sb, BAR_SFREE), (fa_u32)((n - 1) & 1), abort_flag);
-        FA_TRACE(2);   // MMA A: wait for S^T/dP^T of the previous pair to be read
+        FA_TRACE(2); FA_STAMP(2);   // MMA A: wait for S^T/dP^T of the previous pair to be read
         if (!ok) break;
         fa_tc_fence_after();
         const fa_u32 loQ = fa_desc_lo(sb + OFF_Q + s * ATOM_BYTES, 16), loDO = fa_desc_lo(sb + OFF_DO + s * ATOM_BYTES, 16);
@@ -309,8 +326,9 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
         for (int kk = 0; kk < D / 16; ++kk)
           fa_mma_ss(tmem + COL_DP, fa_desc_make(loV_k + kk * 2, HI), fa_desc_make(loDO + kk * 2, HI), IDESC_KK, kk > 0);
         fa_mma_commit(bar_addr(sb, BAR_SFULL));
-        fa_mma_commit(bar_addr(sb, BAR_QEMPTY + s));  // first of the two arrivals that free the stage
-        FA_TRACE(3);   // MMA A: issue products 1-2
+        fa_mma_commit(bar_addr(sb, BAR_QEMPTY + s));  // first of the two arrivals that free each tile of the stage
+        fa_mma_commit(bar_addr(sb, BAR_DOEMPTY + s));
+        FA_TRACE(3); FA_STAMP(3);   // MMA A: issue products 1-2
       }
     }
   } else if (warp == WARP_MMA_B) {
@@ -326,9 +344,9 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
       for (int n = 0; n < npairs && ok; ++n) {
         const int s = n % NSTAGE;
         ok = fa_mbar_wait(bar_addr(sb, BAR_PREADY), (fa_u32)(n & 1), abort_flag);
-        FA_TRACE(4);     // MMA B: wait for P^T / dS^T
+        FA_TRACE(4); FA_STAMP(4);     // MMA B: wait for P^T / dS^T
         if (ok && n > 0) ok = fa_mbar_wait(bar_addr(sb, BAR_DQFREE), (fa_u32)((n - 1) & 1), abort_flag);
-        FA_TRACE(5);     // MMA B: wait for the dQ drain
+        FA_TRACE(5); FA_STAMP(5);     // MMA B: wait for the dQ drain
         if (!ok) break;
         fa_tc_fence_after();
         {
@@ -339,13 +357,15 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
 #pragma unroll
           for (int kk = 0; kk < BT / 16; ++kk)
             fa_mma_ts(tmem + COL_DV, tmem + COL_P + kk * 8, fa_desc_make(loDO_mn + kk * 128, HI), IDESC_TN, acc | (kk > 0));
-          FA_TRACE(7);   // MMA B: issue product 3
+          fa_mma_commit(bar_addr(sb, BAR_DOEMPTY + s));  // second arrival: the dO tile is free
+          FA_TRACE(7); FA_STAMP(7);   // MMA B: issue product 3
           // 4. dK += dS^T Q     (A = dS^T K-major: k-step kk is 32 bytes into atom kk / 4)
 #pragma unroll
           for (int kk = 0; kk < BT / 16; ++kk)
             fa_mma_ss(tmem + COL_DK, fa_desc_make(loDS_k + (kk >> 2) * (ATOM_BYTES >> 4) + (kk & 3) * 2, HI),
                       fa_desc_make(loQ_mn + kk * 128, HI), IDESC_TN, acc | (kk > 0));
-          FA_TRACE(8);   // MMA B: issue product 4
+          fa_mma_commit(bar_addr(sb, BAR_QEMPTY + s));   // second arrival: the Q tile and row scalars are free
+          FA_TRACE(8); FA_STAMP(8);   // MMA B: issue product 4
           // 5. dQ = dS K        (A = dS^T read MN-major: M chunks of 64 q one atom apart; K = 128 kv rows)
 #pragma unroll
           for (int kk = 0; kk < BT / 16; ++kk)
@@ -353,9 +373,8 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
         }
         fa_mma_commit(bar_addr(sb, BAR_PFREE));
         fa_mma_commit(bar_addr(sb, BAR_DQFULL));
-        fa_mma_commit(bar_addr(sb, BAR_QEMPTY + s));  // second arrival: the stage is free
         if (n + 1 == npairs) fa_mma_commit(bar_addr(sb, BAR_FINAL));
-        FA_TRACE(6);     // MMA B: issue product 5 + commits
+        FA_TRACE(6); FA_STAMP(6);     // MMA B: issue product 5 + commits
       }
     }
   } else if (warp < 8) {
@@ -377,7 +396,7 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
       const int pr = pairs[n];
       const int m0 = (pr & 0xffff) * BT, mode = (pr >> 16) & 0xf, gh = hk * G + (pr >> 20) + p.h_off;
       ok = fa_mbar_wait_warp(bar_addr(sb, BAR_SFULL), (fa_u32)(n & 1), abort_flag);
-      if (warp == 0) { FA_TRACE(10); }  // compute: wait for S^T/dP^T
+      if (warp == 0) { FA_TRACE(10); FA_STAMP(10); }  // compute: wait for S^T/dP^T
       if (ok) ok = fa_mbar_wait_warp(bar_addr(sb, BAR_QFULL + s), (fa_u32)((n / NSTAGE) & 1), abort_flag);
       if (!ok) break;
       fa_tc_fence_after();
@@ -394,7 +413,7 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
       }
       fa_tc_fence_before();
       fa_mbar_arrive(bar_addr(sb, BAR_SFREE));
-      if (warp == 0) { FA_TRACE(11); }  // compute: TMEM loads
+      if (warp == 0) { FA_TRACE(11); FA_STAMP(11); }  // compute: TMEM loads
 
       const float* rowp = (const float*)(sm + OFF_ROW + s * 2 * 128 * 4);
       fa_u32 pp0[16], pp1[16], ds0[16], ds1[16];
@@ -410,14 +429,18 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
 #pragma unroll
         for (int e = 0; e < 16; ++e) pp0[e] = pp1[e] = ds0[e] = ds1[e] = 0u;
       }
-      if (warp == 0) { FA_TRACE(12); }  // compute: element-wise math
+      // pin the packed results here: without this the compiler sinks part of the math below the
+      // wait that follows, onto the critical path between two groups of products
+#pragma unroll
+      for (int e = 0; e < 16; ++e) asm volatile("" : "+r"(pp0[e]), "+r"(pp1[e]), "+r"(ds0[e]), "+r"(ds1[e]));
+      if (warp == 0) { FA_TRACE(12); FA_STAMP(12); }  // compute: element-wise math
       // products 3-5 of the previous pair must be done with P^T and dS^T
       if (n > 0) {
         ok = fa_mbar_wait_warp(bar_addr(sb, BAR_PFREE), (fa_u32)((n - 1) & 1), abort_flag);
         if (!ok) break;
         fa_tc_fence_after();
       }
-      if (warp == 0) { FA_TRACE(13); }  // compute: wait for products 3-5 of the previous pair
+      if (warp == 0) { FA_TRACE(13); FA_STAMP(13); }  // compute: wait for products 3-5 of the previous pair
       fa_tmem_st16(t_row + COL_P + half * 32, pp0);
       fa_tmem_st16(t_row + COL_P + half * 32 + 16, pp1);
       if (!(FA_TC_EXP & 2)) {
@@ -439,7 +462,7 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
       fence_proxy_async();
       fa_tc_fence_before();
       fa_mbar_arrive(bar_addr(sb, BAR_PREADY));
-      if (warp == 0) { FA_TRACE(14); }  // compute: stores of P^T / dS^T
+      if (warp == 0) { FA_TRACE(14); FA_STAMP(14); }  // compute: stores of P^T / dS^T
     }
     // ---- epilogue: dK (scaled) by warps 0-3, dV by warps 4-7 ----------------------------------
     if (ok && npairs > 0) ok = fa_mbar_wait_warp(bar_addr(sb, BAR_FINAL), 0, abort_flag);
@@ -483,47 +506,42 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
       const int pr = pairs[n];
       const int qt = pr & 0xffff, h = hk * G + (pr >> 20);
       ok = fa_mbar_wait_warp(bar_addr(sb, BAR_DQFULL), (fa_u32)(n & 1), abort_flag);
-      if (warp == 8) { FA_TRACE(20); }  // drain: wait for dQ
+      if (warp == 8) { FA_TRACE(20); FA_STAMP(20); }  // drain: wait for dQ
       if (!ok) break;
       fa_tc_fence_after();
-      // the previous bulk reduce must have finished reading the staging tile
-      if (dtid == 0) bulk_wait_read0();
-      named_bar_sync(1, 128);
-      if (warp == 8) { FA_TRACE(21); }  // drain: wait for the previous bulk reduce
-      // 16-byte chunk k of row r goes to position k ^ (r & 15): spreads the rows of a warp over
-      // the banks; the accumulation buffer in global memory uses the same permutation
-      unsigned char* strow = sm + OFF_DQ + r * 256;
-      if (FA_TC_EXP & 1) {
-        float a[32];
-        fa_tmem_ld32(t_dq, a);
-        fa_tmem_wait_ld();
-        fa_tc_fence_before();
-        fa_mbar_arrive(bar_addr(sb, BAR_DQFREE));
-        continue;
-      }
-      {
-        float a[32];
-        fa_tmem_ld32(t_dq, a);
-        fa_tmem_wait_ld();
+      // The 128 x 64 tile leaves in two halves of 32 columns through one 16 KB staging buffer: each
+      // half is one contiguous 16 KB block of the accumulation buffer.  16-byte chunk k of row r
+      // goes to position k ^ (r & 7), which spreads the rows of a warp over the banks.
+      float* gdst = P.dq_acc + (((long long)b * p.Hq + h) * sq_pad + (long long)qt * BT) * D;
+      unsigned char* strow = sm + OFF_DQ + r * 128;
+      float a[32];
+      fa_tmem_ld32(t_dq, a);
+      fa_tmem_wait_ld();
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          *(float4*)(strow + ((k ^ (r & 15)) * 16)) = make_float4(a[4 * k], a[4 * k + 1], a[4 * k + 2], a[4 * k + 3]);
-        fa_tmem_ld32(t_dq + 32, a);
-        fa_tmem_wait_ld();
-        fa_tc_fence_before();
-        fa_mbar_arrive(bar_addr(sb, BAR_DQFREE));
+      for (int hf = 0; hf < 2; ++hf) {
+        // the previous bulk reduce must have finished reading the staging buffer
+        if (dtid == 0) bulk_wait_read0();
+        named_bar_sync(1, 128);
+        if (hf == 0 && warp == 8) { FA_TRACE(21); FA_STAMP(21); }  // drain: wait for the previous bulk reduce
+        if (!(FA_TC_EXP & 1)) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          *(float4*)(strow + (((k + 8) ^ (r & 15)) * 16)) = make_float4(a[4 * k], a[4 * k + 1], a[4 * k + 2], a[4 * k + 3]);
+          for (int k = 0; k < 8; ++k)
+            *(float4*)(strow + ((k ^ (r & 7)) * 16)) = make_float4(a[4 * k], a[4 * k + 1], a[4 * k + 2], a[4 * k + 3]);
+        }
+        if (hf == 0) {
+          fa_tmem_ld32(t_dq + 32, a);
+          fa_tmem_wait_ld();
+          fa_tc_fence_before();
+          fa_mbar_arrive(bar_addr(sb, BAR_DQFREE));
+        }
+        fence_proxy_async();
+        named_bar_sync(1, 128);
+        if (dtid == 0 && !(FA_TC_EXP & 1)) {
+          bulk_reduce_add_f32(gdst + hf * (DQ_HALF_BYTES / 4), sb + OFF_DQ, DQ_HALF_BYTES);
+          bulk_commit();
+        }
       }
-      fence_proxy_async();
-      named_bar_sync(1, 128);
-      if (dtid == 0) {
-        float* gdst = P.dq_acc + (((long long)b * p.Hq + h) * sq_pad + (long long)qt * BT) * D;
-        bulk_reduce_add_f32(gdst, sb + OFF_DQ, 128 * 64 * 4);
-        bulk_commit();
-      }
-      if (warp == 8) { FA_TRACE(22); }  // drain: TMEM -> staging -> reduce issue
+      if (warp == 8) { FA_TRACE(22); FA_STAMP(22); }  // drain: TMEM -> staging -> reduce issue
     }
     if (dtid == 0) bulk_wait0();
   }

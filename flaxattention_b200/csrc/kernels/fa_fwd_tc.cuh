@@ -41,7 +41,7 @@ constexpr int NSTAGE = D == 64 ? 3 : 2;
 constexpr int Q_BYTES = 2 * ATOMS * ATOM_BYTES;
 constexpr int KV_STAGE = ATOMS * ATOM_BYTES;
 constexpr int MAXT = 256;                // kv tiles per row of the block grid (Skv <= 32768)
-constexpr int NBARS = 1 + 4 * NSTAGE + 12;
+constexpr int NBARS = 1 + 4 * NSTAGE + 8;
 constexpr int OFF_K = Q_BYTES;
 constexpr int OFF_V = OFF_K + NSTAGE * KV_STAGE;
 constexpr int OFF_BAR = OFF_V + NSTAGE * KV_STAGE;
@@ -74,15 +74,27 @@ constexpr int COL_P = 384;
 #define FA_TRACE_DECL
 #define FA_TRACE(slot)
 #endif
+// FA_TC_TRACE == 2 additionally records the SM clock at each phase boundary of kv steps 6..8 of
+// CTA (0,0,0) in status[64 + 32 * (step - 6) + slot] (the status buffer must hold 160 ints).
+#if FA_TC_TRACE == 2
+#define FA_STAMP(slot)                                                                        \
+  do {                                                                                        \
+    if (trace_on && j >= 6 && j < 9) p.status[64 + (j - 6) * 32 + (slot)] = (int)clock64();   \
+  } while (0)
+#else
+#define FA_STAMP(slot)
+#endif
 #ifndef FA_TC_HALF_EXP
 #define FA_TC_HALF_EXP 0
 #endif
-#ifndef FA_TC_SETMAXNREG
-#define FA_TC_SETMAXNREG 0
-#endif
 constexpr int NT = 384;
+// Register split (setmaxnreg): the kernel starts with 168 registers per thread (65536 / 384, rounded
+// down to a multiple of 8).  The third warpgroup gives up 72 each (128 x 72 = 9216) and the two
+// softmax warpgroups take 32 each (256 x 32 = 8192).  The increase must not ask for more than the
+// decrease releases: setmaxnreg.inc blocks until the registers are there, without a time limit.
+constexpr int REGS_SOFTMAX = 200, REGS_OTHER = 96;
+static_assert(256 * (REGS_SOFTMAX - 168) <= 128 * (168 - REGS_OTHER), "setmaxnreg.inc would wait forever");
 constexpr int WARP_PRODUCER = 8, WARP_MMA = 9, WARP_MMA_B = 10;
-constexpr int REGS_SOFTMAX = 200, REGS_OTHER = 112;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
 
 static_assert(D == 64 || D == 128, "head dim 64 or 128");
@@ -91,37 +103,31 @@ static_assert(DT == FA_DT_F16 || DT == FA_DT_BF16, "16-bit inputs");
 __device__ __forceinline__ fa_u32 bar_addr(fa_u32 sbase, int i) { return sbase + OFF_BAR + i * 8; }
 constexpr int BAR_Q = 0;
 constexpr int BAR_KFULL = 1, BAR_KEMPTY = 1 + NSTAGE, BAR_VFULL = 1 + 2 * NSTAGE, BAR_VEMPTY = 1 + 3 * NSTAGE;
-constexpr int BAR_S = 1 + 4 * NSTAGE, BAR_P = BAR_S + 2, BAR_O = BAR_S + 4, BAR_SFREE = BAR_S + 6;
-// With separate P columns S is produced and released in two 64-column halves, so that the
-// first half of the next step is already being computed while the second is still being read.
-constexpr int BAR_S2 = BAR_S + 8, BAR_SFREE2 = BAR_S + 10;
-#ifndef FA_TC_AFFINE_RECOMP
-#define FA_TC_AFFINE_RECOMP 0  // measured slower than writing the modified scores back to TMEM
-#endif
-#ifndef FA_TC_SPLIT_S
-#define FA_TC_SPLIT_S 0  // measured slower on B200: twice the S instructions load the MMA issuer
-#endif
-constexpr bool SPLIT_S = SEP_P && FA_TC_SPLIT_S;
+constexpr int BAR_S = 1 + 4 * NSTAGE, BAR_P = BAR_S + 2, BAR_O = BAR_S + 4;
+// With separate P columns the S columns of a tile are released as soon as the softmax warps
+// hold the scores in registers, and S of the next step is produced during the softmax.
+constexpr int BAR_SFREE2 = BAR_S + 6;
 
-// Pass-1 work on one 32-column chunk of a score row (columns C0 .. C0+31 of the kv tile that
-// starts at key n0).  C0 is a template parameter and n0 a multiple of 128, so the low bits of
-// every key index are compile-time constants inside the mods.
+// Work on one 32-column chunk of a score row held in registers (columns C0 .. C0+31 of the kv
+// tile that starts at key n0).  C0 is a template parameter and n0 a multiple of 128, so the low
+// bits of every key index are compile-time constants inside the mods.
 struct RowMax {
   float a, b, c, d;
 };
-template <int C0>
-__device__ __forceinline__ void pass1_chunk(float (&v)[32], RowMax& mx, bool plain, bool recomp, bool ragged, int mode, int n0,
-                                            int qi, int gb, int gh, float scale, float sc2, int Skv) {
-  if (plain) {
+__device__ __forceinline__ void max_chunk(const float (&v)[32], RowMax& mx) {
 #pragma unroll
-    for (int e = 0; e < 32; e += 8) {
-      mx.a = fa_max3(mx.a, v[e], v[e + 1]);
-      mx.b = fa_max3(mx.b, v[e + 2], v[e + 3]);
-      mx.c = fa_max3(mx.c, v[e + 4], v[e + 5]);
-      mx.d = fa_max3(mx.d, v[e + 6], v[e + 7]);
-    }
-    return;
+  for (int e = 0; e < 32; e += 8) {
+    mx.a = fa_max3(mx.a, v[e], v[e + 1]);
+    mx.b = fa_max3(mx.b, v[e + 2], v[e + 3]);
+    mx.c = fa_max3(mx.c, v[e + 4], v[e + 5]);
+    mx.d = fa_max3(mx.d, v[e + 6], v[e + 7]);
   }
+}
+// score_mod (and the rounding of the raw scores to the input type, when asked for) in place;
+// the results are in log2 units.  An affine score_mod (A * score + B) costs one FMA: A and B
+// absorb the scale and log2(e).
+template <int C0>
+__device__ __forceinline__ void mod_chunk(float (&v)[32], int n0, int qi, int gb, int gh, float scale, float sc2) {
 #pragma unroll
   for (int e = 0; e < 32; e += 2) {
     float x0 = v[e], x1 = v[e + 1];
@@ -140,48 +146,23 @@ __device__ __forceinline__ void pass1_chunk(float (&v)[32], RowMax& mx, bool pla
     x0 *= sc2;
     x1 *= sc2;
 #endif
-    bool k0 = true, k1 = true;
-#if FA_HAS_MASK_MOD
-    if (mode == 1) {
-      k0 = fa_mask_mod(gb, gh, qi, kv0);
-      k1 = fa_mask_mod(gb, gh, qi, kv1);
-    }
-#endif
-    if (ragged) {
-      k0 = k0 && (kv0 < Skv);
-      k1 = k1 && (kv1 < Skv);
-    }
-    x0 = k0 ? x0 : FA_NEG_INF;
-    x1 = k1 ? x1 : FA_NEG_INF;
-    if (!recomp) {
-      v[e] = x0;
-      v[e + 1] = x1;
-    }
-    if ((e & 6) == 0) mx.a = fa_max3(mx.a, x0, x1);
-    else if ((e & 6) == 2) mx.b = fa_max3(mx.b, x0, x1);
-    else if ((e & 6) == 4) mx.c = fa_max3(mx.c, x0, x1);
-    else mx.d = fa_max3(mx.d, x0, x1);
+    v[e] = x0;
+    v[e + 1] = x1;
   }
 }
-
-// Pass-2 work on one chunk for a cheap affine score_mod on an unmasked tile: the raw scores are
-// still in TMEM, the exponent is A * s + (B - m) with A and B evaluated again.
+// mask_mod (on tiles the BlockMask lists as partial) and the end of the sequence (ragged last
+// tile): masked scores become -inf.  Only the few tiles that need it come here.
 template <int C0>
-__device__ __forceinline__ void pass2_chunk_affine(const float (&v)[32], fa_u32 (&pk)[16], float negm, fa_u64& sum_a,
-                                                   fa_u64& sum_b, int n0, int qi, int gb, int gh, float sc2) {
-#if FA_HAS_SCORE_MOD && defined(FA_SCORE_AFFINE)
+__device__ __forceinline__ void mask_chunk(float (&v)[32], bool use_mask, int n0, int qi, int gb, int gh, int Skv) {
 #pragma unroll
-  for (int e = 0; e < 16; ++e) {
-    const int kv0 = n0 | (C0 + 2 * e), kv1 = n0 | (C0 + 2 * e + 1);
-    const float a0 = fmaf(v[2 * e], fa_score_mul(0.f, gb, gh, qi, kv0) * sc2, fa_score_add2(0.f, gb, gh, qi, kv0) + negm);
-    const float a1 = fmaf(v[2 * e + 1], fa_score_mul(0.f, gb, gh, qi, kv1) * sc2, fa_score_add2(0.f, gb, gh, qi, kv1) + negm);
-    const float p0 = fa_ex2(a0), p1 = fa_ex2(a1);
-    pk[e] = fa_pack2<DT>(p0, p1);
-    const fa_u64 pf = fa_f2(p0, p1);
-    if (e & 1) sum_b = fa_add2(sum_b, pf);
-    else sum_a = fa_add2(sum_a, pf);
-  }
+  for (int e = 0; e < 32; ++e) {
+    const int kv = n0 | (C0 + e);
+    bool keep = kv < Skv;
+#if FA_HAS_MASK_MOD
+    if (use_mask) keep = keep && fa_mask_mod(gb, gh, qi, kv);
 #endif
+    v[e] = keep ? v[e] : FA_NEG_INF;
+  }
 }
 
 // Pass-2 work on one chunk: p = 2^(x * cmul - m), packed to 16 bits, and the row-sum chains.
@@ -204,6 +185,147 @@ __device__ __forceinline__ void pass2_chunk(const float (&v)[32], fa_u32 (&pk)[1
   }
 }
 
+// State of one softmax warpgroup thread that a kv step reads and updates.
+struct SoftmaxCtx {
+  const FaParams& p;
+  fa_u32 sb, t_s, t_o, t_p;
+  int i, warp, qi, gb, gh;
+  float sc2;
+  volatile int* abort_flag;
+  const short* sched_tile;
+  float m_ref, l;
+  fa_u32 cnt;
+#if FA_TC_TRACE
+  bool trace_on;
+  long long trace_t0;
+#endif
+};
+
+// One kv step of this warpgroup's tile.  MASKED (compile time) selects the version for the few
+// tiles that need mask_mod or end beyond the sequence; the common version carries no mask code,
+// and keeping the two apart keeps the 128 score registers of each out of local memory.
+template <bool MASKED>
+__device__ __forceinline__ bool softmax_step(SoftmaxCtx& c, const int j, const int mode) {
+  const FaParams& p = c.p;
+  const fa_u32 sb = c.sb, t_s = c.t_s, t_o = c.t_o, t_p = c.t_p;
+  const int i = c.i, warp = c.warp, qi = c.qi, gb = c.gb, gh = c.gh;
+  const float sc2 = c.sc2;
+  volatile int* abort_flag = c.abort_flag;
+  float& m_ref = c.m_ref;
+  float& l = c.l;
+  fa_u32& cnt = c.cnt;
+#if FA_TC_TRACE
+  const bool trace_on = c.trace_on;
+  long long& trace_t0 = c.trace_t0;
+#endif
+  const short* sched_tile = c.sched_tile;
+  const int n0 = (int)sched_tile[j] * BN;
+  if (!fa_mbar_wait_warp(bar_addr(sb, BAR_S + i), cnt & 1u, abort_flag)) return false;
+  if (warp == 0) { FA_TRACE(10); FA_STAMP(10); }  // softmax: wait S
+  fa_tc_fence_after();
+  // ---- pass 1: the whole score row (128 fp32 values) comes into registers, chunk by chunk,
+  // with the score_mod (when there is one), the mask and the row maximum of a chunk computed
+  // while the next chunk is on its way.  Without a score_mod the raw scores are kept and the
+  // scale is folded into the exponent of pass 2.  The S columns are free again as soon as the
+  // last load has landed, long before the softmax of the step is done.
+  float s0[32], s1[32], s2[32], s3[32];
+  RowMax rm = {FA_NEG_INF, FA_NEG_INF, FA_NEG_INF, FA_NEG_INF};
+  // (the host routes a non-positive scale, which would turn the maximum around, elsewhere)
+  constexpr bool in_place = FA_HAS_SCORE_MOD || FA_ROUND_SCORES;
+  const bool use_mask = FA_HAS_MASK_MOD && mode == 1;
+#define FA_P1(V, C0)                                                          \
+  if (in_place) mod_chunk<C0>(V, n0, qi, gb, gh, p.scale, sc2);                \
+  if (MASKED) mask_chunk<C0>(V, use_mask, n0, qi, gb, gh, p.Skv);              \
+  max_chunk(V, rm);
+  fa_tmem_ld32(t_s, s0);
+  fa_tmem_wait_ld();
+  fa_tmem_ld32(t_s + 32, s1);
+  FA_P1(s0, 0)
+  fa_tmem_wait_ld();
+  fa_tmem_ld32(t_s + 64, s2);
+  FA_P1(s1, 32)
+  fa_tmem_wait_ld();
+  fa_tmem_ld32(t_s + 96, s3);
+  FA_P1(s2, 64)
+  fa_tmem_wait_ld();
+  if (SEP_P) {
+    fa_tc_fence_before();
+    fa_mbar_arrive(bar_addr(sb, BAR_SFREE2 + i));
+  }
+  if (warp == 0) { FA_STAMP(13); }
+  FA_P1(s3, 96)
+#undef FA_P1
+  if (warp == 0) { FA_TRACE(11); FA_STAMP(11); }  // softmax: loads + pass 1
+  float mx = fmaxf(fmaxf(rm.a, rm.b), fmaxf(rm.c, rm.d));
+  if (!in_place) mx *= sc2;
+  // running maximum, raised lazily
+  const float m_new = fmaxf(m_ref, mx);
+  bool need = false;
+  float corr = 1.f;
+  if (m_ref == FA_NEG_INF) {
+    m_ref = m_new;  // nothing accumulated yet for this row
+  } else if (m_new - m_ref > RESCALE_THRESHOLD) {
+    need = true;
+    corr = fa_ex2(m_ref - m_new);
+    m_ref = m_new;
+    l *= corr;
+  }
+  const bool rescale = cnt > 0 && __any_sync(0xffffffffu, need);
+  if (cnt > 0 && (SEP_P || rescale)) {
+    // the previous PV product of this tile must be complete: it reads the P columns that
+    // are about to be overwritten (separate P columns), and O is rescaled in place
+    if (!fa_mbar_wait_warp(bar_addr(sb, BAR_O + i), (cnt - 1) & 1u, abort_flag)) return false;
+    fa_tc_fence_after();
+  }
+  if (warp == 0) { FA_STAMP(14); }
+  if (rescale) {
+#pragma unroll 1
+    for (int c = 0; c < D / 16; ++c) {
+      float o[16];
+      fa_tmem_ld16(t_o + c * 16, o);
+      fa_tmem_wait_ld();
+#pragma unroll
+      for (int e = 0; e < 16; ++e) o[e] *= corr;
+      fa_tmem_st16f(t_o + c * 16, o);
+    }
+  }
+  // ---- pass 2: p = 2^(x * cmul - m) and the row sum; P goes to TMEM as 16-bit pairs (its own
+  // columns with D = 64, over the first 64 score columns otherwise).
+  // With FA_TC_HALF_EXP the exponent is rounded to the 16-bit input type first and one SFU
+  // operation yields both values of a pair already in the format the second product needs;
+  // the row sum is then taken over exactly the values that product sees.
+  const float m_use = (m_ref == FA_NEG_INF) ? 0.f : m_ref;
+  const fa_u64 negm = fa_f2(-m_use, -m_use);
+  const float cm = in_place ? 1.f : sc2;
+  const fa_u64 cmul = fa_f2(cm, cm);
+  fa_u64 sum_a = fa_f2(0.f, 0.f), sum_b = fa_f2(0.f, 0.f);
+  {
+    fa_u32 pk[16];
+    pass2_chunk(s0, pk, cmul, negm, sum_a, sum_b);
+    fa_tmem_st16(t_p, pk);
+    pass2_chunk(s1, pk, cmul, negm, sum_a, sum_b);
+    fa_tmem_st16(t_p + 16, pk);
+    pass2_chunk(s2, pk, cmul, negm, sum_a, sum_b);
+    fa_tmem_st16(t_p + 32, pk);
+    pass2_chunk(s3, pk, cmul, negm, sum_a, sum_b);
+    fa_tmem_st16(t_p + 48, pk);
+  }
+  float sum;
+  {
+    float a0, a1;
+    fa_f2_unpack(fa_add2(sum_a, sum_b), a0, a1);
+    sum = a0 + a1;
+  }
+  l += sum;
+  if (warp == 0) { FA_STAMP(15); }
+  fa_tmem_wait_st();
+  fa_tc_fence_before();
+  fa_mbar_arrive(bar_addr(sb, BAR_P + i));
+  ++cnt;
+  if (warp == 0) { FA_TRACE(12); FA_STAMP(12); }  // softmax: pass 2 + stores
+  return true;
+}
+
 }  // namespace fa_tc
 
 extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(const __grid_constant__ FaTcParams P) {
@@ -215,8 +337,8 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
   unsigned char* sm = smem_raw + (sb - raw);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int pair = gridDim.x - 1 - blockIdx.x;
-  const int h = blockIdx.y, b = blockIdx.z;
+  const int pair = gridDim.z - 1 - blockIdx.z;  // grid: (heads, batch, tile pairs), the last pair first
+  const int h = blockIdx.x, b = blockIdx.y;
   const int m0 = pair * 2 * BM;
   const int hk = h / (p.Hq / p.Hkv);
   const int gb = b + p.b_off, gh = h + p.h_off;
@@ -242,8 +364,6 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
       fa_mbar_init(bar_addr(sb, BAR_S + i), 1);
       fa_mbar_init(bar_addr(sb, BAR_P + i), 128);
       fa_mbar_init(bar_addr(sb, BAR_O + i), 1);
-      fa_mbar_init(bar_addr(sb, BAR_SFREE + i), 128);
-      fa_mbar_init(bar_addr(sb, BAR_S2 + i), 1);
       fa_mbar_init(bar_addr(sb, BAR_SFREE2 + i), 128);
     }
     fa_mbar_init_fence();
@@ -300,13 +420,7 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
   const int nsteps = misc[2];
   volatile int* abort_flag = misc + 1;
 
-#if FA_TC_SETMAXNREG
-  if (warp >= 8) {
-    fa_setmaxnreg_dec<REGS_OTHER>();
-  } else {
-    fa_setmaxnreg_inc<REGS_SOFTMAX>();
-  }
-#endif
+  if (warp >= 8) fa_setmaxnreg_dec<REGS_OTHER>();
   if (warp == WARP_PRODUCER) {
     // ================================ TMA producer =======================================
     if (lane == 0) {
@@ -348,12 +462,12 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
         for (int j = 0; j < nsteps && ok; ++j) {
           const int s = j % NSTAGE;
           ok = fa_mbar_wait(bar_addr(sb, BAR_KFULL + s), (fa_u32)((j / NSTAGE) & 1), abort_flag);
-          FA_TRACE(4);  // MMA A: wait K
+          FA_TRACE(4); FA_STAMP(4);  // MMA A: wait K
           for (int i = 0; i < 2 && ok; ++i) {
             if (!sched_mode[2 * j + i]) continue;
             if (nsi[i] > 0) {
               ok = fa_mbar_wait(bar_addr(sb, BAR_SFREE2 + i), (nsi[i] - 1) & 1u, abort_flag);
-              FA_TRACE(6);  // MMA A: wait for the previous S of the tile to be read
+              FA_TRACE(6); FA_STAMP(6);  // MMA A: wait for the previous S of the tile to be read
               if (!ok) break;
             }
             fa_tc_fence_after();
@@ -365,7 +479,7 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
             }
             fa_mma_commit(bar_addr(sb, BAR_S + i));
             ++nsi[i];
-            FA_TRACE(5);  // MMA A: issue S
+            FA_TRACE(5); FA_STAMP(5);  // MMA A: issue S
           }
           fa_mma_commit(bar_addr(sb, BAR_KEMPTY + s));
         }
@@ -377,11 +491,11 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
         for (int j = 0; j < nsteps && ok; ++j) {
           const int s = j % NSTAGE;
           ok = fa_mbar_wait(bar_addr(sb, BAR_VFULL + s), (fa_u32)((j / NSTAGE) & 1), abort_flag);
-          FA_TRACE(1);  // MMA B: wait V
+          FA_TRACE(1); FA_STAMP(1);  // MMA B: wait V
           for (int i = 0; i < 2 && ok; ++i) {
             if (!sched_mode[2 * j + i]) continue;
             ok = fa_mbar_wait(bar_addr(sb, BAR_P + i), cnt[i] & 1u, abort_flag);
-            FA_TRACE(2);  // MMA B: wait P
+            FA_TRACE(2); FA_STAMP(2);  // MMA B: wait P
             if (!ok) break;
             fa_tc_fence_after();
             const fa_u32 loV = fa_desc_lo(sb + OFF_V + s * KV_STAGE, ATOM_BYTES);
@@ -391,7 +505,7 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
               fa_mma_ts(tmem + COL_O + i * D, tmem + COL_P + i * 64 + kk * 8, fa_desc_make(loV + kk * 128, HI), IDESC_O, acc | (kk > 0));
             fa_mma_commit(bar_addr(sb, BAR_O + i));
             ++cnt[i];
-            FA_TRACE(3);  // MMA B: issue PV
+            FA_TRACE(3); FA_STAMP(3);  // MMA B: issue PV
           }
           fa_mma_commit(bar_addr(sb, BAR_VEMPTY + s));
         }
@@ -404,24 +518,20 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
       constexpr fa_u32 IDESC_O = fa_idesc(DT, BM, D, 0, 1);
       bool ok = nsteps == 0 || fa_mbar_wait(bar_addr(sb, BAR_Q), 0, abort_flag);
       fa_u32 cnt[2] = {0, 0};  // PV products issued so far per query tile
-      fa_u32 nsi[2] = {0, 0};  // S products issued so far per query tile
       // Descriptors: constant high word; the low word (start address and MN-chunk distance in
       // 16-byte units) is stepped with one add per k-step.
       constexpr fa_u32 HI = fa_desc_hi_sw128();
       // S_i = Q_i K^T for step j into TMEM columns COL_S + 128 i
-      // (with SEP_P: one 64-column half, `half` = 0 / 1; otherwise all 128 columns)
-      constexpr fa_u32 IDESC_S64 = fa_idesc(DT, BM, 64, 0, 0);
-      auto issue_s = [&](int i, int j, int half) {
+      auto issue_s = [&](int i, int j) {
         const int s = j % NSTAGE;
         const fa_u32 loQ = fa_desc_lo(sb + i * ATOMS * ATOM_BYTES, 16);
-        const fa_u32 loK = fa_desc_lo(sb + OFF_K + s * KV_STAGE + (SPLIT_S ? half * 64 * 128 : 0), 16);
+        const fa_u32 loK = fa_desc_lo(sb + OFF_K + s * KV_STAGE, 16);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk) {
           const fa_u32 koff = ((kk / 4) * ATOM_BYTES + (kk % 4) * 32) >> 4;
-          fa_mma_ss(tmem + COL_S + i * BN + (SPLIT_S ? half * 64 : 0), fa_desc_make(loQ + koff, HI), fa_desc_make(loK + koff, HI),
-                    SPLIT_S ? IDESC_S64 : IDESC_S, kk > 0);
+          fa_mma_ss(tmem + COL_S + i * BN, fa_desc_make(loQ + koff, HI), fa_desc_make(loK + koff, HI), IDESC_S, kk > 0);
         }
-        fa_mma_commit(bar_addr(sb, (half ? BAR_S2 : BAR_S) + i));
+        fa_mma_commit(bar_addr(sb, BAR_S + i));
       };
       // O_i += P_i V for step j (P_i: 16-bit, in the first 64 columns of S_i)
       auto issue_pv = [&](int i, int j, bool first) {
@@ -430,7 +540,7 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
         const fa_u32 acc = !first;
 #pragma unroll
         for (int kk = 0; kk < BN / 16; ++kk)
-          fa_mma_ts(tmem + COL_O + i * D, tmem + (SEP_P ? COL_P + i * 64 : COL_S + i * BN) + kk * 8, fa_desc_make(loV + kk * 128, HI), IDESC_O, acc | (kk > 0));
+          fa_mma_ts(tmem + COL_O + i * D, tmem + COL_S + i * BN + kk * 8, fa_desc_make(loV + kk * 128, HI), IDESC_O, acc | (kk > 0));
         fa_mma_commit(bar_addr(sb, BAR_O + i));
       };
       if (ok && nsteps > 0) {
@@ -438,11 +548,7 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
         if (ok) {
           fa_tc_fence_after();
           for (int i = 0; i < 2; ++i)
-            if (sched_mode[i]) {
-              issue_s(i, 0, 0);
-              if (SPLIT_S) issue_s(i, 0, 1);
-              ++nsi[i];
-            }
+            if (sched_mode[i]) issue_s(i, 0);
           fa_mma_commit(bar_addr(sb, BAR_KEMPTY + 0));
         }
       }
@@ -455,55 +561,37 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
         const fa_u32 ph1 = (fa_u32)(((j + 1) / NSTAGE) & 1);
         bool k_ready = false;
         ok = fa_mbar_wait(bar_addr(sb, BAR_VFULL + s), ph, abort_flag);
-        FA_TRACE(1);  // MMA: wait V
+        FA_TRACE(1); FA_STAMP(1);  // MMA: wait V
         for (int i = 0; i < 2 && ok; ++i) {
-          const bool next_s = more && sched_mode[2 * (j + 1) + i];
-          auto do_s = [&]() {
-            if (!k_ready) {
-              ok = fa_mbar_wait(bar_addr(sb, BAR_KFULL + s1), ph1, abort_flag);
-              if (!ok) return;
-              fa_tc_fence_after();
-              k_ready = true;
-              FA_TRACE(4);  // MMA: wait K
-            }
-            if (SEP_P) {
-              // each half as soon as the softmax warps have read the previous one (without
-              // SPLIT_S: the whole tile once its second half has been read)
-              for (int half = SPLIT_S ? 0 : 1; half < 2; ++half) {
-                if (nsi[i] > 0) {
-                  ok = fa_mbar_wait(bar_addr(sb, (half ? BAR_SFREE2 : BAR_SFREE) + i), (nsi[i] - 1) & 1u, abort_flag);
-                  if (!ok) return;
-                  fa_tc_fence_after();
-                  FA_TRACE(6);  // MMA: wait S read
-                }
-                issue_s(i, j + 1, SPLIT_S ? half : 0);
-              }
-            } else {
-              issue_s(i, j + 1, 0);
-            }
-            ++nsi[i];
-            FA_TRACE(5);  // MMA: issue S
-          };
-          if (SEP_P && next_s) do_s();  // S of the next step does not have to wait for P
-          if (!ok) break;
           if (sched_mode[2 * j + i]) {
             ok = fa_mbar_wait(bar_addr(sb, BAR_P + i), cnt[i] & 1u, abort_flag);
-            FA_TRACE(2);  // MMA: wait P
+            FA_TRACE(2); FA_STAMP(2);  // MMA: wait P
             if (!ok) break;
             fa_tc_fence_after();
             issue_pv(i, j, cnt[i] == 0);
             ++cnt[i];
-            FA_TRACE(3);  // MMA: issue PV
+            FA_TRACE(3); FA_STAMP(3);  // MMA: issue PV
           }
           if (i == 1) fa_mma_commit(bar_addr(sb, BAR_VEMPTY + s));
-          if (!SEP_P && next_s) do_s();
-          if (!ok) break;
+          // S of the next step overwrites the columns P was read from: it follows the PV product
+          if (more && sched_mode[2 * (j + 1) + i]) {
+            if (!k_ready) {
+              ok = fa_mbar_wait(bar_addr(sb, BAR_KFULL + s1), ph1, abort_flag);
+              if (!ok) break;
+              fa_tc_fence_after();
+              k_ready = true;
+              FA_TRACE(4); FA_STAMP(4);  // MMA: wait K
+            }
+            issue_s(i, j + 1);
+            FA_TRACE(5); FA_STAMP(5);  // MMA: issue S
+          }
           if (i == 1 && more) fa_mma_commit(bar_addr(sb, BAR_KEMPTY + s1));
         }
       }
     }
   } else if (warp < 8) {
     // ================================ softmax warpgroups ==================================
+    fa_setmaxnreg_inc<REGS_SOFTMAX>();
     const int i = warp >> 2;                       // query tile of this warpgroup
     const int lane_base = (warp & 3) * 32;         // TMEM lanes this warp may touch
     const int r = lane_base + lane;                // row inside the tile
@@ -511,152 +599,20 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
     const fa_u32 t_s = tmem + ((fa_u32)lane_base << 16) + COL_S + i * BN;
     const fa_u32 t_o = tmem + ((fa_u32)lane_base << 16) + COL_O + i * D;
     const fa_u32 t_p = SEP_P ? tmem + ((fa_u32)lane_base << 16) + COL_P + i * 64 : t_s;
-    float m_ref = FA_NEG_INF, l = 0.f;
-    fa_u32 cnt = 0;
     bool ok = true;
-    const float sc2 = p.scale * FA_LOG2E;
-    FA_TRACE_DECL
+    SoftmaxCtx c = {p, sb, t_s, t_o, t_p, i, warp, qi, gb, gh, p.scale * FA_LOG2E, abort_flag, sched_tile, FA_NEG_INF, 0.f, 0u
+#if FA_TC_TRACE
+                    , trace_on, clock64()
+#endif
+    };
     for (int j = 0; j < nsteps && ok; ++j) {
       const int mode = sched_mode[2 * j + i];
       if (mode == 0) continue;
-      const int n0 = (int)sched_tile[j] * BN;
-      ok = fa_mbar_wait_warp(bar_addr(sb, BAR_S + i), cnt & 1u, abort_flag);
-      if (warp == 0) { FA_TRACE(10); }  // softmax: wait S
-      if (!ok) break;
-      fa_tc_fence_after();
-      const bool ragged = n0 + BN > p.Skv;
-#if FA_HAS_SCORE_MOD || FA_HAS_MASK_MOD || FA_ROUND_SCORES
-      const bool plain = false;
-#else
-      const bool plain = !ragged && sc2 > 0.f;
-#endif
-#if FA_TC_AFFINE_RECOMP && FA_HAS_SCORE_MOD && defined(FA_SCORE_AFFINE_CHEAP) && !FA_ROUND_SCORES
-      const bool recomp = !ragged && !(FA_HAS_MASK_MOD && mode == 1);
-#else
-      const bool recomp = false;
-#endif
-      // ---- pass 1: row maximum.  The plain path (no mods, full tile) takes it over the raw
-      // scores; otherwise the scores are scaled / modded / masked, converted to log2 units
-      // and written back to TMEM in place, so that pass 2 can read them again.  An affine
-      // score_mod (A * score + B) costs one FMA: A and B absorb the scale and log2(e).
-      RowMax rm = {FA_NEG_INF, FA_NEG_INF, FA_NEG_INF, FA_NEG_INF};
-      {
-        float va[32], vb[32];
-#define FA_P1(V, C0)                                                                                   \
-  pass1_chunk<C0>(V, rm, plain, recomp, ragged, mode, n0, qi, gb, gh, p.scale, sc2, p.Skv);             \
-  if (!plain && !recomp) fa_tmem_st32(t_s + C0, V);
-        fa_tmem_ld32(t_s, va);
-        fa_tmem_wait_ld();
-        fa_tmem_ld32(t_s + 32, vb);
-        FA_P1(va, 0)
-        fa_tmem_wait_ld();
-        if (SPLIT_S) {
-          ok = fa_mbar_wait_warp(bar_addr(sb, BAR_S2 + i), cnt & 1u, abort_flag);
-          fa_tc_fence_after();
-        }
-        fa_tmem_ld32(t_s + 64, va);
-        FA_P1(vb, 32)
-        fa_tmem_wait_ld();
-        fa_tmem_ld32(t_s + 96, vb);
-        FA_P1(va, 64)
-        fa_tmem_wait_ld();
-        FA_P1(vb, 96)
-#undef FA_P1
-        if (!plain && !recomp) fa_tmem_wait_st();
-      }
-      if (warp == 0) { FA_TRACE(11); }  // softmax: pass 1
-      float mx = fmaxf(fmaxf(rm.a, rm.b), fmaxf(rm.c, rm.d));
-      if (plain) mx *= sc2;
-      // running maximum, raised lazily
-      const float m_new = fmaxf(m_ref, mx);
-      bool need = false;
-      float corr = 1.f;
-      if (m_ref == FA_NEG_INF) {
-        m_ref = m_new;  // nothing accumulated yet for this row
-      } else if (m_new - m_ref > RESCALE_THRESHOLD) {
-        need = true;
-        corr = fa_ex2(m_ref - m_new);
-        m_ref = m_new;
-        l *= corr;
-      }
-      if (cnt > 0 && __any_sync(0xffffffffu, need)) {
-        // O_i of the previous steps has to be complete before it is rescaled in place
-        ok = fa_mbar_wait_warp(bar_addr(sb, BAR_O + i), (cnt - 1) & 1u, abort_flag);
-        if (!ok) break;
-        fa_tc_fence_after();
-#pragma unroll 1
-        for (int c = 0; c < D / 16; ++c) {
-          float o[16];
-          fa_tmem_ld16(t_o + c * 16, o);
-          fa_tmem_wait_ld();
-#pragma unroll
-          for (int e = 0; e < 16; ++e) o[e] *= corr;
-          fa_tmem_st16f(t_o + c * 16, o);
-        }
-      }
-      // ---- pass 2: p = 2^(x * cmul - m) and the row sum; P goes to TMEM as 16-bit pairs.
-      // P chunk c (16 columns) overwrites score columns that have already been read.
-      // With FA_TC_HALF_EXP the exponent is rounded to the 16-bit input type first and one SFU
-      // operation yields both values of a pair already in the format the second product needs;
-      // the row sum is then taken over exactly the values that product sees.
-      const float m_use = (m_ref == FA_NEG_INF) ? 0.f : m_ref;
-      const fa_u64 negm = fa_f2(-m_use, -m_use);
-      const float cm = plain ? sc2 : 1.f;
-      const fa_u64 cmul = fa_f2(cm, cm);
-      fa_u64 sum_a = fa_f2(0.f, 0.f), sum_b = fa_f2(0.f, 0.f);
-      if (SEP_P && cnt > 0) {
-        // P has its own columns: the previous PV product must be done reading them
-        ok = fa_mbar_wait_warp(bar_addr(sb, BAR_O + i), (cnt - 1) & 1u, abort_flag);
-        if (!ok) break;
-        fa_tc_fence_after();
-      }
-      {
-        float va[32], vb[32];
-        fa_u32 pk[16];
-        fa_tmem_ld32(t_s, va);
-        fa_tmem_wait_ld();
-        fa_tmem_ld32(t_s + 32, vb);
-#define FA_P2(V, C0)                                                                           \
-  if (recomp) pass2_chunk_affine<C0>(V, pk, -m_use, sum_a, sum_b, n0, qi, gb, gh, sc2);         \
-  else pass2_chunk(V, pk, cmul, negm, sum_a, sum_b);
-        FA_P2(va, 0)
-        fa_tmem_st16(t_p, pk);
-        fa_tmem_wait_ld();
-        if (SPLIT_S) {
-          // columns 0..63 of this step's scores are in registers
-          fa_tc_fence_before();
-          fa_mbar_arrive(bar_addr(sb, BAR_SFREE + i));
-        }
-        fa_tmem_ld32(t_s + 64, va);
-        FA_P2(vb, 32)
-        fa_tmem_st16(t_p + 16, pk);
-        fa_tmem_wait_ld();
-        fa_tmem_ld32(t_s + 96, vb);
-        FA_P2(va, 64)
-        fa_tmem_st16(t_p + 32, pk);
-        fa_tmem_wait_ld();
-        if (SEP_P) {
-          // every score of this step is in registers: columns 64..127 may be overwritten too
-          fa_tc_fence_before();
-          fa_mbar_arrive(bar_addr(sb, BAR_SFREE2 + i));
-        }
-        FA_P2(vb, 96)
-        fa_tmem_st16(t_p + 48, pk);
-#undef FA_P2
-      }
-      float sum;
-      {
-        float s0, s1;
-        fa_f2_unpack(fa_add2(sum_a, sum_b), s0, s1);
-        sum = s0 + s1;
-      }
-      l += sum;
-      fa_tmem_wait_st();
-      fa_tc_fence_before();
-      fa_mbar_arrive(bar_addr(sb, BAR_P + i));
-      ++cnt;
-      if (warp == 0) { FA_TRACE(12); }  // softmax: pass 2 + stores
+      const bool masked = (FA_HAS_MASK_MOD && mode == 1) || (int)sched_tile[j] * BN + BN > p.Skv;
+      ok = masked ? softmax_step<true>(c, j, mode) : softmax_step<false>(c, j, mode);
     }
+    const float m_ref = c.m_ref, l = c.l;
+    const fa_u32 cnt = c.cnt;
     // ---- epilogue: O / l and the logsumexp of this thread's row ---------------------------
     if (ok && cnt > 0) ok = fa_mbar_wait_warp(bar_addr(sb, BAR_O + i), (cnt - 1) & 1u, abort_flag);
     if (ok) {

@@ -46,6 +46,9 @@ __device__ __forceinline__ fa_u64 fa_globaltimer() {
 #ifndef FA_WAIT_SLEEP_NS
 #define FA_WAIT_SLEEP_NS 40
 #endif
+#ifndef FA_WAIT_ISSUER_SLEEP
+#define FA_WAIT_ISSUER_SLEEP 0
+#endif
 // SLEEP: back off between polls so that waiting warps leave the issue slots of their scheduler
 // to the warps that have work (the MMA issuer polls without sleeping).
 template <bool SLEEP>
@@ -67,7 +70,7 @@ __device__ __forceinline__ bool fa_mbar_wait_t(fa_u32 bar, fa_u32 parity, volati
   }
 }
 __device__ __forceinline__ bool fa_mbar_wait(fa_u32 bar, fa_u32 parity, volatile int* abort_flag) {
-  return fa_mbar_wait_t<false>(bar, parity, abort_flag);
+  return fa_mbar_wait_t<FA_WAIT_ISSUER_SLEEP != 0>(bar, parity, abort_flag);
 }
 // warp-uniform variant: every lane waits, the warp agrees on the outcome (needed before
 // warp-collective tcgen05 instructions)
