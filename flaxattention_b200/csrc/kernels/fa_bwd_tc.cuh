@@ -129,21 +129,21 @@ __device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.
 __device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // Element-wise work of one thread on a 32-column chunk: scores s and dp (fp32, raw) for kv row
-// `kv` and q columns q0 .. q0+31 -> packed P^T and dS^T (16 bit).  C0 (chunk offset inside the
-// 128-column tile) is a template parameter and q0 a multiple of 128 plus C0, so the low bits of
-// the q index are compile-time constants inside the mods.
-template <int C0>
+// `kv` and q columns q0 .. q0+31 -> packed P^T and dS^T (16 bit).  q0 is a multiple of 32 (the
+// compiler can see that from how the caller builds it), so the low five bits of every q index are
+// compile-time constants inside the mods while one copy of this code serves all four chunks of a
+// tile row.  nlse2 / ndelta point at the row scalars of column q0.
 __device__ __forceinline__ void chunk(const float (&s)[32], const float (&dp)[32], const float* nlse2, const float* ndelta,
-                                      fa_u32 (&pp)[16], fa_u32 (&ds)[16], int mode, int m0, int kv, int gb, int gh,
+                                      fa_u32 (&pp)[16], fa_u32 (&ds)[16], int mode, int q0, int kv, int gb, int gh,
                                       float scale, float sc2) {
 #pragma unroll
   for (int e = 0; e < 32; e += 4) {
-    const float4 nl = *(const float4*)(nlse2 + C0 + e);
-    const float4 nd = *(const float4*)(ndelta + C0 + e);
+    const float4 nl = *(const float4*)(nlse2 + e);
+    const float4 nd = *(const float4*)(ndelta + e);
     float pv[4], dv[4];
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-      const int qi = m0 | (C0 + e + u);
+      const int qi = q0 | (e + u);
       const float nlu = u == 0 ? nl.x : (u == 1 ? nl.y : (u == 2 ? nl.z : nl.w));
       const float ndu = u == 0 ? nd.x : (u == 1 ? nd.y : (u == 2 ? nd.z : nd.w));
       float x = s[e + u];
@@ -262,6 +262,9 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
   const fa_u32 tmem = (fa_u32)misc[0];
   npairs = misc[2];
   volatile int* abort_flag = misc + 1;
+  // copies the compiler can see are the same in every lane (read through a broadcast)
+  const fa_u32 tmem_u = __shfl_sync(0xffffffffu, tmem, 0);
+  const int npairs_u = __shfl_sync(0xffffffffu, npairs, 0);
 
   if (warp >= 8) fa_setmaxnreg_dec<REGS_OTHER>();
 
@@ -303,50 +306,55 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
   } else if (warp == WARP_MMA) {
     // ================================ MMA issuer A: products 1-2 ===============================
     // (two issuing warps, so that the waits of one overlap the issue of the other; warp A also
-    //  owns the TMEM allocation)
-    if (lane == 0 && npairs > 0) {
+    //  owns the TMEM allocation).  The whole warp runs the loop and one elected lane issues: with
+    //  uniform control flow the descriptors live in uniform registers, which makes each
+    //  tcgen05.mma cheaper to issue than from a single-lane branch, and the issue rate of this
+    //  one thread is what bounds the tensor core here.
+    if (npairs_u > 0) {
+      const bool leader = fa_elect_one();
       constexpr fa_u32 IDESC_KK = fa_idesc(DT, 128, 128, 0, 0);  // A, B K-major, N = 128
       constexpr fa_u32 HI = fa_desc_hi_sw128();
       const fa_u32 loK_k = fa_desc_lo(sb + OFF_K, 16), loV_k = fa_desc_lo(sb + OFF_V, 16);
-      bool ok = fa_mbar_wait(bar_addr(sb, BAR_KV), 0, abort_flag);
+      bool ok = fa_mbar_wait_all(bar_addr(sb, BAR_KV), 0, abort_flag);
       FA_TRACE_DECL
-      for (int n = 0; n < npairs && ok; ++n) {
+      for (int n = 0; n < npairs_u && ok; ++n) {
         const int s = n % NSTAGE;
-        ok = fa_mbar_wait(bar_addr(sb, BAR_QFULL + s), (fa_u32)((n / NSTAGE) & 1), abort_flag);
+        ok = fa_mbar_wait_all(bar_addr(sb, BAR_QFULL + s), (fa_u32)((n / NSTAGE) & 1), abort_flag);
         FA_TRACE(1); FA_STAMP(1);   // MMA A: wait for Q/dO
-        if (ok && n > 0) ok = fa_mbar_wait(bar_addr(sb, BAR_SFREE), (fa_u32)((n - 1) & 1), abort_flag);
+        if (ok && n > 0) ok = fa_mbar_wait_all(bar_addr(sb, BAR_SFREE), (fa_u32)((n - 1) & 1), abort_flag);
         FA_TRACE(2); FA_STAMP(2);   // MMA A: wait for S^T/dP^T of the previous pair to be read
         if (!ok) break;
         fa_tc_fence_after();
         const fa_u32 loQ = fa_desc_lo(sb + OFF_Q + s * ATOM_BYTES, 16), loDO = fa_desc_lo(sb + OFF_DO + s * ATOM_BYTES, 16);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          fa_mma_ss(tmem + COL_S, fa_desc_make(loK_k + kk * 2, HI), fa_desc_make(loQ + kk * 2, HI), IDESC_KK, kk > 0);
+          if (leader) fa_mma_ss(tmem_u + COL_S, fa_desc_make(loK_k + kk * 2, HI), fa_desc_make(loQ + kk * 2, HI), IDESC_KK, kk > 0);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          fa_mma_ss(tmem + COL_DP, fa_desc_make(loV_k + kk * 2, HI), fa_desc_make(loDO + kk * 2, HI), IDESC_KK, kk > 0);
-        fa_mma_commit(bar_addr(sb, BAR_SFULL));
-        fa_mma_commit(bar_addr(sb, BAR_QEMPTY + s));  // first of the two arrivals that free each tile of the stage
-        fa_mma_commit(bar_addr(sb, BAR_DOEMPTY + s));
+          if (leader) fa_mma_ss(tmem_u + COL_DP, fa_desc_make(loV_k + kk * 2, HI), fa_desc_make(loDO + kk * 2, HI), IDESC_KK, kk > 0);
+        if (leader) {
+          fa_mma_commit(bar_addr(sb, BAR_SFULL));
+          fa_mma_commit(bar_addr(sb, BAR_QEMPTY + s));  // first of the two arrivals that free each tile of the stage
+          fa_mma_commit(bar_addr(sb, BAR_DOEMPTY + s));
+        }
         FA_TRACE(3); FA_STAMP(3);   // MMA A: issue products 1-2
       }
     }
   } else if (warp == WARP_MMA_B) {
     // ================================ MMA issuer B: products 3-5 ===============================
-    if (lane == 0 && npairs > 0) {
+    if (npairs_u > 0) {
+      const bool leader = fa_elect_one();
       constexpr fa_u32 IDESC_TN = fa_idesc(DT, 128, D, 0, 1);    // A K-major (TMEM or smem), B MN-major, N = 64
       constexpr fa_u32 IDESC_NN = fa_idesc(DT, 128, D, 1, 1);    // A, B MN-major
       constexpr fa_u32 HI = fa_desc_hi_sw128();
       const fa_u32 loK_mn = fa_desc_lo(sb + OFF_K, ATOM_BYTES);
       const fa_u32 loDS_k = fa_desc_lo(sb + OFF_DS, 16), loDS_mn = fa_desc_lo(sb + OFF_DS, ATOM_BYTES);
-      bool ok = fa_mbar_wait(bar_addr(sb, BAR_KV), 0, abort_flag);
+      bool ok = fa_mbar_wait_all(bar_addr(sb, BAR_KV), 0, abort_flag);
       FA_TRACE_DECL
-      for (int n = 0; n < npairs && ok; ++n) {
+      for (int n = 0; n < npairs_u && ok; ++n) {
         const int s = n % NSTAGE;
-        ok = fa_mbar_wait(bar_addr(sb, BAR_PREADY), (fa_u32)(n & 1), abort_flag);
+        ok = fa_mbar_wait_all(bar_addr(sb, BAR_PREADY), (fa_u32)(n & 1), abort_flag);
         FA_TRACE(4); FA_STAMP(4);     // MMA B: wait for P^T / dS^T
-        if (ok && n > 0) ok = fa_mbar_wait(bar_addr(sb, BAR_DQFREE), (fa_u32)((n - 1) & 1), abort_flag);
-        FA_TRACE(5); FA_STAMP(5);     // MMA B: wait for the dQ drain
         if (!ok) break;
         fa_tc_fence_after();
         {
@@ -356,24 +364,32 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
           // 3. dV += P^T dO      (K = 128 q values, 8 steps of 16 rows = 2048 bytes; A from TMEM)
 #pragma unroll
           for (int kk = 0; kk < BT / 16; ++kk)
-            fa_mma_ts(tmem + COL_DV, tmem + COL_P + kk * 8, fa_desc_make(loDO_mn + kk * 128, HI), IDESC_TN, acc | (kk > 0));
-          fa_mma_commit(bar_addr(sb, BAR_DOEMPTY + s));  // second arrival: the dO tile is free
+            if (leader) fa_mma_ts(tmem_u + COL_DV, tmem_u + COL_P + kk * 8, fa_desc_make(loDO_mn + kk * 128, HI), IDESC_TN, acc | (kk > 0));
+          if (leader) fa_mma_commit(bar_addr(sb, BAR_DOEMPTY + s));  // second arrival: the dO tile is free
           FA_TRACE(7); FA_STAMP(7);   // MMA B: issue product 3
           // 4. dK += dS^T Q     (A = dS^T K-major: k-step kk is 32 bytes into atom kk / 4)
 #pragma unroll
           for (int kk = 0; kk < BT / 16; ++kk)
-            fa_mma_ss(tmem + COL_DK, fa_desc_make(loDS_k + (kk >> 2) * (ATOM_BYTES >> 4) + (kk & 3) * 2, HI),
-                      fa_desc_make(loQ_mn + kk * 128, HI), IDESC_TN, acc | (kk > 0));
-          fa_mma_commit(bar_addr(sb, BAR_QEMPTY + s));   // second arrival: the Q tile and row scalars are free
+            if (leader)
+              fa_mma_ss(tmem_u + COL_DK, fa_desc_make(loDS_k + (kk >> 2) * (ATOM_BYTES >> 4) + (kk & 3) * 2, HI),
+                        fa_desc_make(loQ_mn + kk * 128, HI), IDESC_TN, acc | (kk > 0));
+          if (leader) fa_mma_commit(bar_addr(sb, BAR_QEMPTY + s));   // second arrival: the Q tile and row scalars are free
           FA_TRACE(8); FA_STAMP(8);   // MMA B: issue product 4
-          // 5. dQ = dS K        (A = dS^T read MN-major: M chunks of 64 q one atom apart; K = 128 kv rows)
+          // 5. dQ = dS K        (A = dS^T read MN-major: M chunks of 64 q one atom apart; K = 128 kv rows);
+          //                      the drain warps must have emptied the dQ columns of the previous pair
+          if (n > 0) ok = fa_mbar_wait_all(bar_addr(sb, BAR_DQFREE), (fa_u32)((n - 1) & 1), abort_flag);
+          FA_TRACE(5); FA_STAMP(5);   // MMA B: wait for the dQ drain
+          if (!ok) break;
+          fa_tc_fence_after();
 #pragma unroll
           for (int kk = 0; kk < BT / 16; ++kk)
-            fa_mma_ss(tmem + COL_DQ, fa_desc_make(loDS_mn + kk * 128, HI), fa_desc_make(loK_mn + kk * 128, HI), IDESC_NN, kk > 0);
+            if (leader) fa_mma_ss(tmem_u + COL_DQ, fa_desc_make(loDS_mn + kk * 128, HI), fa_desc_make(loK_mn + kk * 128, HI), IDESC_NN, kk > 0);
         }
-        fa_mma_commit(bar_addr(sb, BAR_PFREE));
-        fa_mma_commit(bar_addr(sb, BAR_DQFULL));
-        if (n + 1 == npairs) fa_mma_commit(bar_addr(sb, BAR_FINAL));
+        if (leader) {
+          fa_mma_commit(bar_addr(sb, BAR_PFREE));
+          fa_mma_commit(bar_addr(sb, BAR_DQFULL));
+          if (n + 1 == npairs_u) fa_mma_commit(bar_addr(sb, BAR_FINAL));
+        }
         FA_TRACE(6); FA_STAMP(6);     // MMA B: issue product 5 + commits
       }
     }
@@ -418,13 +434,9 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
       const float* rowp = (const float*)(sm + OFF_ROW + s * 2 * 128 * 4);
       fa_u32 pp0[16], pp1[16], ds0[16], ds1[16];
       if (row_ok && !(FA_TC_EXP & 4)) {
-        if (half == 0) {
-          chunk<0>(sa, da, rowp, rowp + 128, pp0, ds0, mode, m0, kv, gb, gh, p.scale, sc2);
-          chunk<32>(sb2, db, rowp, rowp + 128, pp1, ds1, mode, m0, kv, gb, gh, p.scale, sc2);
-        } else {
-          chunk<64>(sa, da, rowp, rowp + 128, pp0, ds0, mode, m0, kv, gb, gh, p.scale, sc2);
-          chunk<96>(sb2, db, rowp, rowp + 128, pp1, ds1, mode, m0, kv, gb, gh, p.scale, sc2);
-        }
+        const int c0 = half * 64;  // first q column of this thread inside the tile
+        chunk(sa, da, rowp + c0, rowp + 128 + c0, pp0, ds0, mode, m0 + c0, kv, gb, gh, p.scale, sc2);
+        chunk(sb2, db, rowp + c0 + 32, rowp + 128 + c0 + 32, pp1, ds1, mode, m0 + c0 + 32, kv, gb, gh, p.scale, sc2);
       } else {
 #pragma unroll
         for (int e = 0; e < 16; ++e) pp0[e] = pp1[e] = ds0[e] = ds1[e] = 0u;

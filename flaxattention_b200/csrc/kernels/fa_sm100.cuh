@@ -79,6 +79,24 @@ __device__ __forceinline__ bool fa_mbar_wait_warp(fa_u32 bar, fa_u32 parity, vol
   return __all_sync(0xffffffffu, ok);
 }
 
+// every lane polls (no back-off) and the warp agrees on the outcome: for a warp whose control
+// flow stays uniform while one elected lane issues the tcgen05.mma instructions (every lane,
+// the elected one included, has then observed the barrier itself)
+__device__ __forceinline__ bool fa_mbar_wait_all(fa_u32 bar, fa_u32 parity, volatile int* abort_flag) {
+  const bool ok = fa_mbar_wait_t<false>(bar, parity, abort_flag);
+  return __all_sync(0xffffffffu, ok);
+}
+// true in exactly one lane of a converged warp
+__device__ __forceinline__ bool fa_elect_one() {
+  fa_u32 pred;
+  asm volatile(
+      "{\n\t.reg .pred P1;\n\t.reg .b32 r;\n\t"
+      "elect.sync r|P1, 0xffffffff;\n\t"
+      "selp.b32 %0, 1, 0, P1;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // ---- TMA -------------------------------------------------------------------------------
 // 4-d tile load (coordinates innermost first), completion counted in bytes on `bar`
 __device__ __forceinline__ void fa_tma_load_4d(fa_u32 dst, const FaTensorMap* map, fa_u32 bar, int c0, int c1, int c2,
