@@ -746,13 +746,44 @@ bool tc_fwd_eligible(const fa_attn_params* p) {
   return true;
 }
 
-int get_fwd_tc_kernel(fa_module* m, int dtype, int D, int flags, Kernel** k) {
-  const int atoms = D / 64, nstage = D == 64 ? 3 : 2;
+// decode = true selects the split-KV variant of the kernel (one query tile per CTA, partial results)
+int get_fwd_tc_kernel(fa_module* m, int dtype, int D, int flags, Kernel** k, bool decode = false) {
+  // must match the shared-memory map of fa_fwd_tc.cuh (fa_tc::SMEM_BYTES)
+  const int atoms = D / 64, nstage = decode ? 5 : (D == 64 ? 3 : 2);
   const int smem = 2 * atoms * 16384 + 2 * nstage * atoms * 16384 + (1 + 4 * nstage + 8) * 8 + 16 + 256 * 2 + 256 * 2 +
                    2 * 256 + 1024;
-  std::string d = defs({{"FA_DTYPE", dtype}, {"FA_D", D}, {"FA_ROUND_SCORES", round_flag(dtype, flags)}});
+  std::string d = defs({{"FA_DTYPE", dtype}, {"FA_D", D}, {"FA_ROUND_SCORES", round_flag(dtype, flags)}, {"FA_TC_DECODE", decode ? 1 : 0}});
   d += extra_defines();
   return get_kernel(m, "fa_fwd_tc.cuh", d, "fa_fwd_tc_kernel", smem, k);
+}
+
+// Shapes the split-KV variant of the tcgen05 kernel covers (`num_splits` partial results per row,
+// two per CTA); everything else runs on the general decode kernel.
+bool tc_decode_eligible(const fa_attn_params* p) {
+  if (p->flags & FA_FLAG_GENERAL_KERNELS) return false;
+  if (p->dtype == FA_F32) return false;
+  if (p->D != 64 || p->Dv != 64) return false;
+  // The kernel gives every query row a thread and pads the tile to 128 rows, so its softmax work
+  // per kv tile does not shrink with Sq: measured against the general decode kernel it wins from
+  // about 33 rows up (0.52 ms against 0.62 ms at 64 rows) and loses below (0.49 against 0.29 at 16).
+  if (p->Sq < 33 || p->Sq > 64 || p->Skv < 1024 || p->Skv > 32768) return false;
+  if (!(p->scale > 0.f)) return false;
+  const fa_block_tables& t = p->tables;
+  if (t.kv_num_blocks) {
+    if (t.num_q_blocks != 1) return false;
+    if (!(t.num_kv_blocks == 1 || t.kv_block_size % 128 == 0)) return false;
+  }
+  return true;
+}
+int launch_decode_tc(fa_module* m, const fa_attn_params* p, const FaParams& kp, int num_splits, void* stream) {
+  Kernel* k = nullptr;
+  if (int rc = get_fwd_tc_kernel(m, p->dtype, p->D, p->flags, &k, true)) return rc;
+  FaTcParamsHost tp;
+  tp.p = kp;
+  if (int rc = make_map(&tp.tq, p->dtype, p->q, p->D, p->Sq, p->Hq, p->B)) return rc;
+  if (int rc = make_map(&tp.tk, p->dtype, p->k, p->D, p->Skv, p->Hkv, p->B)) return rc;
+  if (int rc = make_map(&tp.tv, p->dtype, p->v, p->Dv, p->Skv, p->Hkv, p->B)) return rc;
+  return launch(k, dim3(num_splits / 2, p->Hq, p->B), dim3(384), &tp, stream);
 }
 
 int launch_fwd_tc(fa_module* m, const fa_attn_params* p, const FaParams& kp, void* stream) {
@@ -974,6 +1005,27 @@ int fa_decode_num_splits(const fa_attn_params* p, int sm_count) {
   if (sm_count <= 0) sm_count = 148;
   const long long bh = (long long)p->B * p->Hq;
   const int tiles = (p->Skv + 127) / 128;
+  if (tc_decode_eligible(p)) {
+    // One CTA per SM, two partial results per CTA.  Take the smallest number of CTAs per
+    // (batch, head) whose grid fills its last wave to 95 % (else the best found), with at least
+    // eight kv tiles per CTA.
+    const int cmax = tiles / 8 > 1 ? (tiles / 8 < 64 ? tiles / 8 : 64) : 1;
+    int best = 1;
+    double best_eff = 0.0;
+    for (int c = 1; c <= cmax; ++c) {
+      const double waves = (double)(bh * c) / sm_count;
+      const double eff = waves / (double)(long long)(waves + 0.999999);
+      if (eff > best_eff + 1e-9) {
+        best_eff = eff;
+        best = c;
+      }
+      if (eff >= 0.95) {
+        best = c;
+        break;
+      }
+    }
+    return 2 * best;
+  }
   long long want = (4ll * sm_count + bh - 1) / bh;
   const int cap = tiles / 4 > 1 ? tiles / 4 : 1;
   if (want > cap) want = cap;
@@ -995,20 +1047,27 @@ int fa_decode(fa_module* m, const fa_attn_params* p, int num_splits, void* works
   if (num_splits > 65535) return fail(FA_EINVAL, "too many splits");
   FaParams kp;
   fill_params(p, kp);
+  const bool tc = tc_decode_eligible(p) && num_splits >= 2 && num_splits % 2 == 0;
   DecCfg c;
-  if (int rc = pick_decode(p->dtype, p->D, p->Dv, p->Sq, &kp.t, c)) return rc;
+  if (!tc)
+    if (int rc = pick_decode(p->dtype, p->D, p->Dv, p->Sq, &kp.t, c)) return rc;
   const size_t need = fa_decode_workspace_bytes(p, num_splits);
   if (need && (!workspace || workspace_bytes < need)) return fail(FA_EWORKSPACE, "decode workspace too small");
   if (need && ((uintptr_t)workspace & 15)) return fail(FA_EINVAL, "workspace must be 16-byte aligned");
-  Kernel* k = nullptr;
-  if (int rc = get_decode_kernel(m, p->dtype, p->D, p->Dv, p->flags, c, &k)) return rc;
   kp.num_splits = num_splits;
   if (need) {
     const size_t rows = (size_t)p->B * p->Hq * num_splits * p->Sq;
     kp.part_o = (float*)workspace;
     kp.part_ml = (float*)((char*)workspace + (rows * p->Dv * sizeof(float) + 255) / 256 * 256);
   }
-  if (int rc = launch(k, dim3(num_splits, p->Hq, p->B), dim3(128), &kp, stream)) return rc;
+  if (tc) {
+    // tcgen05 kernel: num_splits / 2 CTAs per (batch, head), each writing two partial results
+    if (int rc = launch_decode_tc(m, p, kp, num_splits, stream)) return rc;
+  } else {
+    Kernel* k = nullptr;
+    if (int rc = get_decode_kernel(m, p->dtype, p->D, p->Dv, p->flags, c, &k)) return rc;
+    if (int rc = launch(k, dim3(num_splits, p->Hq, p->B), dim3(128), &kp, stream)) return rc;
+  }
   if (num_splits > 1) {
     const long long n_rows = (long long)p->B * p->Hq * p->Sq;
     const unsigned blocks = (unsigned)((n_rows + 3) / 4);

@@ -37,7 +37,16 @@ constexpr int D = FA_D;
 constexpr int BM = 128, BN = 128;
 constexpr int ATOMS = D / 64;            // 64-element (128-byte) column groups per row
 constexpr int ATOM_BYTES = 128 * 128;    // 128 rows x 128 bytes
-constexpr int NSTAGE = D == 64 ? 3 : 2;
+// Split-KV decode variant (FA_TC_DECODE, D = 64): the CTA owns ONE query tile (Sq <= 128 rows,
+// the rest of the 128 is padding) and a contiguous share of the kv tiles the BlockMask lists; the
+// two softmax warpgroups take alternate kv tiles of that share, so both work on the same
+// query rows, and each writes its own un-normalised partial result (running maximum, sum, O)
+// for the combine kernel.  More stages, since the kv stream is all there is.
+#ifndef FA_TC_DECODE
+#define FA_TC_DECODE 0
+#endif
+constexpr bool DECODE = FA_TC_DECODE != 0;
+constexpr int NSTAGE = DECODE ? 5 : (D == 64 ? 3 : 2);
 constexpr int Q_BYTES = 2 * ATOMS * ATOM_BYTES;
 constexpr int KV_STAGE = ATOMS * ATOM_BYTES;
 constexpr int MAXT = 256;                // kv tiles per row of the block grid (Skv <= 32768)
@@ -98,6 +107,7 @@ constexpr int WARP_PRODUCER = 8, WARP_MMA = 9, WARP_MMA_B = 10;
 constexpr float RESCALE_THRESHOLD = 8.0f;  // log2 units
 
 static_assert(D == 64 || D == 128, "head dim 64 or 128");
+static_assert(!DECODE || D == 64, "the decode variant is written for head dim 64");
 static_assert(DT == FA_DT_F16 || DT == FA_DT_BF16, "16-bit inputs");
 
 __device__ __forceinline__ fa_u32 bar_addr(fa_u32 sbase, int i) { return sbase + OFF_BAR + i * 8; }
@@ -219,7 +229,7 @@ __device__ __forceinline__ bool softmax_step(SoftmaxCtx& c, const int j, const i
   long long& trace_t0 = c.trace_t0;
 #endif
   const short* sched_tile = c.sched_tile;
-  const int n0 = (int)sched_tile[j] * BN;
+  const int n0 = (int)sched_tile[DECODE ? 2 * j + i : j] * BN;
   if (!fa_mbar_wait_warp(bar_addr(sb, BAR_S + i), cnt & 1u, abort_flag)) return false;
   if (warp == 0) { FA_TRACE(10); FA_STAMP(10); }  // softmax: wait S
   fa_tc_fence_after();
@@ -337,9 +347,14 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
   unsigned char* sm = smem_raw + (sb - raw);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#if FA_TC_DECODE
+  const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;  // grid: (kv shares, heads, batch)
+  const int m0 = 0;
+#else
   const int pair = gridDim.z - 1 - blockIdx.z;  // grid: (heads, batch, tile pairs), the last pair first
   const int h = blockIdx.x, b = blockIdx.y;
   const int m0 = pair * 2 * BM;
+#endif
   const int hk = h / (p.Hq / p.Hkv);
   const int gb = b + p.b_off, gh = h + p.h_off;
 
@@ -375,7 +390,7 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
   if (warp == WARP_MMA) fa_tmem_alloc(sb + OFF_MISC, TMEM_COLS);
   __syncthreads();
   // class of every kv tile for both query tiles: 0 skip, 1 apply mask_mod, 2 full
-  for (int i = 0; i < 2; ++i) {
+  for (int i = 0; i < (DECODE ? 1 : 2); ++i) {
     const int mi = m0 + i * BM;
     if (mi >= p.Sq) continue;
     if (p.t.kv_num == nullptr) {
@@ -401,6 +416,26 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
   }
   __syncthreads();
   if (tid == 0) {
+#if FA_TC_DECODE
+    // this CTA's share of the listed kv tiles; entry k of the share belongs to warpgroup k % 2
+    int n_all = 0;
+    for (int t = 0; t < ntiles; ++t) n_all += cls[t] != 0;
+    const int per = (n_all + (int)gridDim.x - 1) / (int)gridDim.x;
+    const int lo = split * per, hi = min(n_all, lo + per);
+    int n = 0, k = 0;
+    for (int t = 0; t < ntiles; ++t) {
+      if (!cls[t]) continue;
+      if (n >= lo && n < hi) {
+        sched_tile[k] = (short)t;
+        sched_mode[k] = cls[t];
+        ++k;
+      }
+      ++n;
+    }
+    sched_mode[k] = 0;  // an odd share leaves the second warpgroup without a tile in the last step
+    misc[2] = (k + 1) / 2;
+    misc[3] = k;
+#else
     int n = 0;
     for (int t = 0; t < ntiles; ++t) {
       const unsigned char c0 = cls[t], c1 = cls[MAXT + t];
@@ -412,12 +447,15 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
       }
     }
     misc[2] = n;
+    misc[3] = n;
+#endif
   }
   fa_tc_fence_before();
   __syncthreads();
   fa_tc_fence_after();
   const fa_u32 tmem = (fa_u32)misc[0];
-  const int nsteps = misc[2];
+  const int nsteps = misc[2];   // steps of the softmax / MMA loops
+  const int nloads = misc[3];   // kv tiles the producer brings in (two per step in the decode variant)
   volatile int* abort_flag = misc + 1;
 
   if (warp >= 8) fa_setmaxnreg_dec<REGS_OTHER>();
@@ -427,12 +465,12 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
       fa_tma_prefetch_desc(&P.tq);
       fa_tma_prefetch_desc(&P.tk);
       fa_tma_prefetch_desc(&P.tv);
-      fa_mbar_expect_tx(bar_addr(sb, BAR_Q), Q_BYTES);
-      for (int i = 0; i < 2; ++i)
+      fa_mbar_expect_tx(bar_addr(sb, BAR_Q), DECODE ? Q_BYTES / 2 : Q_BYTES);
+      for (int i = 0; i < (DECODE ? 1 : 2); ++i)
         for (int a = 0; a < ATOMS; ++a)
           fa_tma_load_4d(sb + (i * ATOMS + a) * ATOM_BYTES, &P.tq, bar_addr(sb, BAR_Q), a * 64, m0 + i * BM, h, b);
       bool ok = true;
-      for (int j = 0; j < nsteps && ok; ++j) {
+      for (int j = 0; j < nloads && ok; ++j) {
         const int s = j % NSTAGE;
         const fa_u32 ph = (fa_u32)((j / NSTAGE) & 1);
         const int n0 = (int)sched_tile[j] * BN;
@@ -460,28 +498,37 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
         fa_u32 nsi[2] = {0, 0};
         FA_TRACE_DECL
         for (int j = 0; j < nsteps && ok; ++j) {
-          const int s = j % NSTAGE;
-          ok = fa_mbar_wait(bar_addr(sb, BAR_KFULL + s), (fa_u32)((j / NSTAGE) & 1), abort_flag);
+          // the kv tile of (step, query tile): the same for both tiles in the forward, alternate
+          // tiles of the CTA's share in the decode variant
+          int s = j % NSTAGE;
+          if (!DECODE) ok = fa_mbar_wait(bar_addr(sb, BAR_KFULL + s), (fa_u32)((j / NSTAGE) & 1), abort_flag);
           FA_TRACE(4); FA_STAMP(4);  // MMA A: wait K
           for (int i = 0; i < 2 && ok; ++i) {
             if (!sched_mode[2 * j + i]) continue;
+            if (DECODE) {
+              const int t = 2 * j + i;
+              s = t % NSTAGE;
+              ok = fa_mbar_wait(bar_addr(sb, BAR_KFULL + s), (fa_u32)((t / NSTAGE) & 1), abort_flag);
+              if (!ok) break;
+            }
             if (nsi[i] > 0) {
               ok = fa_mbar_wait(bar_addr(sb, BAR_SFREE2 + i), (nsi[i] - 1) & 1u, abort_flag);
               FA_TRACE(6); FA_STAMP(6);  // MMA A: wait for the previous S of the tile to be read
               if (!ok) break;
             }
             fa_tc_fence_after();
-            const fa_u32 loQ = fa_desc_lo(sb + i * ATOMS * ATOM_BYTES, 16), loK = fa_desc_lo(sb + OFF_K + s * KV_STAGE, 16);
+            const fa_u32 loQ = fa_desc_lo(sb + (DECODE ? 0 : i) * ATOMS * ATOM_BYTES, 16), loK = fa_desc_lo(sb + OFF_K + s * KV_STAGE, 16);
 #pragma unroll
             for (int kk = 0; kk < D / 16; ++kk) {
               const fa_u32 koff = ((kk / 4) * ATOM_BYTES + (kk % 4) * 32) >> 4;
               fa_mma_ss(tmem + COL_S + i * BN, fa_desc_make(loQ + koff, HI), fa_desc_make(loK + koff, HI), IDESC_S, kk > 0);
             }
             fa_mma_commit(bar_addr(sb, BAR_S + i));
+            if (DECODE) fa_mma_commit(bar_addr(sb, BAR_KEMPTY + s));
             ++nsi[i];
             FA_TRACE(5); FA_STAMP(5);  // MMA A: issue S
           }
-          fa_mma_commit(bar_addr(sb, BAR_KEMPTY + s));
+          if (!DECODE) fa_mma_commit(bar_addr(sb, BAR_KEMPTY + s));
         }
       } else {
         constexpr fa_u32 IDESC_O = fa_idesc(DT, BM, D, 0, 1);
@@ -489,11 +536,17 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
         fa_u32 cnt[2] = {0, 0};
         FA_TRACE_DECL
         for (int j = 0; j < nsteps && ok; ++j) {
-          const int s = j % NSTAGE;
-          ok = fa_mbar_wait(bar_addr(sb, BAR_VFULL + s), (fa_u32)((j / NSTAGE) & 1), abort_flag);
+          int s = j % NSTAGE;
+          if (!DECODE) ok = fa_mbar_wait(bar_addr(sb, BAR_VFULL + s), (fa_u32)((j / NSTAGE) & 1), abort_flag);
           FA_TRACE(1); FA_STAMP(1);  // MMA B: wait V
           for (int i = 0; i < 2 && ok; ++i) {
             if (!sched_mode[2 * j + i]) continue;
+            if (DECODE) {
+              const int t = 2 * j + i;
+              s = t % NSTAGE;
+              ok = fa_mbar_wait(bar_addr(sb, BAR_VFULL + s), (fa_u32)((t / NSTAGE) & 1), abort_flag);
+              if (!ok) break;
+            }
             ok = fa_mbar_wait(bar_addr(sb, BAR_P + i), cnt[i] & 1u, abort_flag);
             FA_TRACE(2); FA_STAMP(2);  // MMA B: wait P
             if (!ok) break;
@@ -504,10 +557,11 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
             for (int kk = 0; kk < BN / 16; ++kk)
               fa_mma_ts(tmem + COL_O + i * D, tmem + COL_P + i * 64 + kk * 8, fa_desc_make(loV + kk * 128, HI), IDESC_O, acc | (kk > 0));
             fa_mma_commit(bar_addr(sb, BAR_O + i));
+            if (DECODE) fa_mma_commit(bar_addr(sb, BAR_VEMPTY + s));
             ++cnt[i];
             FA_TRACE(3); FA_STAMP(3);  // MMA B: issue PV
           }
-          fa_mma_commit(bar_addr(sb, BAR_VEMPTY + s));
+          if (!DECODE) fa_mma_commit(bar_addr(sb, BAR_VEMPTY + s));
         }
       }
     }
@@ -595,7 +649,7 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
     const int i = warp >> 2;                       // query tile of this warpgroup
     const int lane_base = (warp & 3) * 32;         // TMEM lanes this warp may touch
     const int r = lane_base + lane;                // row inside the tile
-    const int qi = m0 + i * BM + r;                // query index
+    const int qi = m0 + (DECODE ? 0 : i * BM) + r;  // query index
     const fa_u32 t_s = tmem + ((fa_u32)lane_base << 16) + COL_S + i * BN;
     const fa_u32 t_o = tmem + ((fa_u32)lane_base << 16) + COL_O + i * D;
     const fa_u32 t_p = SEP_P ? tmem + ((fa_u32)lane_base << 16) + COL_P + i * 64 : t_s;
@@ -608,13 +662,37 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
     for (int j = 0; j < nsteps && ok; ++j) {
       const int mode = sched_mode[2 * j + i];
       if (mode == 0) continue;
-      const bool masked = (FA_HAS_MASK_MOD && mode == 1) || (int)sched_tile[j] * BN + BN > p.Skv;
+      const bool masked = (FA_HAS_MASK_MOD && mode == 1) || (int)sched_tile[DECODE ? 2 * j + i : j] * BN + BN > p.Skv;
       ok = masked ? softmax_step<true>(c, j, mode) : softmax_step<false>(c, j, mode);
     }
     const float m_ref = c.m_ref, l = c.l;
     const fa_u32 cnt = c.cnt;
     // ---- epilogue: O / l and the logsumexp of this thread's row ---------------------------
     if (ok && cnt > 0) ok = fa_mbar_wait_warp(bar_addr(sb, BAR_O + i), (cnt - 1) & 1u, abort_flag);
+#if FA_TC_DECODE
+    if (ok) {
+      // un-normalised partial result of this warpgroup: number 2 * share + i of the row
+      fa_tc_fence_after();
+      const long long prow = (((long long)b * p.Hq + h) * p.num_splits + 2 * split + i) * p.Sq + qi;
+#pragma unroll
+      for (int c = 0; c < D / 32; ++c) {
+        float o[32];
+        if (cnt > 0) {
+          fa_tmem_ld32(t_o + c * 32, o);
+          fa_tmem_wait_ld();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) o[e] = 0.f;
+        }
+        if (qi < p.Sq) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 4)
+            *(float4*)(p.part_o + prow * D + c * 32 + e) = make_float4(o[e], o[e + 1], o[e + 2], o[e + 3]);
+        }
+      }
+      if (qi < p.Sq) *(float2*)(p.part_ml + prow * 2) = make_float2(m_ref, l);
+    }
+#else
     if (ok) {
       fa_tc_fence_after();
       const float inv = l > 0.f ? 1.f / l : 0.f;
@@ -644,6 +722,7 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
       if (p.lse != nullptr && qi < p.Sq)
         p.lse[((long long)b * p.Hq + h) * p.Sq + qi] = l > 0.f ? (m_ref + fa_lg2(l)) * FA_LN2 : FA_NEG_INF;
     }
+#endif
   }
 
   // ---- teardown ----------------------------------------------------------------------------
