@@ -872,6 +872,8 @@ int fa_module_prepare(fa_module* m, int kind, int dtype, int D, int Dv, int Sq_h
     case FA_KIND_DECODE: {
       DecCfg c;
       if (int rc = pick_decode(dtype, D, Dv, Sq_hint, nullptr, c)) return rc;
+      if (dtype != FA_F32 && D == 64 && Dv == 64 && Sq_hint >= 33)
+        if (int rc = get_fwd_tc_kernel(m, dtype, D, 0, &k, true)) return rc;
       return get_decode_kernel(m, dtype, D, Dv, 0, c, &k);
     }
     case FA_KIND_BLOCKMASK:

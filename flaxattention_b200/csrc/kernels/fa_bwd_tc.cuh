@@ -20,7 +20,7 @@
 //
 // Warp roles (16 warps): 0-3 and 4-7 compute (q columns 0-63 / 64-127 of the pair tile),
 // 8-11 dQ drain, 12 TMA producer, 13 MMA issuer A (products 1-2, TMEM owner), 14 MMA issuer B
-// (products 3-5).
+// (products 3-4), 15 MMA issuer C (product 5).
 // S^T/dP^T of pair n+1 are issued as soon as the compute warps hold pair n in registers, so
 // the tensor core runs ahead of the element-wise work.
 //
@@ -49,7 +49,10 @@ struct FaBwdTcParams {
 #ifndef FA_TC_TRACE
 #define FA_TC_TRACE 0
 #endif
-#if FA_TC_TRACE
+#ifndef FA_TC_A_AFTER_B
+#define FA_TC_A_AFTER_B 0
+#endif
+#if FA_TC_TRACE == 1
 #define FA_TRACE_DECL long long trace_t0 = clock64();
 #define FA_TRACE(slot)                                                                        \
   do {                                                                                        \
@@ -61,15 +64,20 @@ struct FaBwdTcParams {
 #define FA_TRACE_DECL
 #define FA_TRACE(slot)
 #endif
-// FA_TC_TRACE == 2 additionally records the SM clock at each phase boundary of pairs 6..8 of
+// FA_TC_TRACE == 2 instead records the SM clock at each phase boundary of pairs 6..8 of
 // CTA (0,0,0) in status[64 + 32 * (pair - 6) + slot] (the status buffer must hold 160 ints).
 #if FA_TC_TRACE == 2
 #define FA_STAMP(slot)                                                                        \
   do {                                                                                        \
     if (trace_on && n >= 6 && n < 9) p.status[64 + (n - 6) * 32 + (slot)] = (int)clock64();   \
   } while (0)
+#define FA_MARK(k)                                                                     \
+  do {                                                                                  \
+    if (trace_on) p.status[176 + (k)] = (int)clock64();                                 \
+  } while (0)
 #else
 #define FA_STAMP(slot)
+#define FA_MARK(k)
 #endif
 
 namespace fa_btc {
@@ -81,7 +89,7 @@ constexpr int ATOM_BYTES = 128 * 128;    // 128 rows x 128 bytes
 constexpr int NSTAGE = 4;
 constexpr int MAXP = 512;                // (head, q tile) pairs per CTA
 constexpr int NT = 512;
-constexpr int WARP_PRODUCER = 12, WARP_MMA = 13, WARP_MMA_B = 14;
+constexpr int WARP_PRODUCER = 12, WARP_MMA = 13, WARP_MMA_B = 14, WARP_MMA_C = 15;
 constexpr int REGS_COMPUTE = 200, REGS_OTHER = 56;
 
 // shared memory map (from a 1024-byte aligned base)
@@ -198,6 +206,7 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
 #if FA_TC_TRACE
   const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && p.status != nullptr;
 #endif
+  if (warp == 0) { FA_MARK(0); }  // kernel start
   volatile int* misc = (volatile int*)(sm + OFF_MISC);  // [0] tmem base, [1] abort, [2] npairs
   int* pairs = (int*)(sm + OFF_PAIR);
   unsigned char* cls = sm + OFF_CLS;
@@ -213,13 +222,20 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
     fa_mbar_init(bar_addr(sb, BAR_SFULL), 1);
     fa_mbar_init(bar_addr(sb, BAR_SFREE), 256);
     fa_mbar_init(bar_addr(sb, BAR_PREADY), 256);
-    fa_mbar_init(bar_addr(sb, BAR_PFREE), 1);
+    fa_mbar_init(bar_addr(sb, BAR_PFREE), 2);  // one arrival from each of the issuers of products 3-4 and 5
     fa_mbar_init(bar_addr(sb, BAR_DQFULL), 1);
     fa_mbar_init(bar_addr(sb, BAR_DQFREE), 128);
     fa_mbar_init(bar_addr(sb, BAR_FINAL), 1);
     fa_mbar_init_fence();
     misc[1] = 0;
     misc[2] = 0;
+    // K and V of this CTA's tile do not depend on the pair list: their loads start now and run
+    // while the list is being built
+    fa_tma_prefetch_desc(&P.tk);
+    fa_tma_prefetch_desc(&P.tv);
+    fa_mbar_expect_tx(bar_addr(sb, BAR_KV), 2 * ATOM_BYTES);
+    fa_tma_load_4d(sb + OFF_K, &P.tk, bar_addr(sb, BAR_KV), 0, n0, hk, b);
+    fa_tma_load_4d(sb + OFF_V, &P.tv, bar_addr(sb, BAR_KV), 0, n0, hk, b);
   }
   if (warp == WARP_MMA) fa_tmem_alloc(sb + OFF_MISC, TMEM_COLS);
   // (head, q tile) pairs of this kv tile: per head, classify the q tiles (0 skip, 1 mask, 2 full)
@@ -259,6 +275,7 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
   fa_tc_fence_before();
   __syncthreads();
   fa_tc_fence_after();
+  if (warp == 0) { FA_MARK(1); }  // set-up done
   const fa_u32 tmem = (fa_u32)misc[0];
   npairs = misc[2];
   volatile int* abort_flag = misc + 1;
@@ -272,14 +289,9 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
     // ================================ producer ================================================
     if (lane == 0) {
       fa_tma_prefetch_desc(&P.tq);
-      fa_tma_prefetch_desc(&P.tk);
-      fa_tma_prefetch_desc(&P.tv);
       fa_tma_prefetch_desc(&P.tdo);
-      if (npairs > 0) {
-        fa_mbar_expect_tx(bar_addr(sb, BAR_KV), 2 * ATOM_BYTES);
-        fa_tma_load_4d(sb + OFF_K, &P.tk, bar_addr(sb, BAR_KV), 0, n0, hk, b);
-        fa_tma_load_4d(sb + OFF_V, &P.tv, bar_addr(sb, BAR_KV), 0, n0, hk, b);
-      }
+      // a CTA without pairs still has to see its K / V loads land before it may exit
+      if (npairs == 0) fa_mbar_wait(bar_addr(sb, BAR_KV), 0, abort_flag);
     }
     if (lane == 0) {
       bool ok = true;
@@ -322,6 +334,12 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
         ok = fa_mbar_wait_all(bar_addr(sb, BAR_QFULL + s), (fa_u32)((n / NSTAGE) & 1), abort_flag);
         FA_TRACE(1); FA_STAMP(1);   // MMA A: wait for Q/dO
         if (ok && n > 0) ok = fa_mbar_wait_all(bar_addr(sb, BAR_SFREE), (fa_u32)((n - 1) & 1), abort_flag);
+#if FA_TC_A_AFTER_B
+        // Products 3-5 of pair n-2 go first: they are what the compute warps wait for next, while
+        // S^T/dP^T of this pair are not needed before the stores of pair n-1 are done.  Issued
+        // right away they would sit in the middle of those products in the in-order tensor pipe.
+        if (ok && n > 1) ok = fa_mbar_wait_all(bar_addr(sb, BAR_PFREE), (fa_u32)((n - 2) & 1), abort_flag);
+#endif
         FA_TRACE(2); FA_STAMP(2);   // MMA A: wait for S^T/dP^T of the previous pair to be read
         if (!ok) break;
         fa_tc_fence_after();
@@ -341,14 +359,12 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
       }
     }
   } else if (warp == WARP_MMA_B) {
-    // ================================ MMA issuer B: products 3-5 ===============================
+    // ================================ MMA issuer B: products 3-4 ===============================
     if (npairs_u > 0) {
       const bool leader = fa_elect_one();
       constexpr fa_u32 IDESC_TN = fa_idesc(DT, 128, D, 0, 1);    // A K-major (TMEM or smem), B MN-major, N = 64
-      constexpr fa_u32 IDESC_NN = fa_idesc(DT, 128, D, 1, 1);    // A, B MN-major
       constexpr fa_u32 HI = fa_desc_hi_sw128();
-      const fa_u32 loK_mn = fa_desc_lo(sb + OFF_K, ATOM_BYTES);
-      const fa_u32 loDS_k = fa_desc_lo(sb + OFF_DS, 16), loDS_mn = fa_desc_lo(sb + OFF_DS, ATOM_BYTES);
+      const fa_u32 loDS_k = fa_desc_lo(sb + OFF_DS, 16);
       bool ok = fa_mbar_wait_all(bar_addr(sb, BAR_KV), 0, abort_flag);
       FA_TRACE_DECL
       for (int n = 0; n < npairs_u && ok; ++n) {
@@ -357,40 +373,57 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
         FA_TRACE(4); FA_STAMP(4);     // MMA B: wait for P^T / dS^T
         if (!ok) break;
         fa_tc_fence_after();
-        {
-          const fa_u32 loQ_mn = fa_desc_lo(sb + OFF_Q + s * ATOM_BYTES, ATOM_BYTES);
-          const fa_u32 loDO_mn = fa_desc_lo(sb + OFF_DO + s * ATOM_BYTES, ATOM_BYTES);
-          const fa_u32 acc = n > 0;
-          // 3. dV += P^T dO      (K = 128 q values, 8 steps of 16 rows = 2048 bytes; A from TMEM)
+        const fa_u32 loQ_mn = fa_desc_lo(sb + OFF_Q + s * ATOM_BYTES, ATOM_BYTES);
+        const fa_u32 loDO_mn = fa_desc_lo(sb + OFF_DO + s * ATOM_BYTES, ATOM_BYTES);
+        const fa_u32 acc = n > 0;
+        // 3. dV += P^T dO      (K = 128 q values, 8 steps of 16 rows = 2048 bytes; A from TMEM)
 #pragma unroll
-          for (int kk = 0; kk < BT / 16; ++kk)
-            if (leader) fa_mma_ts(tmem_u + COL_DV, tmem_u + COL_P + kk * 8, fa_desc_make(loDO_mn + kk * 128, HI), IDESC_TN, acc | (kk > 0));
-          if (leader) fa_mma_commit(bar_addr(sb, BAR_DOEMPTY + s));  // second arrival: the dO tile is free
-          FA_TRACE(7); FA_STAMP(7);   // MMA B: issue product 3
-          // 4. dK += dS^T Q     (A = dS^T K-major: k-step kk is 32 bytes into atom kk / 4)
+        for (int kk = 0; kk < BT / 16; ++kk)
+          if (leader) fa_mma_ts(tmem_u + COL_DV, tmem_u + COL_P + kk * 8, fa_desc_make(loDO_mn + kk * 128, HI), IDESC_TN, acc | (kk > 0));
+        if (leader) fa_mma_commit(bar_addr(sb, BAR_DOEMPTY + s));  // second arrival: the dO tile is free
+        FA_TRACE(7); FA_STAMP(7);   // MMA B: issue product 3
+        // 4. dK += dS^T Q     (A = dS^T K-major: k-step kk is 32 bytes into atom kk / 4)
 #pragma unroll
-          for (int kk = 0; kk < BT / 16; ++kk)
-            if (leader)
-              fa_mma_ss(tmem_u + COL_DK, fa_desc_make(loDS_k + (kk >> 2) * (ATOM_BYTES >> 4) + (kk & 3) * 2, HI),
-                        fa_desc_make(loQ_mn + kk * 128, HI), IDESC_TN, acc | (kk > 0));
-          if (leader) fa_mma_commit(bar_addr(sb, BAR_QEMPTY + s));   // second arrival: the Q tile and row scalars are free
-          FA_TRACE(8); FA_STAMP(8);   // MMA B: issue product 4
-          // 5. dQ = dS K        (A = dS^T read MN-major: M chunks of 64 q one atom apart; K = 128 kv rows);
-          //                      the drain warps must have emptied the dQ columns of the previous pair
-          if (n > 0) ok = fa_mbar_wait_all(bar_addr(sb, BAR_DQFREE), (fa_u32)((n - 1) & 1), abort_flag);
-          FA_TRACE(5); FA_STAMP(5);   // MMA B: wait for the dQ drain
-          if (!ok) break;
-          fa_tc_fence_after();
-#pragma unroll
-          for (int kk = 0; kk < BT / 16; ++kk)
-            if (leader) fa_mma_ss(tmem_u + COL_DQ, fa_desc_make(loDS_mn + kk * 128, HI), fa_desc_make(loK_mn + kk * 128, HI), IDESC_NN, kk > 0);
+        for (int kk = 0; kk < BT / 16; ++kk)
+          if (leader)
+            fa_mma_ss(tmem_u + COL_DK, fa_desc_make(loDS_k + (kk >> 2) * (ATOM_BYTES >> 4) + (kk & 3) * 2, HI),
+                      fa_desc_make(loQ_mn + kk * 128, HI), IDESC_TN, acc | (kk > 0));
+        if (leader) {
+          fa_mma_commit(bar_addr(sb, BAR_QEMPTY + s));   // second arrival: the Q tile and row scalars are free
+          fa_mma_commit(bar_addr(sb, BAR_PFREE));        // one of the two arrivals that free P^T and dS^T
+          if (n + 1 == npairs_u) fa_mma_commit(bar_addr(sb, BAR_FINAL));
         }
+        FA_TRACE(8); FA_STAMP(8);   // MMA B: issue product 4
+      }
+    }
+  } else if (warp == WARP_MMA_C) {
+    // ================================ MMA issuer C: product 5 ==================================
+    // (a third issuing warp: what bounds the tensor core in this kernel is how fast one thread
+    //  can issue, so the 32 instructions of a pair are spread over three threads)
+    if (npairs_u > 0) {
+      const bool leader = fa_elect_one();
+      constexpr fa_u32 IDESC_NN = fa_idesc(DT, 128, D, 1, 1);    // A, B MN-major
+      constexpr fa_u32 HI = fa_desc_hi_sw128();
+      const fa_u32 loK_mn = fa_desc_lo(sb + OFF_K, ATOM_BYTES);
+      const fa_u32 loDS_mn = fa_desc_lo(sb + OFF_DS, ATOM_BYTES);
+      bool ok = fa_mbar_wait_all(bar_addr(sb, BAR_KV), 0, abort_flag);
+      FA_TRACE_DECL
+      for (int n = 0; n < npairs_u && ok; ++n) {
+        ok = fa_mbar_wait_all(bar_addr(sb, BAR_PREADY), (fa_u32)(n & 1), abort_flag);
+        // the drain warps must have emptied the dQ columns of the previous pair
+        if (ok && n > 0) ok = fa_mbar_wait_all(bar_addr(sb, BAR_DQFREE), (fa_u32)((n - 1) & 1), abort_flag);
+        FA_TRACE(5); FA_STAMP(5);   // MMA C: wait for dS^T and the dQ drain
+        if (!ok) break;
+        fa_tc_fence_after();
+        // 5. dQ = dS K        (A = dS^T read MN-major: M chunks of 64 q one atom apart; K = 128 kv rows)
+#pragma unroll
+        for (int kk = 0; kk < BT / 16; ++kk)
+          if (leader) fa_mma_ss(tmem_u + COL_DQ, fa_desc_make(loDS_mn + kk * 128, HI), fa_desc_make(loK_mn + kk * 128, HI), IDESC_NN, kk > 0);
         if (leader) {
           fa_mma_commit(bar_addr(sb, BAR_PFREE));
           fa_mma_commit(bar_addr(sb, BAR_DQFULL));
-          if (n + 1 == npairs_u) fa_mma_commit(bar_addr(sb, BAR_FINAL));
         }
-        FA_TRACE(6); FA_STAMP(6);     // MMA B: issue product 5 + commits
+        FA_TRACE(6); FA_STAMP(6);   // MMA C: issue product 5 + commits
       }
     }
   } else if (warp < 8) {
@@ -413,6 +446,9 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
       const int m0 = (pr & 0xffff) * BT, mode = (pr >> 16) & 0xf, gh = hk * G + (pr >> 20) + p.h_off;
       ok = fa_mbar_wait_warp(bar_addr(sb, BAR_SFULL), (fa_u32)(n & 1), abort_flag);
       if (warp == 0) { FA_TRACE(10); FA_STAMP(10); }  // compute: wait for S^T/dP^T
+      if (warp == 0 && n == 0) { FA_MARK(2); }  // first S^T/dP^T there
+      if (warp == 0 && n == 1) { FA_MARK(3); }
+      if (warp == 0 && n == npairs - 1) { FA_MARK(4); }  // last S^T/dP^T there
       if (ok) ok = fa_mbar_wait_warp(bar_addr(sb, BAR_QFULL + s), (fa_u32)((n / NSTAGE) & 1), abort_flag);
       if (!ok) break;
       fa_tc_fence_after();
@@ -477,7 +513,9 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
       if (warp == 0) { FA_TRACE(14); FA_STAMP(14); }  // compute: stores of P^T / dS^T
     }
     // ---- epilogue: dK (scaled) by warps 0-3, dV by warps 4-7 ----------------------------------
+    if (warp == 0) { FA_MARK(5); }  // compute loop done
     if (ok && npairs > 0) ok = fa_mbar_wait_warp(bar_addr(sb, BAR_FINAL), 0, abort_flag);
+    if (warp == 0) { FA_MARK(6); }  // dK / dV complete
     if (ok) {
       fa_tc_fence_after();
       const FaTensor& dst = half == 0 ? p.dk : p.dv;
@@ -555,12 +593,16 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
       }
       if (warp == 8) { FA_TRACE(22); FA_STAMP(22); }  // drain: TMEM -> staging -> reduce issue
     }
+    if (warp == 8) { FA_MARK(8); }  // drain loop done
     if (dtid == 0) bulk_wait0();
+    if (warp == 8) { FA_MARK(9); }  // last reduce complete
   }
 
+  if (warp == 0) { FA_MARK(7); }  // epilogue stores issued
   // ---- teardown ------------------------------------------------------------------------------
   fa_tc_fence_before();
   __syncthreads();
+  if (warp == 0) { FA_MARK(10); }
   if (warp == WARP_MMA) {
     fa_tc_fence_after();
     fa_tmem_dealloc(tmem, TMEM_COLS);

@@ -71,7 +71,7 @@ constexpr int COL_P = 384;
 #ifndef FA_TC_TRACE
 #define FA_TC_TRACE 0
 #endif
-#if FA_TC_TRACE
+#if FA_TC_TRACE == 1
 #define FA_TRACE_DECL long long trace_t0 = clock64();
 #define FA_TRACE(slot)                                                                        \
   do {                                                                                        \
@@ -83,7 +83,7 @@ constexpr int COL_P = 384;
 #define FA_TRACE_DECL
 #define FA_TRACE(slot)
 #endif
-// FA_TC_TRACE == 2 additionally records the SM clock at each phase boundary of kv steps 6..8 of
+// FA_TC_TRACE == 2 instead records the SM clock at each phase boundary of kv steps 6..8 of
 // CTA (0,0,0) in status[64 + 32 * (step - 6) + slot] (the status buffer must hold 160 ints).
 #if FA_TC_TRACE == 2
 #define FA_STAMP(slot)                                                                        \
@@ -95,6 +95,9 @@ constexpr int COL_P = 384;
 #endif
 #ifndef FA_TC_HALF_EXP
 #define FA_TC_HALF_EXP 0
+#endif
+#ifndef FA_TC_POLY_EVERY
+#define FA_TC_POLY_EVERY 0
 #endif
 constexpr int NT = 384;
 // Register split (setmaxnreg): the kernel starts with 168 registers per thread (65536 / 384, rounded
@@ -186,7 +189,15 @@ __device__ __forceinline__ void pass2_chunk(const float (&v)[32], fa_u32 (&pk)[1
     pk[e] = fa_ex2_h2<DT>(fa_pack2<DT>(a0, a1));
     const fa_u64 pf = fa_h2_to_f2<DT>(pk[e]);
 #else
-    const float p0 = fa_ex2(a0), p1 = fa_ex2(a1);
+    // one pair in FA_TC_POLY_EVERY takes its exponentials on the FMA pipe: the SFU (16 per clock
+    // and SM) is what bounds this loop
+    float p0, p1;
+    if (FA_TC_POLY_EVERY > 0 && (e % (FA_TC_POLY_EVERY > 0 ? FA_TC_POLY_EVERY : 1)) == (FA_TC_POLY_EVERY - 1)) {
+      fa_ex2_poly2(a0, a1, p0, p1);
+    } else {
+      p0 = fa_ex2(a0);
+      p1 = fa_ex2(a1);
+    }
     pk[e] = fa_pack2<DT>(p0, p1);
     const fa_u64 pf = fa_f2(p0, p1);
 #endif
@@ -384,6 +395,13 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
     fa_mbar_init_fence();
     misc[1] = 0;
     misc[2] = 0;
+    // the query tiles do not depend on the kv schedule: their loads start now and run while the
+    // schedule is being built
+    fa_tma_prefetch_desc(&P.tq);
+    fa_mbar_expect_tx(bar_addr(sb, BAR_Q), DECODE ? Q_BYTES / 2 : Q_BYTES);
+    for (int i = 0; i < (DECODE ? 1 : 2); ++i)
+      for (int a = 0; a < ATOMS; ++a)
+        fa_tma_load_4d(sb + (i * ATOMS + a) * ATOM_BYTES, &P.tq, bar_addr(sb, BAR_Q), a * 64, m0 + i * BM, h, b);
   }
   const int ntiles = min((p.Skv + BN - 1) / BN, MAXT);
   for (int i = tid; i < 2 * MAXT; i += NT) cls[i] = 0;
@@ -462,14 +480,10 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
   if (warp == WARP_PRODUCER) {
     // ================================ TMA producer =======================================
     if (lane == 0) {
-      fa_tma_prefetch_desc(&P.tq);
       fa_tma_prefetch_desc(&P.tk);
       fa_tma_prefetch_desc(&P.tv);
-      fa_mbar_expect_tx(bar_addr(sb, BAR_Q), DECODE ? Q_BYTES / 2 : Q_BYTES);
-      for (int i = 0; i < (DECODE ? 1 : 2); ++i)
-        for (int a = 0; a < ATOMS; ++a)
-          fa_tma_load_4d(sb + (i * ATOMS + a) * ATOM_BYTES, &P.tq, bar_addr(sb, BAR_Q), a * 64, m0 + i * BM, h, b);
-      bool ok = true;
+      // a CTA without kv tiles still has to see its query loads land before it may exit
+      bool ok = nloads > 0 || fa_mbar_wait(bar_addr(sb, BAR_Q), 0, abort_flag);
       for (int j = 0; j < nloads && ok; ++j) {
         const int s = j % NSTAGE;
         const fa_u32 ph = (fa_u32)((j / NSTAGE) & 1);

@@ -251,6 +251,24 @@ __device__ __forceinline__ fa_u64 fa_fma2(fa_u64 a, fa_u64 b, fa_u64 c) {
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
   return r;
 }
+// 2^x for a pair of values on the FMA pipe instead of the SFU: x = n + r with n = round(x) taken
+// from the mantissa of x + 1.5 * 2^23, a cubic for 2^r on [-0.5, 0.5] (Chebyshev interpolant,
+// relative error 1.0e-4, below half a unit of the 16-bit types the result is rounded to), and n
+// added to the exponent field.  Inputs below -125 (masked scores are -inf) give 2^-125.
+__device__ __forceinline__ void fa_ex2_poly2(float x0, float x1, float& p0, float& p1) {
+  const fa_u64 x = fa_f2(fmaxf(x0, -125.f), fmaxf(x1, -125.f));
+  const fa_u64 t = fa_add2(x, fa_f2(12582912.f, 12582912.f));
+  const fa_u64 n = fa_add2(t, fa_f2(-12582912.f, -12582912.f));
+  const fa_u64 r = fa_fma2(n, fa_f2(-1.f, -1.f), x);
+  fa_u64 q = fa_fma2(r, fa_f2(0.05583828315138817f, 0.05583828315138817f), fa_f2(0.2426394820213318f, 0.2426394820213318f));
+  q = fa_fma2(q, r, fa_f2(0.6931367516517639f, 0.6931367516517639f));
+  q = fa_fma2(q, r, fa_f2(0.9999245405197144f, 0.9999245405197144f));
+  float t0, t1, q0, q1;
+  fa_f2_unpack(t, t0, t1);
+  fa_f2_unpack(q, q0, q1);
+  p0 = __int_as_float(__float_as_int(q0) + (__float_as_int(t0) << 23));
+  p1 = __int_as_float(__float_as_int(q1) + (__float_as_int(t1) << 23));
+}
 // max of three; written as nested fmaxf so that the compiler may pick the three-input form
 __device__ __forceinline__ float fa_max3(float a, float b, float c) { return fmaxf(fmaxf(a, b), c); }
 // register re-allocation between warpgroups (all four warps of a warpgroup must execute it)

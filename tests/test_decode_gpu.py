@@ -81,3 +81,33 @@ def test_decode_benchmark_shape():
         assert max_abs(lse[:1, :2], ref_lse) <= 2e-2 * max(1.0, ref_lse.abs().max().item())
         out2, lse2 = _decode(q, k, v, s, m, 5)
         assert max_abs(out, out2) <= 2e-3 and max_abs(lse, lse2) <= 1e-3 * max(1.0, lse.abs().max().item())
+
+
+@pytest.mark.parametrize("dt", ["f16", "bf16"])
+@pytest.mark.parametrize("Sq,splits", [(33, 2), (48, 4), (64, 6), (64, 3), (40, 0)])
+def test_tcgen05_decode_and_general_decode_agree_with_the_oracle(Sq, splits, dt):
+    """33..64 query rows with an even split count run on the split-KV variant of the tcgen05
+    kernel (two partial results per CTA), an odd count or the `general` option on the general
+    decode kernel: both within tolerance of the oracle and close to each other, and the status
+    word of the tcgen05 kernel (bounded waits) stays 0."""
+    import flaxattention_b200 as fa
+
+    B, Hq, Hkv, Skv, D = 2, 4, 4, 3000, 64      # ragged last tile, 24 kv tiles
+    s, m = _mods(Hq, Sq, Skv, "offset")
+    q, k, v = qkv(B, Hq, Hkv, Sq, Skv, D, dtype=DTYPES[dt])
+    ref, ref_lse = flax_attention_oracle(q, k, v, s, m)
+    bm = fa.create_block_mask(m, B, Hq, Sq, Skv)
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    outs = []
+    for opts in ({"path": "decode", "status": status}, {"path": "decode", "kernels": "general"}):
+        if splits:
+            opts["num_splits"] = splits
+        out, lse = fa.flax_attention(q.cuda(), k.cuda(), v.cuda(), score_mod=s, block_mask=bm, return_lse=True,
+                                     kernel_options=opts)
+        torch.cuda.synchronize()
+        assert max_abs(out.cpu(), ref) <= 2e-2
+        err, same = lse_err(lse.cpu(), ref_lse)
+        assert same and err <= 2e-2 * max(1.0, ref_lse.abs().max().item())
+        outs.append(out.cpu())
+    assert int(status.item()) == 0
+    assert max_abs(outs[0], outs[1]) <= (8e-3 if dt == "f16" else 3.2e-2)

@@ -143,6 +143,19 @@ def test_tcgen05_and_general_kernels_agree_with_the_oracle(case):
     assert max_abs(outs[0], outs[1]) <= (8e-3 if dt == "f16" else 3.2e-2)
 
 
+@pytest.mark.parametrize("scale", [-0.125, 0.0])
+def test_non_positive_scale(scale):
+    """The tcgen05 forward takes row maxima over unscaled scores, which needs a positive scale:
+    any other scale has to be routed to the general kernel and still match the oracle."""
+    import flaxattention_b200 as fa
+
+    q, k, v = qkv(1, 2, 2, 256, 256, 64, dtype=torch.float16)
+    out, lse = fa.flax_attention(q.cuda(), k.cuda(), v.cuda(), scale=scale, return_lse=True)
+    torch.cuda.synchronize()
+    ref_out, ref_lse = flax_attention_oracle(q, k, v, None, None, scale=scale)
+    _check(out.cpu(), lse.cpu(), ref_out, ref_lse, TOL["f16"])
+
+
 def test_mask_without_tables_equals_mask_with_tables():
     from flaxattention_b200.masks import generate_attention_sink
 
