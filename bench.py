@@ -52,7 +52,7 @@ DT = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from ncu captures (profiles/); None = not captured
 # (captured on the B=2 profile case and scaled by 4 to the B=8 workload: traffic grows with the batch)
-NCU_TRAFFIC = {"fa_fwd_tc_kernel": 4 * 12.91e6, "fa_bwd_tc_kernel": 4 * 25.49e6, "fa_fwd_kernel": None, "fa_bwd_dkdv_kernel": None,
+NCU_TRAFFIC = {"fa_fwd_tc_kernel": 4 * 12.66e6, "fa_bwd_tc_kernel": 4 * 25.49e6, "fa_fwd_kernel": None, "fa_bwd_dkdv_kernel": None,
                "fa_bwd_dq_kernel": None}
 
 
@@ -323,20 +323,22 @@ def main():
         out, lse = A._forward(call, q, k, v)
         t_fwd = timed(lambda: A._forward(call, q, k, v), steps_k, 3)
         # this workload runs the tcgen05 kernels: the forward, and a single-pass backward made
-        # of fa_delta_kernel, fa_bwd_tc_kernel (preceded by the memset of the dQ accumulator)
-        # and fa_dq_convert_kernel; the FA_FLAG_BWD_SKIP_* aids isolate them
+        # of fa_bwd_prep_kernel (row scalars; it also clears the dQ accumulator), fa_bwd_tc_kernel
+        # and fa_dq_convert_kernel; the FA_FLAG_BWD_SKIP_* aids isolate them (run alone, the main
+        # kernel is preceded by a memset of the accumulator instead)
         tc = w["D"] == 64 and w["dtype"] != "f32"
         fwd_name = "fa_fwd_tc_kernel" if tc else "fa_fwd_kernel"
         main_name, post_name = ("fa_bwd_tc_kernel", "fa_dq_convert_kernel") if tc else ("fa_bwd_dkdv_kernel", "fa_bwd_dq_kernel")
+        pre_name = "fa_bwd_prep_kernel" if tc else "fa_delta_kernel"
         only = {
             main_name: _cabi.FLAG_BWD_SKIP_DELTA | _cabi.FLAG_BWD_SKIP_DQ,
             post_name: _cabi.FLAG_BWD_SKIP_DELTA | _cabi.FLAG_BWD_SKIP_DKDV,
-            "fa_delta_kernel": _cabi.FLAG_BWD_SKIP_DKDV | _cabi.FLAG_BWD_SKIP_DQ,
+            pre_name: _cabi.FLAG_BWD_SKIP_DKDV | _cabi.FLAG_BWD_SKIP_DQ,
         }
         A._backward(call, q, k, v, out, lse, dout)  # delta is in place for the partial runs
         unit = fl_fwd / 4.0  # one S x S x D product = 2*B*H*Sq*Skv*D
         alg = {fwd_name: 2 * unit, main_name: (5 if tc else 4) * unit, post_name: (0 if tc else 1) * unit,
-               "fa_delta_kernel": 0.0}
+               pre_name: 0.0}
         kernels = {fwd_name: {"ms": t_fwd}}
         for name, flags in only.items():
             c2 = make_call(flags)
