@@ -62,7 +62,7 @@ _lib: Optional[C.CDLL] = None
 # every symbol include/flaxattn.h declares
 EXPORTS = [
     "fa_last_error", "fa_version", "fa_set_kernel_dir", "fa_set_cache_dir", "fa_module_create",
-    "fa_module_destroy", "fa_module_prepare", "fa_compile_count", "fa_fwd", "fa_bwd_workspace_bytes",
+    "fa_module_set_buffers", "fa_module_destroy", "fa_module_prepare", "fa_compile_count", "fa_fwd", "fa_bwd_workspace_bytes",
     "fa_bwd", "fa_decode_num_splits", "fa_decode_workspace_bytes", "fa_decode",
     "fa_block_mask_workspace_bytes", "fa_block_mask", "fa_decode_static_capacity", "fa_decode_static",
 ]
@@ -81,6 +81,7 @@ def lib() -> C.CDLL:
     L.fa_last_error.restype = C.c_char_p
     L.fa_module_create.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]
     L.fa_module_destroy.argtypes = [C.c_void_p]
+    L.fa_module_set_buffers.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_int]
     L.fa_module_destroy.restype = None
     L.fa_module_prepare.argtypes = [C.c_void_p] + [C.c_int] * 6
     L.fa_set_kernel_dir.argtypes = [C.c_char_p]
@@ -131,6 +132,11 @@ class Module:
         h = C.c_void_p()
         check(L.fa_module_create(mod_source.encode() if mod_source else None, C.byref(h)))
         self.handle = h
+
+    def set_buffers(self, ptrs) -> None:
+        """Device addresses of the tensors the mods index (``fa_module_set_buffers``)."""
+        arr = (C.c_void_p * max(len(ptrs), 1))(*ptrs)
+        check(lib().fa_module_set_buffers(self.handle, arr, len(ptrs)))
 
     def prepare(self, kind: int, dtype: int, D: int, Dv: int, sq_hint: int = 1024, skv_hint: int = 1024) -> None:
         check(lib().fa_module_prepare(self.handle, kind, dtype, D, Dv, sq_hint, skv_hint))

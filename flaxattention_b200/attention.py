@@ -18,7 +18,7 @@ import numpy as np
 import torch
 
 from . import _cabi
-from .blockmask import BlockMask, module_for, noop_mask
+from .blockmask import BlockMask, bind_mod_buffers, module_for, noop_mask
 
 _DTYPES = {torch.float16: _cabi.FA_F16, torch.bfloat16: _cabi.FA_BF16, torch.float32: _cabi.FA_F32}
 
@@ -111,6 +111,7 @@ class _Call:
         if block_mask is not None and block_mask.kv_indices.ndim != 4:
             raise ValueError("BlockMask tables must be 4-dimensional [B, H, nQ, nKV]")
         self.module = module_for(score_mod, mask_mod)
+        self.score_mod, self.mask_mod = score_mod, mask_mod
         self.options = dict(options or {})
         self.round_scores = bool(self.options.get("round_scores", round_scores))
 
@@ -167,6 +168,7 @@ def _forward(call: _Call, q, k, v):
     p = call.params(q, k, v, out, lse)
     stream = torch.cuda.current_stream(q.device).cuda_stream
     with torch.cuda.device(q.device):
+        bind_mod_buffers(call.module, call.score_mod, call.mask_mod, q.device)
         if call.use_decode():
             splits = int(call.options.get("num_splits", 0))
             if splits <= 0:
@@ -190,6 +192,7 @@ def _backward(call: _Call, q, k, v, out, lse, dout):
     ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device=q.device)
     stream = torch.cuda.current_stream(q.device).cuda_stream
     with torch.cuda.device(q.device):
+        bind_mod_buffers(call.module, call.score_mod, call.mask_mod, q.device)
         _cabi.check(L.fa_bwd(call.module.handle, p, _tensor(dout, call.layout), _tensor(dq, call.layout),
                              _tensor(dk, call.layout), _tensor(dv, call.layout), ws.data_ptr(), nbytes, stream))
     return dq, dk, dv

@@ -266,6 +266,41 @@ def module_for(score_mod: Optional[Callable], mask_mod: Optional[Callable]):
     return m
 
 
+_DEVICE_BUFFERS = {}
+
+
+def bind_mod_buffers(module, score_mod: Optional[Callable], mask_mod: Optional[Callable], device) -> None:
+    """Hands the module the device addresses of the tensors the mods close over and index
+    (the reference's score_mod_other_buffers / mask_mod_other_buffers,
+    flaxattention/core/attention.py:22-23).  Tensors that live elsewhere (CPU, another GPU) are
+    copied to `device` once per tensor version; the copies are kept while the mods are cached."""
+    if mask_mod is noop_mask:
+        mask_mod = None
+    ms = lower_mods(score_mod, mask_mod)
+    if not ms.buffers:
+        return
+    ptrs, keep = [], []
+    for t in ms.buffers:
+        if not isinstance(t, torch.Tensor):
+            t = torch.as_tensor(t)
+        if t.device != device:
+            key = (id(t), t._version, str(device))
+            hit = _DEVICE_BUFFERS.get(key)
+            if hit is None or hit[0] is not t:
+                if len(_DEVICE_BUFFERS) > 256:
+                    _DEVICE_BUFFERS.clear()
+                # same strides as the original: the load indices were built from them
+                span = 1 + sum((d - 1) * st for d, st in zip(t.shape, t.stride()))
+                flat = torch.as_strided(t, (span,), (1,)).to(device)
+                hit = (t, flat)
+                _DEVICE_BUFFERS[key] = hit
+            t = hit[1]
+        keep.append(t)
+        ptrs.append(t.data_ptr())
+    module.set_buffers(ptrs)
+    module._bound_buffers = keep  # the addresses stay valid at least until the next binding
+
+
 def _require_cuda(device) -> torch.device:
     if not torch.cuda.is_available():
         raise RuntimeError("flaxattention_b200 needs a CUDA device (B200, sm_100a); there is no CPU path")
@@ -322,6 +357,7 @@ def create_block_mask(
         fq_num, fq_idx = mk(B, H, nkv), mk(B, H, nkv, nq)
         ws_bytes = L.fa_block_mask_workspace_bytes(B, H, Q_LEN, KV_LEN, Q_BLOCK_SIZE, KV_BLOCK_SIZE)
         ws = torch.empty(ws_bytes, dtype=torch.int8, device=dev)
+        bind_mod_buffers(module, None, mask_mod, dev)
         _cabi.check(L.fa_block_mask(
             module.handle, B, H, Q_LEN, KV_LEN, Q_BLOCK_SIZE, KV_BLOCK_SIZE, b_offset, h_offset,
             kv_num.data_ptr(), kv_idx.data_ptr(), fkv_num.data_ptr(), fkv_idx.data_ptr(),

@@ -161,13 +161,21 @@ struct Kernel {
   cudaKernel_t fn = nullptr;
   int smem = 0;
   unsigned long long smem_set_mask = 0;  // devices on which the dynamic smem limit was raised
+  fa_module* owner = nullptr;
+  // device address of the kernel image's `fa_mod_buf` table per device (null: the image has none)
+  void* buf_table[64] = {nullptr};
+  unsigned long long buf_table_known = 0;
 };
 
 }  // namespace
 
+constexpr int kMaxModBuffers = 8;
+
 struct fa_module {
   std::string mod_source;
   std::map<std::string, Kernel*> kernels;  // key: template + defines
+  const void* bufs[kMaxModBuffers] = {nullptr};  // device addresses of the captured buffers of the mods
+  int nbufs = 0;
 };
 
 namespace {
@@ -217,6 +225,7 @@ int get_kernel(fa_module* m, const std::string& tmpl, const std::string& defines
   k->cubin.swap(cubin);
   k->entry = entry;
   k->smem = smem;
+  k->owner = m;
   m->kernels[key] = k;
   *out = k;
   return FA_OK;
@@ -239,8 +248,44 @@ int ready_kernel(Kernel* k) {
   return FA_OK;
 }
 
+// Mods that read captured buffers find their addresses in the `fa_mod_buf` table of the kernel
+// image: it is rewritten, in stream order, before every launch of a kernel of such a module.
+int upload_buffers(Kernel* k, void* stream) {
+  fa_module* m = k->owner;
+  if (m == nullptr) return FA_OK;
+  const void* local[kMaxModBuffers];
+  int n = 0;
+  void* table = nullptr;
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    n = m->nbufs;
+    if (n == 0) return FA_OK;
+    for (int i = 0; i < n; ++i) local[i] = m->bufs[i];
+    int dev = 0;
+    FA_CUDA_CHECK(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64) return fail(FA_EUNSUPPORTED, "device ordinal above 63");
+    if (!(k->buf_table_known >> dev & 1ull)) {
+      void* dptr = nullptr;
+      size_t bytes = 0;
+      if (cudaLibraryGetGlobal(&dptr, &bytes, k->lib, "fa_mod_buf") != cudaSuccess) {
+        cudaGetLastError();  // this kernel image does not reference the table
+        dptr = nullptr;
+      } else if (bytes < (size_t)n * sizeof(void*)) {
+        return fail(FA_EINVAL, "fa_module_set_buffers: more buffers than the mod source declares");
+      }
+      k->buf_table[dev] = dptr;
+      k->buf_table_known |= 1ull << dev;
+    }
+    table = k->buf_table[dev];
+  }
+  if (table != nullptr)
+    FA_CUDA_CHECK(cudaMemcpyAsync(table, local, (size_t)n * sizeof(void*), cudaMemcpyHostToDevice, (cudaStream_t)stream));
+  return FA_OK;
+}
+
 int launch(Kernel* k, dim3 grid, dim3 block, void* params, void* stream) {
   if (int rc = ready_kernel(k)) return rc;
+  if (int rc = upload_buffers(k, stream)) return rc;
   void* args[] = {params};
   FA_CUDA_CHECK(cudaLaunchKernel((const void*)k->fn, grid, block, args, (size_t)k->smem, (cudaStream_t)stream));
   return FA_OK;
@@ -645,6 +690,18 @@ int fa_module_create(const char* mod_source, fa_module** out) {
   fa_module* m = new fa_module();
   m->mod_source = (mod_source && *mod_source) ? mod_source : kDefaultMods;
   *out = m;
+  return FA_OK;
+}
+
+int fa_module_set_buffers(fa_module* m, const void* const* ptrs, int n) {
+  if (!m) return fail(FA_EINVAL, "module is null");
+  if (n < 0 || n > kMaxModBuffers) return fail(FA_EINVAL, "between 0 and 8 captured buffers");
+  if (n > 0 && !ptrs) return fail(FA_EINVAL, "ptrs is null");
+  for (int i = 0; i < n; ++i)
+    if (!ptrs[i]) return fail(FA_EINVAL, "captured buffer " + std::to_string(i) + " is null");
+  std::lock_guard<std::mutex> lk(g_mu);
+  for (int i = 0; i < n; ++i) m->bufs[i] = ptrs[i];
+  m->nbufs = n;
   return FA_OK;
 }
 

@@ -144,6 +144,46 @@ __device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_
 __device__ __forceinline__ void chunk(const float (&s)[32], const float (&dp)[32], const float* nlse2, const float* ndelta,
                                       fa_u32 (&pp)[16], fa_u32 (&ds)[16], int mode, int q0, int kv, int gb, int gh,
                                       float scale, float sc2) {
+#if !FA_ROUND_SCORES && (!FA_HAS_SCORE_MOD || defined(FA_SCORE_AFFINE))
+  // no score_mod, or an affine one: two elements per instruction (packed fp32) wherever the
+  // hardware has the form; only the exponentials and the mask are per element
+#pragma unroll
+  for (int e = 0; e < 32; e += 4) {
+    const float4 nl = *(const float4*)(nlse2 + e);
+    const float4 nd = *(const float4*)(ndelta + e);
+#pragma unroll
+    for (int u = 0; u < 4; u += 2) {
+      const int qi0 = q0 | (e + u), qi1 = q0 | (e + u + 1);
+      const fa_u64 nl2 = u == 0 ? fa_f2(nl.x, nl.y) : fa_f2(nl.z, nl.w);
+      const fa_u64 nd2 = u == 0 ? fa_f2(nd.x, nd.y) : fa_f2(nd.z, nd.w);
+      const fa_u64 s2 = fa_f2(s[e + u], s[e + u + 1]);
+#if FA_HAS_SCORE_MOD
+      const fa_u64 g2 = fa_f2(fa_score_mul(0.f, gb, gh, qi0, kv), fa_score_mul(0.f, gb, gh, qi1, kv));
+      const fa_u64 b2 = fa_add2(fa_f2(fa_score_add2(0.f, gb, gh, qi0, kv), fa_score_add2(0.f, gb, gh, qi1, kv)), nl2);
+      const fa_u64 x2 = fa_fma2(s2, fa_mul2(g2, fa_f2(sc2, sc2)), b2);
+#else
+      const fa_u64 x2 = fa_fma2(s2, fa_f2(sc2, sc2), nl2);
+#endif
+      float x0, x1;
+      fa_f2_unpack(x2, x0, x1);
+      float p0 = fa_ex2(x0), p1 = fa_ex2(x1);
+#if FA_HAS_MASK_MOD
+      if (mode == 1) {
+        p0 = fa_mask_mod(gb, gh, qi0, kv) ? p0 : 0.f;
+        p1 = fa_mask_mod(gb, gh, qi1, kv) ? p1 : 0.f;
+      }
+#endif
+      fa_u64 d2 = fa_mul2(fa_f2(p0, p1), fa_add2(fa_f2(dp[e + u], dp[e + u + 1]), nd2));
+#if FA_HAS_SCORE_MOD
+      d2 = fa_mul2(d2, g2);
+#endif
+      float d0, d1;
+      fa_f2_unpack(d2, d0, d1);
+      pp[(e + u) / 2] = fa_pack2<DT>(p0, p1);
+      ds[(e + u) / 2] = fa_pack2<DT>(d0, d1);
+    }
+  }
+#else
 #pragma unroll
   for (int e = 0; e < 32; e += 4) {
     const float4 nl = *(const float4*)(nlse2 + e);
@@ -183,6 +223,7 @@ __device__ __forceinline__ void chunk(const float (&s)[32], const float (&dp)[32
     ds[e / 2] = fa_pack2<DT>(dv[0], dv[1]);
     ds[e / 2 + 1] = fa_pack2<DT>(dv[2], dv[3]);
   }
+#endif
 }
 
 }  // namespace fa_btc

@@ -47,7 +47,7 @@ class Expr:
         self.dtype = dtype
         self.args = args
         self.value = value
-        self._key = (op, dtype, tuple(id(a) for a in args), value if op == "const" else None)
+        self._key = (op, dtype, tuple(id(a) for a in args), value if op in ("const", "load") else None)
 
     def __repr__(self):
         if self.op == "const":
@@ -79,10 +79,10 @@ class _Builder:
                 e = Expr("const", dtype, (), v)
                 self._table[key] = e
             return e
-        key = (op, dtype, tuple(id(a) for a in args))
+        key = (op, dtype, tuple(id(a) for a in args), value if op == "load" else None)
         e = self._table.get(key)
         if e is None:
-            e = Expr(op, dtype, tuple(args))
+            e = Expr(op, dtype, tuple(args), value if op == "load" else None)
             self._table[key] = e
         return e
 
@@ -171,6 +171,8 @@ def _rebuild(e: Expr, args) -> Expr:
         return select(args[0], args[1], args[2])
     if e.op.startswith("cast_"):
         return cast(args[0], e.dtype)
+    if e.op == "load":
+        return _B._mk("load", e.dtype, (args[0],), e.value)
     raise NotImplementedError(e.op)
 
 
@@ -419,6 +421,59 @@ def _lift(x) -> Expr:
     )
 
 
+# --------------------------------------------------------------------------------------
+# captured buffers: tensors a mod closes over and indexes with traced values
+# (score_mod_other_buffers / mask_mod_other_buffers of flaxattention/core/attention.py:22-23,
+#  :35-52; in the reference they are jaxpr constants, here the tensors the closure holds)
+# --------------------------------------------------------------------------------------
+MAX_MOD_BUFFERS = 8
+_ELEM_TYPES = {
+    "torch.int32": ("i32", I32), "torch.int64": ("i64", I32), "torch.uint8": ("u8", I32), "torch.bool": ("u8", B1),
+    "torch.float32": ("f32", F32),
+    "int32": ("i32", I32), "int64": ("i64", I32), "uint8": ("u8", I32), "bool": ("u8", B1), "float32": ("f32", F32),
+}
+_TRACE_BUFFERS: Optional[List[object]] = None  # buffers of the mod pair being traced
+
+
+def _buffer_load(buf, index) -> "Sym":
+    """``buf[index]`` with traced indices: registers the tensor and records a load node.  The
+    linear index is built from the tensor's strides; out-of-range indices (rows and keys of the
+    padding of a ragged tile reach the mods too) are clamped by the generated code."""
+    if _TRACE_BUFFERS is None:
+        raise TypeError("a tensor can only be indexed with a traced value while a mod is being lowered")
+    et = _ELEM_TYPES.get(str(buf.dtype))
+    if et is None:
+        raise TypeError(f"captured buffers of dtype {buf.dtype} are not supported (int32, int64, uint8, bool, float32 are)")
+    idx = index if isinstance(index, tuple) else (index,)
+    shape = tuple(int(d) for d in buf.shape)
+    if len(idx) != len(shape):
+        raise TypeError(f"a captured buffer of {len(shape)} dimensions needs {len(shape)} indices, got {len(idx)}")
+    if hasattr(buf, "stride") and callable(buf.stride):
+        strides = tuple(int(x) for x in buf.stride())
+    else:
+        strides = tuple(int(x // buf.itemsize) for x in buf.strides)
+    numel = 1
+    for d in shape:
+        numel *= d
+    if numel == 0 or numel >= (1 << 31):
+        raise TypeError("captured buffers must hold between 1 and 2^31-1 elements")
+    span = 1 + sum((d - 1) * st for d, st in zip(shape, strides))
+    k = None
+    for i, b in enumerate(_TRACE_BUFFERS):
+        if b is buf:
+            k = i
+    if k is None:
+        if len(_TRACE_BUFFERS) >= MAX_MOD_BUFFERS:
+            raise TypeError(f"at most {MAX_MOD_BUFFERS} captured buffers per (score_mod, mask_mod) pair")
+        _TRACE_BUFFERS.append(buf)
+        k = len(_TRACE_BUFFERS) - 1
+    lin = _B.const(0, I32)
+    for i, st in zip(idx, strides):
+        e = cast(_lift(i), I32)
+        lin = binary("add", lin, binary("mul", e, _B.const(st, I32)))
+    return Sym(_B._mk("load", et[1], (lin,), (k, span, et[0])))
+
+
 def _bin(op):
     def f(self, other):
         try:
@@ -509,6 +564,8 @@ class Sym:
     @classmethod
     def __torch_function__(cls, func, types, args=(), kwargs=None):
         name = getattr(func, "__name__", "")
+        if name == "__getitem__" and len(args) == 2 and not isinstance(args[0], Sym):
+            return _buffer_load(args[0], args[1])
         fn = _TORCH_FUNCS.get(name)
         if fn is None or kwargs:
             return NotImplemented
@@ -750,9 +807,10 @@ def mod_arity(fn: Callable) -> int:
 class TracedMod:
     """Result of tracing: ``kind`` is 'score' (float32 result) or 'mask' (bool result)."""
 
-    def __init__(self, kind: str, root: Expr):
+    def __init__(self, kind: str, root: Expr, buffers: Optional[List[object]] = None):
         self.kind = kind
         self.root = root
+        self.buffers = buffers  # captured tensors the load nodes refer to (shared by a mod pair)
 
     @property
     def is_identity(self) -> bool:
@@ -770,23 +828,38 @@ def _leaf_syms():
     return tuple(Sym(_B.leaf(n)) for n in _LEAVES)
 
 
-def trace_score_mod(fn: Callable) -> TracedMod:
-    s, b, h, q, kv = _leaf_syms()
-    out = fn(s, b, h, q, kv)
-    return TracedMod("score", cast(_lift(out), F32))
+def _traced(buffers: Optional[List[object]], run: Callable[[], Expr], kind: str) -> TracedMod:
+    """Runs a trace with `buffers` as the registry that tensor[traced index] fills."""
+    global _TRACE_BUFFERS
+    bufs = [] if buffers is None else buffers
+    prev, _TRACE_BUFFERS = _TRACE_BUFFERS, bufs
+    try:
+        root = run()
+    finally:
+        _TRACE_BUFFERS = prev
+    return TracedMod(kind, root, bufs)
 
 
-def trace_mask_mod(fn: Callable) -> TracedMod:
+def trace_score_mod(fn: Callable, buffers: Optional[List[object]] = None) -> TracedMod:
+    def run():
+        s, b, h, q, kv = _leaf_syms()
+        return cast(_lift(fn(s, b, h, q, kv)), F32)
+
+    return _traced(buffers, run, "score")
+
+
+def trace_mask_mod(fn: Callable, buffers: Optional[List[object]] = None) -> TracedMod:
     """Traces a mask_mod.  A 5-argument function is accepted as well and is then a
     score_mod evaluated on a zero score whose -inf results mark masked positions, the
     rule ``create_mask`` applies (flaxattention/core/blockmask.py:303-315)."""
-    s, b, h, q, kv = _leaf_syms()
-    if mod_arity(fn) == 5:
-        out = fn(Sym(_B.const(0.0, F32)), b, h, q, kv)
-        root = unary("not", unary("isneginf", cast(_lift(out), F32)))
-        return TracedMod("mask", root)
-    out = fn(b, h, q, kv)
-    return TracedMod("mask", cast(_lift(out), B1))
+    def run():
+        s, b, h, q, kv = _leaf_syms()
+        if mod_arity(fn) == 5:
+            out = fn(Sym(_B.const(0.0, F32)), b, h, q, kv)
+            return unary("not", unary("isneginf", cast(_lift(out), F32)))
+        return cast(_lift(fn(b, h, q, kv)), B1)
+
+    return _traced(buffers, run, "mask")
 
 
 def _depends_on_score(e: Expr, memo) -> bool:
@@ -881,7 +954,7 @@ def derivative(mod: TracedMod) -> TracedMod:
         memo[id(e)] = r
         return r
 
-    return TracedMod("score", cast(d(mod.root), F32))
+    return TracedMod("score", cast(d(mod.root), F32), mod.buffers)
 
 
 # --------------------------------------------------------------------------------------
@@ -941,7 +1014,7 @@ def affine_parts(mod: TracedMod):
     res = go(mod.root)
     if res is None:
         return None
-    return TracedMod("score", cast(res[0], F32)), TracedMod("score", cast(res[1], F32))
+    return TracedMod("score", cast(res[0], F32), mod.buffers), TracedMod("score", cast(res[1], F32), mod.buffers)
 
 
 # --------------------------------------------------------------------------------------
@@ -1123,6 +1196,11 @@ def to_cuda(mod: TracedMod, name: str) -> str:
             rhs = f"(int)({a[0]})" if e.args[0].dtype == F32 else f"({a[0]} ? 1 : 0)"
         elif op == "cast_b1":
             rhs = f"({a[0]} != 0)" if e.args[0].dtype == I32 else f"({a[0]} != 0.0f)"
+        elif op == "load":
+            k, span, elem = e.value
+            rhs = f"fa_ld_{elem}({k}, min(max({a[0]}, 0), {span - 1}))"
+            if t == B1:
+                rhs = f"({rhs} != 0)"
         else:
             raise NotImplementedError(op)
         var = f"t{n}"
@@ -1135,6 +1213,19 @@ def to_cuda(mod: TracedMod, name: str) -> str:
     else:
         head = f"__device__ __forceinline__ bool {name}(int b, int h, int q, int kv) {{"
     return "\n".join([head] + lines + [f"  return {ret};", "}"]) + "\n"
+
+
+def _buffer_storage(buf, span: int) -> np.ndarray:
+    """The first `span` elements of the storage behind a captured tensor (strided view undone)."""
+    try:
+        import torch
+
+        if isinstance(buf, torch.Tensor):
+            return torch.as_strided(buf.detach().cpu(), (span,), (1,)).numpy()
+    except ImportError:  # pragma: no cover
+        pass
+    a = np.asarray(buf)
+    return np.lib.stride_tricks.as_strided(a, (span,), (a.itemsize,))
 
 
 def evaluate(mod: TracedMod, score, b, h, q, kv):
@@ -1216,6 +1307,11 @@ def evaluate(mod: TracedMod, score, b, h, q, kv):
                 r = np.where(a[0], a[1], a[2])
             elif op.startswith("cast_"):
                 r = a[0] != 0 if e.dtype == B1 else a[0]
+            elif op == "load":
+                k, span, _elem = e.value
+                if mod.buffers is None:
+                    raise ValueError("this mod reads captured buffers; evaluate a mod obtained from lower_mods")
+                r = _buffer_storage(mod.buffers[k], span)[np.clip(np.asarray(a[0], dtype=np.int64), 0, span - 1)]
             else:
                 raise NotImplementedError(op)
             env[id(e)] = np.asarray(r).astype(t, copy=False)
@@ -1243,6 +1339,16 @@ __device__ __forceinline__ float fa_pymod_f32(float a, float b) {
 """
 
 
+_BUFFER_PRELUDE = r"""
+// Captured buffers: the host writes the device addresses here before every launch.
+__constant__ const void* fa_mod_buf[FA_NUM_MOD_BUFS];
+__device__ __forceinline__ int fa_ld_i32(int k, int i) { return __ldg((const int*)fa_mod_buf[k] + i); }
+__device__ __forceinline__ int fa_ld_i64(int k, int i) { return (int)__ldg((const long long*)fa_mod_buf[k] + i); }
+__device__ __forceinline__ int fa_ld_u8(int k, int i) { return (int)__ldg((const unsigned char*)fa_mod_buf[k] + i); }
+__device__ __forceinline__ float fa_ld_f32(int k, int i) { return __ldg((const float*)fa_mod_buf[k] + i); }
+"""
+
+
 class ModSet:
     """The (score_mod, mask_mod) pair of one attention call, lowered.
 
@@ -1252,10 +1358,16 @@ class ModSet:
     compiled kernels and of this object.
     """
 
-    def __init__(self, score: Optional[TracedMod], mask: Optional[TracedMod]):
+    def __init__(self, score: Optional[TracedMod], mask: Optional[TracedMod], buffers: Optional[List[object]] = None):
         self.score = score if (score is not None and not score.is_identity) else None
         self.mask = mask if (mask is not None and not mask.is_all_true) else None
+        # tensors the mods close over and index (document ids, learned biases ...); the load
+        # nodes of both mods number them in this list
+        self.buffers: List[object] = list(buffers) if buffers else []
         parts = [_PRELUDE]
+        if self.buffers:
+            parts.append(f"#define FA_NUM_MOD_BUFS {len(self.buffers)}\n")
+            parts.append(_BUFFER_PRELUDE)
         parts.append(f"#define FA_HAS_SCORE_MOD {1 if self.score is not None else 0}\n")
         parts.append(f"#define FA_HAS_MASK_MOD {1 if self.mask is not None else 0}\n")
         self.affine = None
@@ -1275,7 +1387,7 @@ class ModSet:
                 parts.append(to_cuda(self.affine[0], "fa_score_mul"))
                 parts.append(to_cuda(self.affine[1], "fa_score_add"))
                 # B already multiplied by log2(e), with the constant folded into row-invariant factors
-                b2 = TracedMod("score", binary("mul", self.affine[1].root, _B.const(math.log2(math.e), F32)))
+                b2 = TracedMod("score", binary("mul", self.affine[1].root, _B.const(math.log2(math.e), F32)), self.affine[1].buffers)
                 parts.append(to_cuda(b2, "fa_score_add2"))
         else:
             self.grad = None
@@ -1302,9 +1414,10 @@ def lower_mods(score_mod: Optional[Callable], mask_mod: Optional[Callable]) -> M
     hit = _MODSET_CACHE.get(k)
     if hit is not None and hit[0] is score_mod and hit[1] is mask_mod:
         return hit[2]
-    s = trace_score_mod(score_mod) if score_mod is not None else None
-    m = trace_mask_mod(mask_mod) if mask_mod is not None else None
-    ms = ModSet(s, m)
+    bufs: List[object] = []
+    s = trace_score_mod(score_mod, bufs) if score_mod is not None else None
+    m = trace_mask_mod(mask_mod, bufs) if mask_mod is not None else None
+    ms = ModSet(s, m, bufs)
     if len(_MODSET_CACHE) > 4096:
         _MODSET_CACHE.clear()
     _MODSET_CACHE[k] = (score_mod, mask_mod, ms)

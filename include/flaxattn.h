@@ -108,6 +108,13 @@ int fa_set_cache_dir(const char* path);
  * FA_HAS_SCORE_MOD / FA_HAS_MASK_MOD.  NULL or "" = identity score_mod and no mask. */
 int fa_module_create(const char* mod_source, fa_module** out);
 void fa_module_destroy(fa_module* m);
+/* Device addresses of the buffers the mods of this module read (`fa_mod_buf[k]` in mod_source, at
+ * most 8): the tensors a score_mod / mask_mod closes over and indexes with b, h, q, kv - the
+ * reference's score_mod_other_buffers / mask_mod_other_buffers (flaxattention/core/attention.py:22-23,
+ * :35-52), there jaxpr constants.  The addresses are copied into the kernel image, in stream order,
+ * before every later launch of a kernel of the module; calls that use one module with different
+ * buffer sets must not overlap, and such launches cannot be stream-captured. */
+int fa_module_set_buffers(fa_module* m, const void* const* ptrs, int n);
 /* Compiles (or fetches from the cache) the kernels of one kind for a dtype / head-dim pair.
  * Needs no GPU.  seq_hint selects the tile configuration the same way a later launch would. */
 int fa_module_prepare(fa_module* m, int kind, int dtype, int D, int Dv, int Sq_hint, int Skv_hint);

@@ -147,3 +147,40 @@ def test_lowered_mods_compile_for_sm100a(tmp_path):
     finally:
         import os
         L.fa_set_cache_dir(os.path.join(os.path.dirname(_cabi.LIB_PATH), "_kernel_cache").encode())
+
+
+def test_captured_buffers_trace_evaluate_and_lower():
+    """Tensors a mod closes over and indexes with traced values become load nodes (the
+    reference's score_mod_other_buffers, flaxattention/core/attention.py:22-23): numbered per
+    mod pair, linear index from the strides, clamped in the generated code."""
+    import torch
+
+    doc = torch.tensor([0, 0, 0, 1, 1, 2, 2, 2, 2, 3], dtype=torch.int64)
+    bias = torch.arange(4 * 10 * 10, dtype=torch.float32).reshape(4, 10, 10).transpose(1, 2)  # non-contiguous view
+
+    def doc_mask(b, h, q, kv):
+        return (doc[q] == doc[kv]) & (q >= kv)
+
+    def bias_mod(s, b, h, q, kv):
+        return s + bias[h, q, kv] * 2.0
+
+    mt = modtrace
+    ms = mt.lower_mods(bias_mod, doc_mask)
+    assert len(ms.buffers) == 2 and ms.buffers[0] is bias and ms.buffers[1] is doc
+    assert "FA_NUM_MOD_BUFS 2" in ms.source and "fa_ld_i64(1," in ms.source and "fa_ld_f32(0," in ms.source
+    assert ms.affine is not None                      # score + table[...] is affine in the score
+    q = np.arange(10)[:, None]
+    kv = np.arange(10)[None, :]
+    got = mt.evaluate(ms.mask, None, 0, 0, q, kv)
+    assert np.array_equal(got, (doc.numpy()[q] == doc.numpy()[kv]) & (q >= kv))
+    sc = np.linspace(-1, 1, 100, dtype=np.float32).reshape(10, 10)
+    got = mt.evaluate(ms.score, sc, 0, 3, q, kv)
+    assert np.allclose(got, sc + bias.numpy()[3][q, kv] * 2.0)
+    assert np.all(mt.evaluate(ms.grad, sc, 0, 3, q, kv) == 1.0)
+    # out-of-range indices (padding rows of a ragged tile) read a clamped element instead of faulting
+    assert mt.evaluate(ms.mask, None, 0, 0, np.array([50]), np.array([9]))[0] == True  # noqa: E712  doc[9] == doc[clamp(50)]
+
+    with pytest.raises(TypeError, match="2 dimensions"):
+        mt.lower_mods(None, lambda b, h, q, kv: torch.zeros(3, 3)[q] > 0)
+    with pytest.raises(TypeError, match="dtype"):
+        mt.lower_mods(None, lambda b, h, q, kv: torch.zeros(3, dtype=torch.float16)[q] > 0)
