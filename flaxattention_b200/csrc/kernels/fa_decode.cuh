@@ -80,9 +80,21 @@ extern "C" __global__ void __launch_bounds__(fa_dec::NT) fa_decode_kernel(const 
     }
     return false;
   };
+  // With one row group (Sq <= 16) every warp reads only its own WN keys of a tile: it then loads
+  // just those rows itself and the warps run as independent pipelines, with no block-wide
+  // barrier inside the kv loop.  With several row groups the tile is loaded cooperatively.
+  constexpr bool PRIVATE = RG == 1;
   auto load_kv = [&](int stage, int n0) {
-    fa_load_tile<D, ES, NT>(sK + stage * K_BYTES, kg + (long long)n0 * p.k.ss * ES, p.k.ss * ES, BN, p.Skv - n0, tid);
-    fa_load_tile<DV, ES, NT>(sV + stage * V_BYTES, vg + (long long)n0 * p.v.ss * ES, p.v.ss * ES, BN, p.Skv - n0, tid);
+    if (PRIVATE) {
+      const int first = n0 + cg * WN, vr = p.Skv - first;
+      const long long koff = vr > 0 ? (long long)first * p.k.ss * ES : 0;
+      const long long voff = vr > 0 ? (long long)first * p.v.ss * ES : 0;
+      fa_load_tile<D, ES, 32>(sK + stage * K_BYTES + cg * WN * PQ, kg + koff, p.k.ss * ES, WN, vr, lane);
+      fa_load_tile<DV, ES, 32>(sV + stage * V_BYTES + cg * WN * PV, vg + voff, p.v.ss * ES, WN, vr, lane);
+    } else {
+      fa_load_tile<D, ES, NT>(sK + stage * K_BYTES, kg + (long long)n0 * p.k.ss * ES, p.k.ss * ES, BN, p.Skv - n0, tid);
+      fa_load_tile<DV, ES, NT>(sV + stage * V_BYTES, vg + (long long)n0 * p.v.ss * ES, p.v.ss * ES, BN, p.Skv - n0, tid);
+    }
   };
 
   float o[DV / 8][4];
@@ -113,7 +125,8 @@ extern "C" __global__ void __launch_bounds__(fa_dec::NT) fa_decode_kernel(const 
     if (haves[pf]) load_kv(pf, n0s[pf]);
     fa_cp_commit();
     fa_cp_wait<STAGES - 1>();
-    __syncthreads();
+    if (PRIVATE && q_loaded) __syncwarp();
+    else __syncthreads();  // (first iteration: the query tile was loaded by all threads)
 
     if (!q_loaded) {
       q_loaded = true;
@@ -188,7 +201,8 @@ extern "C" __global__ void __launch_bounds__(fa_dec::NT) fa_decode_kernel(const 
     }
     fa_mma_nn<DT, WN, DV>(o, s, sV + cur * V_BYTES + cg * WN * PV, PV, lane);
 
-    __syncthreads();
+    if (PRIVATE) __syncwarp();
+    else __syncthreads();
     cur = (cur + 1) % STAGES;
   }
 

@@ -1,27 +1,32 @@
 // Flash-attention forward for sm_100a on the 5th-generation tensor cores:
 //   S = Q K^T and O += P V are tcgen05.mma instructions with accumulators in TMEM,
 //   Q / K / V tiles arrive by TMA (128-byte swizzle) through an mbarrier ring,
-//   the softmax runs thread-per-row on data read with tcgen05.ld, and P goes back to TMEM
-//   (16-bit, aliasing S) to be the A operand of the second product.
+//   the softmax runs thread-per-row on scores read once from TMEM into registers, and P goes
+//   back to TMEM as 16-bit pairs to be the A operand of the second product (its own columns
+//   with D = 64, over the score columns with D = 128).
 // Same math and BlockMask walk as fa_fwd.cuh (see there for the reference citations); this
-// kernel covers fp16 / bf16, D = Dv in {64, 128}, block sizes that are multiples of 128.
+// kernel covers fp16 / bf16, D = Dv in {64, 128}, block sizes that are multiples of 128 and a
+// positive scale.
 //
 // One CTA owns two 128-row query tiles of one (batch, head) and streams 128-row K/V tiles
 // past both.  Warp roles (12 warps = 3 warpgroups):
 //   warps 0-3  softmax warpgroup of query tile 0      warps 4-7  of query tile 1
 //   warp 8     TMA producer (one lane)
-//   warp 9     MMA issuer (one lane); also allocates / frees TMEM       warps 10-11 idle
+//   warp 9     MMA issuer (one lane); also allocates / frees TMEM.  With D = 64 it issues the S
+//              products only and warp 10 the PV products; warp 11 is idle
 // Registers are moved from the third warpgroup to the two softmax warpgroups (setmaxnreg),
 // which hold a whole 128-column score row per thread.
-// While one warpgroup does the softmax of its tile, the tensor core works on the other
-// tile: the issue order per kv step j is  PV0(j), S0(j+1), PV1(j), S1(j+1).
+// The S columns of a tile are released as soon as its scores are in registers, so with D = 64
+// S of step j+1 is computed while the softmax of step j runs; with D = 128 (P over the S
+// columns) the issue order per kv step j is  PV0(j), S0(j+1), PV1(j), S1(j+1).
 // The running maximum is only raised when it grew by more than 2^8 (the stale maximum is
 // exact as long as it is used consistently), so rescaling O in TMEM is rare.
 //
 // Every mbarrier wait is bounded; on expiry the CTA raises FA_STATUS_WAIT_TIMEOUT in the
 // status word, all roles leave their loops, TMEM is freed and the kernel returns.
 //
-// Compile-time parameters (macros): FA_DTYPE (0 fp16, 1 bf16), FA_D (64 or 128).
+// Compile-time parameters (macros): FA_DTYPE (0 fp16, 1 bf16), FA_D (64 or 128), FA_TC_DECODE
+// (split-KV variant, see below); tuning aids FA_TC_TRACE, FA_TC_HALF_EXP, FA_TC_POLY_EVERY.
 #pragma once
 #include "fa_sm100.cuh"
 
