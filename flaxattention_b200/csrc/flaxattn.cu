@@ -364,15 +364,23 @@ int pick_decode(int dtype, int D, int Dv, int Sq, const FaTables* t, DecCfg& c) 
   if (t && t->kv_num && t->nQ != 1) return fail(FA_EUNSUPPORTED, "decode needs a BlockMask with a single q block");
   const int BM = Sq <= 16 ? 16 : (Sq <= 32 ? 32 : 64);
   const int CG = 4 / (BM / 16);
+  // tuning aid: FLAXATTN_DECODE_BN / FLAXATTN_DECODE_STAGES restrict the search below
+  const char* env_bn = getenv("FLAXATTN_DECODE_BN");
+  const char* env_st = getenv("FLAXATTN_DECODE_STAGES");
+  const int only_bn = env_bn ? atoi(env_bn) : 0, only_st = env_st ? atoi(env_st) : 0;
   for (int BN : {128, 64, 32, 16}) {
+    if (only_bn && BN != only_bn) continue;
     if (BN / CG < 16) continue;
     if (D > 64 && BN > 64) continue;
     if (t && t->kv_num && !divides_or_single(BN, t->KVB, t->nKV)) continue;
-    for (int stages : {3, 2}) {
+    // Two stages first: the kernel is bound by the latency its few resident warps can hide, and
+    // the smaller ring lets a third CTA share the SM (B32 H8 Skv16384 D64: 0.187 ms with two
+    // stages against 0.218 ms with three at one query row, 0.224 against 0.269 at sixteen).
+    for (int stages : {2, 3, 4}) {
+      if (only_st ? stages != only_st : stages == 4) continue;
       const int pipe = stages * (BN * pitch(D, 2) + BN * pitch(Dv, 2));
       const int mrg = CG * BM * (Dv + 4) * 4;
       const int smem = BM * pitch(D, 2) + (pipe > mrg ? pipe : mrg);
-      if (smem > 113 * 1024 && stages == 3) continue;  // keep two CTAs per SM when possible
       if (smem > kMaxSmem) continue;
       c = {BM, BN, stages, smem};
       return FA_OK;
@@ -1098,11 +1106,17 @@ int fa_decode_num_splits(const fa_attn_params* p, int sm_count) {
     const int cmax = tiles / 8 > 1 ? (tiles / 8 < 64 ? tiles / 8 : 64) : 1;
     return 2 * fill_waves(bh, cmax, sm_count);
   }
-  // general kernel: two CTAs per SM with its three-stage tiles, at least four kv tiles per CTA.
-  // A grid that ends in a part-filled wave costs more than a few extra partial results: at
-  // B*H = 256 on 148 SMs, 8 splits (6.9 waves) measured 0.224 ms against 0.244 ms for 3 (2.6 waves).
+  // general kernel: as many CTAs per SM as its shared memory allows (at most four by registers),
+  // at least four kv tiles per CTA.  A grid that ends in a part-filled wave costs more than a few
+  // extra partial results.
+  int per_sm = 2;
+  DecCfg c;
+  if (pick_decode(p->dtype, p->D, p->Dv, p->Sq, nullptr, c) == FA_OK) {
+    per_sm = (228 * 1024) / (c.smem + 1024);
+    per_sm = per_sm < 1 ? 1 : (per_sm > 4 ? 4 : per_sm);
+  }
   const int cmax = tiles / 4 > 1 ? (tiles / 4 < 64 ? tiles / 4 : 64) : 1;
-  return fill_waves(bh, cmax, 2 * sm_count);
+  return fill_waves(bh, cmax, per_sm * sm_count);
 }
 
 size_t fa_decode_workspace_bytes(const fa_attn_params* p, int num_splits) {
