@@ -549,27 +549,23 @@ __global__ void fa_delta_kernel(FaTensor o, FaTensor dout, float* __restrict__ d
 template <int DT, int LPR>
 __global__ void fa_bwd_prep_kernel(FaTensor o, FaTensor dout, const float* __restrict__ lse, float* __restrict__ nlse2,
                                    float* __restrict__ ndelta, float* __restrict__ dq_acc, int Hq, int Sq, int sq_pad,
-                                   int Dv, long long n_rows_pad) {
+                                   int Dv, int n_bh) {
+  // grid: x over the padded rows of one (batch, head), LPR lanes per row; (y, z) over the heads
   constexpr int EPC = 8;
-  const long long gt = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  const long long row = gt / LPR;
-  const int sub = (int)(gt % LPR);
-  if (dq_acc != nullptr && row < n_rows_pad) {
+  const int bh = blockIdx.y + blockIdx.z * gridDim.y;
+  const int gt = blockIdx.x * blockDim.x + threadIdx.x;
+  const int q = gt / LPR, sub = gt % LPR;
+  const bool in_range = bh < n_bh && q < sq_pad;
+  const long long row = (long long)bh * sq_pad + q;
+  if (dq_acc != nullptr && in_range) {
     float4* z = (float4*)(dq_acc + row * 64) + sub;
 #pragma unroll
     for (int i = 0; i < 16 / LPR; ++i) z[i * LPR] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
   float acc = 0.f;
-  bool valid = false;
-  long long bh = 0;
-  int q = 0;
-  if (row < n_rows_pad) {
-    bh = row / sq_pad;
-    q = (int)(row - bh * sq_pad);
-    valid = q < Sq;
-  }
+  const bool valid = in_range && q < Sq;
   if (valid) {
-    const int b = (int)(bh / Hq), h = (int)(bh - (long long)b * Hq);
+    const int b = bh / Hq, h = bh - b * Hq;
     const char* po = (const char*)o.ptr + ((long long)b * o.sb + (long long)h * o.sh + (long long)q * o.ss) * 2;
     const char* pd = (const char*)dout.ptr + ((long long)b * dout.sb + (long long)h * dout.sh + (long long)q * dout.ss) * 2;
     for (int c = sub; c * EPC < Dv; c += LPR) {
@@ -591,10 +587,10 @@ __global__ void fa_bwd_prep_kernel(FaTensor o, FaTensor dout, const float* __res
   }
 #pragma unroll
   for (int off = LPR / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-  if (row < n_rows_pad && sub == 0) {
+  if (in_range && sub == 0) {
     float nl = -INFINITY;
     if (valid) {
-      const float l = lse[bh * Sq + q];
+      const float l = lse[(long long)bh * Sq + q];
       nl = (l == -INFINITY) ? -INFINITY : -l * 1.4426950408889634f;
     }
     nlse2[row] = nl;
@@ -607,16 +603,15 @@ __global__ void fa_bwd_prep_kernel(FaTensor o, FaTensor dout, const float* __res
 // eight 16-byte chunks of a block row r sit at position k ^ (r & 7).
 template <int DT>
 __global__ void fa_dq_convert_kernel(const float* __restrict__ acc, FaTensor dq, int Hq, int Sq, int sq_pad, float scale,
-                                     long long n_chunks) {
-  const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;  // one 8-element output chunk each
-  if (i >= n_chunks) return;
-  const int k8 = (int)(i & 7);
-  const long long row = i >> 3;
-  const long long bh = row / Sq;
-  const int q = (int)(row - bh * Sq);
-  const int b = (int)(bh / Hq), h = (int)(bh - (long long)b * Hq);
+                                     int n_bh) {
+  // grid: x over the rows of one (batch, head), one 8-element output chunk per thread; (y, z) over the heads
+  const int bh = blockIdx.y + blockIdx.z * gridDim.y;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const int k8 = i & 7, q = i >> 3;
+  if (bh >= n_bh || q >= Sq) return;
+  const int b = bh / Hq, h = bh - b * Hq;
   const int r = q & 127, c = 2 * (k8 & 3);
-  const float* src = acc + (bh * sq_pad + (q - r)) * 64 + (k8 >> 2) * (128 * 32) + r * 32;
+  const float* src = acc + ((long long)bh * sq_pad + (q - r)) * 64 + (k8 >> 2) * (128 * 32) + r * 32;
   const float4 lo = *(const float4*)(src + ((c ^ (r & 7)) * 4));
   const float4 hi = *(const float4*)(src + (((c + 1) ^ (r & 7)) * 4));
   char* dst = (char*)dq.ptr + ((long long)b * dq.sb + (long long)h * dq.sh + (long long)q * dq.ss) * 2 + k8 * 16;
@@ -1015,13 +1010,14 @@ int fa_bwd(fa_module* m, const fa_attn_params* p, const fa_tensor* dout, const f
     const bool run_main = !(p->flags & FA_FLAG_BWD_SKIP_DKDV);
     bool zeroed = false;
     if (!(p->flags & FA_FLAG_BWD_SKIP_DELTA)) {
-      const long long n_rows_pad = (long long)p->B * p->Hq * sq_pad;
-      const unsigned blocks = (unsigned)((n_rows_pad * 8 + 255) / 256);
+      const int n_bh = p->B * p->Hq;
+      const int gy = n_bh < 32768 ? n_bh : 32768;
+      const dim3 grid((unsigned)((sq_pad * 8 + 255) / 256), (unsigned)gy, (unsigned)((n_bh + gy - 1) / gy));
       float* zero = run_main ? dq_acc : nullptr;  // the prep pass also clears the dQ accumulator
       if (p->dtype == FA_F16)
-        fa_bwd_prep_kernel<FA_F16, 8><<<blocks, 256, 0, st>>>(kp.o, kp.dout, p->lse, nlse2, ndelta, zero, p->Hq, p->Sq, sq_pad, p->Dv, n_rows_pad);
+        fa_bwd_prep_kernel<FA_F16, 8><<<grid, 256, 0, st>>>(kp.o, kp.dout, p->lse, nlse2, ndelta, zero, p->Hq, p->Sq, sq_pad, p->Dv, n_bh);
       else
-        fa_bwd_prep_kernel<FA_BF16, 8><<<blocks, 256, 0, st>>>(kp.o, kp.dout, p->lse, nlse2, ndelta, zero, p->Hq, p->Sq, sq_pad, p->Dv, n_rows_pad);
+        fa_bwd_prep_kernel<FA_BF16, 8><<<grid, 256, 0, st>>>(kp.o, kp.dout, p->lse, nlse2, ndelta, zero, p->Hq, p->Sq, sq_pad, p->Dv, n_bh);
       FA_CUDA_CHECK(cudaGetLastError());
       zeroed = run_main;
     }
@@ -1040,12 +1036,13 @@ int fa_bwd(fa_module* m, const fa_attn_params* p, const fa_tensor* dout, const f
       if (int rc = launch(ktc, dim3(p->Hkv, p->B, (p->Skv + 127) / 128), dim3(512), &tp, stream)) return rc;
     }
     if (!(p->flags & FA_FLAG_BWD_SKIP_DQ)) {
-      const long long n_chunks = (long long)p->B * p->Hq * p->Sq * 8;
-      const unsigned blocks = (unsigned)((n_chunks + 255) / 256);
+      const int n_bh = p->B * p->Hq;
+      const int gy = n_bh < 32768 ? n_bh : 32768;
+      const dim3 grid((unsigned)((p->Sq * 8 + 255) / 256), (unsigned)gy, (unsigned)((n_bh + gy - 1) / gy));
       if (p->dtype == FA_F16)
-        fa_dq_convert_kernel<FA_F16><<<blocks, 256, 0, st>>>(dq_acc, kp.dq, p->Hq, p->Sq, sq_pad, p->scale, n_chunks);
+        fa_dq_convert_kernel<FA_F16><<<grid, 256, 0, st>>>(dq_acc, kp.dq, p->Hq, p->Sq, sq_pad, p->scale, n_bh);
       else
-        fa_dq_convert_kernel<FA_BF16><<<blocks, 256, 0, st>>>(dq_acc, kp.dq, p->Hq, p->Sq, sq_pad, p->scale, n_chunks);
+        fa_dq_convert_kernel<FA_BF16><<<grid, 256, 0, st>>>(dq_acc, kp.dq, p->Hq, p->Sq, sq_pad, p->scale, n_bh);
       FA_CUDA_CHECK(cudaGetLastError());
     }
     return FA_OK;
