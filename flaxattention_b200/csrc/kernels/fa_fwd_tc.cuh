@@ -45,8 +45,10 @@ constexpr int ATOM_BYTES = 128 * 128;    // 128 rows x 128 bytes
 // Split-KV decode variant (FA_TC_DECODE, D = 64): the CTA owns ONE query tile (Sq <= 128 rows,
 // the rest of the 128 is padding) and a contiguous share of the kv tiles the BlockMask lists; the
 // two softmax warpgroups take alternate kv tiles of that share, so both work on the same
-// query rows, and each writes its own un-normalised partial result (running maximum, sum, O)
-// for the combine kernel.  More stages, since the kv stream is all there is.
+// query rows (at most 64: the first warpgroup has them in rows 0-63 of its tile, the second in
+// rows 64-127 of a copy of the tile loaded 64 rows down, and warps without a real row idle), and
+// each writes its own un-normalised partial result (running maximum, sum, O) for the combine
+// kernel.  More stages, since the kv stream is all there is.
 #ifndef FA_TC_DECODE
 #define FA_TC_DECODE 0
 #endif
@@ -403,10 +405,14 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
     // the query tiles do not depend on the kv schedule: their loads start now and run while the
     // schedule is being built
     fa_tma_prefetch_desc(&P.tq);
-    fa_mbar_expect_tx(bar_addr(sb, BAR_Q), DECODE ? Q_BYTES / 2 : Q_BYTES);
-    for (int i = 0; i < (DECODE ? 1 : 2); ++i)
+    // (decode variant: both warpgroups work on the same <= 64 query rows.  The second copy of the
+    //  tile is loaded 64 rows down - rows -64..-1 of the tensor are out of range and read as zero -
+    //  so that the second warpgroup finds its rows in TMEM lanes 64-127 and the four warps that
+    //  have real rows sit on four different SM sub-partitions)
+    fa_mbar_expect_tx(bar_addr(sb, BAR_Q), Q_BYTES);
+    for (int i = 0; i < 2; ++i)
       for (int a = 0; a < ATOMS; ++a)
-        fa_tma_load_4d(sb + (i * ATOMS + a) * ATOM_BYTES, &P.tq, bar_addr(sb, BAR_Q), a * 64, m0 + i * BM, h, b);
+        fa_tma_load_4d(sb + (i * ATOMS + a) * ATOM_BYTES, &P.tq, bar_addr(sb, BAR_Q), a * 64, DECODE ? -64 * i : m0 + i * BM, h, b);
   }
   const int ntiles = min((p.Skv + BN - 1) / BN, MAXT);
   for (int i = tid; i < 2 * MAXT; i += NT) cls[i] = 0;
@@ -536,7 +542,7 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
               if (!ok) break;
             }
             fa_tc_fence_after();
-            const fa_u32 loQ = fa_desc_lo(sb + (DECODE ? 0 : i) * ATOMS * ATOM_BYTES, 16), loK = fa_desc_lo(sb + OFF_K + s * KV_STAGE, 16);
+            const fa_u32 loQ = fa_desc_lo(sb + i * ATOMS * ATOM_BYTES, 16), loK = fa_desc_lo(sb + OFF_K + s * KV_STAGE, 16);
 #pragma unroll
             for (int kk = 0; kk < D / 16; ++kk) {
               const fa_u32 koff = ((kk / 4) * ATOM_BYTES + (kk % 4) * 32) >> 4;
@@ -668,7 +674,10 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
     const int i = warp >> 2;                       // query tile of this warpgroup
     const int lane_base = (warp & 3) * 32;         // TMEM lanes this warp may touch
     const int r = lane_base + lane;                // row inside the tile
-    const int qi = m0 + (DECODE ? 0 : i * BM) + r;  // query index
+    const int qi = DECODE ? r - 64 * i : m0 + i * BM + r;  // query index
+    // decode variant: warps whose 32 rows are all padding only keep the barrier protocol going
+    const bool warp_active = !DECODE || (lane_base - 64 * i >= 0 && lane_base - 64 * i < p.Sq);
+    fa_u32 idle_cnt = 0;
     const fa_u32 t_s = tmem + ((fa_u32)lane_base << 16) + COL_S + i * BN;
     const fa_u32 t_o = tmem + ((fa_u32)lane_base << 16) + COL_O + i * D;
     const fa_u32 t_p = SEP_P ? tmem + ((fa_u32)lane_base << 16) + COL_P + i * 64 : t_s;
@@ -681,11 +690,26 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
     for (int j = 0; j < nsteps && ok; ++j) {
       const int mode = sched_mode[2 * j + i];
       if (mode == 0) continue;
+      if (!warp_active) {
+        // in step with the working warps: S of this step is there, then both arrivals they also make
+        ok = fa_mbar_wait_warp(bar_addr(sb, BAR_S + i), idle_cnt & 1u, abort_flag);
+        // The PV product of the previous step must be complete before this warp arrives on the P
+        // barrier again: otherwise its arrival would be counted into the previous phase, which the
+        // working warps may not have reached yet, and that product would start on unwritten P.
+        if (ok && idle_cnt > 0) ok = fa_mbar_wait_warp(bar_addr(sb, BAR_O + i), (idle_cnt - 1) & 1u, abort_flag);
+        if (!ok) break;
+        fa_tc_fence_after();
+        fa_tc_fence_before();
+        if (SEP_P) fa_mbar_arrive(bar_addr(sb, BAR_SFREE2 + i));
+        fa_mbar_arrive(bar_addr(sb, BAR_P + i));
+        ++idle_cnt;
+        continue;
+      }
       const bool masked = (FA_HAS_MASK_MOD && mode == 1) || (int)sched_tile[DECODE ? 2 * j + i : j] * BN + BN > p.Skv;
       ok = masked ? softmax_step<true>(c, j, mode) : softmax_step<false>(c, j, mode);
     }
     const float m_ref = c.m_ref, l = c.l;
-    const fa_u32 cnt = c.cnt;
+    const fa_u32 cnt = warp_active ? c.cnt : idle_cnt;
     // ---- epilogue: O / l and the logsumexp of this thread's row ---------------------------
     if (ok && cnt > 0) ok = fa_mbar_wait_warp(bar_addr(sb, BAR_O + i), (cnt - 1) & 1u, abort_flag);
 #if FA_TC_DECODE
@@ -703,13 +727,13 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
 #pragma unroll
           for (int e = 0; e < 32; ++e) o[e] = 0.f;
         }
-        if (qi < p.Sq) {
+        if (qi >= 0 && qi < p.Sq) {
 #pragma unroll
           for (int e = 0; e < 32; e += 4)
             *(float4*)(p.part_o + prow * D + c * 32 + e) = make_float4(o[e], o[e + 1], o[e + 2], o[e + 3]);
         }
       }
-      if (qi < p.Sq) *(float2*)(p.part_ml + prow * 2) = make_float2(m_ref, l);
+      if (qi >= 0 && qi < p.Sq) *(float2*)(p.part_ml + prow * 2) = make_float2(m_ref, l);
     }
 #else
     if (ok) {
