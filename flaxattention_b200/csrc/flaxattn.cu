@@ -833,8 +833,12 @@ bool tc_decode_eligible(const fa_attn_params* p) {
   if (p->D != 64 || p->Dv != 64) return false;
   // The kernel gives every query row a thread and pads the tile to 128 rows, so its softmax work
   // per kv tile does not shrink with Sq: measured against the general decode kernel it wins from
-  // about 33 rows up (0.52 ms against 0.62 ms at 64 rows) and loses below (0.49 against 0.29 at 16).
-  if (p->Sq < 33 || p->Sq > 64 || p->Skv < 1024 || p->Skv > 32768) return false;
+  // 33 rows up (0.46 ms against 0.55 ms at 40-64 rows) and loses below (0.43 against 0.35 at 17-32).
+  static const int min_rows = [] {  // tuning aid: FLAXATTN_TC_DECODE_MIN_SQ moves the lower limit
+    const char* e = getenv("FLAXATTN_TC_DECODE_MIN_SQ");
+    return e ? atoi(e) : 33;
+  }();
+  if (p->Sq < min_rows || p->Sq > 64 || p->Skv < 1024 || p->Skv > 32768) return false;
   if (!(p->scale > 0.f)) return false;
   const fa_block_tables& t = p->tables;
   if (t.kv_num_blocks) {
