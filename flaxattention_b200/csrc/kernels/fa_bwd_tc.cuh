@@ -52,6 +52,9 @@ struct FaBwdTcParams {
 #ifndef FA_TC_A_AFTER_B
 #define FA_TC_A_AFTER_B 0
 #endif
+#ifndef FA_TC_BWD_STEP16
+#define FA_TC_BWD_STEP16 1
+#endif
 #if FA_TC_TRACE == 1
 #define FA_TRACE_DECL long long trace_t0 = clock64();
 #define FA_TRACE(slot)                                                                        \
@@ -137,18 +140,19 @@ __device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.
 __device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // Element-wise work of one thread on a 32-column chunk: scores s and dp (fp32, raw) for kv row
-// `kv` and q columns q0 .. q0+31 -> packed P^T and dS^T (16 bit).  q0 is a multiple of 32 (the
-// compiler can see that from how the caller builds it), so the low five bits of every q index are
-// compile-time constants inside the mods while one copy of this code serves all four chunks of a
+// `kv` and q columns q0 .. q0+W-1 -> packed P^T and dS^T (16 bit).  q0 is a multiple of W (the
+// compiler can see that from how the caller builds it), so the low bits of every q index are
+// compile-time constants inside the mods while one copy of this code serves all chunks of a
 // tile row.  nlse2 / ndelta point at the row scalars of column q0.
-__device__ __forceinline__ void chunk(const float (&s)[32], const float (&dp)[32], const float* nlse2, const float* ndelta,
-                                      fa_u32 (&pp)[16], fa_u32 (&ds)[16], int mode, int q0, int kv, int gb, int gh,
+template <int W>
+__device__ __forceinline__ void chunk(const float (&s)[W], const float (&dp)[W], const float* nlse2, const float* ndelta,
+                                      fa_u32 (&pp)[W / 2], fa_u32 (&ds)[W / 2], int mode, int q0, int kv, int gb, int gh,
                                       float scale, float sc2) {
 #if !FA_ROUND_SCORES && (!FA_HAS_SCORE_MOD || defined(FA_SCORE_AFFINE))
   // no score_mod, or an affine one: two elements per instruction (packed fp32) wherever the
   // hardware has the form; only the exponentials and the mask are per element
 #pragma unroll
-  for (int e = 0; e < 32; e += 4) {
+  for (int e = 0; e < W; e += 4) {
     const float4 nl = *(const float4*)(nlse2 + e);
     const float4 nd = *(const float4*)(ndelta + e);
 #pragma unroll
@@ -185,7 +189,7 @@ __device__ __forceinline__ void chunk(const float (&s)[32], const float (&dp)[32
   }
 #else
 #pragma unroll
-  for (int e = 0; e < 32; e += 4) {
+  for (int e = 0; e < W; e += 4) {
     const float4 nl = *(const float4*)(nlse2 + e);
     const float4 nd = *(const float4*)(ndelta + e);
     float pv[4], dv[4];
@@ -465,6 +469,11 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
           fa_mma_commit(bar_addr(sb, BAR_DQFULL));
         }
         FA_TRACE(6); FA_STAMP(6);   // MMA C: issue product 5 + commits
+#if FA_TC_TRACE == 2
+        // tuning aid: when do products 3-5 of the pair actually complete
+        if (leader) { fa_mbar_wait(bar_addr(sb, BAR_DQFULL), (fa_u32)(n & 1), abort_flag); FA_STAMP(23); }
+        if (leader) { fa_mbar_wait(bar_addr(sb, BAR_PFREE), (fa_u32)(n & 1), abort_flag); FA_STAMP(9); }
+#endif
       }
     }
   } else if (warp < 8) {
@@ -493,6 +502,47 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
       if (ok) ok = fa_mbar_wait_warp(bar_addr(sb, BAR_QFULL + s), (fa_u32)((n / NSTAGE) & 1), abort_flag);
       if (!ok) break;
       fa_tc_fence_after();
+      const float* rowp = (const float*)(sm + OFF_ROW + s * 2 * 128 * 4);
+      fa_u32 pp0[16], pp1[16], ds0[16], ds1[16];
+#if FA_TC_BWD_STEP16 && !(FA_TC_EXP & 12)
+      // The 64 columns of this thread come in four steps of 16 (S^T and dP^T), the loads of a step
+      // in flight while the previous one is computed: few values are live at a time, which leaves
+      // the scheduler registers to overlap the latencies of independent elements (with all 128
+      // values loaded up front this loop ran at 28 clocks per element).
+      {
+        const fa_u32 tS = t_row + COL_S + half * 64, tD = t_row + COL_DP + half * 64;
+        const int c0 = half * 64;  // first q column of this thread inside the tile
+        float sA[16], dA[16], sB[16], dB[16];
+        fa_u32 p8[8], d8[8];
+        fa_tmem_ld16(tS, sA);
+        fa_tmem_ld16(tD, dA);
+        fa_tmem_wait_ld();
+#define FA_STEP(SC, DC, SN, DN, C, PP, DS, OFF, LAST)                                                      \
+  if (!(LAST)) {                                                                                           \
+    fa_tmem_ld16(tS + (C) + 16, SN);                                                                       \
+    fa_tmem_ld16(tD + (C) + 16, DN);                                                                       \
+  }                                                                                                        \
+  if (row_ok) {                                                                                            \
+    chunk<16>(SC, DC, rowp + c0 + (C), rowp + 128 + c0 + (C), p8, d8, mode, m0 + c0 + (C), kv, gb, gh, p.scale, sc2); \
+  } else {                                                                                                 \
+    _Pragma("unroll") for (int e = 0; e < 8; ++e) p8[e] = d8[e] = 0u;                                      \
+  }                                                                                                        \
+  _Pragma("unroll") for (int e = 0; e < 8; ++e) {                                                          \
+    PP[(OFF) + e] = p8[e];                                                                                 \
+    DS[(OFF) + e] = d8[e];                                                                                 \
+  }                                                                                                        \
+  if (!(LAST)) fa_tmem_wait_ld();
+        FA_STEP(sA, dA, sB, dB, 0, pp0, ds0, 0, false)
+        FA_STEP(sB, dB, sA, dA, 16, pp0, ds0, 8, false)
+        FA_STEP(sA, dA, sB, dB, 32, pp1, ds1, 0, false)
+        // every score of the pair is in registers: the S^T / dP^T columns may be overwritten
+        fa_tc_fence_before();
+        fa_mbar_arrive(bar_addr(sb, BAR_SFREE));
+        if (warp == 0) { FA_TRACE(11); FA_STAMP(11); }  // compute: TMEM loads done
+        FA_STEP(sB, dB, sA, dA, 48, pp1, ds1, 8, true)
+#undef FA_STEP
+      }
+#else
       float sa[32], sb2[32], da[32], db[32];
       if (FA_TC_EXP & 8) {
 #pragma unroll
@@ -508,16 +558,15 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
       fa_mbar_arrive(bar_addr(sb, BAR_SFREE));
       if (warp == 0) { FA_TRACE(11); FA_STAMP(11); }  // compute: TMEM loads
 
-      const float* rowp = (const float*)(sm + OFF_ROW + s * 2 * 128 * 4);
-      fa_u32 pp0[16], pp1[16], ds0[16], ds1[16];
       if (row_ok && !(FA_TC_EXP & 4)) {
         const int c0 = half * 64;  // first q column of this thread inside the tile
-        chunk(sa, da, rowp + c0, rowp + 128 + c0, pp0, ds0, mode, m0 + c0, kv, gb, gh, p.scale, sc2);
-        chunk(sb2, db, rowp + c0 + 32, rowp + 128 + c0 + 32, pp1, ds1, mode, m0 + c0 + 32, kv, gb, gh, p.scale, sc2);
+        chunk<32>(sa, da, rowp + c0, rowp + 128 + c0, pp0, ds0, mode, m0 + c0, kv, gb, gh, p.scale, sc2);
+        chunk<32>(sb2, db, rowp + c0 + 32, rowp + 128 + c0 + 32, pp1, ds1, mode, m0 + c0 + 32, kv, gb, gh, p.scale, sc2);
       } else {
 #pragma unroll
         for (int e = 0; e < 16; ++e) pp0[e] = pp1[e] = ds0[e] = ds1[e] = 0u;
       }
+#endif
       // pin the packed results here: without this the compiler sinks part of the math below the
       // wait that follows, onto the critical path between two groups of products
 #pragma unroll
