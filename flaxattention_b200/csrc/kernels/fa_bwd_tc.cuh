@@ -42,7 +42,9 @@ struct FaBwdTcParams {
 // Optional phase timing (tuning aid): with FA_TC_TRACE the status buffer must hold at least
 // 64 ints; slot k accumulates the SM cycles CTA (0,0,0) spent in phase k.
 // experiments (wrong results, timing only): bit 0 drain skips staging+reduce, bit 1 compute skips
-// the dS^T smem stores, bit 2 compute skips the math, bit 3 compute skips the TMEM loads
+// the dS^T smem stores, bit 2 compute skips the math, bit 3 compute skips the TMEM loads,
+// bit 4 the row scalars are constants instead of shared-memory loads, bit 5 drain stages but does
+// not reduce, bit 6 drain reduces without staging
 #ifndef FA_TC_EXP
 #define FA_TC_EXP 0
 #endif
@@ -153,8 +155,12 @@ __device__ __forceinline__ void chunk(const float (&s)[W], const float (&dp)[W],
   // hardware has the form; only the exponentials and the mask are per element
 #pragma unroll
   for (int e = 0; e < W; e += 4) {
+#if FA_TC_EXP & 16
+    const float4 nl = make_float4(-8.f, -8.f, -8.f, -8.f), nd = make_float4(0.f, 0.f, 0.f, 0.f);  // (timing experiment)
+#else
     const float4 nl = *(const float4*)(nlse2 + e);
     const float4 nd = *(const float4*)(ndelta + e);
+#endif
 #pragma unroll
     for (int u = 0; u < 4; u += 2) {
       const int qi0 = q0 | (e + u), qi1 = q0 | (e + u + 1);
@@ -663,7 +669,7 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
         if (dtid == 0) bulk_wait_read0();
         named_bar_sync(1, 128);
         if (hf == 0 && warp == 8) { FA_TRACE(21); FA_STAMP(21); }  // drain: wait for the previous bulk reduce
-        if (!(FA_TC_EXP & 1)) {
+        if (!(FA_TC_EXP & (1 | 64))) {
 #pragma unroll
           for (int k = 0; k < 8; ++k)
             *(float4*)(strow + ((k ^ (r & 7)) * 16)) = make_float4(a[4 * k], a[4 * k + 1], a[4 * k + 2], a[4 * k + 3]);
@@ -676,7 +682,7 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
         }
         fence_proxy_async();
         named_bar_sync(1, 128);
-        if (dtid == 0 && !(FA_TC_EXP & 1)) {
+        if (dtid == 0 && !(FA_TC_EXP & (1 | 32))) {
           bulk_reduce_add_f32(gdst + hf * (DQ_HALF_BYTES / 4), sb + OFF_DQ, DQ_HALF_BYTES);
           bulk_commit();
         }
