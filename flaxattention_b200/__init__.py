@@ -2,8 +2,9 @@
 
 Export list follows flaxattention/__init__.py:11-22 (without the matplotlib visualiser).
 """
-from .attention import flax_attention, flax_attention_pallas, math_attention
+from .attention import check_status, flax_attention, flax_attention_pallas, math_attention
 from .blockmask import BlockMask, and_masks, create_block_mask, noop_mask, or_masks
+from .pipeline import HostPipeline
 from . import fnp, masks, mods  # noqa: F401
 from typing import Callable
 
@@ -21,6 +22,8 @@ __all__ = [
     "noop_mask",
     "_mask_mod_signature",
     "_score_mod_signature",
+    "check_status",
+    "HostPipeline",
     "fnp",
     "masks",
     "mods",

@@ -15,7 +15,6 @@ LIB_PATH = os.path.join(_HERE, "libflaxattn.so")
 
 FA_F16, FA_BF16, FA_F32 = 0, 1, 2
 FLAG_ROUND_SCORES = 1
-FLAG_BWD_SKIP_DELTA, FLAG_BWD_SKIP_DKDV, FLAG_BWD_SKIP_DQ = 2, 4, 8
 FLAG_GENERAL_KERNELS = 16
 KIND_FWD, KIND_BWD, KIND_DECODE, KIND_BLOCKMASK = 0, 1, 2, 3
 
@@ -65,6 +64,7 @@ EXPORTS = [
     "fa_module_set_buffers", "fa_module_destroy", "fa_module_prepare", "fa_compile_count", "fa_fwd", "fa_bwd_workspace_bytes",
     "fa_bwd", "fa_decode_num_splits", "fa_decode_workspace_bytes", "fa_decode",
     "fa_block_mask_workspace_bytes", "fa_block_mask", "fa_decode_static_capacity", "fa_decode_static",
+    "fa_profile_enable", "fa_profile_read",
 ]
 
 
@@ -103,6 +103,8 @@ def lib() -> C.CDLL:
     if hasattr(L, "fa_decode_static"):
         L.fa_decode_static_capacity.restype = C.c_size_t
         L.fa_decode_static.argtypes = [C.c_void_p, C.POINTER(FaAttnParams), C.c_int, C.c_void_p]
+    L.fa_profile_enable.argtypes = [C.c_int]
+    L.fa_profile_read.argtypes = [C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_char_p)]
     L.fa_set_kernel_dir(os.path.join(_HERE, "csrc", "kernels").encode())
     cache = os.environ.get("FLAXATTN_CACHE_DIR")
     if cache is None:
@@ -148,3 +150,18 @@ class Module:
                 self.handle = None
         except Exception:
             pass
+
+
+def profile_enable(on: bool) -> None:
+    """Switches the per-kernel event timing of fa_fwd / fa_bwd / fa_decode on or off."""
+    check(lib().fa_profile_enable(1 if on else 0))
+
+
+def profile_read(max_kernels: int = 16):
+    """[(kernel name, milliseconds)] of this thread's most recent timed call, in launch order."""
+    ms = (C.c_float * max_kernels)()
+    names = (C.c_char_p * max_kernels)()
+    n = lib().fa_profile_read(max_kernels, ms, names)
+    if n < 0:
+        check(n)
+    return [(names[i].decode(), float(ms[i])) for i in range(min(n, max_kernels))]

@@ -75,6 +75,33 @@ def _validate_heads(hq: int, hkv: int, enable_gqa: bool):
 # --------------------------------------------------------------------------------------
 # C-ABI call plumbing
 # --------------------------------------------------------------------------------------
+# One status word for the whole process, in pinned host memory (which every GPU can address):
+# the tcgen05 kernels OR FA_STATUS_WAIT_TIMEOUT into it when one of their bounded barrier waits
+# runs out, and the host can look at it at any time without synchronising.  It is checked at
+# the start of the next call and by ``check_status()``.
+_status_word: Optional[torch.Tensor] = None
+
+
+def _status() -> torch.Tensor:
+    global _status_word
+    if _status_word is None:
+        _status_word = torch.zeros(1, dtype=torch.int32).pin_memory()
+    return _status_word
+
+
+def check_status() -> None:
+    """Raises ``FlaxAttnError`` if a kernel launched earlier through this module reported an
+    error (a barrier wait that ran out: the results of that launch are incomplete).  Call it
+    after synchronising to be sure about the launches issued so far; every attention call also
+    runs it first, so an error surfaces at the latest on the next call."""
+    w = _status_word
+    if w is not None and int(w[0]) != 0:
+        bits = int(w[0])
+        w[0] = 0
+        raise _cabi.FlaxAttnError(-3, f"a kernel reported status bits {bits:#x} (bit 0: a bounded barrier wait ran out); "
+                                      "the results of that launch are incomplete")
+
+
 def _tensor(t: torch.Tensor, layout: str) -> _cabi.FaTensor:
     """layout 'bhsd' or 'bshd'; the last dim must be contiguous."""
     if t.stride(-1) != 1:
@@ -127,8 +154,7 @@ class _Call:
         if self.options.get("kernels") == "general":
             p.flags |= _cabi.FLAG_GENERAL_KERNELS
         st = self.options.get("status")  # optional int32 CUDA tensor the kernels OR error bits into
-        if st is not None:
-            p.status = st.data_ptr()
+        p.status = (st if st is not None else _status()).data_ptr()
         bm = self.block_mask
         if bm is not None:
             t = p.tables
@@ -163,6 +189,7 @@ class _Call:
 
 def _forward(call: _Call, q, k, v):
     L = _cabi.lib()
+    check_status()
     out = call.out_like(q)
     lse = torch.empty(call.B, call.Hq, call.Sq, dtype=torch.float32, device=q.device)
     p = call.params(q, k, v, out, lse)
@@ -184,6 +211,7 @@ def _forward(call: _Call, q, k, v):
 
 def _backward(call: _Call, q, k, v, out, lse, dout):
     L = _cabi.lib()
+    check_status()
     if dout.stride(-1) != 1:
         dout = dout.contiguous()
     dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
@@ -283,14 +311,44 @@ def flax_attention(
     return out
 
 
+_BOUND_MODS: Dict[Tuple, Tuple] = {}
+
+
+def _bind_other_buffers(fn: Callable, bufs: Tuple, is_score: bool) -> Callable:
+    """``fn(..., *bufs)`` as a mod of the plain signature.  The reference passes the extra
+    arrays as trailing arguments (core/attention.py:35-52); here they become tensors the mod
+    closes over, which the tracer turns into device loads.  The wrapper is cached on the
+    identity of the function and the buffers so that repeated calls reuse the compiled module."""
+    if not bufs:
+        return fn
+    key = (id(fn), is_score) + tuple(id(b) for b in bufs)
+    hit = _BOUND_MODS.get(key)
+    if hit is not None and hit[0] is fn and len(hit[1]) == len(bufs) and all(a is b for a, b in zip(hit[1], bufs)):
+        return hit[3]
+    tens = tuple(b if isinstance(b, torch.Tensor) else torch.as_tensor(np.asarray(b)) for b in bufs)
+    if is_score:
+        def bound(score, b, h, q_idx, kv_idx):
+            return fn(score, b, h, q_idx, kv_idx, *tens)
+    else:
+        def bound(b, h, q_idx, kv_idx):
+            return fn(b, h, q_idx, kv_idx, *tens)
+    if len(_BOUND_MODS) > 256:
+        _BOUND_MODS.clear()
+    _BOUND_MODS[key] = (fn, tuple(bufs), tens, bound)
+    return bound
+
+
 def math_attention(query, key, value, score_mod, block_mask: Tuple, scale, kernel_options=None,
                    score_mod_other_buffers: Tuple = (), mask_mod_other_buffers: Tuple = (), use_pallas: bool = False):
     """Signature of the reference's ``math_attention`` (core/attention.py:67-106): takes
     ``BlockMask.as_tuple()`` and returns ``(output, logsumexp / ln 2)``.  It runs the same
-    fused kernels as ``flax_attention``; a dense score tensor is never built."""
-    if score_mod_other_buffers or mask_mod_other_buffers:
-        raise NotImplementedError("captured buffers are not supported")
+    fused kernels as ``flax_attention``; a dense score tensor is never built.
+    ``score_mod_other_buffers`` / ``mask_mod_other_buffers`` are passed to the mods as trailing
+    arguments, as the reference does (core/attention.py:35-52)."""
     mask_mod = block_mask[-1]
+    score_mod = _bind_other_buffers(score_mod, tuple(score_mod_other_buffers), True)
+    if mask_mod is not None:
+        mask_mod = _bind_other_buffers(mask_mod, tuple(mask_mod_other_buffers), False)
     bm = BlockMask(*block_mask[:8], (block_mask[8], block_mask[9]), mask_mod)
     call = _Call(query, key, value, score_mod, mask_mod, bm, scale, "bhsd", 0, 0, kernel_options, round_scores=True)
     out, lse = _run(call, query, key, value)

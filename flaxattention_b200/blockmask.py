@@ -21,6 +21,7 @@ always ``num = 0, indices = arange``).  ``reference_q_tables`` reproduces those 
 """
 from __future__ import annotations
 
+import collections
 import functools
 import operator
 from typing import Callable, Optional, Tuple, Union
@@ -301,6 +302,11 @@ def bind_mod_buffers(module, score_mod: Optional[Callable], mask_mod: Optional[C
     module._bound_buffers = keep  # the addresses stay valid at least until the next binding
 
 
+# finished tables of create_block_mask(..., _compile=True), least recently used first
+_TABLE_CACHE: "collections.OrderedDict" = collections.OrderedDict()
+_TABLE_CACHE_MAX = 64
+
+
 def _require_cuda(device) -> torch.device:
     if not torch.cuda.is_available():
         raise RuntimeError("flaxattention_b200 needs a CUDA device (B200, sm_100a); there is no CPU path")
@@ -324,8 +330,12 @@ def create_block_mask(
 ) -> BlockMask:
     """Builds the BlockMask of ``mask_mod`` on the GPU.
 
-    Same arguments as the reference (``_compile`` is accepted and ignored: the kernels are
-    always compiled).  ``b_offset`` / ``h_offset`` give the global index of the first batch
+    Same arguments as the reference.  The kernels are always compiled; ``_compile=True`` (the
+    reference jits the construction so that repeated calls are cheap,
+    flaxattention/core/blockmask.py:445-448) additionally keeps the finished tables, keyed by the
+    lowered mask source, the shape, the block sizes, the offsets and the device, so a repeated
+    call launches nothing.  Masks that read captured tensors are not kept (their contents may
+    change between calls).  ``b_offset`` / ``h_offset`` give the global index of the first batch
     / head when the tables of one batch x heads shard are built.  A 5-argument function is
     treated as a score_mod whose ``-inf`` results mark masked positions.
     """
@@ -348,6 +358,15 @@ def create_block_mask(
     dev = _require_cuda(device)
     nq, nkv = Q_LEN // Q_BLOCK_SIZE, KV_LEN // KV_BLOCK_SIZE
     module = module_for(None, mask_mod)
+    cache_key = None
+    if _compile:
+        ms = lower_mods(None, None if mask_mod is noop_mask else mask_mod)
+        if not ms.buffers:
+            cache_key = (ms.key, B, H, Q_LEN, KV_LEN, Q_BLOCK_SIZE, KV_BLOCK_SIZE, int(b_offset), int(h_offset), str(dev))
+            hit = _TABLE_CACHE.get(cache_key)
+            if hit is not None:
+                _TABLE_CACHE.move_to_end(cache_key)
+                return BlockMask(*hit, (Q_BLOCK_SIZE, KV_BLOCK_SIZE), mask_mod)
     L = _cabi.lib()
     with torch.cuda.device(dev):
         mk = lambda *s: torch.empty(*s, dtype=torch.int32, device=dev)  # noqa: E731
@@ -363,5 +382,9 @@ def create_block_mask(
             kv_num.data_ptr(), kv_idx.data_ptr(), fkv_num.data_ptr(), fkv_idx.data_ptr(),
             q_num.data_ptr(), q_idx.data_ptr(), fq_num.data_ptr(), fq_idx.data_ptr(),
             ws.data_ptr(), ws_bytes, torch.cuda.current_stream(dev).cuda_stream))
+    if cache_key is not None:
+        _TABLE_CACHE[cache_key] = (kv_num, kv_idx, fkv_num, fkv_idx, q_num, q_idx, fq_num, fq_idx)
+        while len(_TABLE_CACHE) > _TABLE_CACHE_MAX:
+            _TABLE_CACHE.popitem(last=False)
     return BlockMask(kv_num, kv_idx, fkv_num, fkv_idx, q_num, q_idx, fq_num, fq_idx,
                      (Q_BLOCK_SIZE, KV_BLOCK_SIZE), mask_mod)

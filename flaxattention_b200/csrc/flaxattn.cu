@@ -283,10 +283,64 @@ int upload_buffers(Kernel* k, void* stream) {
   return FA_OK;
 }
 
+// ---- per-kernel device times (fa_profile_enable / fa_profile_read) -----------------------
+// While profiling is on, every kernel launched by an entry point is bracketed by two CUDA events
+// on the caller's stream.  The records belong to the calling thread and are reset at the start of
+// each fa_fwd / fa_bwd / fa_decode call; the results of the call are the same with and without.
+struct ProfRecord {
+  const char* name;
+  cudaEvent_t e0, e1;
+};
+std::atomic<int> g_profile_on{0};
+thread_local std::vector<ProfRecord> t_prof;        // records of the most recent call
+thread_local std::vector<cudaEvent_t> t_prof_pool;  // events of this thread, reused between calls
+thread_local size_t t_prof_used = 0;
+thread_local int t_prof_dev = -1;
+
+void prof_reset() {
+  if (!g_profile_on.load(std::memory_order_relaxed)) return;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return;
+  if (dev != t_prof_dev) {  // events belong to the device that was current when they were made
+    for (cudaEvent_t e : t_prof_pool) cudaEventDestroy(e);
+    t_prof_pool.clear();
+    t_prof_dev = dev;
+  }
+  t_prof.clear();
+  t_prof_used = 0;
+}
+cudaEvent_t prof_event() {
+  if (t_prof_used == t_prof_pool.size()) {
+    cudaEvent_t e = nullptr;
+    if (cudaEventCreate(&e) != cudaSuccess) return nullptr;
+    t_prof_pool.push_back(e);
+  }
+  return t_prof_pool[t_prof_used++];
+}
+struct ProfScope {
+  cudaStream_t st;
+  cudaEvent_t e1 = nullptr;
+  ProfScope(const char* name, void* stream) : st((cudaStream_t)stream) {
+    if (!g_profile_on.load(std::memory_order_relaxed)) return;
+    cudaEvent_t e0 = prof_event();
+    e1 = prof_event();
+    if (e0 == nullptr || e1 == nullptr) {
+      e1 = nullptr;
+      return;
+    }
+    cudaEventRecord(e0, st);
+    t_prof.push_back({name, e0, e1});
+  }
+  ~ProfScope() {
+    if (e1 != nullptr) cudaEventRecord(e1, st);
+  }
+};
+
 int launch(Kernel* k, dim3 grid, dim3 block, void* params, void* stream) {
   if (int rc = ready_kernel(k)) return rc;
   if (int rc = upload_buffers(k, stream)) return rc;
   void* args[] = {params};
+  ProfScope prof(k->entry.c_str(), stream);
   FA_CUDA_CHECK(cudaLaunchKernel((const void*)k->fn, grid, block, args, (size_t)k->smem, (cudaStream_t)stream));
   return FA_OK;
 }
@@ -364,20 +418,14 @@ int pick_decode(int dtype, int D, int Dv, int Sq, const FaTables* t, DecCfg& c) 
   if (t && t->kv_num && t->nQ != 1) return fail(FA_EUNSUPPORTED, "decode needs a BlockMask with a single q block");
   const int BM = Sq <= 16 ? 16 : (Sq <= 32 ? 32 : 64);
   const int CG = 4 / (BM / 16);
-  // tuning aid: FLAXATTN_DECODE_BN / FLAXATTN_DECODE_STAGES restrict the search below
-  const char* env_bn = getenv("FLAXATTN_DECODE_BN");
-  const char* env_st = getenv("FLAXATTN_DECODE_STAGES");
-  const int only_bn = env_bn ? atoi(env_bn) : 0, only_st = env_st ? atoi(env_st) : 0;
   for (int BN : {128, 64, 32, 16}) {
-    if (only_bn && BN != only_bn) continue;
     if (BN / CG < 16) continue;
     if (D > 64 && BN > 64) continue;
     if (t && t->kv_num && !divides_or_single(BN, t->KVB, t->nKV)) continue;
     // Two stages first: the kernel is bound by the latency its few resident warps can hide, and
     // the smaller ring lets a third CTA share the SM (B32 H8 Skv16384 D64: 0.187 ms with two
     // stages against 0.218 ms with three at one query row, 0.224 against 0.269 at sixteen).
-    for (int stages : {2, 3, 4}) {
-      if (only_st ? stages != only_st : stages == 4) continue;
+    for (int stages : {2, 3}) {
       const int pipe = stages * (BN * pitch(D, 2) + BN * pitch(Dv, 2));
       const int mrg = CG * BM * (Dv + 4) * 4;
       const int smem = BM * pitch(D, 2) + (pipe > mrg ? pipe : mrg);
@@ -688,6 +736,22 @@ int fa_set_cache_dir(const char* path) {
 }
 int fa_compile_count(void) { return g_compile_count.load(); }
 
+int fa_profile_enable(int on) {
+  g_profile_on.store(on ? 1 : 0);
+  return FA_OK;
+}
+int fa_profile_read(int max_kernels, float* ms, const char** names) {
+  const int n = (int)t_prof.size();
+  if (n == 0) return 0;
+  if (max_kernels > 0 && (!ms || !names)) return fail(FA_EINVAL, "ms and names are required");
+  FA_CUDA_CHECK(cudaEventSynchronize(t_prof.back().e1));
+  for (int i = 0; i < n && i < max_kernels; ++i) {
+    FA_CUDA_CHECK(cudaEventElapsedTime(&ms[i], t_prof[i].e0, t_prof[i].e1));
+    names[i] = t_prof[i].name;
+  }
+  return n;
+}
+
 int fa_module_create(const char* mod_source, fa_module** out) {
   if (!out) return fail(FA_EINVAL, "out is null");
   fa_module* m = new fa_module();
@@ -741,20 +805,6 @@ int get_decode_kernel(fa_module* m, int dtype, int D, int Dv, int flags, const D
                           {"FA_STAGES", c.stages}, {"FA_ROUND_SCORES", round_flag(dtype, flags)}}),
                     "fa_decode_kernel", c.smem, k);
 }
-// tuning aid: extra "NAME=VALUE,NAME=VALUE" defines for the tcgen05 kernels from $FLAXATTN_TC_DEFS
-std::string extra_defines() {
-  std::string d;
-  if (const char* e = getenv("FLAXATTN_TC_DEFS")) {
-    std::string t = e, item;
-    std::stringstream ss(t);
-    while (std::getline(ss, item, ',')) {
-      const size_t eq = item.find('=');
-      if (eq != std::string::npos) d += "#define " + item.substr(0, eq) + " " + item.substr(eq + 1) + "\n";
-    }
-  }
-  return d;
-}
-
 // ---- tcgen05 forward: TMA tensor maps and dispatch -----------------------------------------
 struct alignas(64) FaTensorMapHost {
   unsigned long long v[16];
@@ -821,7 +871,6 @@ int get_fwd_tc_kernel(fa_module* m, int dtype, int D, int flags, Kernel** k, boo
   const int smem = 2 * atoms * 16384 + 2 * nstage * atoms * 16384 + (1 + 4 * nstage + 8) * 8 + 16 + 256 * 2 + 256 * 2 +
                    2 * 256 + 1024;
   std::string d = defs({{"FA_DTYPE", dtype}, {"FA_D", D}, {"FA_ROUND_SCORES", round_flag(dtype, flags)}, {"FA_TC_DECODE", decode ? 1 : 0}});
-  d += extra_defines();
   return get_kernel(m, "fa_fwd_tc.cuh", d, "fa_fwd_tc_kernel", smem, k);
 }
 
@@ -834,11 +883,7 @@ bool tc_decode_eligible(const fa_attn_params* p) {
   // The kernel gives every query row a thread and pads the tile to 128 rows, so its softmax work
   // per kv tile does not shrink with Sq: measured against the general decode kernel it wins from
   // 33 rows up (0.46 ms against 0.55 ms at 40-64 rows) and loses below (0.43 against 0.35 at 17-32).
-  static const int min_rows = [] {  // tuning aid: FLAXATTN_TC_DECODE_MIN_SQ moves the lower limit
-    const char* e = getenv("FLAXATTN_TC_DECODE_MIN_SQ");
-    return e ? atoi(e) : 33;
-  }();
-  if (p->Sq < min_rows || p->Sq > 64 || p->Skv < 1024 || p->Skv > 32768) return false;
+  if (p->Sq < 33 || p->Sq > 64 || p->Skv < 1024 || p->Skv > 32768) return false;
   if (!(p->scale > 0.f)) return false;
   const fa_block_tables& t = p->tables;
   if (t.kv_num_blocks) {
@@ -909,7 +954,7 @@ int get_bwd_tc_kernel(fa_module* m, int dtype, int flags, Kernel** k) {
   // must match the shared-memory map of fa_bwd_tc.cuh (fa_btc::SMEM_BYTES)
   const int nstage = 4;
   const int smem = (2 + 2 * nstage) * 16384 + 2 * 16384 + 128 * 32 * 4 + nstage * 2 * 128 * 4 + (1 + 3 * nstage + 7) * 8 + 16 + 512 * 4 + 256 + 1024;
-  std::string d = defs({{"FA_DTYPE", dtype}, {"FA_ROUND_SCORES", round_flag(dtype, flags)}}) + extra_defines();
+  std::string d = defs({{"FA_DTYPE", dtype}, {"FA_ROUND_SCORES", round_flag(dtype, flags)}});
   return get_kernel(m, "fa_bwd_tc.cuh", d, "fa_bwd_tc_kernel", smem, k);
 }
 
@@ -957,6 +1002,7 @@ int fa_module_prepare(fa_module* m, int kind, int dtype, int D, int Dv, int Sq_h
 
 int fa_fwd(fa_module* m, const fa_attn_params* p, void* stream) {
   if (int rc = check_common(m, p)) return rc;
+  prof_reset();
   FaParams kp;
   fill_params(p, kp);
   if (tc_fwd_eligible(p)) return launch_fwd_tc(m, p, kp, stream);
@@ -990,6 +1036,7 @@ int fa_bwd(fa_module* m, const fa_attn_params* p, const fa_tensor* dout, const f
     return fail(FA_EINVAL, "full q tables and full kv tables must be given together");
   const size_t need = fa_bwd_workspace_bytes(p);
   if (!workspace || workspace_bytes < need) return fail(FA_EWORKSPACE, "backward workspace too small");
+  prof_reset();
   FaParams kp;
   fill_params(p, kp);
   kp.dout = cvt(*dout); kp.dq = cvt(*dq); kp.dk = cvt(*dk); kp.dv = cvt(*dv);
@@ -1011,38 +1058,32 @@ int fa_bwd(fa_module* m, const fa_attn_params* p, const fa_tensor* dout, const f
     float* ndelta = (float*)((char*)workspace + rows_pad_bytes(p));
     float* dq_acc = (float*)((char*)workspace + 2 * rows_pad_bytes(p));
     const int sq_pad = (p->Sq + 127) / 128 * 128;
-    const bool run_main = !(p->flags & FA_FLAG_BWD_SKIP_DKDV);
-    bool zeroed = false;
-    if (!(p->flags & FA_FLAG_BWD_SKIP_DELTA)) {
-      const int n_bh = p->B * p->Hq;
-      const int gy = n_bh < 32768 ? n_bh : 32768;
+    const int n_bh = p->B * p->Hq;
+    const int gy = n_bh < 32768 ? n_bh : 32768;
+    {
+      // row scalars; the same pass clears the dQ accumulator
       const dim3 grid((unsigned)((sq_pad * 8 + 255) / 256), (unsigned)gy, (unsigned)((n_bh + gy - 1) / gy));
-      float* zero = run_main ? dq_acc : nullptr;  // the prep pass also clears the dQ accumulator
+      ProfScope prof("fa_bwd_prep_kernel", stream);
       if (p->dtype == FA_F16)
-        fa_bwd_prep_kernel<FA_F16, 8><<<grid, 256, 0, st>>>(kp.o, kp.dout, p->lse, nlse2, ndelta, zero, p->Hq, p->Sq, sq_pad, p->Dv, n_bh);
+        fa_bwd_prep_kernel<FA_F16, 8><<<grid, 256, 0, st>>>(kp.o, kp.dout, p->lse, nlse2, ndelta, dq_acc, p->Hq, p->Sq, sq_pad, p->Dv, n_bh);
       else
-        fa_bwd_prep_kernel<FA_BF16, 8><<<grid, 256, 0, st>>>(kp.o, kp.dout, p->lse, nlse2, ndelta, zero, p->Hq, p->Sq, sq_pad, p->Dv, n_bh);
+        fa_bwd_prep_kernel<FA_BF16, 8><<<grid, 256, 0, st>>>(kp.o, kp.dout, p->lse, nlse2, ndelta, dq_acc, p->Hq, p->Sq, sq_pad, p->Dv, n_bh);
       FA_CUDA_CHECK(cudaGetLastError());
-      zeroed = run_main;
     }
-    if (run_main) {
-      if (!zeroed) FA_CUDA_CHECK(cudaMemsetAsync(dq_acc, 0, dq_acc_bytes(p), st));
-      FaBwdTcParamsHost tp;
-      tp.p = kp;
-      tp.dq_acc = dq_acc;
-      tp.nlse2 = nlse2;
-      tp.ndelta = ndelta;
-      if (int rc = make_map(&tp.tq, p->dtype, p->q, p->D, p->Sq, p->Hq, p->B)) return rc;
-      if (int rc = make_map(&tp.tk, p->dtype, p->k, p->D, p->Skv, p->Hkv, p->B)) return rc;
-      if (int rc = make_map(&tp.tv, p->dtype, p->v, p->Dv, p->Skv, p->Hkv, p->B)) return rc;
-      if (int rc = make_map(&tp.tdo, p->dtype, *dout, p->Dv, p->Sq, p->Hq, p->B)) return rc;
-      // heads fastest, kv tile slowest: under a causal mask the first kv tiles meet the most q tiles
-      if (int rc = launch(ktc, dim3(p->Hkv, p->B, (p->Skv + 127) / 128), dim3(512), &tp, stream)) return rc;
-    }
-    if (!(p->flags & FA_FLAG_BWD_SKIP_DQ)) {
-      const int n_bh = p->B * p->Hq;
-      const int gy = n_bh < 32768 ? n_bh : 32768;
+    FaBwdTcParamsHost tp;
+    tp.p = kp;
+    tp.dq_acc = dq_acc;
+    tp.nlse2 = nlse2;
+    tp.ndelta = ndelta;
+    if (int rc = make_map(&tp.tq, p->dtype, p->q, p->D, p->Sq, p->Hq, p->B)) return rc;
+    if (int rc = make_map(&tp.tk, p->dtype, p->k, p->D, p->Skv, p->Hkv, p->B)) return rc;
+    if (int rc = make_map(&tp.tv, p->dtype, p->v, p->Dv, p->Skv, p->Hkv, p->B)) return rc;
+    if (int rc = make_map(&tp.tdo, p->dtype, *dout, p->Dv, p->Sq, p->Hq, p->B)) return rc;
+    // heads fastest, kv tile slowest: under a causal mask the first kv tiles meet the most q tiles
+    if (int rc = launch(ktc, dim3(p->Hkv, p->B, (p->Skv + 127) / 128), dim3(512), &tp, stream)) return rc;
+    {
       const dim3 grid((unsigned)((p->Sq * 8 + 255) / 256), (unsigned)gy, (unsigned)((n_bh + gy - 1) / gy));
+      ProfScope prof("fa_dq_convert_kernel", stream);
       if (p->dtype == FA_F16)
         fa_dq_convert_kernel<FA_F16><<<grid, 256, 0, st>>>(dq_acc, kp.dq, p->Hq, p->Sq, sq_pad, p->scale, n_bh);
       else
@@ -1051,13 +1092,14 @@ int fa_bwd(fa_module* m, const fa_attn_params* p, const fa_tensor* dout, const f
     }
     return FA_OK;
   }
-  if (!(p->flags & FA_FLAG_BWD_SKIP_DELTA)) {
+  {
     cudaStream_t st = (cudaStream_t)stream;
     const long long n_rows = (long long)p->B * p->Hq * p->Sq;
     const int chunks = p->Dv * es / 16;
     const int lpr = chunks >= 8 ? 8 : (chunks >= 4 ? 4 : (chunks >= 2 ? 2 : 1));
     const long long threads = n_rows * lpr;
     const unsigned blocks = (unsigned)((threads + 255) / 256);
+    ProfScope prof("fa_delta_kernel", stream);
 #define FA_DELTA(DT, L) fa_delta_kernel<DT, L><<<blocks, 256, 0, st>>>(kp.o, kp.dout, kp.delta, p->Hq, p->Sq, p->Dv, n_rows)
 #define FA_DELTA_DT(L)                                      \
   do {                                                      \
@@ -1073,10 +1115,8 @@ int fa_bwd(fa_module* m, const fa_attn_params* p, const fa_tensor* dout, const f
 #undef FA_DELTA
     FA_CUDA_CHECK(cudaGetLastError());
   }
-  if (!(p->flags & FA_FLAG_BWD_SKIP_DKDV))
-    if (int rc = launch(kdkdv, dim3((p->Skv + c.tile - 1) / c.tile, p->Hkv, p->B), dim3(c.warps * 32), &kp, stream))
-      return rc;
-  if (p->flags & FA_FLAG_BWD_SKIP_DQ) return FA_OK;
+  if (int rc = launch(kdkdv, dim3((p->Skv + c.tile - 1) / c.tile, p->Hkv, p->B), dim3(c.warps * 32), &kp, stream))
+    return rc;
   return launch(kdq, dim3((p->Sq + c.tile - 1) / c.tile, p->Hq, p->B), dim3(c.warps * 32), &kp, stream);
 }
 
@@ -1131,6 +1171,7 @@ int fa_decode(fa_module* m, const fa_attn_params* p, int num_splits, void* works
   if (int rc = check_common(m, p)) return rc;
   if (num_splits <= 0) num_splits = fa_decode_num_splits(p, 0);
   if (num_splits > 65535) return fail(FA_EINVAL, "too many splits");
+  prof_reset();
   FaParams kp;
   fill_params(p, kp);
   const bool tc = tc_decode_eligible(p) && num_splits >= 2 && num_splits % 2 == 0;
@@ -1158,6 +1199,7 @@ int fa_decode(fa_module* m, const fa_attn_params* p, int num_splits, void* works
     const long long n_rows = (long long)p->B * p->Hq * p->Sq;
     const unsigned blocks = (unsigned)((n_rows + 3) / 4);
     cudaStream_t st = (cudaStream_t)stream;
+    ProfScope prof("fa_decode_combine_kernel", stream);
     if (p->dtype == FA_F16)
       fa_decode_combine_kernel<FA_F16><<<blocks, 128, 0, st>>>(kp.part_o, kp.part_ml, kp.o, kp.lse, p->Hq, p->Sq, p->Dv, num_splits, n_rows);
     else
@@ -1234,10 +1276,18 @@ void* g_static_ptr[64] = {nullptr};
 
 // In host code `g_static_scratch` is only a handle for the symbol, not a device address; the
 // address a kernel can use has to be asked for, once per device, with that device current.
-int static_scratch(void** out) {
+int static_scratch(void** out, void* stream) {
   int dev = 0;
   FA_CUDA_CHECK(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return fail(FA_EUNSUPPORTED, "device ordinal above 63");
+  // the scratch address is the current device's: a stream of another device would run the kernels there
+  if (stream != nullptr && stream != (void*)cudaStreamLegacy && stream != (void*)cudaStreamPerThread) {
+    int sdev = dev;
+    if (cudaStreamGetDevice((cudaStream_t)stream, &sdev) == cudaSuccess && sdev != dev)
+      return fail(FA_EINVAL, "fa_decode_static: the stream belongs to device " + std::to_string(sdev) +
+                                 ", the current device is " + std::to_string(dev));
+    cudaGetLastError();
+  }
   std::lock_guard<std::mutex> lk(g_static_mu);
   if (g_static_ptr[dev] == nullptr) {
     void* ptr = nullptr;
@@ -1256,15 +1306,19 @@ extern "C" {
 size_t fa_decode_static_capacity(void) { return kStaticScratchBytes; }
 
 int fa_decode_static(fa_module* m, const fa_attn_params* p, int num_splits, void* stream) {
-  if (!p) return fail(FA_EINVAL, "params is null");
+  // arguments first: the sizes below are products of fields that have to be positive
+  if (int rc = check_common(m, p)) return rc;
+  if (p->dtype == FA_F32) return fail(FA_EUNSUPPORTED, "the decode kernel takes fp16 / bf16 inputs");
+  if (p->Sq > 64) return fail(FA_EUNSUPPORTED, "the decode kernel handles at most 64 query rows");
   if (num_splits <= 0) num_splits = fa_decode_num_splits(p, 0);
   const size_t need = fa_decode_workspace_bytes(p, num_splits);
+  if (need == 0) return fa_decode(m, p, num_splits, nullptr, 0, stream);  // a single split needs no scratch
   if (need > kStaticScratchBytes)
     return fail(FA_EWORKSPACE, "fa_decode_static: this problem needs " + std::to_string(need) +
                                    " bytes of split-KV scratch, the built-in scratch holds " +
                                    std::to_string(kStaticScratchBytes) + "; use fewer splits or fa_decode");
   void* ws = nullptr;
-  if (int rc = static_scratch(&ws)) return rc;
+  if (int rc = static_scratch(&ws, stream)) return rc;
   return fa_decode(m, p, num_splits, ws, kStaticScratchBytes, stream);
 }
 

@@ -39,52 +39,6 @@ struct FaBwdTcParams {
   const float* ndelta;          // same shape: -rowsum(O * dO); 0 beyond Sq
 };
 
-// Optional phase timing (tuning aid): with FA_TC_TRACE the status buffer must hold at least
-// 64 ints; slot k accumulates the SM cycles CTA (0,0,0) spent in phase k.
-// experiments (wrong results, timing only): bit 0 drain skips staging+reduce, bit 1 compute skips
-// the dS^T smem stores, bit 2 compute skips the math, bit 3 compute skips the TMEM loads,
-// bit 4 the row scalars are constants instead of shared-memory loads, bit 5 drain stages but does
-// not reduce, bit 6 drain reduces without staging
-#ifndef FA_TC_EXP
-#define FA_TC_EXP 0
-#endif
-#ifndef FA_TC_TRACE
-#define FA_TC_TRACE 0
-#endif
-#ifndef FA_TC_A_AFTER_B
-#define FA_TC_A_AFTER_B 0
-#endif
-#ifndef FA_TC_BWD_STEP16
-#define FA_TC_BWD_STEP16 1
-#endif
-#if FA_TC_TRACE == 1
-#define FA_TRACE_DECL long long trace_t0 = clock64();
-#define FA_TRACE(slot)                                                                        \
-  do {                                                                                        \
-    const long long t1_ = clock64();                                                          \
-    if (trace_on) atomicAdd(p.status + (slot), (int)(t1_ - trace_t0));                        \
-    trace_t0 = t1_;                                                                           \
-  } while (0)
-#else
-#define FA_TRACE_DECL
-#define FA_TRACE(slot)
-#endif
-// FA_TC_TRACE == 2 instead records the SM clock at each phase boundary of pairs 6..8 of
-// CTA (0,0,0) in status[64 + 32 * (pair - 6) + slot] (the status buffer must hold 160 ints).
-#if FA_TC_TRACE == 2
-#define FA_STAMP(slot)                                                                        \
-  do {                                                                                        \
-    if (trace_on && n >= 6 && n < 9) p.status[64 + (n - 6) * 32 + (slot)] = (int)clock64();   \
-  } while (0)
-#define FA_MARK(k)                                                                     \
-  do {                                                                                  \
-    if (trace_on) p.status[176 + (k)] = (int)clock64();                                 \
-  } while (0)
-#else
-#define FA_STAMP(slot)
-#define FA_MARK(k)
-#endif
-
 namespace fa_btc {
 
 constexpr int DT = FA_DTYPE;
@@ -95,7 +49,11 @@ constexpr int NSTAGE = 4;
 constexpr int MAXP = 512;                // (head, q tile) pairs per CTA
 constexpr int NT = 512;
 constexpr int WARP_PRODUCER = 12, WARP_MMA = 13, WARP_MMA_B = 14, WARP_MMA_C = 15;
+// Register split (setmaxnreg): the kernel starts with 128 registers per thread (65536 / 512).  The
+// eight warps that are not compute warps give up 72 each and the eight compute warps take 72 each;
+// an increase that asked for more than the decrease releases would wait forever.
 constexpr int REGS_COMPUTE = 200, REGS_OTHER = 56;
+static_assert(256 * (REGS_COMPUTE - 128) <= 256 * (128 - REGS_OTHER), "setmaxnreg.inc would wait forever");
 
 // shared memory map (from a 1024-byte aligned base)
 constexpr int OFF_K = 0;
@@ -155,12 +113,8 @@ __device__ __forceinline__ void chunk(const float (&s)[W], const float (&dp)[W],
   // hardware has the form; only the exponentials and the mask are per element
 #pragma unroll
   for (int e = 0; e < W; e += 4) {
-#if FA_TC_EXP & 16
-    const float4 nl = make_float4(-8.f, -8.f, -8.f, -8.f), nd = make_float4(0.f, 0.f, 0.f, 0.f);  // (timing experiment)
-#else
     const float4 nl = *(const float4*)(nlse2 + e);
     const float4 nd = *(const float4*)(ndelta + e);
-#endif
 #pragma unroll
     for (int u = 0; u < 4; u += 2) {
       const int qi0 = q0 | (e + u), qi1 = q0 | (e + u + 1);
@@ -254,11 +208,7 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
   const int n_qtiles = (p.Sq + BT - 1) / BT;
   const int sq_pad = n_qtiles * BT;
 
-#if FA_TC_TRACE
-  const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && p.status != nullptr;
-#endif
-  if (warp == 0) { FA_MARK(0); }  // kernel start
-  volatile int* misc = (volatile int*)(sm + OFF_MISC);  // [0] tmem base, [1] abort, [2] npairs
+  volatile int* misc = (volatile int*)(sm + OFF_MISC);  // [0] tmem base, [1] abort, [2] npairs, [3] drain warps leave
   int* pairs = (int*)(sm + OFF_PAIR);
   unsigned char* cls = sm + OFF_CLS;
 
@@ -280,6 +230,7 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
     fa_mbar_init_fence();
     misc[1] = 0;
     misc[2] = 0;
+    misc[3] = 0;
     // K and V of this CTA's tile do not depend on the pair list: their loads start now and run
     // while the list is being built
     fa_tma_prefetch_desc(&P.tk);
@@ -326,7 +277,6 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
   fa_tc_fence_before();
   __syncthreads();
   fa_tc_fence_after();
-  if (warp == 0) { FA_MARK(1); }  // set-up done
   const fa_u32 tmem = (fa_u32)misc[0];
   npairs = misc[2];
   volatile int* abort_flag = misc + 1;
@@ -379,19 +329,10 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
       constexpr fa_u32 HI = fa_desc_hi_sw128();
       const fa_u32 loK_k = fa_desc_lo(sb + OFF_K, 16), loV_k = fa_desc_lo(sb + OFF_V, 16);
       bool ok = fa_mbar_wait_all(bar_addr(sb, BAR_KV), 0, abort_flag);
-      FA_TRACE_DECL
       for (int n = 0; n < npairs_u && ok; ++n) {
         const int s = n % NSTAGE;
         ok = fa_mbar_wait_all(bar_addr(sb, BAR_QFULL + s), (fa_u32)((n / NSTAGE) & 1), abort_flag);
-        FA_TRACE(1); FA_STAMP(1);   // MMA A: wait for Q/dO
         if (ok && n > 0) ok = fa_mbar_wait_all(bar_addr(sb, BAR_SFREE), (fa_u32)((n - 1) & 1), abort_flag);
-#if FA_TC_A_AFTER_B
-        // Products 3-5 of pair n-2 go first: they are what the compute warps wait for next, while
-        // S^T/dP^T of this pair are not needed before the stores of pair n-1 are done.  Issued
-        // right away they would sit in the middle of those products in the in-order tensor pipe.
-        if (ok && n > 1) ok = fa_mbar_wait_all(bar_addr(sb, BAR_PFREE), (fa_u32)((n - 2) & 1), abort_flag);
-#endif
-        FA_TRACE(2); FA_STAMP(2);   // MMA A: wait for S^T/dP^T of the previous pair to be read
         if (!ok) break;
         fa_tc_fence_after();
         const fa_u32 loQ = fa_desc_lo(sb + OFF_Q + s * ATOM_BYTES, 16), loDO = fa_desc_lo(sb + OFF_DO + s * ATOM_BYTES, 16);
@@ -406,7 +347,6 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
           fa_mma_commit(bar_addr(sb, BAR_QEMPTY + s));  // first of the two arrivals that free each tile of the stage
           fa_mma_commit(bar_addr(sb, BAR_DOEMPTY + s));
         }
-        FA_TRACE(3); FA_STAMP(3);   // MMA A: issue products 1-2
       }
     }
   } else if (warp == WARP_MMA_B) {
@@ -417,11 +357,9 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
       constexpr fa_u32 HI = fa_desc_hi_sw128();
       const fa_u32 loDS_k = fa_desc_lo(sb + OFF_DS, 16);
       bool ok = fa_mbar_wait_all(bar_addr(sb, BAR_KV), 0, abort_flag);
-      FA_TRACE_DECL
       for (int n = 0; n < npairs_u && ok; ++n) {
         const int s = n % NSTAGE;
         ok = fa_mbar_wait_all(bar_addr(sb, BAR_PREADY), (fa_u32)(n & 1), abort_flag);
-        FA_TRACE(4); FA_STAMP(4);     // MMA B: wait for P^T / dS^T
         if (!ok) break;
         fa_tc_fence_after();
         const fa_u32 loQ_mn = fa_desc_lo(sb + OFF_Q + s * ATOM_BYTES, ATOM_BYTES);
@@ -432,7 +370,6 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
         for (int kk = 0; kk < BT / 16; ++kk)
           if (leader) fa_mma_ts(tmem_u + COL_DV, tmem_u + COL_P + kk * 8, fa_desc_make(loDO_mn + kk * 128, HI), IDESC_TN, acc | (kk > 0));
         if (leader) fa_mma_commit(bar_addr(sb, BAR_DOEMPTY + s));  // second arrival: the dO tile is free
-        FA_TRACE(7); FA_STAMP(7);   // MMA B: issue product 3
         // 4. dK += dS^T Q     (A = dS^T K-major: k-step kk is 32 bytes into atom kk / 4)
 #pragma unroll
         for (int kk = 0; kk < BT / 16; ++kk)
@@ -444,7 +381,6 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
           fa_mma_commit(bar_addr(sb, BAR_PFREE));        // one of the two arrivals that free P^T and dS^T
           if (n + 1 == npairs_u) fa_mma_commit(bar_addr(sb, BAR_FINAL));
         }
-        FA_TRACE(8); FA_STAMP(8);   // MMA B: issue product 4
       }
     }
   } else if (warp == WARP_MMA_C) {
@@ -458,12 +394,10 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
       const fa_u32 loK_mn = fa_desc_lo(sb + OFF_K, ATOM_BYTES);
       const fa_u32 loDS_mn = fa_desc_lo(sb + OFF_DS, ATOM_BYTES);
       bool ok = fa_mbar_wait_all(bar_addr(sb, BAR_KV), 0, abort_flag);
-      FA_TRACE_DECL
       for (int n = 0; n < npairs_u && ok; ++n) {
         ok = fa_mbar_wait_all(bar_addr(sb, BAR_PREADY), (fa_u32)(n & 1), abort_flag);
         // the drain warps must have emptied the dQ columns of the previous pair
         if (ok && n > 0) ok = fa_mbar_wait_all(bar_addr(sb, BAR_DQFREE), (fa_u32)((n - 1) & 1), abort_flag);
-        FA_TRACE(5); FA_STAMP(5);   // MMA C: wait for dS^T and the dQ drain
         if (!ok) break;
         fa_tc_fence_after();
         // 5. dQ = dS K        (A = dS^T read MN-major: M chunks of 64 q one atom apart; K = 128 kv rows)
@@ -474,12 +408,6 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
           fa_mma_commit(bar_addr(sb, BAR_PFREE));
           fa_mma_commit(bar_addr(sb, BAR_DQFULL));
         }
-        FA_TRACE(6); FA_STAMP(6);   // MMA C: issue product 5 + commits
-#if FA_TC_TRACE == 2
-        // tuning aid: when do products 3-5 of the pair actually complete
-        if (leader) { fa_mbar_wait(bar_addr(sb, BAR_DQFULL), (fa_u32)(n & 1), abort_flag); FA_STAMP(23); }
-        if (leader) { fa_mbar_wait(bar_addr(sb, BAR_PFREE), (fa_u32)(n & 1), abort_flag); FA_STAMP(9); }
-#endif
       }
     }
   } else if (warp < 8) {
@@ -493,24 +421,16 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
     const fa_u32 t_row = tmem + ((fa_u32)lane_base << 16);
     const float sc2 = p.scale * FA_LOG2E;
     bool ok = true;
-#if FA_TC_TRACE
-#endif
-    FA_TRACE_DECL
     for (int n = 0; n < npairs && ok; ++n) {
       const int s = n % NSTAGE;
       const int pr = pairs[n];
       const int m0 = (pr & 0xffff) * BT, mode = (pr >> 16) & 0xf, gh = hk * G + (pr >> 20) + p.h_off;
       ok = fa_mbar_wait_warp(bar_addr(sb, BAR_SFULL), (fa_u32)(n & 1), abort_flag);
-      if (warp == 0) { FA_TRACE(10); FA_STAMP(10); }  // compute: wait for S^T/dP^T
-      if (warp == 0 && n == 0) { FA_MARK(2); }  // first S^T/dP^T there
-      if (warp == 0 && n == 1) { FA_MARK(3); }
-      if (warp == 0 && n == npairs - 1) { FA_MARK(4); }  // last S^T/dP^T there
       if (ok) ok = fa_mbar_wait_warp(bar_addr(sb, BAR_QFULL + s), (fa_u32)((n / NSTAGE) & 1), abort_flag);
       if (!ok) break;
       fa_tc_fence_after();
       const float* rowp = (const float*)(sm + OFF_ROW + s * 2 * 128 * 4);
       fa_u32 pp0[16], pp1[16], ds0[16], ds1[16];
-#if FA_TC_BWD_STEP16 && !(FA_TC_EXP & 12)
       // The 64 columns of this thread come in four steps of 16 (S^T and dP^T), the loads of a step
       // in flight while the previous one is computed: few values are live at a time, which leaves
       // the scheduler registers to overlap the latencies of independent elements (with all 128
@@ -544,50 +464,22 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
         // every score of the pair is in registers: the S^T / dP^T columns may be overwritten
         fa_tc_fence_before();
         fa_mbar_arrive(bar_addr(sb, BAR_SFREE));
-        if (warp == 0) { FA_TRACE(11); FA_STAMP(11); }  // compute: TMEM loads done
         FA_STEP(sB, dB, sA, dA, 48, pp1, ds1, 8, true)
 #undef FA_STEP
       }
-#else
-      float sa[32], sb2[32], da[32], db[32];
-      if (FA_TC_EXP & 8) {
-#pragma unroll
-        for (int e = 0; e < 32; ++e) sa[e] = sb2[e] = da[e] = db[e] = 0.f;
-      } else {
-        fa_tmem_ld32(t_row + COL_S + half * 64, sa);
-        fa_tmem_ld32(t_row + COL_S + half * 64 + 32, sb2);
-        fa_tmem_ld32(t_row + COL_DP + half * 64, da);
-        fa_tmem_ld32(t_row + COL_DP + half * 64 + 32, db);
-        fa_tmem_wait_ld();
-      }
-      fa_tc_fence_before();
-      fa_mbar_arrive(bar_addr(sb, BAR_SFREE));
-      if (warp == 0) { FA_TRACE(11); FA_STAMP(11); }  // compute: TMEM loads
-
-      if (row_ok && !(FA_TC_EXP & 4)) {
-        const int c0 = half * 64;  // first q column of this thread inside the tile
-        chunk<32>(sa, da, rowp + c0, rowp + 128 + c0, pp0, ds0, mode, m0 + c0, kv, gb, gh, p.scale, sc2);
-        chunk<32>(sb2, db, rowp + c0 + 32, rowp + 128 + c0 + 32, pp1, ds1, mode, m0 + c0 + 32, kv, gb, gh, p.scale, sc2);
-      } else {
-#pragma unroll
-        for (int e = 0; e < 16; ++e) pp0[e] = pp1[e] = ds0[e] = ds1[e] = 0u;
-      }
-#endif
       // pin the packed results here: without this the compiler sinks part of the math below the
       // wait that follows, onto the critical path between two groups of products
 #pragma unroll
       for (int e = 0; e < 16; ++e) asm volatile("" : "+r"(pp0[e]), "+r"(pp1[e]), "+r"(ds0[e]), "+r"(ds1[e]));
-      if (warp == 0) { FA_TRACE(12); FA_STAMP(12); }  // compute: element-wise math
       // products 3-5 of the previous pair must be done with P^T and dS^T
       if (n > 0) {
         ok = fa_mbar_wait_warp(bar_addr(sb, BAR_PFREE), (fa_u32)((n - 1) & 1), abort_flag);
         if (!ok) break;
         fa_tc_fence_after();
       }
-      if (warp == 0) { FA_TRACE(13); FA_STAMP(13); }  // compute: wait for products 3-5 of the previous pair
       fa_tmem_st16(t_row + COL_P + half * 32, pp0);
       fa_tmem_st16(t_row + COL_P + half * 32 + 16, pp1);
-      if (!(FA_TC_EXP & 2)) {
+      {
         unsigned char* dsrow = sm + OFF_DS + half * ATOM_BYTES + r * 128;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
@@ -606,12 +498,9 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
       fence_proxy_async();
       fa_tc_fence_before();
       fa_mbar_arrive(bar_addr(sb, BAR_PREADY));
-      if (warp == 0) { FA_TRACE(14); FA_STAMP(14); }  // compute: stores of P^T / dS^T
     }
     // ---- epilogue: dK (scaled) by warps 0-3, dV by warps 4-7 ----------------------------------
-    if (warp == 0) { FA_MARK(5); }  // compute loop done
     if (ok && npairs > 0) ok = fa_mbar_wait_warp(bar_addr(sb, BAR_FINAL), 0, abort_flag);
-    if (warp == 0) { FA_MARK(6); }  // dK / dV complete
     if (ok) {
       fa_tc_fence_after();
       const FaTensor& dst = half == 0 ? p.dk : p.dv;
@@ -647,13 +536,14 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
     const fa_u32 t_dq = tmem + ((fa_u32)lane_base << 16) + COL_DQ;
     const int dtid = tid - 256;
     bool ok = true;
-    FA_TRACE_DECL
     for (int n = 0; n < npairs && ok; ++n) {
       const int pr = pairs[n];
       const int qt = pr & 0xffff, h = hk * G + (pr >> 20);
       ok = fa_mbar_wait_warp(bar_addr(sb, BAR_DQFULL), (fa_u32)(n & 1), abort_flag);
-      if (warp == 8) { FA_TRACE(20); FA_STAMP(20); }  // drain: wait for dQ
-      if (!ok) break;
+      // The four drain warps meet at named barriers below, so they have to leave this loop together:
+      // a warp whose wait failed says so in a flag only the drain warps write, joins the first
+      // barrier of the pair like the others, and all four read the flag behind that barrier.
+      if (!ok) misc[3] = 1;
       fa_tc_fence_after();
       // The 128 x 64 tile leaves in two halves of 32 columns through one 16 KB staging buffer: each
       // half is one contiguous 16 KB block of the accumulation buffer.  16-byte chunk k of row r
@@ -661,19 +551,22 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
       float* gdst = P.dq_acc + (((long long)b * p.Hq + h) * sq_pad + (long long)qt * BT) * D;
       unsigned char* strow = sm + OFF_DQ + r * 128;
       float a[32];
-      fa_tmem_ld32(t_dq, a);
-      fa_tmem_wait_ld();
+      if (ok) {
+        fa_tmem_ld32(t_dq, a);
+        fa_tmem_wait_ld();
+      }
 #pragma unroll
       for (int hf = 0; hf < 2; ++hf) {
         // the previous bulk reduce must have finished reading the staging buffer
         if (dtid == 0) bulk_wait_read0();
         named_bar_sync(1, 128);
-        if (hf == 0 && warp == 8) { FA_TRACE(21); FA_STAMP(21); }  // drain: wait for the previous bulk reduce
-        if (!(FA_TC_EXP & (1 | 64))) {
-#pragma unroll
-          for (int k = 0; k < 8; ++k)
-            *(float4*)(strow + ((k ^ (r & 7)) * 16)) = make_float4(a[4 * k], a[4 * k + 1], a[4 * k + 2], a[4 * k + 3]);
+        if (hf == 0 && misc[3] != 0) {
+          ok = false;
+          break;
         }
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          *(float4*)(strow + ((k ^ (r & 7)) * 16)) = make_float4(a[4 * k], a[4 * k + 1], a[4 * k + 2], a[4 * k + 3]);
         if (hf == 0) {
           fa_tmem_ld32(t_dq + 32, a);
           fa_tmem_wait_ld();
@@ -682,23 +575,18 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
         }
         fence_proxy_async();
         named_bar_sync(1, 128);
-        if (dtid == 0 && !(FA_TC_EXP & (1 | 32))) {
+        if (dtid == 0) {
           bulk_reduce_add_f32(gdst + hf * (DQ_HALF_BYTES / 4), sb + OFF_DQ, DQ_HALF_BYTES);
           bulk_commit();
         }
       }
-      if (warp == 8) { FA_TRACE(22); FA_STAMP(22); }  // drain: TMEM -> staging -> reduce issue
     }
-    if (warp == 8) { FA_MARK(8); }  // drain loop done
     if (dtid == 0) bulk_wait0();
-    if (warp == 8) { FA_MARK(9); }  // last reduce complete
   }
 
-  if (warp == 0) { FA_MARK(7); }  // epilogue stores issued
   // ---- teardown ------------------------------------------------------------------------------
   fa_tc_fence_before();
   __syncthreads();
-  if (warp == 0) { FA_MARK(10); }
   if (warp == WARP_MMA) {
     fa_tc_fence_after();
     fa_tmem_dealloc(tmem, TMEM_COLS);

@@ -26,7 +26,7 @@
 // status word, all roles leave their loops, TMEM is freed and the kernel returns.
 //
 // Compile-time parameters (macros): FA_DTYPE (0 fp16, 1 bf16), FA_D (64 or 128), FA_TC_DECODE
-// (split-KV variant, see below); tuning aids FA_TC_TRACE, FA_TC_HALF_EXP, FA_TC_POLY_EVERY.
+// (split-KV variant, see below).
 #pragma once
 #include "fa_sm100.cuh"
 
@@ -73,33 +73,6 @@ constexpr int COL_S = 0, COL_O = 256;
 // 512 columns are taken by S and O, and P overwrites the S columns it was computed from.
 constexpr bool SEP_P = D == 64;
 constexpr int COL_P = 384;
-// Optional phase timing (tuning aid): with FA_TC_TRACE the status buffer must hold at least
-// 64 ints; slot k accumulates the SM cycles CTA (0,0,0) spent in phase k.
-#ifndef FA_TC_TRACE
-#define FA_TC_TRACE 0
-#endif
-#if FA_TC_TRACE == 1
-#define FA_TRACE_DECL long long trace_t0 = clock64();
-#define FA_TRACE(slot)                                                                        \
-  do {                                                                                        \
-    const long long t1_ = clock64();                                                          \
-    if (trace_on) atomicAdd(p.status + (slot), (int)(t1_ - trace_t0));                        \
-    trace_t0 = t1_;                                                                           \
-  } while (0)
-#else
-#define FA_TRACE_DECL
-#define FA_TRACE(slot)
-#endif
-// FA_TC_TRACE == 2 instead records the SM clock at each phase boundary of kv steps 6..8 of
-// CTA (0,0,0) in status[64 + 32 * (step - 6) + slot] (the status buffer must hold 160 ints).
-#if FA_TC_TRACE == 2
-#define FA_STAMP(slot)                                                                        \
-  do {                                                                                        \
-    if (trace_on && j >= 6 && j < 9) p.status[64 + (j - 6) * 32 + (slot)] = (int)clock64();   \
-  } while (0)
-#else
-#define FA_STAMP(slot)
-#endif
 #ifndef FA_TC_HALF_EXP
 #define FA_TC_HALF_EXP 0
 #endif
@@ -231,10 +204,6 @@ struct SoftmaxCtx {
   const short* sched_tile;
   float m_ref, l;
   fa_u32 cnt;
-#if FA_TC_TRACE
-  bool trace_on;
-  long long trace_t0;
-#endif
 };
 
 // One kv step of this warpgroup's tile.  MASKED (compile time) selects the version for the few
@@ -250,14 +219,9 @@ __device__ __forceinline__ bool softmax_step(SoftmaxCtx& c, const int j, const i
   float& m_ref = c.m_ref;
   float& l = c.l;
   fa_u32& cnt = c.cnt;
-#if FA_TC_TRACE
-  const bool trace_on = c.trace_on;
-  long long& trace_t0 = c.trace_t0;
-#endif
   const short* sched_tile = c.sched_tile;
   const int n0 = (int)sched_tile[DECODE ? 2 * j + i : j] * BN;
   if (!fa_mbar_wait_warp(bar_addr(sb, BAR_S + i), cnt & 1u, abort_flag)) return false;
-  if (warp == 0) { FA_TRACE(10); FA_STAMP(10); }  // softmax: wait S
   fa_tc_fence_after();
   // ---- pass 1: the whole score row (128 fp32 values) comes into registers, chunk by chunk,
   // with the score_mod (when there is one), the mask and the row maximum of a chunk computed
@@ -288,10 +252,8 @@ __device__ __forceinline__ bool softmax_step(SoftmaxCtx& c, const int j, const i
     fa_tc_fence_before();
     fa_mbar_arrive(bar_addr(sb, BAR_SFREE2 + i));
   }
-  if (warp == 0) { FA_STAMP(13); }
   FA_P1(s3, 96)
 #undef FA_P1
-  if (warp == 0) { FA_TRACE(11); FA_STAMP(11); }  // softmax: loads + pass 1
   float mx = fmaxf(fmaxf(rm.a, rm.b), fmaxf(rm.c, rm.d));
   if (!in_place) mx *= sc2;
   // running maximum, raised lazily
@@ -313,7 +275,6 @@ __device__ __forceinline__ bool softmax_step(SoftmaxCtx& c, const int j, const i
     if (!fa_mbar_wait_warp(bar_addr(sb, BAR_O + i), (cnt - 1) & 1u, abort_flag)) return false;
     fa_tc_fence_after();
   }
-  if (warp == 0) { FA_STAMP(14); }
   if (rescale) {
 #pragma unroll 1
     for (int c = 0; c < D / 16; ++c) {
@@ -353,12 +314,10 @@ __device__ __forceinline__ bool softmax_step(SoftmaxCtx& c, const int j, const i
     sum = a0 + a1;
   }
   l += sum;
-  if (warp == 0) { FA_STAMP(15); }
   fa_tmem_wait_st();
   fa_tc_fence_before();
   fa_mbar_arrive(bar_addr(sb, BAR_P + i));
   ++cnt;
-  if (warp == 0) { FA_TRACE(12); FA_STAMP(12); }  // softmax: pass 2 + stores
   return true;
 }
 
@@ -384,9 +343,6 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
   const int hk = h / (p.Hq / p.Hkv);
   const int gb = b + p.b_off, gh = h + p.h_off;
 
-#if FA_TC_TRACE
-  const bool trace_on = blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && lane == 0 && p.status != nullptr;
-#endif
   volatile int* misc = (volatile int*)(sm + OFF_MISC);  // [0] tmem base, [1] abort, [2] nsteps
   short* sched_tile = (short*)(sm + OFF_SCHED);
   unsigned char* sched_mode = sm + OFF_MODE;
@@ -529,13 +485,11 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
         constexpr fa_u32 IDESC_S = fa_idesc(DT, BM, BN, 0, 0);
         bool ok = fa_mbar_wait(bar_addr(sb, BAR_Q), 0, abort_flag);
         fa_u32 nsi[2] = {0, 0};
-        FA_TRACE_DECL
         for (int j = 0; j < nsteps && ok; ++j) {
           // the kv tile of (step, query tile): the same for both tiles in the forward, alternate
           // tiles of the CTA's share in the decode variant
           int s = j % NSTAGE;
           if (!DECODE) ok = fa_mbar_wait(bar_addr(sb, BAR_KFULL + s), (fa_u32)((j / NSTAGE) & 1), abort_flag);
-          FA_TRACE(4); FA_STAMP(4);  // MMA A: wait K
           for (int i = 0; i < 2 && ok; ++i) {
             if (!sched_mode[2 * j + i]) continue;
             if (DECODE) {
@@ -546,7 +500,6 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
             }
             if (nsi[i] > 0) {
               ok = fa_mbar_wait(bar_addr(sb, BAR_SFREE2 + i), (nsi[i] - 1) & 1u, abort_flag);
-              FA_TRACE(6); FA_STAMP(6);  // MMA A: wait for the previous S of the tile to be read
               if (!ok) break;
             }
             fa_tc_fence_after();
@@ -559,7 +512,6 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
             fa_mma_commit(bar_addr(sb, BAR_S + i));
             if (DECODE) fa_mma_commit(bar_addr(sb, BAR_KEMPTY + s));
             ++nsi[i];
-            FA_TRACE(5); FA_STAMP(5);  // MMA A: issue S
           }
           if (!DECODE) fa_mma_commit(bar_addr(sb, BAR_KEMPTY + s));
         }
@@ -567,11 +519,9 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
         constexpr fa_u32 IDESC_O = fa_idesc(DT, BM, D, 0, 1);
         bool ok = true;
         fa_u32 cnt[2] = {0, 0};
-        FA_TRACE_DECL
         for (int j = 0; j < nsteps && ok; ++j) {
           int s = j % NSTAGE;
           if (!DECODE) ok = fa_mbar_wait(bar_addr(sb, BAR_VFULL + s), (fa_u32)((j / NSTAGE) & 1), abort_flag);
-          FA_TRACE(1); FA_STAMP(1);  // MMA B: wait V
           for (int i = 0; i < 2 && ok; ++i) {
             if (!sched_mode[2 * j + i]) continue;
             if (DECODE) {
@@ -581,7 +531,6 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
               if (!ok) break;
             }
             ok = fa_mbar_wait(bar_addr(sb, BAR_P + i), cnt[i] & 1u, abort_flag);
-            FA_TRACE(2); FA_STAMP(2);  // MMA B: wait P
             if (!ok) break;
             fa_tc_fence_after();
             const fa_u32 loV = fa_desc_lo(sb + OFF_V + s * KV_STAGE, ATOM_BYTES);
@@ -592,7 +541,6 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
             fa_mma_commit(bar_addr(sb, BAR_O + i));
             if (DECODE) fa_mma_commit(bar_addr(sb, BAR_VEMPTY + s));
             ++cnt[i];
-            FA_TRACE(3); FA_STAMP(3);  // MMA B: issue PV
           }
           if (!DECODE) fa_mma_commit(bar_addr(sb, BAR_VEMPTY + s));
         }
@@ -639,7 +587,6 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
           fa_mma_commit(bar_addr(sb, BAR_KEMPTY + 0));
         }
       }
-      FA_TRACE_DECL
       for (int j = 0; j < nsteps && ok; ++j) {
         const int s = j % NSTAGE;
         const fa_u32 ph = (fa_u32)((j / NSTAGE) & 1);
@@ -648,16 +595,13 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
         const fa_u32 ph1 = (fa_u32)(((j + 1) / NSTAGE) & 1);
         bool k_ready = false;
         ok = fa_mbar_wait(bar_addr(sb, BAR_VFULL + s), ph, abort_flag);
-        FA_TRACE(1); FA_STAMP(1);  // MMA: wait V
         for (int i = 0; i < 2 && ok; ++i) {
           if (sched_mode[2 * j + i]) {
             ok = fa_mbar_wait(bar_addr(sb, BAR_P + i), cnt[i] & 1u, abort_flag);
-            FA_TRACE(2); FA_STAMP(2);  // MMA: wait P
             if (!ok) break;
             fa_tc_fence_after();
             issue_pv(i, j, cnt[i] == 0);
             ++cnt[i];
-            FA_TRACE(3); FA_STAMP(3);  // MMA: issue PV
           }
           if (i == 1) fa_mma_commit(bar_addr(sb, BAR_VEMPTY + s));
           // S of the next step overwrites the columns P was read from: it follows the PV product
@@ -667,10 +611,8 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
               if (!ok) break;
               fa_tc_fence_after();
               k_ready = true;
-              FA_TRACE(4); FA_STAMP(4);  // MMA: wait K
             }
             issue_s(i, j + 1);
-            FA_TRACE(5); FA_STAMP(5);  // MMA: issue S
           }
           if (i == 1 && more) fa_mma_commit(bar_addr(sb, BAR_KEMPTY + s1));
         }
@@ -690,11 +632,7 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
     const fa_u32 t_o = tmem + ((fa_u32)lane_base << 16) + COL_O + i * D;
     const fa_u32 t_p = SEP_P ? tmem + ((fa_u32)lane_base << 16) + COL_P + i * 64 : t_s;
     bool ok = true;
-    SoftmaxCtx c = {p, sb, t_s, t_o, t_p, i, warp, qi, gb, gh, p.scale * FA_LOG2E, abort_flag, sched_tile, FA_NEG_INF, 0.f, 0u
-#if FA_TC_TRACE
-                    , trace_on, clock64()
-#endif
-    };
+    SoftmaxCtx c = {p, sb, t_s, t_o, t_p, i, warp, qi, gb, gh, p.scale * FA_LOG2E, abort_flag, sched_tile, FA_NEG_INF, 0.f, 0u};
     for (int j = 0; j < nsteps && ok; ++j) {
       const int mode = sched_mode[2 * j + i];
       if (mode == 0) continue;
@@ -741,12 +679,14 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
             *(float4*)(p.part_o + prow * D + c * 32 + e) = make_float4(o[e], o[e + 1], o[e + 2], o[e + 3]);
         }
       }
-      if (qi >= 0 && qi < p.Sq) *(float2*)(p.part_ml + prow * 2) = make_float2(m_ref, l);
+      if (qi >= 0 && qi < p.Sq) *(float2*)(p.part_ml + prow * 2) = make_float2(m_ref, m_ref != FA_NEG_INF ? l : 0.f);
     }
 #else
     if (ok) {
       fa_tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
+      // a row that never saw an unmasked key has no mass (its sum may hold the tiny values the
+      // polynomial exponential returns for -inf): its output is 0
+      const float inv = (l > 0.f && m_ref != FA_NEG_INF) ? 1.f / l : 0.f;
       char* og = (char*)p.o.ptr + ((long long)b * p.o.sb + (long long)h * p.o.sh + (long long)qi * p.o.ss) * 2;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
@@ -771,7 +711,7 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
         }
       }
       if (p.lse != nullptr && qi < p.Sq)
-        p.lse[((long long)b * p.Hq + h) * p.Sq + qi] = l > 0.f ? (m_ref + fa_lg2(l)) * FA_LN2 : FA_NEG_INF;
+        p.lse[((long long)b * p.Hq + h) * p.Sq + qi] = (l > 0.f && m_ref != FA_NEG_INF) ? (m_ref + fa_lg2(l)) * FA_LN2 : FA_NEG_INF;
     }
 #endif
   }

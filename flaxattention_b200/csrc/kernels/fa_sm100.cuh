@@ -42,7 +42,9 @@ __device__ __forceinline__ fa_u64 fa_globaltimer() {
 // Bounded wait: gives up after ~2 s, or as soon as another thread of the CTA has given up
 // (*abort != 0).  Returns false on failure; the caller then leaves its loop and the kernel
 // tears down normally (no trap, the context stays usable, the host sees the status word).
+#ifndef FA_WAIT_LIMIT_NS
 #define FA_WAIT_LIMIT_NS 2000000000ull
+#endif
 #ifndef FA_WAIT_SLEEP_NS
 #define FA_WAIT_SLEEP_NS 40
 #endif

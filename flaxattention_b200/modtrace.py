@@ -945,7 +945,14 @@ def derivative(mod: TracedMod) -> TracedMod:
             r = select(binary("ge", a[0], a[1]), d(a[0]), d(a[1]))
         elif op == "select":
             r = select(a[0], d(a[1]), d(a[2]))
-        elif op in ("floor", "ceil", "sign", "cast_i32", "cast_b1", "floordiv", "rem"):
+        elif op == "rem":
+            # float remainder u - floor(u / c) * c with a divisor that does not depend on the
+            # score: piecewise u + const, so the derivative is u'; integer remainders are steps
+            if e.dtype == F32 and not _depends_on_score(a[1], dep):
+                r = d(a[0])
+            else:
+                r = zero
+        elif op in ("floor", "ceil", "sign", "cast_i32", "cast_b1", "floordiv"):
             r = zero
         elif op == "cast_f32":
             r = zero  # the operand is an integer or bool: piecewise constant

@@ -44,11 +44,6 @@ extern "C" {
  * (flaxattention/core/attention.py:27).  Without it the fp32 product is kept, as in the
  * reference's fused kernel (flaxattention/kernel/attention.py:82).  No effect for FA_F32. */
 #define FA_FLAG_ROUND_SCORES 1
-/* Measurement aids for fa_bwd: leave out one of its three kernels (the results of a call
- * that sets any of them are incomplete). */
-#define FA_FLAG_BWD_SKIP_DELTA 2
-#define FA_FLAG_BWD_SKIP_DKDV 4
-#define FA_FLAG_BWD_SKIP_DQ 8
 /* Use the general (mma.sync) kernels even where a tcgen05 kernel covers the shape. */
 #define FA_FLAG_GENERAL_KERNELS 16
 
@@ -120,6 +115,17 @@ int fa_module_set_buffers(fa_module* m, const void* const* ptrs, int n);
 int fa_module_prepare(fa_module* m, int kind, int dtype, int D, int Dv, int Sq_hint, int Skv_hint);
 /* Number of kernels compiled (not fetched from a cache) since the library was loaded. */
 int fa_compile_count(void);
+
+/* Per-kernel device times.  While enabled (process-wide switch), fa_fwd, fa_bwd and fa_decode
+ * record a pair of CUDA events around every kernel they launch on the caller's stream; results
+ * are unaffected.  fa_profile_read waits for the calling thread's most recent such call to finish
+ * on the device and stores, in launch order, the kernel names and their durations in milliseconds
+ * (at most max_kernels of them); it returns the number of kernels that call launched, or a
+ * negative FA_E* code.  The names stay valid until their module is destroyed.  This is what takes
+ * the place of the per-program timings a Pallas/Triton profile of the reference's launches gives
+ * (flaxattention/kernel/attention.py:243, :321, :352, :612). */
+int fa_profile_enable(int on);
+int fa_profile_read(int max_kernels, float* ms, const char** names);
 
 int fa_fwd(fa_module* m, const fa_attn_params* p, void* stream);
 

@@ -117,3 +117,56 @@ def test_decode_with_a_document_mask():
     assert max_abs(out.cpu(), ref) <= 2e-2
     err, same = lse_err(lse.cpu(), ref_lse)
     assert same and err <= 2e-2 * max(1.0, ref_lse.abs().max().item())
+
+
+def test_math_attention_with_explicit_other_buffers():
+    """The reference's explicit form: mods that take the arrays as trailing arguments, passed in
+    ``score_mod_other_buffers`` / ``mask_mod_other_buffers`` (core/attention.py:67-78)."""
+    import math
+
+    import flaxattention_b200 as fa
+
+    B, H, S, D = 1, 2, 256, 64
+    doc = _documents(S, device="cuda", dtype=torch.int32)
+    table = normal(5, (H, S, S)).cuda()
+
+    def score(s, b, h, q_idx, kv_idx, t):
+        return s + t[h, q_idx, kv_idx]
+
+    def mask(b, h, q_idx, kv_idx, ids):
+        return (ids[q_idx] == ids[kv_idx]) & (q_idx >= kv_idx)
+
+    q, k, v = qkv(B, H, H, S, S, D, dtype=torch.float16)
+    bm = fa.create_block_mask(_doc_causal(doc), B, H, S, S)
+    tup = bm.as_tuple()[:-1] + (mask,)
+    out, lse2 = fa.math_attention(q.cuda(), k.cuda(), v.cuda(), score, tup, 0.125,
+                                  score_mod_other_buffers=(table,), mask_mod_other_buffers=(doc,))
+    torch.cuda.synchronize()
+    ref, ref_lse = flax_attention_oracle(q, k, v, _bias_mod(table.cpu()), _doc_causal(doc.cpu()), 0.125)
+    assert max_abs(out.cpu(), ref) <= 2e-2
+    err, same = lse_err(lse2.cpu() * math.log(2.0), ref_lse)
+    assert same and err <= 2e-2 * max(1.0, ref_lse.abs().max().item())
+
+
+def test_compiled_block_mask_tables_are_kept():
+    """create_block_mask(..., _compile=True) keeps the finished tables per (mask source, shape,
+    block sizes, offsets, device): a repeated call returns the same tensors without a launch;
+    masks over captured tensors are rebuilt every time."""
+    from flaxattention_b200 import create_block_mask
+    from flaxattention_b200.masks import causal_mask, generate_sliding_window
+
+    a = create_block_mask(causal_mask, 2, 2, 512, 512, _compile=True)
+    b = create_block_mask(causal_mask, 2, 2, 512, 512, _compile=True)
+    assert b.kv_indices.data_ptr() == a.kv_indices.data_ptr() and b.q_num_blocks.data_ptr() == a.q_num_blocks.data_ptr()
+    c = create_block_mask(causal_mask, 2, 2, 512, 512, _compile=True, h_offset=2)
+    d = create_block_mask(generate_sliding_window(64), 2, 2, 512, 512, _compile=True)
+    e = create_block_mask(causal_mask, 2, 2, 512, 512)
+    assert len({t.kv_indices.data_ptr() for t in (a, c, d, e)}) == 4
+    want = create_block_mask_oracle(causal_mask, 2, 2, 512, 512)
+    for k in TABLE_KEYS:
+        assert np.array_equal(getattr(b, k).cpu().numpy(), want[k]), k
+    doc = _documents(512, device="cuda", dtype=torch.int32)
+    m = _doc_causal(doc)
+    f = create_block_mask(m, 1, 1, 512, 512, _compile=True)
+    g = create_block_mask(m, 1, 1, 512, 512, _compile=True)
+    assert f.kv_indices.data_ptr() != g.kv_indices.data_ptr()

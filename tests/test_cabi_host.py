@@ -139,3 +139,72 @@ def test_reference_validation_messages():
         fa.flax_attention(q[0], q[0], q[0])
     with pytest.raises(ValueError, match="same number of heads"):
         fa.flax_attention_pallas(q, q[:, :2], q[:, :2])
+
+
+def test_decode_static_rejects_bad_arguments_first():
+    """fa_decode_static validates before it sizes its scratch: negative or zero extents are
+    FA_EINVAL, not a workspace error with a wrapped-around byte count."""
+    L = _cabi.lib()
+    m = _cabi.Module(None)
+    for kw in (dict(B=-2), dict(Sq=0), dict(Hq=-4, Hkv=-4)):
+        assert L.fa_decode_static(m.handle, C.byref(_params(Skv=4096, **kw)), 4, None) == -1, kw
+    assert L.fa_decode_static(m.handle, C.byref(_params(Sq=65, Skv=4096)), 4, None) == -4
+    assert L.fa_decode_static(m.handle, C.byref(_params(dtype=2, Sq=8, Skv=4096)), 4, None) == -4
+    assert L.fa_decode_static(m.handle, None, 4, None) == -1
+
+
+def test_status_word_raises_on_the_next_check():
+    """A kernel that gave up on a barrier wait ORs a bit into the status word; the wrapper raises
+    on the next call or on check_status() and clears the word."""
+    import torch
+    from flaxattention_b200 import attention as A
+
+    old = A._status_word
+    try:
+        A._status_word = torch.zeros(1, dtype=torch.int32)
+        A.check_status()
+        A._status_word[0] = 1
+        with pytest.raises(_cabi.FlaxAttnError, match="barrier wait"):
+            A.check_status()
+        A.check_status()  # cleared
+    finally:
+        A._status_word = old
+
+
+def test_profile_read_without_a_call_is_empty():
+    L = _cabi.lib()
+    assert L.fa_profile_enable(1) == 0
+    assert _cabi.profile_read() == []
+    assert L.fa_profile_enable(0) == 0
+
+
+def test_other_buffers_are_bound_as_trailing_arguments():
+    """math_attention(..., score_mod_other_buffers, mask_mod_other_buffers): the reference calls
+    the mods with the buffers appended (core/attention.py:35-52)."""
+    import torch
+    from flaxattention_b200 import attention as A, modtrace
+
+    bias = torch.arange(12, dtype=torch.float32).reshape(3, 4)
+    doc = torch.tensor([0, 0, 1, 1], dtype=torch.int32)
+
+    def score(s, b, h, q, kv, table):
+        return s + table[h, kv]
+
+    def mask(b, h, q, kv, ids):
+        return ids[q] == ids[kv]
+
+    sb = A._bind_other_buffers(score, (bias,), True)
+    mb = A._bind_other_buffers(mask, (doc,), False)
+    assert A._bind_other_buffers(score, (bias,), True) is sb  # cached on identity
+    assert modtrace.mod_arity(sb) == 5 and modtrace.mod_arity(mb) == 4
+    ms = modtrace.lower_mods(sb, mb)
+    assert len(ms.buffers) == 2
+    import numpy as np
+    b = np.zeros((1, 1, 1, 1), np.int32)
+    h = np.arange(3, dtype=np.int32).reshape(1, 3, 1, 1)
+    q = np.arange(4, dtype=np.int32).reshape(1, 1, 4, 1)
+    kv = np.arange(4, dtype=np.int32).reshape(1, 1, 1, 4)
+    got = modtrace.evaluate(modtrace.trace_score_mod(sb), np.zeros((1, 3, 4, 4), np.float32), b, h, q, kv)
+    assert np.array_equal(np.broadcast_to(got, (1, 3, 4, 4))[0, :, 0, :], bias.numpy())
+    gm = modtrace.evaluate(modtrace.trace_mask_mod(mb), None, b, h, q, kv)
+    assert np.array_equal(np.broadcast_to(gm, (1, 1, 4, 4))[0, 0], doc.numpy()[:, None] == doc.numpy()[None, :])

@@ -74,6 +74,17 @@ def test_symbolic_derivative(fn):
     np.testing.assert_allclose(np.broadcast_to(g, fd.shape)[ok], fd[ok], rtol=2e-3, atol=2e-3)
 
 
+def test_derivative_of_a_float_remainder():
+    """score % c is score minus a step function: its derivative is 1 away from the steps
+    (an integer remainder stays piecewise constant, derivative 0)."""
+    def wrap(score, b, h, q, kv):
+        return (score * 2.0) % 0.75 + ((q - kv) % 3) * 0.5
+
+    s, b, h, q, kv = _grid()
+    g = modtrace.evaluate(modtrace.derivative(modtrace.trace_score_mod(wrap)), s, b, h, q, kv)
+    np.testing.assert_allclose(np.broadcast_to(g, s.shape), np.full(s.shape, 2.0, np.float32))
+
+
 def test_python_mod_semantics():
     def m(score, b, h, q, kv):
         return fnp.where(((q - kv) % 4 == 3) & ((q - kv) // 4 == -1), 1.0, 0.0)

@@ -54,9 +54,13 @@ def _run_both(call, q, k, v, splits):
 
 
 def test_static_scratch_decode_equals_workspace_decode_twice():
-    # first call: many rows and splits; second call: a smaller problem that reuses the scratch
-    for shift, shape, splits in ((0, (2, 4, 16, 4096, 64), 6), (1, (1, 4, 1, 2048, 64), 3)):
-        call, q, k, v = _problem(shift, *shape, torch.float16)
+    # first call: many rows and splits; second call: a smaller problem that reuses the scratch;
+    # then the 33..64-row case, where a different kernel (the tcgen05 split-KV variant) writes the
+    # scratch, in bf16, again followed by a smaller problem
+    cases = ((0, (2, 4, 16, 4096, 64), 6, torch.float16), (1, (1, 4, 1, 2048, 64), 3, torch.float16),
+             (0, (2, 4, 48, 4096, 64), 4, torch.bfloat16), (1, (1, 2, 64, 2048, 64), 2, torch.bfloat16))
+    for shift, shape, splits, dtype in cases:
+        call, q, k, v = _problem(shift, *shape, dtype)
         (o_ws, l_ws), (o_st, l_st) = _run_both(call, q, k, v, splits)
         assert not torch.isnan(o_st.float()).any()
         assert max_abs(o_st, o_ws) <= 2e-3
@@ -78,3 +82,17 @@ def test_static_scratch_rejects_oversized_problems():
     assert rc == -5
     msg = L.fa_last_error().decode()
     assert str(cap) in msg and "scratch" in msg
+
+
+def test_static_scratch_validates_before_sizing():
+    """Bad shapes are argument errors (FA_EINVAL), whatever their product would be as a size."""
+    from flaxattention_b200 import _cabi
+
+    L = _cabi.lib()
+    call, q, k, v = _problem(0, 1, 2, 4, 1024, 64, torch.float16)
+    out = call.out_like(q)
+    stream = torch.cuda.current_stream().cuda_stream
+    for field, value in (("B", -1), ("Sq", 0), ("Hq", -4)):
+        p = call.params(q, k, v, out, None)
+        setattr(p, field, value)
+        assert L.fa_decode_static(call.module.handle, C.byref(p), 4, stream) == -1, field
