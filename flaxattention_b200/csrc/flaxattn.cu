@@ -592,12 +592,12 @@ __global__ void fa_delta_kernel(FaTensor o, FaTensor dout, float* __restrict__ d
 // Per-row scalars of the tcgen05 backward, padded to whole 128-row tiles so that a q tile's
 // values are one aligned 512-byte run: nlse2 = -lse * log2(e) (-inf for rows without mass or
 // beyond Sq, which makes p = 0 there) and ndelta = -sum_d O * dO (0 beyond Sq).
-// The same pass zeroes the dQ accumulation buffer when `dq_acc` is given (64 floats per padded
+// The same pass zeroes the dQ accumulation buffer when `dq_acc` is given (D floats per padded
 // row, whatever their order inside a tile): one launch and one pass less than a separate memset.
 template <int DT, int LPR>
 __global__ void fa_bwd_prep_kernel(FaTensor o, FaTensor dout, const float* __restrict__ lse, float* __restrict__ nlse2,
                                    float* __restrict__ ndelta, float* __restrict__ dq_acc, int Hq, int Sq, int sq_pad,
-                                   int Dv, int n_bh) {
+                                   int Dv, int D, int n_bh) {
   // grid: x over the padded rows of one (batch, head), LPR lanes per row; (y, z) over the heads
   constexpr int EPC = 8;
   const int bh = blockIdx.y + blockIdx.z * gridDim.y;
@@ -606,9 +606,8 @@ __global__ void fa_bwd_prep_kernel(FaTensor o, FaTensor dout, const float* __res
   const bool in_range = bh < n_bh && q < sq_pad;
   const long long row = (long long)bh * sq_pad + q;
   if (dq_acc != nullptr && in_range) {
-    float4* z = (float4*)(dq_acc + row * 64) + sub;
-#pragma unroll
-    for (int i = 0; i < 16 / LPR; ++i) z[i * LPR] = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4* z = (float4*)(dq_acc + row * D);
+    for (int i = sub; i < D / 4; i += LPR) z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
   }
   float acc = 0.f;
   const bool valid = in_range && q < Sq;
@@ -670,6 +669,39 @@ __global__ void fa_dq_convert_kernel(const float* __restrict__ acc, FaTensor dq,
   } else {
     __nv_bfloat162 o[4] = {__floats2bfloat162_rn(lo.x * scale, lo.y * scale), __floats2bfloat162_rn(lo.z * scale, lo.w * scale),
                            __floats2bfloat162_rn(hi.x * scale, hi.y * scale), __floats2bfloat162_rn(hi.z * scale, hi.w * scale)};
+    *(uint4*)dst = *reinterpret_cast<uint4*>(o);
+  }
+}
+
+// The same for head dim 128, where the kernel accumulates dQ transposed: per (b, h, 64-row q
+// tile) the buffer holds two [128 head-dim lanes][32 query columns] blocks (query columns 0-31,
+// then 32-63), 16-byte chunks of a block row d at position k ^ (d & 7).  A warp takes 32
+// consecutive query rows and one group of 8 head-dim values: each of its 8 reads is one 128-byte
+// row of a block, and every thread writes one 16-byte chunk of its output row.
+template <int DT>
+__global__ void fa_dq_convert_t_kernel(const float* __restrict__ acc, FaTensor dq, int Hq, int Sq, int sq_pad, float scale,
+                                       int n_bh) {
+  const int bh = blockIdx.y + blockIdx.z * gridDim.y;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  const int dg = (i >> 5) & 15, q = ((i >> 9) << 5) | (i & 31);
+  if (bh >= n_bh || q >= Sq) return;
+  const int b = bh / Hq, h = bh - b * Hq;
+  const int c = q & 63, hf = c >> 5, k = (c & 31) >> 2, w = c & 3;
+  const float* src = acc + ((long long)bh * (sq_pad >> 6) + (q >> 6)) * (128 * 64) + hf * (128 * 32) + w;
+  float v[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) {
+    const int d = dg * 8 + j;
+    v[j] = src[d * 32 + ((k ^ (d & 7)) << 2)] * scale;
+  }
+  char* dst = (char*)dq.ptr + ((long long)b * dq.sb + (long long)h * dq.sh + (long long)q * dq.ss) * 2 + dg * 16;
+  if (DT == FA_F16) {
+    __half2 o[4] = {__floats2half2_rn(v[0], v[1]), __floats2half2_rn(v[2], v[3]), __floats2half2_rn(v[4], v[5]),
+                    __floats2half2_rn(v[6], v[7])};
+    *(uint4*)dst = *reinterpret_cast<uint4*>(o);
+  } else {
+    __nv_bfloat162 o[4] = {__floats2bfloat162_rn(v[0], v[1]), __floats2bfloat162_rn(v[2], v[3]),
+                           __floats2bfloat162_rn(v[4], v[5]), __floats2bfloat162_rn(v[6], v[7])};
     *(uint4*)dst = *reinterpret_cast<uint4*>(o);
   }
 }
@@ -833,13 +865,13 @@ int encode_fn(EncodeTiledFn* out) {
   return FA_OK;
 }
 
-// 4-d map (D, S, H, B) over a [.., S, D]-strided tensor; box = 64 elements x 128 rows, 128-byte swizzle
-int make_map(FaTensorMapHost* out, int dtype, const fa_tensor& t, int D, int S, int H, int B) {
+// 4-d map (D, S, H, B) over a [.., S, D]-strided tensor; box = 64 elements x box_rows rows, 128-byte swizzle
+int make_map(FaTensorMapHost* out, int dtype, const fa_tensor& t, int D, int S, int H, int B, int box_rows = 128) {
   EncodeTiledFn enc = nullptr;
   if (int rc = encode_fn(&enc)) return rc;
   const cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)H, (cuuint64_t)B};
   const cuuint64_t strides[3] = {(cuuint64_t)t.stride_s * 2, (cuuint64_t)t.stride_h * 2, (cuuint64_t)t.stride_b * 2};
-  const cuuint32_t box[4] = {64, 128, 1, 1};
+  const cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   CUresult r = enc((CUtensorMap*)out, dtype == FA_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4,
                    t.ptr, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -929,10 +961,12 @@ struct FaBwdTcParamsHost {
 bool tc_bwd_eligible(const fa_attn_params* p) {
   if (p->flags & FA_FLAG_GENERAL_KERNELS) return false;
   if (p->dtype == FA_F32) return false;
-  if (p->D != 64 || p->Dv != 64) return false;
+  if (p->D != p->Dv || !(p->D == 64 || p->D == 128)) return false;
   if (p->Sq < 128 || p->Skv < 128) return false;
+  // a CTA lists its (query head, q tile) pairs in shared memory: at most 256 q tiles of 128 rows
+  // per head and 1024 pairs (a pair is 128 q rows with D = 64, 64 with D = 128)
   const int n_qtiles = (p->Sq + 127) / 128;
-  if (n_qtiles > 256 || (long long)n_qtiles * (p->Hq / p->Hkv) > 512) return false;
+  if (n_qtiles > 256 || (long long)n_qtiles * (p->D / 64) * (p->Hq / p->Hkv) > 1024) return false;
   const fa_block_tables& t = p->tables;
   if (t.kv_num_blocks) {
     if (!(t.num_q_blocks == 1 || t.q_block_size % 128 == 0)) return false;
@@ -947,14 +981,16 @@ size_t rows_pad_bytes(const fa_attn_params* p) {
 }
 size_t dq_acc_bytes(const fa_attn_params* p) {
   const size_t sq_pad = (size_t)((p->Sq + 127) / 128) * 128;
-  return (size_t)p->B * p->Hq * sq_pad * 64 * sizeof(float);
+  return (size_t)p->B * p->Hq * sq_pad * p->D * sizeof(float);
 }
 
-int get_bwd_tc_kernel(fa_module* m, int dtype, int flags, Kernel** k) {
+int get_bwd_tc_kernel(fa_module* m, int dtype, int D, int flags, Kernel** k) {
   // must match the shared-memory map of fa_bwd_tc.cuh (fa_btc::SMEM_BYTES)
-  const int nstage = 4;
-  const int smem = (2 + 2 * nstage) * 16384 + 2 * 16384 + 128 * 32 * 4 + nstage * 2 * 128 * 4 + (1 + 3 * nstage + 7) * 8 + 16 + 512 * 4 + 256 + 1024;
-  std::string d = defs({{"FA_DTYPE", dtype}, {"FA_ROUND_SCORES", round_flag(dtype, flags)}});
+  const int nstage = D == 64 ? 4 : 3, bq = D == 64 ? 128 : 64;
+  const int kv_bytes = (D / 64) * 16384, q_bytes = 16384, ds_bytes = (bq / 64) * 16384;
+  const int smem = 2 * kv_bytes + 2 * nstage * q_bytes + ds_bytes + 128 * 32 * 4 + nstage * 2 * bq * 4 +
+                   (1 + 3 * nstage + 7) * 8 + 16 + 1024 * 4 + 256 + 1024;
+  std::string d = defs({{"FA_DTYPE", dtype}, {"FA_D", D}, {"FA_ROUND_SCORES", round_flag(dtype, flags)}});
   return get_kernel(m, "fa_bwd_tc.cuh", d, "fa_bwd_tc_kernel", smem, k);
 }
 
@@ -981,8 +1017,8 @@ int fa_module_prepare(fa_module* m, int kind, int dtype, int D, int Dv, int Sq_h
     case FA_KIND_BWD: {
       BwdCfg c;
       if (int rc = pick_bwd(dtype, D, Dv, nullptr, c)) return rc;
-      if (dtype != FA_F32 && D == 64 && Dv == 64 && Sq_hint >= 128)
-        if (int rc = get_bwd_tc_kernel(m, dtype, 0, &k)) return rc;
+      if (dtype != FA_F32 && D == Dv && (D == 64 || D == 128) && Sq_hint >= 128)
+        if (int rc = get_bwd_tc_kernel(m, dtype, D, 0, &k)) return rc;
       if (int rc = get_bwd_kernel(m, dtype, D, Dv, 0, c, true, &k)) return rc;
       return get_bwd_kernel(m, dtype, D, Dv, 0, c, false, &k);
     }
@@ -1045,7 +1081,7 @@ int fa_bwd(fa_module* m, const fa_attn_params* p, const fa_tensor* dout, const f
   BwdCfg c{};
   Kernel *kdq = nullptr, *kdkdv = nullptr, *ktc = nullptr;
   if (use_tc) {
-    if (int rc = get_bwd_tc_kernel(m, p->dtype, p->flags, &ktc)) return rc;
+    if (int rc = get_bwd_tc_kernel(m, p->dtype, p->D, p->flags, &ktc)) return rc;
   } else {
     if (int rc = pick_bwd(p->dtype, p->D, p->Dv, &kp.t, c)) return rc;
     if (int rc = get_bwd_kernel(m, p->dtype, p->D, p->Dv, p->flags, c, true, &kdq)) return rc;
@@ -1065,9 +1101,9 @@ int fa_bwd(fa_module* m, const fa_attn_params* p, const fa_tensor* dout, const f
       const dim3 grid((unsigned)((sq_pad * 8 + 255) / 256), (unsigned)gy, (unsigned)((n_bh + gy - 1) / gy));
       ProfScope prof("fa_bwd_prep_kernel", stream);
       if (p->dtype == FA_F16)
-        fa_bwd_prep_kernel<FA_F16, 8><<<grid, 256, 0, st>>>(kp.o, kp.dout, p->lse, nlse2, ndelta, dq_acc, p->Hq, p->Sq, sq_pad, p->Dv, n_bh);
+        fa_bwd_prep_kernel<FA_F16, 8><<<grid, 256, 0, st>>>(kp.o, kp.dout, p->lse, nlse2, ndelta, dq_acc, p->Hq, p->Sq, sq_pad, p->Dv, p->D, n_bh);
       else
-        fa_bwd_prep_kernel<FA_BF16, 8><<<grid, 256, 0, st>>>(kp.o, kp.dout, p->lse, nlse2, ndelta, dq_acc, p->Hq, p->Sq, sq_pad, p->Dv, n_bh);
+        fa_bwd_prep_kernel<FA_BF16, 8><<<grid, 256, 0, st>>>(kp.o, kp.dout, p->lse, nlse2, ndelta, dq_acc, p->Hq, p->Sq, sq_pad, p->Dv, p->D, n_bh);
       FA_CUDA_CHECK(cudaGetLastError());
     }
     FaBwdTcParamsHost tp;
@@ -1075,19 +1111,28 @@ int fa_bwd(fa_module* m, const fa_attn_params* p, const fa_tensor* dout, const f
     tp.dq_acc = dq_acc;
     tp.nlse2 = nlse2;
     tp.ndelta = ndelta;
-    if (int rc = make_map(&tp.tq, p->dtype, p->q, p->D, p->Sq, p->Hq, p->B)) return rc;
+    const int bq = p->D == 64 ? 128 : 64;  // q rows of a (kv tile, q tile) pair of the kernel
+    if (int rc = make_map(&tp.tq, p->dtype, p->q, p->D, p->Sq, p->Hq, p->B, bq)) return rc;
     if (int rc = make_map(&tp.tk, p->dtype, p->k, p->D, p->Skv, p->Hkv, p->B)) return rc;
     if (int rc = make_map(&tp.tv, p->dtype, p->v, p->Dv, p->Skv, p->Hkv, p->B)) return rc;
-    if (int rc = make_map(&tp.tdo, p->dtype, *dout, p->Dv, p->Sq, p->Hq, p->B)) return rc;
+    if (int rc = make_map(&tp.tdo, p->dtype, *dout, p->Dv, p->Sq, p->Hq, p->B, bq)) return rc;
     // heads fastest, kv tile slowest: under a causal mask the first kv tiles meet the most q tiles
     if (int rc = launch(ktc, dim3(p->Hkv, p->B, (p->Skv + 127) / 128), dim3(512), &tp, stream)) return rc;
     {
-      const dim3 grid((unsigned)((p->Sq * 8 + 255) / 256), (unsigned)gy, (unsigned)((n_bh + gy - 1) / gy));
+      // one 16-byte output chunk per thread: D / 8 chunks per row
+      const dim3 grid((unsigned)(((long long)sq_pad * (p->D / 8) + 255) / 256), (unsigned)gy, (unsigned)((n_bh + gy - 1) / gy));
       ProfScope prof("fa_dq_convert_kernel", stream);
-      if (p->dtype == FA_F16)
-        fa_dq_convert_kernel<FA_F16><<<grid, 256, 0, st>>>(dq_acc, kp.dq, p->Hq, p->Sq, sq_pad, p->scale, n_bh);
-      else
-        fa_dq_convert_kernel<FA_BF16><<<grid, 256, 0, st>>>(dq_acc, kp.dq, p->Hq, p->Sq, sq_pad, p->scale, n_bh);
+      if (p->D == 64) {
+        if (p->dtype == FA_F16)
+          fa_dq_convert_kernel<FA_F16><<<grid, 256, 0, st>>>(dq_acc, kp.dq, p->Hq, p->Sq, sq_pad, p->scale, n_bh);
+        else
+          fa_dq_convert_kernel<FA_BF16><<<grid, 256, 0, st>>>(dq_acc, kp.dq, p->Hq, p->Sq, sq_pad, p->scale, n_bh);
+      } else {
+        if (p->dtype == FA_F16)
+          fa_dq_convert_t_kernel<FA_F16><<<grid, 256, 0, st>>>(dq_acc, kp.dq, p->Hq, p->Sq, sq_pad, p->scale, n_bh);
+        else
+          fa_dq_convert_t_kernel<FA_BF16><<<grid, 256, 0, st>>>(dq_acc, kp.dq, p->Hq, p->Sq, sq_pad, p->scale, n_bh);
+      }
       FA_CUDA_CHECK(cudaGetLastError());
     }
     return FA_OK;

@@ -1,40 +1,50 @@
 // Flash-attention backward for sm_100a on the 5th-generation tensor cores (fp16 / bf16,
-// D = Dv = 64).  One kernel computes dK, dV and dQ in a single pass over the (kv tile, q tile)
-// pairs the BlockMask lists: five tcgen05.mma products per pair and one exponential per
-// score, where the two-scan reference kernel (flaxattention/kernel/attention.py:423-553) and
-// fa_bwd.cuh need seven products and two exponentials.
+// D = Dv = 64 or 128).  One kernel computes dK, dV and dQ in a single pass over the
+// (kv tile, q tile) pairs the BlockMask lists: five tcgen05.mma products per pair and one
+// exponential per score, where the two-scan reference kernel
+// (flaxattention/kernel/attention.py:423-553) and fa_bwd.cuh need seven products and two
+// exponentials.
 //
 // One CTA owns a 128-row kv tile of one (batch, kv head) and walks the q tiles of the query
-// heads that share it.  Everything is kept transposed so that the accumulators dK and dV
+// heads that share it.  A pair is 128 kv rows x BQ query rows, BQ = 128 with D = 64 and 64 with
+// D = 128 (the 512 TMEM columns hold two D-wide accumulators, dK and dV, next to the pair's
+// score tiles only for the smaller q tile).  Everything is kept transposed so that dK and dV
 // have kv rows (TMEM lanes) and P^T can be fed to the tensor core straight from TMEM:
-//   1. S^T  = K Q^T                      (TMEM, 128 kv x 128 q, fp32)
+//   1. S^T  = K Q^T                      (TMEM, 128 kv x BQ q, fp32)
 //   2. dP^T = V dO^T                     (TMEM)
-//      p = 2^(x - lse), ds = p (dp - delta) score_mod'      thread (kv row, 64 q columns)
+//      p = 2^(x - lse), ds = p (dp - delta) score_mod'      thread (kv row, BQ/2 q columns)
 //      P^T -> TMEM (16 bit),  dS^T -> shared memory (16 bit, [kv][q], 128-byte swizzle)
 //   3. dV += P^T dO                      (A from TMEM)
 //   4. dK += dS^T Q                      (A = dS^T from smem, K-major)
-//   5. dQ  = dS K                        (A = the same dS^T tile read MN-major, B = K)
-// dQ of a pair leaves TMEM through a staging buffer and two bulk reduce-adds into an fp32
-// accumulation buffer (summation order over kv tiles is not fixed; a small kernel scales and
-// converts it afterwards).  dK and dV are written once at the end.
+//   5. D = 64:   dQ   = dS K             (A = the same dS^T tile read MN-major, B = K; 128 q x 64 d)
+//      D = 128:  dQ^T = K^T dS^T         (A = K read MN-major, B = dS^T read MN-major; 128 d x 64 q)
+// Either way the dQ tile of a pair is 128 TMEM lanes x 64 columns of fp32.  It leaves through a
+// staging buffer and two bulk reduce-adds into an fp32 accumulation buffer (summation order
+// over kv tiles is not fixed; a small kernel scales, un-permutes and converts it afterwards).
+// dK and dV are written once at the end.
 //
-// Warp roles (16 warps): 0-3 and 4-7 compute (q columns 0-63 / 64-127 of the pair tile),
+// Warp roles (16 warps): 0-3 and 4-7 compute (first / second half of the q columns of the pair),
 // 8-11 dQ drain, 12 TMA producer, 13 MMA issuer A (products 1-2, TMEM owner), 14 MMA issuer B
 // (products 3-4), 15 MMA issuer C (product 5).
 // S^T/dP^T of pair n+1 are issued as soon as the compute warps hold pair n in registers, so
 // the tensor core runs ahead of the element-wise work.
 //
-// TMEM (512 columns): S^T 0-127, dP^T 128-255, P^T 256-319, dV 320-383, dK 384-447, dQ 448-511.
+// TMEM (512 columns)   D = 64:  S^T 0-127, dP^T 128-255, P^T 256-319, dV 320-383, dK 384-447, dQ 448-511
+//                      D = 128: S^T 0-63, dP^T 64-127, P^T 128-159, dQ^T 192-255, dV 256-383, dK 384-511
 // Every mbarrier wait is bounded (see fa_sm100.cuh).
 //
-// Compile-time parameters (macros): FA_DTYPE (0 fp16, 1 bf16); D = Dv = 64.
+// Compile-time parameters (macros): FA_DTYPE (0 fp16, 1 bf16), FA_D (64 or 128; Dv = D).
 #pragma once
 #include "fa_sm100.cuh"
 
+#ifndef FA_D
+#define FA_D 64
+#endif
+
 struct FaBwdTcParams {
   FaParams p;
-  FaTensorMap tq, tk, tv, tdo;  // 4-d maps (D, S, H, B), box 64 x 128 x 1 x 1, 128-byte swizzle
-  float* dq_acc;                // per (b, h, q tile): two [128 rows][32 columns] fp32 blocks, 16-byte chunks of a row permuted
+  FaTensorMap tq, tk, tv, tdo;  // 4-d maps (D, S, H, B), 128-byte swizzle; box 64 x 128 rows (k, v), 64 x BQ rows (q, do)
+  float* dq_acc;                // per (b, h, BQ-row q tile): two [128 lanes][32 columns] fp32 blocks, 16-byte chunks of a row permuted
   const float* nlse2;           // [B, Hq, ceil(Sq/128)*128]: -lse * log2(e); -inf for rows without mass / beyond Sq
   const float* ndelta;          // same shape: -rowsum(O * dO); 0 beyond Sq
 };
@@ -42,11 +52,20 @@ struct FaBwdTcParams {
 namespace fa_btc {
 
 constexpr int DT = FA_DTYPE;
-constexpr int D = 64;
-constexpr int BT = 128;                  // tile edge (kv rows and q columns)
-constexpr int ATOM_BYTES = 128 * 128;    // 128 rows x 128 bytes
-constexpr int NSTAGE = 4;
-constexpr int MAXP = 512;                // (head, q tile) pairs per CTA
+constexpr int D = FA_D;
+static_assert(D == 64 || D == 128, "head dim 64 or 128");
+constexpr int BT = 128;                    // kv rows of a tile
+constexpr int BQ = D == 64 ? 128 : 64;     // q rows of a pair
+constexpr int CW = BQ / 2;                 // q columns of one compute thread
+constexpr int DATOMS = D / 64;             // 64-element (128-byte) column groups of a K / V / Q / dO row
+constexpr int ATOM_BYTES = 128 * 128;      // 128 rows x 128 bytes
+constexpr int KV_BYTES = DATOMS * ATOM_BYTES;        // one K or V tile
+constexpr int Q_ATOM_BYTES = BQ * 128;               // BQ rows x 128 bytes
+constexpr int Q_BYTES = DATOMS * Q_ATOM_BYTES;       // one Q or dO tile (16 KB in both configurations)
+constexpr int DS_ATOMS = BQ / 64;                    // dS^T: [128 kv][BQ q] as atoms of 64 q columns
+constexpr int NSTAGE = D == 64 ? 4 : 3;
+constexpr int MAXP = 1024;               // (head, q tile) pairs per CTA
+constexpr int MAXC = 256;                // 128-row q tiles per head (Sq <= 32768)
 constexpr int NT = 512;
 constexpr int WARP_PRODUCER = 12, WARP_MMA = 13, WARP_MMA_B = 14, WARP_MMA_C = 15;
 // Register split (setmaxnreg): the kernel starts with 128 registers per thread (65536 / 512).  The
@@ -57,21 +76,26 @@ static_assert(256 * (REGS_COMPUTE - 128) <= 256 * (128 - REGS_OTHER), "setmaxnre
 
 // shared memory map (from a 1024-byte aligned base)
 constexpr int OFF_K = 0;
-constexpr int OFF_V = OFF_K + ATOM_BYTES;
-constexpr int OFF_Q = OFF_V + ATOM_BYTES;                   // NSTAGE tiles
-constexpr int OFF_DO = OFF_Q + NSTAGE * ATOM_BYTES;         // NSTAGE tiles
-constexpr int OFF_DS = OFF_DO + NSTAGE * ATOM_BYTES;        // dS^T: two atoms (q 0-63, q 64-127)
-constexpr int OFF_DQ = OFF_DS + 2 * ATOM_BYTES;             // fp32 staging 128 x 32 (half of the dQ tile at a time)
+constexpr int OFF_V = OFF_K + KV_BYTES;
+constexpr int OFF_Q = OFF_V + KV_BYTES;                     // NSTAGE tiles
+constexpr int OFF_DO = OFF_Q + NSTAGE * Q_BYTES;            // NSTAGE tiles
+constexpr int OFF_DS = OFF_DO + NSTAGE * Q_BYTES;           // dS^T
+constexpr int OFF_DQ = OFF_DS + DS_ATOMS * ATOM_BYTES;      // fp32 staging 128 x 32 (half of the dQ tile at a time)
 constexpr int DQ_HALF_BYTES = 128 * 32 * 4;
-constexpr int OFF_ROW = OFF_DQ + DQ_HALF_BYTES;             // NSTAGE x (nlse2[128], ndelta[128]) floats
-constexpr int OFF_BAR = OFF_ROW + NSTAGE * 2 * 128 * 4;
+constexpr int OFF_ROW = OFF_DQ + DQ_HALF_BYTES;             // NSTAGE x (nlse2[BQ], ndelta[BQ]) floats
+constexpr int OFF_BAR = OFF_ROW + NSTAGE * 2 * BQ * 4;
 constexpr int NBARS = 1 + 3 * NSTAGE + 7;
-constexpr int OFF_MISC = OFF_BAR + NBARS * 8;               // tmem base, abort, npairs, pad
-constexpr int OFF_PAIR = OFF_MISC + 16;                     // int pair[MAXP]: tile | mode << 16 | g << 20
-constexpr int OFF_CLS = OFF_PAIR + MAXP * 4;                // uchar cls[256]
-constexpr int SMEM_BYTES = OFF_CLS + 256 + 1024;
+constexpr int OFF_MISC = OFF_BAR + NBARS * 8;               // tmem base, abort, npairs, drain flag
+constexpr int OFF_PAIR = OFF_MISC + 16;                     // int pair[MAXP]: q tile | mode << 16 | g << 20
+constexpr int OFF_CLS = OFF_PAIR + MAXP * 4;                // uchar cls[MAXC]
+constexpr int SMEM_BYTES = OFF_CLS + MAXC + 1024;
+static_assert(SMEM_BYTES <= 227 * 1024, "shared memory");
 constexpr int TMEM_COLS = 512;
-constexpr int COL_S = 0, COL_DP = 128, COL_P = 256, COL_DV = 320, COL_DK = 384, COL_DQ = 448;
+constexpr int COL_S = 0, COL_DP = BQ, COL_P = 2 * BQ;
+constexpr int COL_DQ = D == 64 ? 448 : 192;
+constexpr int COL_DV = D == 64 ? 320 : 256;
+constexpr int COL_DK = D == 64 ? 384 : 384;
+static_assert(COL_P + BQ / 2 <= (D == 64 ? COL_DV : COL_DQ), "TMEM map");
 
 constexpr int BAR_KV = 0;
 // A stage's Q tile (with the row scalars) and dO tile are released separately: dO is last read by
@@ -99,7 +123,13 @@ __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.comm
 __device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
-// Element-wise work of one thread on a 32-column chunk: scores s and dp (fp32, raw) for kv row
+// byte offset (in 16-byte units) of k-step kk of a K-major operand whose 64-element column groups
+// are `atom_bytes` apart: 32 bytes per step inside a 128-byte row, four steps per group
+__device__ __forceinline__ constexpr fa_u32 kstep_kmajor(int kk, int atom_bytes) {
+  return (fa_u32)(((kk >> 2) * atom_bytes + (kk & 3) * 32) >> 4);
+}
+
+// Element-wise work of one thread on a W-column chunk: scores s and dp (fp32, raw) for kv row
 // `kv` and q columns q0 .. q0+W-1 -> packed P^T and dS^T (16 bit).  q0 is a multiple of W (the
 // compiler can see that from how the caller builds it), so the low bits of every q index are
 // compile-time constants inside the mods while one copy of this code serves all chunks of a
@@ -205,8 +235,8 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
   const int n0 = kt * BT;
   const int G = p.Hq / p.Hkv;
   const int gb = b + p.b_off;
-  const int n_qtiles = (p.Sq + BT - 1) / BT;
-  const int sq_pad = n_qtiles * BT;
+  const int n_ctiles = min((p.Sq + 127) / 128, MAXC);  // 128-row q tiles (the grain of the BlockMask walk)
+  const int sq_pad = ((p.Sq + 127) / 128) * 128;
 
   volatile int* misc = (volatile int*)(sm + OFF_MISC);  // [0] tmem base, [1] abort, [2] npairs, [3] drain warps leave
   int* pairs = (int*)(sm + OFF_PAIR);
@@ -235,25 +265,28 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
     // while the list is being built
     fa_tma_prefetch_desc(&P.tk);
     fa_tma_prefetch_desc(&P.tv);
-    fa_mbar_expect_tx(bar_addr(sb, BAR_KV), 2 * ATOM_BYTES);
-    fa_tma_load_4d(sb + OFF_K, &P.tk, bar_addr(sb, BAR_KV), 0, n0, hk, b);
-    fa_tma_load_4d(sb + OFF_V, &P.tv, bar_addr(sb, BAR_KV), 0, n0, hk, b);
+    fa_mbar_expect_tx(bar_addr(sb, BAR_KV), 2 * KV_BYTES);
+    for (int a = 0; a < DATOMS; ++a) {
+      fa_tma_load_4d(sb + OFF_K + a * ATOM_BYTES, &P.tk, bar_addr(sb, BAR_KV), a * 64, n0, hk, b);
+      fa_tma_load_4d(sb + OFF_V + a * ATOM_BYTES, &P.tv, bar_addr(sb, BAR_KV), a * 64, n0, hk, b);
+    }
   }
   if (warp == WARP_MMA) fa_tmem_alloc(sb + OFF_MISC, TMEM_COLS);
-  // (head, q tile) pairs of this kv tile: per head, classify the q tiles (0 skip, 1 mask, 2 full)
+  // (head, q tile) pairs of this kv tile: per head, classify the 128-row q tiles (0 skip, 1 mask,
+  // 2 full); each listed tile gives 128 / BQ pairs
   int npairs = 0;  // meaningful in thread 0 only
   for (int g = 0; g < G; ++g) {
     const int h = hk * G + g;
     __syncthreads();
-    for (int t = tid; t < 256; t += NT) cls[t] = 0;
+    for (int t = tid; t < MAXC; t += NT) cls[t] = 0;
     __syncthreads();
     if (p.t.kv_num == nullptr || p.t.q_num == nullptr) {
-      for (int t = tid; t < min(n_qtiles, 256); t += NT) cls[t] = FA_HAS_MASK_MOD ? 1 : 2;
+      for (int t = tid; t < n_ctiles; t += NT) cls[t] = FA_HAS_MASK_MOD ? 1 : 2;
     } else {
       const int bm = p.t.mB == 1 ? 0 : b, hm = p.t.mH == 1 ? 0 : h;
       const int kvblk = min(n0 / p.t.KVB, p.t.nKV - 1);
       const long long row = ((long long)bm * p.t.mH + hm) * p.t.nKV + kvblk;
-      const int tpb = p.t.nQ == 1 ? n_qtiles : p.t.QB / BT;
+      const int tpb = p.t.nQ == 1 ? n_ctiles : p.t.QB / 128;
       for (int which = 0; which < 2; ++which) {
         const int* nump = which ? p.t.full_q_num : p.t.q_num;
         const int* idxp = which ? p.t.full_q_idx : p.t.q_idx;
@@ -263,14 +296,20 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
           const int bi = e / tpb, ti = e - bi * tpb;
           const int blk = min(max(idxp[row * p.t.nQ + bi], 0), p.t.nQ - 1);
           const int t = blk * tpb + ti;
-          if (t < min(n_qtiles, 256)) cls[t] = (unsigned char)(which ? 2 : 1);
+          if (t < n_ctiles) cls[t] = (unsigned char)(which ? 2 : 1);
         }
       }
     }
     __syncthreads();
     if (tid == 0) {
-      for (int t = 0; t < min(n_qtiles, 256) && npairs < MAXP; ++t)
-        if (cls[t]) pairs[npairs++] = t | ((int)cls[t] << 16) | (g << 20);
+      for (int t = 0; t < n_ctiles; ++t) {
+        if (!cls[t]) continue;
+#pragma unroll
+        for (int u = 0; u < 128 / BQ; ++u) {
+          const int qt = t * (128 / BQ) + u;  // BQ-row tile
+          if (qt * BQ < p.Sq && npairs < MAXP) pairs[npairs++] = qt | ((int)cls[t] << 16) | (g << 20);
+        }
+      }
     }
   }
   if (tid == 0) misc[2] = npairs;
@@ -300,32 +339,34 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
         const int s = n % NSTAGE;
         const fa_u32 ph = (fa_u32)((n / NSTAGE) & 1);
         const int pr = pairs[n];
-        const int m0 = (pr & 0xffff) * BT, h = hk * G + (pr >> 20);
+        const int m0 = (pr & 0xffff) * BQ, h = hk * G + (pr >> 20);
         if (n >= NSTAGE) ok = fa_mbar_wait(bar_addr(sb, BAR_DOEMPTY + s), ph ^ 1u, abort_flag);
         if (!ok) break;
         // Q and dO tiles plus the per-row scalars of the q tile (prepared by fa_bwd_prep_kernel);
-        // one transaction count covers all four copies
+        // one transaction count covers all the copies
         const long long rbase = ((long long)b * p.Hq + h) * sq_pad + m0;
         const fa_u32 full = bar_addr(sb, BAR_QFULL + s);
-        fa_mbar_expect_tx(full, 2 * ATOM_BYTES + 2 * 128 * 4);
-        fa_tma_load_4d(sb + OFF_DO + s * ATOM_BYTES, &P.tdo, full, 0, m0, h, b);
+        fa_mbar_expect_tx(full, 2 * Q_BYTES + 2 * BQ * 4);
+        for (int a = 0; a < DATOMS; ++a)
+          fa_tma_load_4d(sb + OFF_DO + s * Q_BYTES + a * Q_ATOM_BYTES, &P.tdo, full, a * 64, m0, h, b);
         if (n >= NSTAGE) ok = fa_mbar_wait(bar_addr(sb, BAR_QEMPTY + s), ph ^ 1u, abort_flag);
         if (!ok) break;
-        fa_tma_load_4d(sb + OFF_Q + s * ATOM_BYTES, &P.tq, full, 0, m0, h, b);
-        fa_bulk_load(sb + OFF_ROW + s * 2 * 128 * 4, P.nlse2 + rbase, 128 * 4, full);
-        fa_bulk_load(sb + OFF_ROW + s * 2 * 128 * 4 + 128 * 4, P.ndelta + rbase, 128 * 4, full);
+        for (int a = 0; a < DATOMS; ++a)
+          fa_tma_load_4d(sb + OFF_Q + s * Q_BYTES + a * Q_ATOM_BYTES, &P.tq, full, a * 64, m0, h, b);
+        fa_bulk_load(sb + OFF_ROW + s * 2 * BQ * 4, P.nlse2 + rbase, BQ * 4, full);
+        fa_bulk_load(sb + OFF_ROW + s * 2 * BQ * 4 + BQ * 4, P.ndelta + rbase, BQ * 4, full);
       }
     }
   } else if (warp == WARP_MMA) {
     // ================================ MMA issuer A: products 1-2 ===============================
-    // (two issuing warps, so that the waits of one overlap the issue of the other; warp A also
+    // (several issuing warps, so that the waits of one overlap the issue of the other; warp A also
     //  owns the TMEM allocation).  The whole warp runs the loop and one elected lane issues: with
     //  uniform control flow the descriptors live in uniform registers, which makes each
     //  tcgen05.mma cheaper to issue than from a single-lane branch, and the issue rate of this
     //  one thread is what bounds the tensor core here.
     if (npairs_u > 0) {
       const bool leader = fa_elect_one();
-      constexpr fa_u32 IDESC_KK = fa_idesc(DT, 128, 128, 0, 0);  // A, B K-major, N = 128
+      constexpr fa_u32 IDESC_KK = fa_idesc(DT, 128, BQ, 0, 0);  // A, B K-major, N = BQ
       constexpr fa_u32 HI = fa_desc_hi_sw128();
       const fa_u32 loK_k = fa_desc_lo(sb + OFF_K, 16), loV_k = fa_desc_lo(sb + OFF_V, 16);
       bool ok = fa_mbar_wait_all(bar_addr(sb, BAR_KV), 0, abort_flag);
@@ -335,13 +376,17 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
         if (ok && n > 0) ok = fa_mbar_wait_all(bar_addr(sb, BAR_SFREE), (fa_u32)((n - 1) & 1), abort_flag);
         if (!ok) break;
         fa_tc_fence_after();
-        const fa_u32 loQ = fa_desc_lo(sb + OFF_Q + s * ATOM_BYTES, 16), loDO = fa_desc_lo(sb + OFF_DO + s * ATOM_BYTES, 16);
+        const fa_u32 loQ = fa_desc_lo(sb + OFF_Q + s * Q_BYTES, 16), loDO = fa_desc_lo(sb + OFF_DO + s * Q_BYTES, 16);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          if (leader) fa_mma_ss(tmem_u + COL_S, fa_desc_make(loK_k + kk * 2, HI), fa_desc_make(loQ + kk * 2, HI), IDESC_KK, kk > 0);
+          if (leader)
+            fa_mma_ss(tmem_u + COL_S, fa_desc_make(loK_k + kstep_kmajor(kk, ATOM_BYTES), HI),
+                      fa_desc_make(loQ + kstep_kmajor(kk, Q_ATOM_BYTES), HI), IDESC_KK, kk > 0);
 #pragma unroll
         for (int kk = 0; kk < D / 16; ++kk)
-          if (leader) fa_mma_ss(tmem_u + COL_DP, fa_desc_make(loV_k + kk * 2, HI), fa_desc_make(loDO + kk * 2, HI), IDESC_KK, kk > 0);
+          if (leader)
+            fa_mma_ss(tmem_u + COL_DP, fa_desc_make(loV_k + kstep_kmajor(kk, ATOM_BYTES), HI),
+                      fa_desc_make(loDO + kstep_kmajor(kk, Q_ATOM_BYTES), HI), IDESC_KK, kk > 0);
         if (leader) {
           fa_mma_commit(bar_addr(sb, BAR_SFULL));
           fa_mma_commit(bar_addr(sb, BAR_QEMPTY + s));  // first of the two arrivals that free each tile of the stage
@@ -353,7 +398,7 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
     // ================================ MMA issuer B: products 3-4 ===============================
     if (npairs_u > 0) {
       const bool leader = fa_elect_one();
-      constexpr fa_u32 IDESC_TN = fa_idesc(DT, 128, D, 0, 1);    // A K-major (TMEM or smem), B MN-major, N = 64
+      constexpr fa_u32 IDESC_TN = fa_idesc(DT, 128, D, 0, 1);    // A K-major (TMEM or smem), B MN-major, N = D
       constexpr fa_u32 HI = fa_desc_hi_sw128();
       const fa_u32 loDS_k = fa_desc_lo(sb + OFF_DS, 16);
       bool ok = fa_mbar_wait_all(bar_addr(sb, BAR_KV), 0, abort_flag);
@@ -362,19 +407,21 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
         ok = fa_mbar_wait_all(bar_addr(sb, BAR_PREADY), (fa_u32)(n & 1), abort_flag);
         if (!ok) break;
         fa_tc_fence_after();
-        const fa_u32 loQ_mn = fa_desc_lo(sb + OFF_Q + s * ATOM_BYTES, ATOM_BYTES);
-        const fa_u32 loDO_mn = fa_desc_lo(sb + OFF_DO + s * ATOM_BYTES, ATOM_BYTES);
+        // B operands read MN-major: the D columns are 64-element groups Q_ATOM_BYTES apart, a
+        // k-step is 16 q rows = 2048 bytes
+        const fa_u32 loQ_mn = fa_desc_lo(sb + OFF_Q + s * Q_BYTES, Q_ATOM_BYTES);
+        const fa_u32 loDO_mn = fa_desc_lo(sb + OFF_DO + s * Q_BYTES, Q_ATOM_BYTES);
         const fa_u32 acc = n > 0;
-        // 3. dV += P^T dO      (K = 128 q values, 8 steps of 16 rows = 2048 bytes; A from TMEM)
+        // 3. dV += P^T dO      (K = BQ q values; A from TMEM)
 #pragma unroll
-        for (int kk = 0; kk < BT / 16; ++kk)
+        for (int kk = 0; kk < BQ / 16; ++kk)
           if (leader) fa_mma_ts(tmem_u + COL_DV, tmem_u + COL_P + kk * 8, fa_desc_make(loDO_mn + kk * 128, HI), IDESC_TN, acc | (kk > 0));
         if (leader) fa_mma_commit(bar_addr(sb, BAR_DOEMPTY + s));  // second arrival: the dO tile is free
         // 4. dK += dS^T Q     (A = dS^T K-major: k-step kk is 32 bytes into atom kk / 4)
 #pragma unroll
-        for (int kk = 0; kk < BT / 16; ++kk)
+        for (int kk = 0; kk < BQ / 16; ++kk)
           if (leader)
-            fa_mma_ss(tmem_u + COL_DK, fa_desc_make(loDS_k + (kk >> 2) * (ATOM_BYTES >> 4) + (kk & 3) * 2, HI),
+            fa_mma_ss(tmem_u + COL_DK, fa_desc_make(loDS_k + kstep_kmajor(kk, ATOM_BYTES), HI),
                       fa_desc_make(loQ_mn + kk * 128, HI), IDESC_TN, acc | (kk > 0));
         if (leader) {
           fa_mma_commit(bar_addr(sb, BAR_QEMPTY + s));   // second arrival: the Q tile and row scalars are free
@@ -386,10 +433,10 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
   } else if (warp == WARP_MMA_C) {
     // ================================ MMA issuer C: product 5 ==================================
     // (a third issuing warp: what bounds the tensor core in this kernel is how fast one thread
-    //  can issue, so the 32 instructions of a pair are spread over three threads)
+    //  can issue, so the instructions of a pair are spread over three threads)
     if (npairs_u > 0) {
       const bool leader = fa_elect_one();
-      constexpr fa_u32 IDESC_NN = fa_idesc(DT, 128, D, 1, 1);    // A, B MN-major
+      constexpr fa_u32 IDESC_NN = fa_idesc(DT, 128, 64, 1, 1);    // A, B MN-major, M = 128, N = 64
       constexpr fa_u32 HI = fa_desc_hi_sw128();
       const fa_u32 loK_mn = fa_desc_lo(sb + OFF_K, ATOM_BYTES);
       const fa_u32 loDS_mn = fa_desc_lo(sb + OFF_DS, ATOM_BYTES);
@@ -400,10 +447,17 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
         if (ok && n > 0) ok = fa_mbar_wait_all(bar_addr(sb, BAR_DQFREE), (fa_u32)((n - 1) & 1), abort_flag);
         if (!ok) break;
         fa_tc_fence_after();
-        // 5. dQ = dS K        (A = dS^T read MN-major: M chunks of 64 q one atom apart; K = 128 kv rows)
+        // 5. K = 128 kv rows, a k-step is 16 rows = 2048 bytes of either operand.
+        //    D = 64:  dQ = dS K       A = dS^T read MN-major (M = 128 q: two 64-column atoms), B = K (N = 64 d)
+        //    D = 128: dQ^T = K^T dS^T A = K read MN-major (M = 128 d: two atoms), B = dS^T (N = 64 q)
 #pragma unroll
         for (int kk = 0; kk < BT / 16; ++kk)
-          if (leader) fa_mma_ss(tmem_u + COL_DQ, fa_desc_make(loDS_mn + kk * 128, HI), fa_desc_make(loK_mn + kk * 128, HI), IDESC_NN, kk > 0);
+          if (leader) {
+            if (D == 64)
+              fa_mma_ss(tmem_u + COL_DQ, fa_desc_make(loDS_mn + kk * 128, HI), fa_desc_make(loK_mn + kk * 128, HI), IDESC_NN, kk > 0);
+            else
+              fa_mma_ss(tmem_u + COL_DQ, fa_desc_make(loK_mn + kk * 128, HI), fa_desc_make(loDS_mn + kk * 128, HI), IDESC_NN, kk > 0);
+          }
         if (leader) {
           fa_mma_commit(bar_addr(sb, BAR_PFREE));
           fa_mma_commit(bar_addr(sb, BAR_DQFULL));
@@ -413,7 +467,7 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
   } else if (warp < 8) {
     // ================================ compute warps ============================================
     fa_setmaxnreg_inc<REGS_COMPUTE>();
-    const int half = warp >> 2;               // q columns 64*half .. +63 of the pair tile
+    const int half = warp >> 2;               // q columns CW*half .. +CW-1 of the pair tile
     const int lane_base = (warp & 3) * 32;
     const int r = lane_base + lane;           // kv row of this thread
     const int kv = n0 + r;
@@ -424,74 +478,78 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
     for (int n = 0; n < npairs && ok; ++n) {
       const int s = n % NSTAGE;
       const int pr = pairs[n];
-      const int m0 = (pr & 0xffff) * BT, mode = (pr >> 16) & 0xf, gh = hk * G + (pr >> 20) + p.h_off;
+      const int m0 = (pr & 0xffff) * BQ, mode = (pr >> 16) & 0xf, gh = hk * G + (pr >> 20) + p.h_off;
       ok = fa_mbar_wait_warp(bar_addr(sb, BAR_SFULL), (fa_u32)(n & 1), abort_flag);
       if (ok) ok = fa_mbar_wait_warp(bar_addr(sb, BAR_QFULL + s), (fa_u32)((n / NSTAGE) & 1), abort_flag);
       if (!ok) break;
       fa_tc_fence_after();
-      const float* rowp = (const float*)(sm + OFF_ROW + s * 2 * 128 * 4);
-      fa_u32 pp0[16], pp1[16], ds0[16], ds1[16];
-      // The 64 columns of this thread come in four steps of 16 (S^T and dP^T), the loads of a step
-      // in flight while the previous one is computed: few values are live at a time, which leaves
-      // the scheduler registers to overlap the latencies of independent elements (with all 128
+      const float* rowp = (const float*)(sm + OFF_ROW + s * 2 * BQ * 4);
+      fa_u32 pp[CW / 2], ds[CW / 2];
+      // The CW columns of this thread come in steps of 16 (S^T and dP^T), the loads of a step in
+      // flight while the previous one is computed: few values are live at a time, which leaves
+      // the scheduler registers to overlap the latencies of independent elements (with all the
       // values loaded up front this loop ran at 28 clocks per element).
       {
-        const fa_u32 tS = t_row + COL_S + half * 64, tD = t_row + COL_DP + half * 64;
-        const int c0 = half * 64;  // first q column of this thread inside the tile
+        const fa_u32 tS = t_row + COL_S + half * CW, tD = t_row + COL_DP + half * CW;
+        const int c0 = half * CW;  // first q column of this thread inside the tile
         float sA[16], dA[16], sB[16], dB[16];
         fa_u32 p8[8], d8[8];
         fa_tmem_ld16(tS, sA);
         fa_tmem_ld16(tD, dA);
         fa_tmem_wait_ld();
-#define FA_STEP(SC, DC, SN, DN, C, PP, DS, OFF, LAST)                                                      \
+#define FA_STEP(SC, DC, SN, DN, C, LAST)                                                                   \
   if (!(LAST)) {                                                                                           \
     fa_tmem_ld16(tS + (C) + 16, SN);                                                                       \
     fa_tmem_ld16(tD + (C) + 16, DN);                                                                       \
+  } else {                                                                                                 \
+    /* every score of the pair is in registers: the S^T / dP^T columns may be overwritten */              \
+    fa_tc_fence_before();                                                                                  \
+    fa_mbar_arrive(bar_addr(sb, BAR_SFREE));                                                               \
   }                                                                                                        \
   if (row_ok) {                                                                                            \
-    chunk<16>(SC, DC, rowp + c0 + (C), rowp + 128 + c0 + (C), p8, d8, mode, m0 + c0 + (C), kv, gb, gh, p.scale, sc2); \
+    chunk<16>(SC, DC, rowp + c0 + (C), rowp + BQ + c0 + (C), p8, d8, mode, m0 + c0 + (C), kv, gb, gh, p.scale, sc2); \
   } else {                                                                                                 \
     _Pragma("unroll") for (int e = 0; e < 8; ++e) p8[e] = d8[e] = 0u;                                      \
   }                                                                                                        \
   _Pragma("unroll") for (int e = 0; e < 8; ++e) {                                                          \
-    PP[(OFF) + e] = p8[e];                                                                                 \
-    DS[(OFF) + e] = d8[e];                                                                                 \
+    pp[(C) / 2 + e] = p8[e];                                                                               \
+    ds[(C) / 2 + e] = d8[e];                                                                               \
   }                                                                                                        \
   if (!(LAST)) fa_tmem_wait_ld();
-        FA_STEP(sA, dA, sB, dB, 0, pp0, ds0, 0, false)
-        FA_STEP(sB, dB, sA, dA, 16, pp0, ds0, 8, false)
-        FA_STEP(sA, dA, sB, dB, 32, pp1, ds1, 0, false)
-        // every score of the pair is in registers: the S^T / dP^T columns may be overwritten
-        fa_tc_fence_before();
-        fa_mbar_arrive(bar_addr(sb, BAR_SFREE));
-        FA_STEP(sB, dB, sA, dA, 48, pp1, ds1, 8, true)
+        if (CW == 64) {
+          FA_STEP(sA, dA, sB, dB, 0, false)
+          FA_STEP(sB, dB, sA, dA, 16, false)
+          FA_STEP(sA, dA, sB, dB, 32 % CW, false)
+          FA_STEP(sB, dB, sA, dA, 48 % CW, true)
+        } else {
+          FA_STEP(sA, dA, sB, dB, 0, false)
+          FA_STEP(sB, dB, sA, dA, 16, true)
+        }
 #undef FA_STEP
       }
       // pin the packed results here: without this the compiler sinks part of the math below the
       // wait that follows, onto the critical path between two groups of products
 #pragma unroll
-      for (int e = 0; e < 16; ++e) asm volatile("" : "+r"(pp0[e]), "+r"(pp1[e]), "+r"(ds0[e]), "+r"(ds1[e]));
+      for (int e = 0; e < CW / 2; ++e) asm volatile("" : "+r"(pp[e]), "+r"(ds[e]));
       // products 3-5 of the previous pair must be done with P^T and dS^T
       if (n > 0) {
         ok = fa_mbar_wait_warp(bar_addr(sb, BAR_PFREE), (fa_u32)((n - 1) & 1), abort_flag);
         if (!ok) break;
         fa_tc_fence_after();
       }
-      fa_tmem_st16(t_row + COL_P + half * 32, pp0);
-      fa_tmem_st16(t_row + COL_P + half * 32 + 16, pp1);
+#pragma unroll
+      for (int i = 0; i < CW / 32; ++i)
+        fa_tmem_st16(t_row + COL_P + half * (CW / 2) + 16 * i, *(const fa_u32(*)[16])(pp + 16 * i));
       {
-        unsigned char* dsrow = sm + OFF_DS + half * ATOM_BYTES + r * 128;
+        // dS^T row r: this thread's CW columns are CW / 8 sixteen-byte chunks; chunk ck of a 128-byte
+        // atom row goes to position ck ^ (r & 7) (the 128-byte swizzle of the operand layout)
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < CW / 8; ++c) {
+          const int col = half * CW + 8 * c;
+          unsigned char* dsrow = sm + OFF_DS + (col >> 6) * ATOM_BYTES + r * 128;
           uint4 w;
-          w.x = ds0[4 * c]; w.y = ds0[4 * c + 1]; w.z = ds0[4 * c + 2]; w.w = ds0[4 * c + 3];
-          *(uint4*)(dsrow + ((c ^ (r & 7)) * 16)) = w;
-        }
-#pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint4 w;
-          w.x = ds1[4 * c]; w.y = ds1[4 * c + 1]; w.z = ds1[4 * c + 2]; w.w = ds1[4 * c + 3];
-          *(uint4*)(dsrow + (((c + 4) ^ (r & 7)) * 16)) = w;
+          w.x = ds[4 * c]; w.y = ds[4 * c + 1]; w.z = ds[4 * c + 2]; w.w = ds[4 * c + 3];
+          *(uint4*)(dsrow + ((((col & 63) >> 3) ^ (r & 7)) * 16)) = w;
         }
       }
       fa_tmem_wait_st();
@@ -532,9 +590,10 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
   } else if (warp < 12) {
     // ================================ dQ drain warps ===========================================
     const int lane_base = (warp & 3) * 32;
-    const int r = lane_base + lane;  // q row inside the pair tile
+    const int r = lane_base + lane;  // TMEM lane: q row of the pair (D = 64) or head-dim index (D = 128)
     const fa_u32 t_dq = tmem + ((fa_u32)lane_base << 16) + COL_DQ;
     const int dtid = tid - 256;
+    const int n_qtiles = sq_pad / BQ;
     bool ok = true;
     for (int n = 0; n < npairs && ok; ++n) {
       const int pr = pairs[n];
@@ -545,10 +604,10 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
       // barrier of the pair like the others, and all four read the flag behind that barrier.
       if (!ok) misc[3] = 1;
       fa_tc_fence_after();
-      // The 128 x 64 tile leaves in two halves of 32 columns through one 16 KB staging buffer: each
-      // half is one contiguous 16 KB block of the accumulation buffer.  16-byte chunk k of row r
-      // goes to position k ^ (r & 7), which spreads the rows of a warp over the banks.
-      float* gdst = P.dq_acc + (((long long)b * p.Hq + h) * sq_pad + (long long)qt * BT) * D;
+      // The 128 x 64 fp32 tile leaves in two halves of 32 columns through one 16 KB staging buffer:
+      // each half is one contiguous 16 KB block of the accumulation buffer.  16-byte chunk k of
+      // lane r goes to position k ^ (r & 7), which spreads the rows of a warp over the banks.
+      float* gdst = P.dq_acc + (((long long)b * p.Hq + h) * n_qtiles + qt) * (128 * 64);
       unsigned char* strow = sm + OFF_DQ + r * 128;
       float a[32];
       if (ok) {

@@ -66,9 +66,12 @@ def test_causal_alibi_configuration_at_full_size():
     _compare_slice((slice(0, 1), slice(0, 1)), 0, 0, host, dev, dout_h, alibi, causal_mask)
     _compare_slice((slice(7, 8), slice(7, 8)), 7, 7, host, dev, dout_h, alibi, causal_mask)
     out, lse, dq, dk, dv = dev
+    # both sums cancel heavily with a random dO, so the difference is measured against the sums of
+    # absolute values
     a = (dq.double() * q.double()).sum(dim=(2, 3))
     b = (dk.double() * k.double()).sum(dim=(2, 3))
-    assert ((a - b).abs() / (a.abs() + b.abs() + 1.0)).max().item() <= 5e-2
+    den = (dq.double() * q.double()).abs().sum(dim=(2, 3)) + (dk.double() * k.double()).abs().sum(dim=(2, 3))
+    assert ((a - b).abs() / den).max().item() <= 1e-2
     # shard (b 4..7, h 2..5) with global offsets
     sl = (slice(4, 8), slice(2, 6))
     part = _run(fa, q[sl].contiguous(), k[sl].contiguous(), v[sl].contiguous(), dout[sl].contiguous(), alibi,
