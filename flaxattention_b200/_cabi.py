@@ -64,7 +64,7 @@ EXPORTS = [
     "fa_module_set_buffers", "fa_module_destroy", "fa_module_prepare", "fa_compile_count", "fa_fwd", "fa_bwd_workspace_bytes",
     "fa_bwd", "fa_decode_num_splits", "fa_decode_workspace_bytes", "fa_decode",
     "fa_block_mask_workspace_bytes", "fa_block_mask", "fa_decode_static_capacity", "fa_decode_static",
-    "fa_profile_enable", "fa_profile_read",
+    "fa_profile_enable", "fa_profile_read", "fa_decode_packs_heads",
 ]
 
 
@@ -77,6 +77,12 @@ def lib() -> C.CDLL:
         raise FlaxAttnError(
             -3, f"{LIB_PATH} is missing; build it with `python -m flaxattention_b200.csrc.build` "
                 "(the CUDA extension is required, there is no CPU path)")
+    from .csrc.build import is_current
+
+    if not is_current():
+        raise FlaxAttnError(
+            -3, f"{LIB_PATH} was built from other sources than the ones beside it (its launch parameters have to "
+                "match the kernel templates); rebuild it with `python -m flaxattention_b200.csrc.build`")
     L = C.CDLL(LIB_PATH)
     L.fa_last_error.restype = C.c_char_p
     L.fa_module_create.argtypes = [C.c_char_p, C.POINTER(C.c_void_p)]
@@ -97,6 +103,7 @@ def lib() -> C.CDLL:
             C.c_void_p, C.c_size_t, C.c_void_p]
     if hasattr(L, "fa_decode"):
         L.fa_decode_num_splits.argtypes = [C.POINTER(FaAttnParams), C.c_int]
+        L.fa_decode_packs_heads.argtypes = [C.POINTER(FaAttnParams)]
         L.fa_decode_workspace_bytes.restype = C.c_size_t
         L.fa_decode_workspace_bytes.argtypes = [C.POINTER(FaAttnParams), C.c_int]
         L.fa_decode.argtypes = [C.c_void_p, C.POINTER(FaAttnParams), C.c_int, C.c_void_p, C.c_size_t, C.c_void_p]

@@ -98,8 +98,9 @@ def check_status() -> None:
     if w is not None and int(w[0]) != 0:
         bits = int(w[0])
         w[0] = 0
-        raise _cabi.FlaxAttnError(-3, f"a kernel reported status bits {bits:#x} (bit 0: a bounded barrier wait ran out); "
-                                      "the results of that launch are incomplete")
+        raise _cabi.FlaxAttnError(-3, f"a kernel reported status bits {bits:#x} (bit 0: a bounded barrier wait ran out; "
+                                      "bit 1: a launch configuration the kernel refused); the results of that launch "
+                                      "are incomplete")
 
 
 def _tensor(t: torch.Tensor, layout: str) -> _cabi.FaTensor:

@@ -2,6 +2,7 @@
 and checks that every kernel template compiles for sm_100a with a representative mod."""
 from __future__ import annotations
 
+import hashlib
 import os
 import subprocess
 import sys
@@ -14,17 +15,33 @@ NVCC = os.path.join(CUDA_HOME, "bin", "nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 
 
-def _newer(target: str, sources) -> bool:
-    if not os.path.exists(target):
+STAMP = LIB + ".sources"  # hash of the sources the library was built from
+
+
+def sources_hash() -> str:
+    """Hash of everything the host library is compiled from.  The library computes launch
+    parameters (shared-memory sizes, grids, buffer layouts) that have to match the kernel
+    templates it sits beside, so a library built from other sources must not be used."""
+    h = hashlib.sha256()
+    for path in host_sources():
+        with open(path, "rb") as f:
+            h.update(f.read())
+        h.update(b"\0")
+    return h.hexdigest()
+
+
+def is_current() -> bool:
+    if not (os.path.exists(LIB) and os.path.exists(STAMP)):
         return False
-    t = os.path.getmtime(target)
-    return all(os.path.getmtime(s) <= t for s in sources)
+    with open(STAMP) as f:
+        return f.read().strip() == sources_hash()
 
 
 def host_sources():
     srcs = [os.path.join(HERE, "flaxattn.cu"), os.path.join(PKG, "..", "include", "flaxattn.h")]
     kdir = os.path.join(HERE, "kernels")
-    srcs += [os.path.join(kdir, f) for f in sorted(os.listdir(kdir)) if f.endswith(".h")]
+    # the templates count too: the library's launch code mirrors their shared-memory maps
+    srcs += [os.path.join(kdir, f) for f in sorted(os.listdir(kdir)) if f.endswith((".h", ".cuh"))]
     extra = os.path.join(HERE, "flaxattn_static.cu")
     if os.path.exists(extra):
         srcs.append(extra)
@@ -33,7 +50,7 @@ def host_sources():
 
 def build_library(force: bool = False, verbose: bool = False) -> str:
     srcs = host_sources()
-    if not force and _newer(LIB, srcs):
+    if not force and is_current():
         return LIB
     cu = [s for s in srcs if s.endswith(".cu")]
     cmd = [NVCC, *ARCH, "-lineinfo", "-O3", "-std=c++17", "-shared", "-Xcompiler", "-fPIC",
@@ -42,6 +59,8 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
     if verbose:
         cmd.insert(1, "-Xptxas=-v")
     subprocess.run(cmd, check=True, cwd=HERE)
+    with open(STAMP, "w") as f:
+        f.write(sources_hash() + "\n")
     return LIB
 
 

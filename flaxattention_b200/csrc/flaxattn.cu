@@ -831,11 +831,21 @@ int get_bwd_kernel(fa_module* m, int dtype, int D, int Dv, int flags, const BwdC
                           {"FA_WARPS", c.warps}, {"FA_ROUND_SCORES", round_flag(dtype, flags)}}),
                     dq ? "fa_bwd_dq_kernel" : "fa_bwd_dkdv_kernel", dq ? c.smem_dq : c.smem_dkdv, k);
 }
-int get_decode_kernel(fa_module* m, int dtype, int D, int Dv, int flags, const DecCfg& c, Kernel** k) {
+int get_decode_kernel(fa_module* m, int dtype, int D, int Dv, int flags, const DecCfg& c, bool pack, Kernel** k) {
   return get_kernel(m, "fa_decode.cuh",
                     defs({{"FA_DTYPE", dtype}, {"FA_D", D}, {"FA_DV", Dv}, {"FA_BM", c.BM}, {"FA_BN", c.BN},
-                          {"FA_STAGES", c.stages}, {"FA_ROUND_SCORES", round_flag(dtype, flags)}}),
+                          {"FA_STAGES", c.stages}, {"FA_ROUND_SCORES", round_flag(dtype, flags)},
+                          {"FA_PACK_HEADS", pack ? 1 : 0}}),
                     "fa_decode_kernel", c.smem, k);
+}
+// Grouped-query decode: the G query heads of a kv head share one CTA (their G * Sq rows form one
+// tile and K / V are read once) when the rows fit a tile and the kv walk is the same for every
+// head of the group, i.e. there are no tables or the tables are broadcast over the heads.
+bool decode_packs_heads(const fa_attn_params* p) {
+  if (p->Hkv <= 0 || p->Hq % p->Hkv) return false;
+  const int G = p->Hq / p->Hkv;
+  if (G <= 1 || p->dtype == FA_F32 || (long long)G * p->Sq > 64) return false;
+  return p->tables.kv_num_blocks == nullptr || p->tables.mask_H == 1;
 }
 // ---- tcgen05 forward: TMA tensor maps and dispatch -----------------------------------------
 struct alignas(64) FaTensorMapHost {
@@ -1027,7 +1037,7 @@ int fa_module_prepare(fa_module* m, int kind, int dtype, int D, int Dv, int Sq_h
       if (int rc = pick_decode(dtype, D, Dv, Sq_hint, nullptr, c)) return rc;
       if (dtype != FA_F32 && D == 64 && Dv == 64 && Sq_hint >= 33)
         if (int rc = get_fwd_tc_kernel(m, dtype, D, 0, &k, true)) return rc;
-      return get_decode_kernel(m, dtype, D, Dv, 0, c, &k);
+      return get_decode_kernel(m, dtype, D, Dv, 0, c, false, &k);
     }
     case FA_KIND_BLOCKMASK:
       return get_blockmask_kernel(m, &k);
@@ -1182,12 +1192,15 @@ static int fill_waves(long long bh, int cmax, int slots) {
   return best;
 }
 
+int fa_decode_packs_heads(const fa_attn_params* p) { return (p && decode_packs_heads(p)) ? 1 : 0; }
+
 int fa_decode_num_splits(const fa_attn_params* p, int sm_count) {
   if (!p || p->B <= 0 || p->Hq <= 0 || p->Skv <= 0) return 1;
   if (sm_count <= 0) sm_count = 148;
-  const long long bh = (long long)p->B * p->Hq;
+  const bool pack = decode_packs_heads(p);
+  const long long bh = (long long)p->B * (pack ? p->Hkv : p->Hq);
   const int tiles = (p->Skv + 127) / 128;
-  if (tc_decode_eligible(p)) {
+  if (!pack && tc_decode_eligible(p)) {
     // tcgen05 kernel: one CTA per SM, two partial results per CTA, at least eight kv tiles per CTA
     const int cmax = tiles / 8 > 1 ? (tiles / 8 < 64 ? tiles / 8 : 64) : 1;
     return 2 * fill_waves(bh, cmax, sm_count);
@@ -1197,7 +1210,7 @@ int fa_decode_num_splits(const fa_attn_params* p, int sm_count) {
   // extra partial results.
   int per_sm = 2;
   DecCfg c;
-  if (pick_decode(p->dtype, p->D, p->Dv, p->Sq, nullptr, c) == FA_OK) {
+  if (pick_decode(p->dtype, p->D, p->Dv, pack ? p->Sq * (p->Hq / p->Hkv) : p->Sq, nullptr, c) == FA_OK) {
     per_sm = (228 * 1024) / (c.smem + 1024);
     per_sm = per_sm < 1 ? 1 : (per_sm > 4 ? 4 : per_sm);
   }
@@ -1219,10 +1232,11 @@ int fa_decode(fa_module* m, const fa_attn_params* p, int num_splits, void* works
   prof_reset();
   FaParams kp;
   fill_params(p, kp);
-  const bool tc = tc_decode_eligible(p) && num_splits >= 2 && num_splits % 2 == 0;
+  const bool pack = decode_packs_heads(p);
+  const bool tc = !pack && tc_decode_eligible(p) && num_splits >= 2 && num_splits % 2 == 0;
   DecCfg c;
   if (!tc)
-    if (int rc = pick_decode(p->dtype, p->D, p->Dv, p->Sq, &kp.t, c)) return rc;
+    if (int rc = pick_decode(p->dtype, p->D, p->Dv, pack ? p->Sq * (p->Hq / p->Hkv) : p->Sq, &kp.t, c)) return rc;
   const size_t need = fa_decode_workspace_bytes(p, num_splits);
   if (need && (!workspace || workspace_bytes < need)) return fail(FA_EWORKSPACE, "decode workspace too small");
   if (need && ((uintptr_t)workspace & 15)) return fail(FA_EINVAL, "workspace must be 16-byte aligned");
@@ -1237,8 +1251,8 @@ int fa_decode(fa_module* m, const fa_attn_params* p, int num_splits, void* works
     if (int rc = launch_decode_tc(m, p, kp, num_splits, stream)) return rc;
   } else {
     Kernel* k = nullptr;
-    if (int rc = get_decode_kernel(m, p->dtype, p->D, p->Dv, p->flags, c, &k)) return rc;
-    if (int rc = launch(k, dim3(num_splits, p->Hq, p->B), dim3(128), &kp, stream)) return rc;
+    if (int rc = get_decode_kernel(m, p->dtype, p->D, p->Dv, p->flags, c, pack, &k)) return rc;
+    if (int rc = launch(k, dim3(num_splits, pack ? p->Hkv : p->Hq, p->B), dim3(128), &kp, stream)) return rc;
   }
   if (num_splits > 1) {
     const long long n_rows = (long long)p->B * p->Hq * p->Sq;

@@ -11,12 +11,24 @@
 // end; with more than one split the CTA writes un-normalised (O, max, sum) to the workspace
 // and a second kernel combines the splits, with one split it writes O and LSE directly.
 //
+// With grouped-query attention the G query heads of a kv head can share one CTA
+// (FA_PACK_HEADS): its G * Sq query rows form one tile, row r belonging to head r / Sq and
+// query r % Sq, so K and V of the kv head are read once instead of G times.  The mods see the
+// head and query index of each row; the BlockMask walk is the one of the group's first head,
+// which is why the host packs only when the tables do not depend on the head.
+//
 // Compile-time parameters (macros): FA_DTYPE (fp16 / bf16), FA_D, FA_DV, FA_BM (16, 32, 64),
-// FA_BN (kv tile), FA_STAGES.
+// FA_BN (kv tile), FA_STAGES, FA_PACK_HEADS.
 #pragma once
 #include "fa_common.cuh"
 
+#ifndef FA_PACK_HEADS
+#define FA_PACK_HEADS 0
+#endif
+
 namespace fa_dec {
+
+constexpr bool PACK = FA_PACK_HEADS != 0;
 
 constexpr int DT = FA_DTYPE;
 constexpr int D = FA_D;
@@ -51,23 +63,37 @@ extern "C" __global__ void __launch_bounds__(fa_dec::NT) fa_decode_kernel(const 
   extern __shared__ __align__(128) unsigned char smem[];
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int rg = warp % RG, cg = warp / RG;
-  const int split = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
-  const int hk = h / (p.Hq / p.Hkv);
-  const int gb = b + p.b_off, gh = h + p.h_off;
+  // grid: (splits, query heads, batch), or (splits, kv heads, batch) when the heads of a group are packed
+  const int split = blockIdx.x, b = blockIdx.z;
+  const int G = p.Hq / p.Hkv;
+  const int hk = PACK ? (int)blockIdx.y : (int)blockIdx.y / G;
+  const int h0 = PACK ? hk * G : (int)blockIdx.y;  // first query head of this CTA
+  const int R = PACK ? G * p.Sq : p.Sq;            // query rows of this CTA
+  const int gb = b + p.b_off;
 
   const fa_u32 sQ = fa_smem_u32(smem);
   const fa_u32 sK = sQ + Q_BYTES;
   const fa_u32 sV = sK + STAGES * K_BYTES;
 
-  const char* qg = (const char*)p.q.ptr + ((long long)b * p.q.sb + (long long)h * p.q.sh) * ES;
+  const char* qg = (const char*)p.q.ptr + (long long)b * p.q.sb * ES;
   const char* kg = (const char*)p.k.ptr + ((long long)b * p.k.sb + (long long)hk * p.k.sh) * ES;
   const char* vg = (const char*)p.v.ptr + ((long long)b * p.v.sb + (long long)hk * p.v.sh) * ES;
 
-  fa_load_tile<D, ES, NT>(sQ, qg, p.q.ss * ES, BM, p.Sq, tid);
+  {
+    // query tile: row r is query r % Sq of head h0 + r / Sq; rows from R on are zero-filled
+    constexpr int CPR = D * ES / 16;
+    for (int i = tid; i < BM * CPR; i += NT) {
+      const int r = i / CPR, c = i - r * CPR;
+      const bool ok = r < R;
+      const int g = PACK ? r / p.Sq : 0, q = r - g * p.Sq;
+      const char* src = qg + (ok ? ((long long)(h0 + g) * p.q.sh + (long long)q * p.q.ss) * ES + c * 16 : 0);
+      fa_cp_async16(sQ + r * PQ + c * 16, src, ok ? 16 : 0);
+    }
+  }
   fa_cp_commit();
 
   FaWalk walk;
-  walk.init_kv<BN>(p.t, b, h, 0, p.Skv);
+  walk.init_kv<BN>(p.t, b, h0, 0, p.Skv);
   // this split's run of tile slots
   const int per = (walk.total + p.num_splits - 1) / p.num_splits;
   int slot = min(split * per, walk.total);
@@ -144,13 +170,16 @@ extern "C" __global__ void __launch_bounds__(fa_dec::NT) fa_decode_kernel(const 
     const float sc2 = p.scale * FA_LOG2E;
 #pragma unroll
     for (int hh = 0; hh < 2; ++hh) {
-      // rows 8..15 of a row group hold no query when Sq <= 8 (+ 16 rg): nothing to do for them
-      if (rg * 16 + hh * 8 >= p.Sq) {
+      // rows 8..15 of a row group hold no query when there are at most 8 (+ 16 rg) rows: nothing to do for them
+      if (rg * 16 + hh * 8 >= R) {
 #pragma unroll
         for (int j = 0; j < WN / 8; ++j) s[j][hh * 2] = s[j][hh * 2 + 1] = 0.f;
         continue;
       }
-      const int qi = rg * 16 + hh * 8 + (lane >> 2);
+      const int row = rg * 16 + hh * 8 + (lane >> 2);
+      const int g_row = PACK ? row / p.Sq : 0;
+      const int qi = row - g_row * p.Sq;
+      const int gh = h0 + g_row + p.h_off;
       float mx = FA_NEG_INF;
 #pragma unroll
       for (int j = 0; j < WN / 8; ++j) {
@@ -229,10 +258,11 @@ extern "C" __global__ void __launch_bounds__(fa_dec::NT) fa_decode_kernel(const 
     }
   }
   __syncthreads();
-  const int rows = min(p.Sq, BM);
-  const long long bh = (long long)b * p.Hq + h;
+  const int rows = min(R, BM);
   for (int i = tid; i < rows * DV; i += NT) {
     const int r = i / DV, c = i - r * DV;
+    const int g_row = PACK ? r / p.Sq : 0, qr = r - g_row * p.Sq, h = h0 + g_row;
+    const long long bh = (long long)b * p.Hq + h;
     float mstar = FA_NEG_INF;
 #pragma unroll
     for (int g = 0; g < CG; ++g) mstar = fmaxf(mstar, mrg[((long long)g * BM + r) * MRG_PITCH + DV]);
@@ -245,7 +275,7 @@ extern "C" __global__ void __launch_bounds__(fa_dec::NT) fa_decode_kernel(const 
       lstar += w * row[DV + 1];
     }
     if (p.num_splits > 1) {
-      const long long prow = (bh * p.num_splits + split) * p.Sq + r;
+      const long long prow = (bh * p.num_splits + split) * p.Sq + qr;
       p.part_o[prow * DV + c] = acc;
       if (c == 0) {
         p.part_ml[prow * 2] = mstar;
@@ -253,7 +283,7 @@ extern "C" __global__ void __launch_bounds__(fa_dec::NT) fa_decode_kernel(const 
       }
     } else {
       const float inv = lstar > 0.f ? 1.f / lstar : 0.f;
-      char* og = (char*)p.o.ptr + ((long long)b * p.o.sb + (long long)h * p.o.sh + (long long)r * p.o.ss) * ES;
+      char* og = (char*)p.o.ptr + ((long long)b * p.o.sb + (long long)h * p.o.sh + (long long)qr * p.o.ss) * ES;
       const float val = acc * inv;
       if (DT == FA_DT_F16) {
         fa_u16 hv;
@@ -265,7 +295,7 @@ extern "C" __global__ void __launch_bounds__(fa_dec::NT) fa_decode_kernel(const 
         ((fa_u16*)og)[c] = hv;
       }
       if (c == 0 && p.lse != nullptr)
-        p.lse[bh * p.Sq + r] = lstar > 0.f ? (mstar + fa_lg2(lstar)) * FA_LN2 : FA_NEG_INF;
+        p.lse[bh * p.Sq + qr] = lstar > 0.f ? (mstar + fa_lg2(lstar)) * FA_LN2 : FA_NEG_INF;
     }
   }
 }

@@ -327,6 +327,12 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
   using namespace fa_tc;
   const FaParams& p = P.p;
   extern __shared__ unsigned char smem_raw[];
+  // a launch that does not fit the shared-memory map below (a host library built for another
+  // version of this file) is refused before anything is written
+  if (fa_dynamic_smem_size() < (fa_u32)SMEM_BYTES || blockDim.x != NT) {
+    if (threadIdx.x == 0 && p.status != nullptr) atomicOr(p.status, FA_STATUS_BAD_LAUNCH);
+    return;
+  }
   const fa_u32 raw = fa_smem_u32(smem_raw);
   const fa_u32 sb = (raw + 1023u) & ~1023u;  // shared-window address of the aligned base
   unsigned char* sm = smem_raw + (sb - raw);

@@ -11,6 +11,14 @@ struct __align__(64) FaTensorMap {
 
 // status bits a kernel ORs into FaParams::status
 #define FA_STATUS_WAIT_TIMEOUT 1
+#define FA_STATUS_BAD_LAUNCH 2  // launched with less dynamic shared memory or another block size than the kernel is written for
+
+// dynamic shared memory this CTA was launched with
+__device__ __forceinline__ fa_u32 fa_dynamic_smem_size() {
+  fa_u32 v;
+  asm("mov.u32 %0, %%dynamic_smem_size;" : "=r"(v));
+  return v;
+}
 
 // ---- mbarrier --------------------------------------------------------------------------
 __device__ __forceinline__ void fa_mbar_init(fa_u32 bar, fa_u32 count) {

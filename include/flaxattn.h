@@ -87,7 +87,8 @@ typedef struct fa_attn_params {
   float* lse;                 /* [B,Hq,Sq] natural-log logsumexp; fwd/decode: output or NULL; bwd: input */
   fa_block_tables tables;
   int32_t flags;              /* FA_FLAG_* */
-  int32_t* status;            /* optional device word; kernels OR error bits into it (0 = clean) */
+  int32_t* status;            /* optional word the GPU can address; kernels OR error bits into it (0 = clean):
+                                 1 = a bounded barrier wait ran out, 2 = a launch configuration the kernel refused */
 } fa_attn_params;
 
 const char* fa_last_error(void);
@@ -133,7 +134,13 @@ size_t fa_bwd_workspace_bytes(const fa_attn_params* p);
 int fa_bwd(fa_module* m, const fa_attn_params* p, const fa_tensor* dout, const fa_tensor* dq,
            const fa_tensor* dk, const fa_tensor* dv, void* workspace, size_t workspace_bytes, void* stream);
 
-/* Split-KV decode for Sq <= 64.  num_splits <= 0 lets the library choose. */
+/* Split-KV decode for Sq <= 64.  num_splits <= 0 lets the library choose.
+ * Grouped-query attention (Hq = G * Hkv, validated by the reference at
+ * flaxattention/core/attention.py:258-265): when G * Sq <= 64 and the BlockMask tables do not
+ * depend on the head (no tables, or mask_H == 1) the G query heads of a kv head are packed into
+ * one tile, so K and V are read once per kv head; fa_decode_packs_heads tells whether a call
+ * will do that (1) or run one CTA group per query head (0). */
+int fa_decode_packs_heads(const fa_attn_params* p);
 int fa_decode_num_splits(const fa_attn_params* p, int sm_count);
 size_t fa_decode_workspace_bytes(const fa_attn_params* p, int num_splits);
 int fa_decode(fa_module* m, const fa_attn_params* p, int num_splits, void* workspace, size_t workspace_bytes,

@@ -208,3 +208,19 @@ def test_other_buffers_are_bound_as_trailing_arguments():
     assert np.array_equal(np.broadcast_to(got, (1, 3, 4, 4))[0, :, 0, :], bias.numpy())
     gm = modtrace.evaluate(modtrace.trace_mask_mod(mb), None, b, h, q, kv)
     assert np.array_equal(np.broadcast_to(gm, (1, 1, 4, 4))[0, 0], doc.numpy()[:, None] == doc.numpy()[None, :])
+
+
+def test_decode_head_packing_rule():
+    """fa_decode_packs_heads: grouped-query heads are packed when the rows fit one tile and the
+    tables do not depend on the head."""
+    L = _cabi.lib()
+    p = _params(Hq=8, Hkv=2, Sq=4, Skv=4096)
+    assert L.fa_decode_packs_heads(C.byref(p)) == 1
+    assert L.fa_decode_packs_heads(C.byref(_params(Hq=8, Hkv=2, Sq=32, Skv=4096))) == 0   # 4 * 32 rows > 64
+    assert L.fa_decode_packs_heads(C.byref(_params(Hq=4, Hkv=4, Sq=4, Skv=4096))) == 0    # not grouped
+    p.tables.kv_num_blocks, p.tables.kv_indices = 0x2000, 0x3000
+    p.tables.mask_B, p.tables.mask_H = 1, 8
+    assert L.fa_decode_packs_heads(C.byref(p)) == 0                                          # per-head tables
+    p.tables.mask_H = 1
+    assert L.fa_decode_packs_heads(C.byref(p)) == 1
+    assert L.fa_decode_packs_heads(None) == 0

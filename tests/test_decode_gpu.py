@@ -111,3 +111,60 @@ def test_tcgen05_decode_and_general_decode_agree_with_the_oracle(Sq, splits, dt)
         outs.append(out.cpu())
     assert int(status.item()) == 0
     assert max_abs(outs[0], outs[1]) <= (8e-3 if dt == "f16" else 3.2e-2)
+
+
+@pytest.mark.parametrize("Hq,Hkv,Sq,dt", [(8, 2, 1, "f16"), (8, 2, 4, "bf16"), (8, 1, 8, "f16"), (4, 2, 16, "f16"),
+                                          (16, 4, 16, "bf16")])
+def test_grouped_query_decode_packs_the_heads_of_a_group(Hq, Hkv, Sq, dt):
+    """GQA decode with tables that do not depend on the head (built with H = 1): the G query heads
+    of a kv head share one tile and K / V are read once.  ALiBi depends on the head, so every
+    packed row must see its own head index.  Same problem with per-head tables (no packing) and
+    through the forward kernel: all within tolerance of the oracle."""
+    import ctypes as C
+
+    import flaxattention_b200 as fa
+    from flaxattention_b200 import _cabi
+    from flaxattention_b200 import attention as A
+
+    B, Skv, D = 2, 3000, 64
+    s, m = _mods(Hq, Sq, Skv, "offset")
+    q, k, v = qkv(B, Hq, Hkv, Sq, Skv, D, dtype=DTYPES[dt])
+    ref, ref_lse = flax_attention_oracle(q, k, v, s, m)
+    qc, kc, vc = q.cuda(), k.cuda(), v.cuda()
+    outs = {}
+    for name, heads in (("broadcast", 1), ("per_head", Hq)):
+        bm = fa.create_block_mask(m, B, heads, Sq, Skv)
+        call = A._Call(qc, kc, vc, s, m, bm, D ** -0.5, "bhsd", 0, 0, None)
+        packs = _cabi.lib().fa_decode_packs_heads(C.byref(call.params(qc, kc, vc, qc, None)))
+        assert packs == (1 if (name == "broadcast" and (Hq // Hkv) * Sq <= 64) else 0)
+        for splits in (0, 1, 3):
+            opts = {"path": "decode"}
+            if splits:
+                opts["num_splits"] = splits
+            out, lse = fa.flax_attention(qc, kc, vc, score_mod=s, block_mask=bm, enable_gqa=True, return_lse=True,
+                                         kernel_options=opts)
+            torch.cuda.synchronize()
+            assert max_abs(out.cpu(), ref) <= 2e-2, (name, splits)
+            err, same = lse_err(lse.cpu(), ref_lse)
+            assert same and err <= 2e-2 * max(1.0, ref_lse.abs().max().item()), (name, splits)
+            outs[(name, splits)] = out.cpu()
+    assert max_abs(outs[("broadcast", 0)], outs[("per_head", 0)]) <= (4e-3 if dt == "f16" else 3.2e-2)
+    fa.check_status()
+
+
+def test_grouped_query_decode_without_tables_and_sequence_major_layout():
+    """No BlockMask at all (packing applies) and [B, L, H, N] inputs: rows of a packed tile come
+    from different heads, i.e. from addresses a head stride apart."""
+    import flaxattention_b200 as fa
+    from flaxattention_b200.mods import generate_alibi_bias
+
+    B, Hq, Hkv, Sq, Skv, D = 2, 8, 2, 3, 1111, 64
+    alibi = generate_alibi_bias(Hq)
+    q, k, v = qkv(B, Hq, Hkv, Sq, Skv, D, dtype=torch.float16)
+    ref, _ = flax_attention_oracle(q, k, v, alibi, None)
+    o1 = fa.flax_attention(q.cuda(), k.cuda(), v.cuda(), score_mod=alibi, enable_gqa=True)
+    o2 = fa.flax_attention_pallas(q.transpose(1, 2).contiguous().cuda(), k.transpose(1, 2).contiguous().cuda(),
+                                  v.transpose(1, 2).contiguous().cuda(), score_mod=alibi, enable_gqa=True, bhln=False)
+    torch.cuda.synchronize()
+    assert max_abs(o1.cpu(), ref) <= 2e-2
+    assert max_abs(o2.cpu().transpose(1, 2), ref) <= 2e-2
