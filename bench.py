@@ -63,9 +63,13 @@ DT = {"f16": torch.float16, "bf16": torch.bfloat16, "f32": torch.float32}
 MIN_LEG_SECONDS = 0.5
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
-# profiles/ (taken on the B=2 case of the default workload and scaled by 4 to its B=8: the traffic
-# grows with the batch); kernels without a capture are absent
-NCU_TRAFFIC = {"fa_fwd_tc_kernel": 4 * 12.66e6, "fa_bwd_tc_kernel": 4 * 25.49e6}
+# profiles/, per workload and kernel.  The captures were taken on the B=2 case of each workload and are
+# scaled to its full batch (x4 for B=8, x2 for B=4): the traffic grows with the batch.  Workloads and
+# kernels without a capture are absent.
+NCU_TRAFFIC = {
+    "cfg2": {"fa_fwd_tc_kernel": 4 * 12.66e6, "fa_bwd_tc_kernel": 4 * 25.49e6},
+    "cfg4": {"fa_bwd_tc_kernel": 2 * (642.0e6 + 351.9e6)},
+}
 
 # S x S x D products per computed block pair that count as algorithmic work of each kernel: the
 # forward has two, the backward five (S, dP, dV, dK, dQ), however a kernel splits or recomputes them
@@ -277,7 +281,7 @@ def computed_flops_fwd(w, bm):
     return 4.0 * w["D"] * bm.BLOCK_SIZE[0] * bm.BLOCK_SIZE[1] * blocks
 
 
-def measure_workload(bench, w, q, k, v, b_off, h_off, bm, pk, steps, with_kernels=True):
+def measure_workload(bench, w, q, k, v, b_off, h_off, bm, pk, steps, with_kernels=True, name=None):
     """Device-timed forward + backward of one workload with resident inputs: step time, forward
     time, per-kernel times (from the library's event records) and the roofline of the dominant one."""
     from flaxattention_b200 import _cabi
@@ -328,7 +332,7 @@ def measure_workload(bench, w, q, k, v, b_off, h_off, bm, pk, steps, with_kernel
     ach = kernels[dom]["algorithmic_tflops"]
     res["roofline"] = {"bound": "tensor", "kernel": dom, "achieved": ach, "peak": pk["tflops"], "unit": "TFLOP/s",
                        "frac": ach / pk["tflops"], "peak_source": pk["source"] + " (bf16 cuBLAS burst)",
-                       "frac_of_nominal_2250": ach / 2250.0, "traffic": NCU_TRAFFIC.get(dom),
+                       "frac_of_nominal_2250": ach / 2250.0, "traffic": NCU_TRAFFIC.get(name, {}).get(dom),
                        "flops": "S x S x D products of the computed blocks that the kernel owes (2 forward, 5 backward)"}
     t_fwd = res["fwd_ms"]
     res["fwd"] = {"ms": t_fwd, "tflops_dense_equivalent": fl_dense / (t_fwd * 1e-3) / 1e12,
@@ -406,7 +410,8 @@ def main():
 
     # ---- headline: fwd + bwd, inputs resident in HBM -----------------------------------
     sampler = ClockSampler(local_rank) if rank == 0 else None
-    head = measure_workload(bench, w, q, k, v, b_off, 0, bm, pk, args.steps, with_kernels=not args.no_extras)
+    head = measure_workload(bench, w, q, k, v, b_off, 0, bm, pk, args.steps, with_kernels=not args.no_extras,
+                            name=args.workload)
     clocks = sampler.stop() if sampler else None
     ms = bench.max_over_ranks(head["ms_per_step"])
     fl_fwd = flops_fwd(w)
@@ -456,7 +461,7 @@ def main():
                 qq, kk, vv = device_inputs(ww, dev)
                 _, m2 = mods_for(ww)
                 bm2 = fa.create_block_mask(m2, ww["B"], ww["H"], ww["Sq"], ww["Skv"])
-                r = measure_workload(bench, ww, qq, kk, vv, 0, 0, bm2, pk, max(5, args.steps // 4))
+                r = measure_workload(bench, ww, qq, kk, vv, 0, 0, bm2, pk, max(5, args.steps // 4), name=name)
                 r["config"] = {k_: ww[k_] for k_ in ("B", "H", "Sq", "Skv", "D", "dtype", "score", "mask")}
                 line["workloads"][name] = r
                 del qq, kk, vv, bm2
