@@ -224,8 +224,8 @@ def run_reference(args, w, rank, world):
 class Bench:
     """Timing helpers bound to one device and (under torchrun) one process group."""
 
-    def __init__(self, dev, world, steps, warmup):
-        self.dev, self.world, self.steps, self.warmup = dev, world, steps, warmup
+    def __init__(self, dev, world, steps, warmup, leg_seconds=MIN_LEG_SECONDS):
+        self.dev, self.world, self.steps, self.warmup, self.leg_seconds = dev, world, steps, warmup, leg_seconds
         self.flush_buf = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
         self.last_timed_steps = 0
 
@@ -243,10 +243,11 @@ class Bench:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return t.item()
 
-    def timed(self, fn, steps=None, warmup=None, min_seconds=MIN_LEG_SECONDS, sync=True):
+    def timed(self, fn, steps=None, warmup=None, min_seconds=None, sync=True):
         """Mean milliseconds per step of fn: `steps` steps, then further blocks of `steps` until the
         leg has lasted `min_seconds`.  L2 is flushed before every step, outside the events."""
         steps = self.steps if steps is None else steps
+        min_seconds = self.leg_seconds if min_seconds is None else min_seconds
         for _ in range(self.warmup if warmup is None else warmup):
             fn()
         if sync:
@@ -369,6 +370,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
     ap.add_argument("--no-extras", action="store_true", help="skip forward-only, decode, per-kernel and CPU legs")
+    ap.add_argument("--leg-seconds", type=float, default=MIN_LEG_SECONDS,
+                    help="minimum duration of a timed leg (0: exactly --steps steps, e.g. for a profiler's launch list)")
     ap.add_argument("--profile", default=None, choices=["fwd", "bwd", "decode", "decode64"],
                     help="small case for a profiler: a few launches of one kernel family, no JSON line")
     args = ap.parse_args()
@@ -397,7 +400,7 @@ def main():
     if world > 1:
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=dev)
-    bench = Bench(dev, world, args.steps, args.warmup)
+    bench = Bench(dev, world, args.steps, args.warmup, args.leg_seconds)
     pk = peaks()
 
     score, mask = mods_for(w)
@@ -439,7 +442,7 @@ def main():
                    "score_mod": w["score"], "mask": w["mask"], "global_batch": w["B"] * world,
                    "parallelism": f"batch x heads shards, {world} rank(s), no collective",
                    "l2": "flushed between timed steps (256 MiB write)", "flops": "3.5 * 4*B*H*Sq*Skv*D per step",
-                   "leg": f"each timed leg repeats its K steps until it has run for {MIN_LEG_SECONDS} s"},
+                   "leg": f"each timed leg repeats its K steps until it has run for {args.leg_seconds} s"},
         "e2e": e2e, "gpu_launches": launches * head["timed_steps"], "clocks": clocks,
     }
     for key in ("kernels", "roofline", "fwd"):
