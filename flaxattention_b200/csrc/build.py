@@ -64,5 +64,20 @@ def build_library(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+def build_ffi_shim() -> str:
+    """Builds libflaxattn_ffi.so (the jax.ffi handlers of ffi_shim.cc).  Needs the XLA FFI headers
+    that ship with jaxlib; raises where JAX is not installed."""
+    import jax.ffi  # noqa: F401
+
+    out = os.path.join(PKG, "libflaxattn_ffi.so")
+    cmd = ["g++", "-O2", "-std=c++17", "-shared", "-fPIC", os.path.join(HERE, "ffi_shim.cc"),
+           "-I" + os.path.join(PKG, "..", "include"), "-I" + jax.ffi.include_dir(), "-I" + os.path.join(CUDA_HOME, "include"),
+           "-L" + PKG, "-l:libflaxattn.so", "-Wl,-rpath," + PKG, "-o", out]
+    subprocess.run(cmd, check=True, cwd=HERE)
+    return out
+
+
 if __name__ == "__main__":
     print(build_library(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    if "--ffi" in sys.argv:
+        print(build_ffi_shim())

@@ -1410,6 +1410,24 @@ class ModSet:
         self.key = hashlib.sha256(self.source.encode()).hexdigest()
 
 
+def _trace_any(fn: Callable, kind: str, bufs: List[object]) -> TracedMod:
+    """Symbolic call first; a mod written with jax.numpy rejects the symbols and is traced through
+    its jaxpr instead (jax_frontend), when JAX is installed."""
+    try:
+        return trace_score_mod(fn, bufs) if kind == "score" else trace_mask_mod(fn, bufs)
+    except Exception as first:
+        try:
+            import jax  # noqa: F401
+        except ImportError:
+            raise first from None
+        from .jax_frontend import trace_with_jax
+
+        try:
+            return trace_with_jax(fn, kind)
+        except Exception:
+            raise first from None
+
+
 _MODSET_CACHE: Dict[Tuple[Optional[int], Optional[int]], Tuple[object, object, ModSet]] = {}
 
 
@@ -1422,8 +1440,8 @@ def lower_mods(score_mod: Optional[Callable], mask_mod: Optional[Callable]) -> M
     if hit is not None and hit[0] is score_mod and hit[1] is mask_mod:
         return hit[2]
     bufs: List[object] = []
-    s = trace_score_mod(score_mod, bufs) if score_mod is not None else None
-    m = trace_mask_mod(mask_mod, bufs) if mask_mod is not None else None
+    s = _trace_any(score_mod, "score", bufs) if score_mod is not None else None
+    m = _trace_any(mask_mod, "mask", bufs) if mask_mod is not None else None
     ms = ModSet(s, m, bufs)
     if len(_MODSET_CACHE) > 4096:
         _MODSET_CACHE.clear()

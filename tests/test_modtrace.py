@@ -195,3 +195,92 @@ def test_captured_buffers_trace_evaluate_and_lower():
         mt.lower_mods(None, lambda b, h, q, kv: torch.zeros(3, 3)[q] > 0)
     with pytest.raises(TypeError, match="dtype"):
         mt.lower_mods(None, lambda b, h, q, kv: torch.zeros(3, dtype=torch.float16)[q] > 0)
+
+
+def test_jaxpr_replay_builds_the_same_graph_as_the_tracer():
+    """The jaxpr front end (for mods written with jax.numpy) replays a flat list of primitive
+    applications on the tracer's symbols.  JAX is not needed to check the replay itself: the list
+    below is what jax.make_jaxpr gives for the reference's ALiBi bias
+    (score + (q - kv) * exp2(-(h + 1) * 8 / H), flaxattention/mods/alibi.py:15-18) and for a causal
+    sliding window, written out by hand with stand-in equation objects."""
+    from types import SimpleNamespace as NS
+
+    from flaxattention_b200 import jax_frontend as jf
+
+    class Var:
+        pass
+
+    def lit(v):
+        return NS(val=v)
+
+    def eqn(name, ins, outs, **params):
+        return NS(primitive=NS(name=name), invars=ins, outvars=outs, params=params)
+
+    s_, b_, h_, q_, kv_ = (Var() for _ in range(5))
+    t = [Var() for _ in range(8)]
+    alibi_eqns = [
+        eqn("add", [h_, lit(1)], [t[0]]),
+        eqn("convert_element_type", [t[0]], [t[1]], new_dtype=np.float32, weak_type=False),
+        eqn("mul", [t[1], lit(-1.0)], [t[2]]),                       # -(h + 1) * 8 / 8
+        eqn("pjit", [t[2]], [t[3]], jaxpr=NS(jaxpr=NS(constvars=[], invars=[t[2]], outvars=[t[6]],
+                                                      eqns=[eqn("exp2", [t[2]], [t[6]])]), consts=[])),
+        eqn("sub", [q_, kv_], [t[4]]),
+        eqn("convert_element_type", [t[4]], [t[5]], new_dtype=np.float32, weak_type=False),
+        eqn("mul", [t[5], t[3]], [t[7]]),
+    ]
+    out = Var()
+    alibi_eqns.append(eqn("add", [s_, t[7]], [out]))
+    jaxpr = NS(constvars=[], invars=[s_, b_, h_, q_, kv_], outvars=[out], eqns=alibi_eqns)
+
+    def run():
+        leaves = modtrace._leaf_syms()
+        (res,) = jf._run_jaxpr(jaxpr, [], list(leaves))
+        return modtrace.cast(modtrace._lift(res), modtrace.F32)
+
+    tm = modtrace._traced(None, run, "score")
+    s, b, h, q, kv = _grid(H=8)
+    got = modtrace.evaluate(tm, s, b, h, q, kv)
+    want = np.asarray(generate_alibi_bias(8)(s, b, h, q, kv), dtype=np.float32)
+    np.testing.assert_allclose(np.broadcast_to(got, want.shape), want, rtol=2e-6, atol=2e-6)
+    assert modtrace.affine_parts(tm) is not None  # still recognised as A * score + B
+
+    # mask: (q >= kv) & (q - kv <= 5), with lax's select_n / integer rem / trunc-div conventions exercised
+    m = [Var() for _ in range(6)]
+    mout = Var()
+    mask_eqns = [eqn("ge", [q_, kv_], [m[0]]), eqn("sub", [q_, kv_], [m[1]]), eqn("le", [m[1], lit(5)], [m[2]]),
+                 eqn("and", [m[0], m[2]], [m[3]]), eqn("rem", [m[1], lit(-3)], [m[4]]), eqn("eq", [m[4], lit(-7)], [m[5]]),
+                 eqn("select_n", [m[5], m[3], lit(False)], [mout])]
+    mj = NS(constvars=[], invars=[b_, h_, q_, kv_], outvars=[mout], eqns=mask_eqns)
+
+    def run_mask():
+        _, bb, hh, qq, kk = modtrace._leaf_syms()
+        (res,) = jf._run_jaxpr(mj, [], [bb, hh, qq, kk])
+        return modtrace.cast(modtrace._lift(res), modtrace.B1)
+
+    tmask = modtrace._traced(None, run_mask, "mask")
+    gm = np.broadcast_to(modtrace.evaluate(tmask, None, b, h, q, kv), s.shape)
+    wm = np.broadcast_to(np.asarray(generate_sliding_window(5)(b, h, q, kv)).astype(bool), s.shape)
+    assert np.array_equal(gm, wm)
+    # C remainder takes the sign of the dividend (numpy's fmod), truncating division rounds to zero
+    def run_rem():
+        _, bb, hh, qq, kk = modtrace._leaf_syms()
+        return modtrace.cast(modtrace._lift(jf._c_rem(qq - 9, 4) * 100 + jf._trunc_div(qq - 9, 4)), modtrace.F32)
+
+    got = modtrace.evaluate(modtrace._traced(None, run_rem, "score"), s, b, h, q, kv)
+    qv = (q - 9).astype(np.int64)
+    want = np.fmod(qv, 4) * 100 + np.trunc(qv / 4).astype(np.int64)
+    assert np.array_equal(np.broadcast_to(got, s.shape), np.broadcast_to(want, s.shape).astype(np.float32))
+
+
+def test_jnp_mods_go_through_the_jaxpr_front_end():
+    jax = pytest.importorskip("jax")
+    import jax.numpy as jnp
+
+    def alibi(score, b, h, q_idx, kv_idx):
+        return score + (q_idx - kv_idx) * jnp.exp2(-((h + 1) * 8.0 / 8))
+
+    tm = modtrace.lower_mods(alibi, None).score
+    s, b, h, q, kv = _grid(H=8)
+    got = modtrace.evaluate(tm, s, b, h, q, kv)
+    want = np.asarray(generate_alibi_bias(8)(s, b, h, q, kv), dtype=np.float32)
+    np.testing.assert_allclose(np.broadcast_to(got, want.shape), want, rtol=2e-6, atol=2e-6)
