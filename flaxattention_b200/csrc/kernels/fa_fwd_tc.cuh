@@ -12,13 +12,14 @@
 // past both.  Warp roles (12 warps = 3 warpgroups):
 //   warps 0-3  softmax warpgroup of query tile 0      warps 4-7  of query tile 1
 //   warp 8     TMA producer (one lane)
-//   warp 9     MMA issuer (one lane); also allocates / frees TMEM.  With D = 64 it issues the S
-//              products only and warp 10 the PV products; warp 11 is idle
+//   warps 9-10 MMA issuers (one lane each); warp 9 also allocates / frees TMEM.  With D = 64 warp 9
+//              issues the S products and warp 10 the PV products; with D = 128 warp 9 issues both
+//              products of query tile 0 and warp 10 those of tile 1; warp 11 is idle
 // Registers are moved from the third warpgroup to the two softmax warpgroups (setmaxnreg),
 // which hold a whole 128-column score row per thread.
 // The S columns of a tile are released as soon as its scores are in registers, so with D = 64
 // S of step j+1 is computed while the softmax of step j runs; with D = 128 (P over the S
-// columns) the issue order per kv step j is  PV0(j), S0(j+1), PV1(j), S1(j+1).
+// columns) the products of a tile form the chain  PV(j), S(j+1), PV(j+1) ...
 // The running maximum is only raised when it grew by more than 2^8 (the stale maximum is
 // exact as long as it is used consistently), so rescaling O in TMEM is rare.
 //
@@ -359,9 +360,10 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
     fa_mbar_init(bar_addr(sb, BAR_Q), 1);
     for (int s = 0; s < NSTAGE; ++s) {
       fa_mbar_init(bar_addr(sb, BAR_KFULL + s), 1);
-      fa_mbar_init(bar_addr(sb, BAR_KEMPTY + s), 1);
+      // with D = 128 each of the two issuing warps releases a stage once
+      fa_mbar_init(bar_addr(sb, BAR_KEMPTY + s), SEP_P ? 1 : 2);
       fa_mbar_init(bar_addr(sb, BAR_VFULL + s), 1);
-      fa_mbar_init(bar_addr(sb, BAR_VEMPTY + s), 1);
+      fa_mbar_init(bar_addr(sb, BAR_VEMPTY + s), SEP_P ? 1 : 2);
     }
     for (int i = 0; i < 2; ++i) {
       fa_mbar_init(bar_addr(sb, BAR_S + i), 1);
@@ -552,18 +554,24 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
         }
       }
     }
-  } else if (warp == WARP_MMA) {
-    // ================================ MMA issuer =========================================
+  } else if (!SEP_P && (warp == WARP_MMA || warp == WARP_MMA_B)) {
+    // ============ two MMA issuers (D = 128): warp A issues both products of query tile 0, warp B of tile 1 ====
+    // P overwrites the S columns here, so the products of one tile form a chain  PV_i(j), S_i(j+1),
+    // PV_i(j+1) ...; the chains of the two tiles only share the K / V stages.  Issuing the sixteen
+    // instructions of a step's two products takes one thread about as long as the tensor core needs
+    // to run them, so each chain gets its own issuing thread; a K / V stage is released by one
+    // arrival from each.
     if (lane == 0) {
+      const int i = warp == WARP_MMA ? 0 : 1;
       constexpr fa_u32 IDESC_S = fa_idesc(DT, BM, BN, 0, 0);
       constexpr fa_u32 IDESC_O = fa_idesc(DT, BM, D, 0, 1);
       bool ok = nsteps == 0 || fa_mbar_wait(bar_addr(sb, BAR_Q), 0, abort_flag);
-      fa_u32 cnt[2] = {0, 0};  // PV products issued so far per query tile
+      fa_u32 cnt = 0;  // PV products of this tile issued so far
       // Descriptors: constant high word; the low word (start address and MN-chunk distance in
       // 16-byte units) is stepped with one add per k-step.
       constexpr fa_u32 HI = fa_desc_hi_sw128();
       // S_i = Q_i K^T for step j into TMEM columns COL_S + 128 i
-      auto issue_s = [&](int i, int j) {
+      auto issue_s = [&](int j) {
         const int s = j % NSTAGE;
         const fa_u32 loQ = fa_desc_lo(sb + i * ATOMS * ATOM_BYTES, 16);
         const fa_u32 loK = fa_desc_lo(sb + OFF_K + s * KV_STAGE, 16);
@@ -575,7 +583,7 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
         fa_mma_commit(bar_addr(sb, BAR_S + i));
       };
       // O_i += P_i V for step j (P_i: 16-bit, in the first 64 columns of S_i)
-      auto issue_pv = [&](int i, int j, bool first) {
+      auto issue_pv = [&](int j, bool first) {
         const int s = j % NSTAGE;
         const fa_u32 loV = fa_desc_lo(sb + OFF_V + s * KV_STAGE, ATOM_BYTES);
         const fa_u32 acc = !first;
@@ -588,9 +596,8 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
         ok = fa_mbar_wait(bar_addr(sb, BAR_KFULL + 0), 0, abort_flag);
         if (ok) {
           fa_tc_fence_after();
-          for (int i = 0; i < 2; ++i)
-            if (sched_mode[i]) issue_s(i, 0);
-          fa_mma_commit(bar_addr(sb, BAR_KEMPTY + 0));
+          if (sched_mode[i]) issue_s(0);
+          fa_mma_commit(bar_addr(sb, BAR_KEMPTY + 0));  // (a commit with nothing outstanding arrives at once)
         }
       }
       for (int j = 0; j < nsteps && ok; ++j) {
@@ -599,28 +606,29 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
         const bool more = j + 1 < nsteps;
         const int s1 = (j + 1) % NSTAGE;
         const fa_u32 ph1 = (fa_u32)(((j + 1) / NSTAGE) & 1);
-        bool k_ready = false;
+        // Every step waits for its stage to be full before it releases it, with or without a
+        // product of this tile: the load of a stage follows both releases of its previous use, so a
+        // warp whose tile skips several steps cannot release a stage twice before the other warp
+        // has released it once.
         ok = fa_mbar_wait(bar_addr(sb, BAR_VFULL + s), ph, abort_flag);
-        for (int i = 0; i < 2 && ok; ++i) {
-          if (sched_mode[2 * j + i]) {
-            ok = fa_mbar_wait(bar_addr(sb, BAR_P + i), cnt[i] & 1u, abort_flag);
-            if (!ok) break;
-            fa_tc_fence_after();
-            issue_pv(i, j, cnt[i] == 0);
-            ++cnt[i];
-          }
-          if (i == 1) fa_mma_commit(bar_addr(sb, BAR_VEMPTY + s));
+        if (!ok) break;
+        if (sched_mode[2 * j + i]) {
+          ok = fa_mbar_wait(bar_addr(sb, BAR_P + i), cnt & 1u, abort_flag);
+          if (!ok) break;
+          fa_tc_fence_after();
+          issue_pv(j, cnt == 0);
+          ++cnt;
+        }
+        fa_mma_commit(bar_addr(sb, BAR_VEMPTY + s));
+        if (more) {
+          ok = fa_mbar_wait(bar_addr(sb, BAR_KFULL + s1), ph1, abort_flag);
+          if (!ok) break;
           // S of the next step overwrites the columns P was read from: it follows the PV product
-          if (more && sched_mode[2 * (j + 1) + i]) {
-            if (!k_ready) {
-              ok = fa_mbar_wait(bar_addr(sb, BAR_KFULL + s1), ph1, abort_flag);
-              if (!ok) break;
-              fa_tc_fence_after();
-              k_ready = true;
-            }
-            issue_s(i, j + 1);
+          if (sched_mode[2 * (j + 1) + i]) {
+            fa_tc_fence_after();
+            issue_s(j + 1);
           }
-          if (i == 1 && more) fa_mma_commit(bar_addr(sb, BAR_KEMPTY + s1));
+          fa_mma_commit(bar_addr(sb, BAR_KEMPTY + s1));
         }
       }
     }
