@@ -312,21 +312,21 @@ def measure_workload(bench, w, q, k, v, b_off, h_off, bm, pk, steps, with_kernel
             recs = _cabi.profile_read()
             A._backward(call, q, k, v, out, lse, dout)
             recs += _cabi.profile_read()
-            for name, ms in recs:
-                acc[name] = acc.get(name, 0.0) + ms
+            for kname, ms in recs:
+                acc[kname] = acc.get(kname, 0.0) + ms
     finally:
         _cabi.profile_enable(False)
     shard = dict(w, B=q.shape[0], H=q.shape[1])
     fl_dense = flops_fwd(shard)
     fl_comp = computed_flops_fwd(shard, bm)
     kernels = {}
-    for name, ms in acc.items():
+    for kname, ms in acc.items():
         ms /= n
         d = {"ms": ms}
-        if name in PRODUCTS:
-            d["algorithmic_tflops"] = PRODUCTS[name] * (fl_comp / 2.0) / (ms * 1e-3) / 1e12
+        if kname in PRODUCTS:
+            d["algorithmic_tflops"] = PRODUCTS[kname] * (fl_comp / 2.0) / (ms * 1e-3) / 1e12
             d["frac_of_measured_peak"] = d["algorithmic_tflops"] / pk["tflops"]
-        kernels[name] = d
+        kernels[kname] = d
     res["kernels"] = kernels
     res["launches_per_step"] = len(acc)
     dom = max((nm for nm in kernels if nm in PRODUCTS), key=lambda nm: kernels[nm]["ms"])
