@@ -706,7 +706,10 @@ __global__ void fa_dq_convert_t_kernel(const float* __restrict__ acc, FaTensor d
   }
 }
 
-// Combines the per-split partial results of the decode kernel: one warp per output row.
+// Combines the per-split partial results of the decode kernels: one warp per output row.  Lane s
+// takes the (max, sum) pair of split s and its weight 2^(m_s - m*), 32 splits at a time; the
+// weights then go round by shuffle while every lane accumulates its output columns, each read of
+// a partial row being one contiguous run of floats.
 template <int DT>
 __global__ void fa_decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          FaTensor o, float* __restrict__ lse, int Hq, int Sq, int Dv, int ns,
@@ -717,27 +720,45 @@ __global__ void fa_decode_combine_kernel(const float* __restrict__ part_o, const
   const long long bh = row / Sq;
   const int q = (int)(row - bh * Sq);
   const int b = (int)(bh / Hq), h = (int)(bh - (long long)b * Hq);
+  auto prow = [&](int s) -> long long { return (bh * ns + s) * Sq + q; };
   float mstar = -INFINITY;
-  for (int s = 0; s < ns; ++s) mstar = fmaxf(mstar, part_ml[((bh * ns + s) * Sq + q) * 2]);
+  for (int s0 = 0; s0 < ns; s0 += 32)
+    if (s0 + lane < ns) mstar = fmaxf(mstar, part_ml[prow(s0 + lane) * 2]);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) mstar = fmaxf(mstar, __shfl_xor_sync(0xffffffffu, mstar, off));
+  constexpr int MAXC = 8;  // output columns per lane: head dims up to 256
+  float acc[MAXC];
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c) acc[c] = 0.f;
   float lstar = 0.f;
-  for (int s = 0; s < ns; ++s) {
-    const float m = part_ml[((bh * ns + s) * Sq + q) * 2];
-    const float w = m == -INFINITY ? 0.f : exp2f(m - mstar);
-    lstar += w * part_ml[((bh * ns + s) * Sq + q) * 2 + 1];
-  }
-  const float inv = lstar > 0.f ? 1.f / lstar : 0.f;
-  constexpr int ES = 2;
-  char* og = (char*)o.ptr + ((long long)b * o.sb + (long long)h * o.sh + (long long)q * o.ss) * ES;
-  for (int c = lane; c < Dv; c += 32) {
-    float acc = 0.f;
-    for (int s = 0; s < ns; ++s) {
-      const float m = part_ml[((bh * ns + s) * Sq + q) * 2];
-      const float w = m == -INFINITY ? 0.f : exp2f(m - mstar);
-      acc += w * part_o[((bh * ns + s) * Sq + q) * Dv + c];
+  for (int s0 = 0; s0 < ns; s0 += 32) {
+    float w = 0.f;
+    if (s0 + lane < ns) {
+      const float2 ml = *(const float2*)(part_ml + prow(s0 + lane) * 2);
+      w = ml.x == -INFINITY ? 0.f : exp2f(ml.x - mstar);
+      lstar += w * ml.y;
     }
-    acc *= inv;
-    if (DT == FA_F16) ((__half*)og)[c] = __float2half_rn(acc);
-    else ((__nv_bfloat16*)og)[c] = __float2bfloat16_rn(acc);
+    const int cnt = ns - s0 < 32 ? ns - s0 : 32;
+    for (int t = 0; t < cnt; ++t) {
+      const float wt = __shfl_sync(0xffffffffu, w, t);
+      if (wt == 0.f) continue;
+      const float* src = part_o + prow(s0 + t) * Dv;
+#pragma unroll
+      for (int c = 0; c < MAXC; ++c)
+        if (c * 32 + lane < Dv) acc[c] += wt * src[c * 32 + lane];
+    }
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) lstar += __shfl_xor_sync(0xffffffffu, lstar, off);
+  const float inv = lstar > 0.f ? 1.f / lstar : 0.f;
+  char* og = (char*)o.ptr + ((long long)b * o.sb + (long long)h * o.sh + (long long)q * o.ss) * 2;
+#pragma unroll
+  for (int c = 0; c < MAXC; ++c) {
+    const int col = c * 32 + lane;
+    if (col < Dv) {
+      if (DT == FA_F16) ((__half*)og)[col] = __float2half_rn(acc[c] * inv);
+      else ((__nv_bfloat16*)og)[col] = __float2bfloat16_rn(acc[c] * inv);
+    }
   }
   if (lane == 0 && lse != nullptr) lse[row] = lstar > 0.f ? (mstar + log2f(lstar)) * 0.6931471805599453f : -INFINITY;
 }
@@ -911,21 +932,21 @@ int get_fwd_tc_kernel(fa_module* m, int dtype, int D, int flags, Kernel** k, boo
   // must match the shared-memory map of fa_fwd_tc.cuh (fa_tc::SMEM_BYTES)
   const int atoms = D / 64, nstage = decode ? 5 : (D == 64 ? 3 : 2);
   const int smem = 2 * atoms * 16384 + 2 * nstage * atoms * 16384 + (1 + 4 * nstage + 8) * 8 + 16 + 256 * 2 + 256 * 2 +
-                   2 * 256 + 1024;
+                   2 * 256 + (256 / 32) * 4 + 1024;
   std::string d = defs({{"FA_DTYPE", dtype}, {"FA_D", D}, {"FA_ROUND_SCORES", round_flag(dtype, flags)}, {"FA_TC_DECODE", decode ? 1 : 0}});
   return get_kernel(m, "fa_fwd_tc.cuh", d, "fa_fwd_tc_kernel", smem, k);
 }
 
 // Shapes the split-KV variant of the tcgen05 kernel covers (`num_splits` partial results per row,
-// two per CTA); everything else runs on the general decode kernel.
+// four per CTA: two warpgroups x two column halves); everything else runs on the general decode kernel.
 bool tc_decode_eligible(const fa_attn_params* p) {
   if (p->flags & FA_FLAG_GENERAL_KERNELS) return false;
   if (p->dtype == FA_F32) return false;
   if (p->D != 64 || p->Dv != 64) return false;
-  // The kernel gives every query row a thread and pads the tile to 128 rows, so its softmax work
-  // per kv tile does not shrink with Sq: measured against the general decode kernel it wins from
-  // 33 rows up (0.46 ms against 0.55 ms at 40-64 rows) and loses below (0.43 against 0.35 at 17-32).
-  if (p->Sq < 33 || p->Sq > 64 || p->Skv < 1024 || p->Skv > 32768) return false;
+  // The kernel gives every query row two threads (64 kv columns of a tile each), whatever Sq is:
+  // measured on B32 H8 Skv16384 against the general decode kernel it takes 0.23 ms at 64 rows
+  // (general: 0.55) and wins from 17 rows up (general: 0.36 at 32 rows, 0.22 at 16).
+  if (p->Sq < 17 || p->Sq > 64 || p->Skv < 1024 || p->Skv > 32768) return false;
   if (!(p->scale > 0.f)) return false;
   const fa_block_tables& t = p->tables;
   if (t.kv_num_blocks) {
@@ -939,10 +960,10 @@ int launch_decode_tc(fa_module* m, const fa_attn_params* p, const FaParams& kp, 
   if (int rc = get_fwd_tc_kernel(m, p->dtype, p->D, p->flags, &k, true)) return rc;
   FaTcParamsHost tp;
   tp.p = kp;
-  if (int rc = make_map(&tp.tq, p->dtype, p->q, p->D, p->Sq, p->Hq, p->B)) return rc;
+  if (int rc = make_map(&tp.tq, p->dtype, p->q, p->D, p->Sq, p->Hq, p->B, 64)) return rc;  // the queries go into a tile twice
   if (int rc = make_map(&tp.tk, p->dtype, p->k, p->D, p->Skv, p->Hkv, p->B)) return rc;
   if (int rc = make_map(&tp.tv, p->dtype, p->v, p->Dv, p->Skv, p->Hkv, p->B)) return rc;
-  return launch(k, dim3(num_splits / 2, p->Hq, p->B), dim3(384), &tp, stream);
+  return launch(k, dim3(num_splits / 4, p->Hq, p->B), dim3(384), &tp, stream);
 }
 
 int launch_fwd_tc(fa_module* m, const fa_attn_params* p, const FaParams& kp, void* stream) {
@@ -1035,7 +1056,7 @@ int fa_module_prepare(fa_module* m, int kind, int dtype, int D, int Dv, int Sq_h
     case FA_KIND_DECODE: {
       DecCfg c;
       if (int rc = pick_decode(dtype, D, Dv, Sq_hint, nullptr, c)) return rc;
-      if (dtype != FA_F32 && D == 64 && Dv == 64 && Sq_hint >= 33)
+      if (dtype != FA_F32 && D == 64 && Dv == 64 && Sq_hint >= 17)
         if (int rc = get_fwd_tc_kernel(m, dtype, D, 0, &k, true)) return rc;
       return get_decode_kernel(m, dtype, D, Dv, 0, c, false, &k);
     }
@@ -1201,9 +1222,9 @@ int fa_decode_num_splits(const fa_attn_params* p, int sm_count) {
   const long long bh = (long long)p->B * (pack ? p->Hkv : p->Hq);
   const int tiles = (p->Skv + 127) / 128;
   if (!pack && tc_decode_eligible(p)) {
-    // tcgen05 kernel: one CTA per SM, two partial results per CTA, at least eight kv tiles per CTA
+    // tcgen05 kernel: one CTA per SM, four partial results per CTA, at least eight kv tiles per CTA
     const int cmax = tiles / 8 > 1 ? (tiles / 8 < 64 ? tiles / 8 : 64) : 1;
-    return 2 * fill_waves(bh, cmax, sm_count);
+    return 4 * fill_waves(bh, cmax, sm_count);
   }
   // general kernel: as many CTAs per SM as its shared memory allows (at most four by registers),
   // at least four kv tiles per CTA.  A grid that ends in a part-filled wave costs more than a few
@@ -1233,7 +1254,7 @@ int fa_decode(fa_module* m, const fa_attn_params* p, int num_splits, void* works
   FaParams kp;
   fill_params(p, kp);
   const bool pack = decode_packs_heads(p);
-  const bool tc = !pack && tc_decode_eligible(p) && num_splits >= 2 && num_splits % 2 == 0;
+  const bool tc = !pack && tc_decode_eligible(p) && num_splits >= 4 && num_splits % 4 == 0;
   DecCfg c;
   if (!tc)
     if (int rc = pick_decode(p->dtype, p->D, p->Dv, pack ? p->Sq * (p->Hq / p->Hkv) : p->Sq, &kp.t, c)) return rc;
@@ -1247,7 +1268,7 @@ int fa_decode(fa_module* m, const fa_attn_params* p, int num_splits, void* works
     kp.part_ml = (float*)((char*)workspace + (rows * p->Dv * sizeof(float) + 255) / 256 * 256);
   }
   if (tc) {
-    // tcgen05 kernel: num_splits / 2 CTAs per (batch, head), each writing two partial results
+    // tcgen05 kernel: num_splits / 4 CTAs per (batch, head), each writing four partial results
     if (int rc = launch_decode_tc(m, p, kp, num_splits, stream)) return rc;
   } else {
     Kernel* k = nullptr;

@@ -43,13 +43,17 @@ constexpr int D = FA_D;
 constexpr int BM = 128, BN = 128;
 constexpr int ATOMS = D / 64;            // 64-element (128-byte) column groups per row
 constexpr int ATOM_BYTES = 128 * 128;    // 128 rows x 128 bytes
-// Split-KV decode variant (FA_TC_DECODE, D = 64): the CTA owns ONE query tile (Sq <= 128 rows,
-// the rest of the 128 is padding) and a contiguous share of the kv tiles the BlockMask lists; the
-// two softmax warpgroups take alternate kv tiles of that share, so both work on the same
-// query rows (at most 64: the first warpgroup has them in rows 0-63 of its tile, the second in
-// rows 64-127 of a copy of the tile loaded 64 rows down, and warps without a real row idle), and
-// each writes its own un-normalised partial result (running maximum, sum, O) for the combine
-// kernel.  More stages, since the kv stream is all there is.
+// Split-KV decode variant (FA_TC_DECODE, D = 64, at most 64 query rows): the CTA owns a contiguous
+// share of the kv tiles the BlockMask lists and the two softmax warpgroups take alternate kv tiles
+// of that share.  A warpgroup's 128-row tile holds the query rows twice, in rows 0-63 and again in
+// rows 64-127, so that two threads work on one query row: the thread of TMEM lane r < 64 takes kv
+// columns 0-63 of the tile, the thread of lane r + 64 columns 64-127.  Each thread runs its own
+// online softmax over its half tiles (own running maximum and sum) and writes P for its columns
+// only; the other 64 columns of its lane are zero, so the P.V product gives every lane the
+// partial output of its own columns.  No thread sits on a padding row while there are at least
+// 33 queries, and a thread's serial work per kv tile is half that of the forward.  Every thread
+// writes an un-normalised partial result (running maximum, sum, O): four per CTA and row, merged
+// by the combine kernel.  More stages, since the kv stream is all there is.
 #ifndef FA_TC_DECODE
 #define FA_TC_DECODE 0
 #endif
@@ -66,7 +70,8 @@ constexpr int OFF_MISC = OFF_BAR + NBARS * 8;       // tmem base, abort flag, ns
 constexpr int OFF_SCHED = OFF_MISC + 16;            // short tile[MAXT]
 constexpr int OFF_MODE = OFF_SCHED + MAXT * 2;      // uchar mode[MAXT][2]
 constexpr int OFF_CLS = OFF_MODE + MAXT * 2;        // uchar cls[2][MAXT]
-constexpr int SMEM_BYTES = OFF_CLS + 2 * MAXT + 1024;  // + slack for the 1024-byte alignment
+constexpr int OFF_WCNT = OFF_CLS + 2 * MAXT;        // int wcount[MAXT / 32]: listed tiles per warp of the schedule build
+constexpr int SMEM_BYTES = OFF_WCNT + (MAXT / 32) * 4 + 1024;  // + slack for the 1024-byte alignment
 constexpr int TMEM_COLS = 512;
 constexpr int COL_S = 0, COL_O = 256;
 // With D = 64 there is TMEM left for P next to S (columns 384..511): S of the next kv step can
@@ -200,6 +205,7 @@ struct SoftmaxCtx {
   const FaParams& p;
   fa_u32 sb, t_s, t_o, t_p;
   int i, warp, qi, gb, gh;
+  int half;  // decode variant: which 64 kv columns of a tile this thread owns (0 in the forward)
   float sc2;
   volatile int* abort_flag;
   const short* sched_tile;
@@ -221,7 +227,9 @@ __device__ __forceinline__ bool softmax_step(SoftmaxCtx& c, const int j, const i
   float& l = c.l;
   fa_u32& cnt = c.cnt;
   const short* sched_tile = c.sched_tile;
-  const int n0 = (int)sched_tile[DECODE ? 2 * j + i : j] * BN;
+  // first key of this thread's columns (decode variant: the thread's 64-column half of the tile)
+  const int n0 = (int)sched_tile[DECODE ? 2 * j + i : j] * BN + (DECODE ? c.half * 64 : 0);
+  const fa_u32 t_sh = DECODE ? t_s + c.half * 64 : t_s;
   if (!fa_mbar_wait_warp(bar_addr(sb, BAR_S + i), cnt & 1u, abort_flag)) return false;
   fa_tc_fence_after();
   // ---- pass 1: the whole score row (128 fp32 values) comes into registers, chunk by chunk,
@@ -238,22 +246,29 @@ __device__ __forceinline__ bool softmax_step(SoftmaxCtx& c, const int j, const i
   if (in_place) mod_chunk<C0>(V, n0, qi, gb, gh, p.scale, sc2);                \
   if (MASKED) mask_chunk<C0>(V, use_mask, n0, qi, gb, gh, p.Skv);              \
   max_chunk(V, rm);
-  fa_tmem_ld32(t_s, s0);
+  fa_tmem_ld32(t_sh, s0);
   fa_tmem_wait_ld();
-  fa_tmem_ld32(t_s + 32, s1);
+  fa_tmem_ld32(t_sh + 32, s1);
   FA_P1(s0, 0)
   fa_tmem_wait_ld();
-  fa_tmem_ld32(t_s + 64, s2);
-  FA_P1(s1, 32)
-  fa_tmem_wait_ld();
-  fa_tmem_ld32(t_s + 96, s3);
-  FA_P1(s2, 64)
-  fa_tmem_wait_ld();
-  if (SEP_P) {
+  if (DECODE) {
+    // two chunks are the whole share of this thread
     fa_tc_fence_before();
     fa_mbar_arrive(bar_addr(sb, BAR_SFREE2 + i));
+    FA_P1(s1, 32)
+  } else {
+    fa_tmem_ld32(t_s + 64, s2);
+    FA_P1(s1, 32)
+    fa_tmem_wait_ld();
+    fa_tmem_ld32(t_s + 96, s3);
+    FA_P1(s2, 64)
+    fa_tmem_wait_ld();
+    if (SEP_P) {
+      fa_tc_fence_before();
+      fa_mbar_arrive(bar_addr(sb, BAR_SFREE2 + i));
+    }
+    FA_P1(s3, 96)
   }
-  FA_P1(s3, 96)
 #undef FA_P1
   float mx = fmaxf(fmaxf(rm.a, rm.b), fmaxf(rm.c, rm.d));
   if (!in_place) mx *= sc2;
@@ -299,14 +314,17 @@ __device__ __forceinline__ bool softmax_step(SoftmaxCtx& c, const int j, const i
   fa_u64 sum_a = fa_f2(0.f, 0.f), sum_b = fa_f2(0.f, 0.f);
   {
     fa_u32 pk[16];
+    const fa_u32 t_ph = DECODE ? t_p + c.half * 32 : t_p;  // (the other 32 columns of the lane stay zero)
     pass2_chunk(s0, pk, cmul, negm, sum_a, sum_b);
-    fa_tmem_st16(t_p, pk);
+    fa_tmem_st16(t_ph, pk);
     pass2_chunk(s1, pk, cmul, negm, sum_a, sum_b);
-    fa_tmem_st16(t_p + 16, pk);
-    pass2_chunk(s2, pk, cmul, negm, sum_a, sum_b);
-    fa_tmem_st16(t_p + 32, pk);
-    pass2_chunk(s3, pk, cmul, negm, sum_a, sum_b);
-    fa_tmem_st16(t_p + 48, pk);
+    fa_tmem_st16(t_ph + 16, pk);
+    if (!DECODE) {
+      pass2_chunk(s2, pk, cmul, negm, sum_a, sum_b);
+      fa_tmem_st16(t_p + 32, pk);
+      pass2_chunk(s3, pk, cmul, negm, sum_a, sum_b);
+      fa_tmem_st16(t_p + 48, pk);
+    }
   }
   float sum;
   {
@@ -377,14 +395,18 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
     // the query tiles do not depend on the kv schedule: their loads start now and run while the
     // schedule is being built
     fa_tma_prefetch_desc(&P.tq);
-    // (decode variant: both warpgroups work on the same <= 64 query rows.  The second copy of the
-    //  tile is loaded 64 rows down - rows -64..-1 of the tensor are out of range and read as zero -
-    //  so that the second warpgroup finds its rows in TMEM lanes 64-127 and the four warps that
-    //  have real rows sit on four different SM sub-partitions)
+    // (decode variant: the query map's box is 64 rows and each warpgroup's tile gets the queries
+    //  twice, in rows 0-63 and in rows 64-127; rows beyond Sq are out of range and read as zero)
     fa_mbar_expect_tx(bar_addr(sb, BAR_Q), Q_BYTES);
     for (int i = 0; i < 2; ++i)
-      for (int a = 0; a < ATOMS; ++a)
-        fa_tma_load_4d(sb + (i * ATOMS + a) * ATOM_BYTES, &P.tq, bar_addr(sb, BAR_Q), a * 64, DECODE ? -64 * i : m0 + i * BM, h, b);
+      for (int a = 0; a < ATOMS; ++a) {
+        if (DECODE) {
+          fa_tma_load_4d(sb + (i * ATOMS + a) * ATOM_BYTES, &P.tq, bar_addr(sb, BAR_Q), a * 64, 0, h, b);
+          fa_tma_load_4d(sb + (i * ATOMS + a) * ATOM_BYTES + 64 * 128, &P.tq, bar_addr(sb, BAR_Q), a * 64, 0, h, b);
+        } else {
+          fa_tma_load_4d(sb + (i * ATOMS + a) * ATOM_BYTES, &P.tq, bar_addr(sb, BAR_Q), a * 64, m0 + i * BM, h, b);
+        }
+      }
   }
   const int ntiles = min((p.Skv + BN - 1) / BN, MAXT);
   for (int i = tid; i < 2 * MAXT; i += NT) cls[i] = 0;
@@ -416,40 +438,51 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
     }
   }
   __syncthreads();
-  if (tid == 0) {
+  // The kv schedule: the listed tiles in ascending order, compacted by the first 256 threads (one
+  // tile each) with a ballot per warp and a prefix over the eight warp counts.
+  {
+    int* wcount = (int*)(sm + OFF_WCNT);
+    const bool mine = tid < MAXT;
+    const unsigned char c0 = (mine && tid < ntiles) ? cls[tid] : 0;
+    const unsigned char c1 = (!DECODE && mine && tid < ntiles) ? cls[MAXT + tid] : 0;
+    const bool listed = (c0 | c1) != 0;
+    const unsigned vote = __ballot_sync(0xffffffffu, listed);
+    if (mine && lane == 0) wcount[warp] = __popc(vote);
+    __syncthreads();
+    if (mine) {
+      int before = 0, total = 0;
+      for (int w = 0; w < MAXT / 32; ++w) {
+        const int n = wcount[w];
+        before += w < warp ? n : 0;
+        total += n;
+      }
+      const int pos = before + __popc(vote & ((1u << lane) - 1u));
 #if FA_TC_DECODE
-    // this CTA's share of the listed kv tiles; entry k of the share belongs to warpgroup k % 2
-    int n_all = 0;
-    for (int t = 0; t < ntiles; ++t) n_all += cls[t] != 0;
-    const int per = (n_all + (int)gridDim.x - 1) / (int)gridDim.x;
-    const int lo = split * per, hi = min(n_all, lo + per);
-    int n = 0, k = 0;
-    for (int t = 0; t < ntiles; ++t) {
-      if (!cls[t]) continue;
-      if (n >= lo && n < hi) {
-        sched_tile[k] = (short)t;
-        sched_mode[k] = cls[t];
-        ++k;
+      // this CTA's share of the listed kv tiles; entry k of the share belongs to warpgroup k % 2
+      const int per = (total + (int)gridDim.x - 1) / (int)gridDim.x;
+      const int lo = split * per, hi = min(total, lo + per);
+      if (listed && pos >= lo && pos < hi) {
+        sched_tile[pos - lo] = (short)tid;
+        sched_mode[pos - lo] = c0;
       }
-      ++n;
-    }
-    sched_mode[k] = 0;  // an odd share leaves the second warpgroup without a tile in the last step
-    misc[2] = (k + 1) / 2;
-    misc[3] = k;
+      if (tid == 0) {
+        const int k = max(hi - lo, 0);
+        sched_mode[k] = 0;  // an odd share leaves the second warpgroup without a tile in the last step
+        misc[2] = (k + 1) / 2;
+        misc[3] = k;
+      }
 #else
-    int n = 0;
-    for (int t = 0; t < ntiles; ++t) {
-      const unsigned char c0 = cls[t], c1 = cls[MAXT + t];
-      if (c0 | c1) {
-        sched_tile[n] = (short)t;
-        sched_mode[2 * n] = c0;
-        sched_mode[2 * n + 1] = c1;
-        ++n;
+      if (listed) {
+        sched_tile[pos] = (short)tid;
+        sched_mode[2 * pos] = c0;
+        sched_mode[2 * pos + 1] = c1;
       }
-    }
-    misc[2] = n;
-    misc[3] = n;
+      if (tid == 0) {
+        misc[2] = total;
+        misc[3] = total;
+      }
 #endif
+    }
   }
   fa_tc_fence_before();
   __syncthreads();
@@ -644,15 +677,25 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
     const int i = warp >> 2;                       // query tile of this warpgroup
     const int lane_base = (warp & 3) * 32;         // TMEM lanes this warp may touch
     const int r = lane_base + lane;                // row inside the tile
-    const int qi = DECODE ? r - 64 * i : m0 + i * BM + r;  // query index
-    // decode variant: warps whose 32 rows are all padding only keep the barrier protocol going
-    const bool warp_active = !DECODE || (lane_base - 64 * i >= 0 && lane_base - 64 * i < p.Sq);
+    const int qi = DECODE ? (r & 63) : m0 + i * BM + r;  // query index
+    const int half = DECODE ? (r >> 6) : 0;               // decode variant: kv columns 64 * half .. + 63 of every tile
+    // decode variant: warps whose 32 rows are all padding (fewer than 33 queries) only keep the barrier protocol going
+    const bool warp_active = !DECODE || (lane_base & 63) < p.Sq;
     fa_u32 idle_cnt = 0;
     const fa_u32 t_s = tmem + ((fa_u32)lane_base << 16) + COL_S + i * BN;
     const fa_u32 t_o = tmem + ((fa_u32)lane_base << 16) + COL_O + i * D;
     const fa_u32 t_p = SEP_P ? tmem + ((fa_u32)lane_base << 16) + COL_P + i * 64 : t_s;
     bool ok = true;
-    SoftmaxCtx c = {p, sb, t_s, t_o, t_p, i, warp, qi, gb, gh, p.scale * FA_LOG2E, abort_flag, sched_tile, FA_NEG_INF, 0.f, 0u};
+    SoftmaxCtx c = {p, sb, t_s, t_o, t_p, i, warp, qi, gb, gh, half, p.scale * FA_LOG2E, abort_flag, sched_tile, FA_NEG_INF, 0.f, 0u};
+    if (DECODE) {
+      // the P columns of the other half of this lane's kv columns are never written again
+      fa_u32 z[16];
+#pragma unroll
+      for (int e = 0; e < 16; ++e) z[e] = 0u;
+      fa_tmem_st16(t_p + (1 - half) * 32, z);
+      fa_tmem_st16(t_p + (1 - half) * 32 + 16, z);
+      fa_tmem_wait_st();
+    }
     for (int j = 0; j < nsteps && ok; ++j) {
       const int mode = sched_mode[2 * j + i];
       if (mode == 0) continue;
@@ -680,9 +723,9 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
     if (ok && cnt > 0) ok = fa_mbar_wait_warp(bar_addr(sb, BAR_O + i), (cnt - 1) & 1u, abort_flag);
 #if FA_TC_DECODE
     if (ok) {
-      // un-normalised partial result of this warpgroup: number 2 * share + i of the row
+      // un-normalised partial result of this thread's columns: number 4 * share + 2 * i + half of the row
       fa_tc_fence_after();
-      const long long prow = (((long long)b * p.Hq + h) * p.num_splits + 2 * split + i) * p.Sq + qi;
+      const long long prow = (((long long)b * p.Hq + h) * p.num_splits + 4 * split + 2 * i + half) * p.Sq + qi;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         float o[32];
@@ -693,13 +736,13 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
 #pragma unroll
           for (int e = 0; e < 32; ++e) o[e] = 0.f;
         }
-        if (qi >= 0 && qi < p.Sq) {
+        if (qi < p.Sq) {
 #pragma unroll
           for (int e = 0; e < 32; e += 4)
             *(float4*)(p.part_o + prow * D + c * 32 + e) = make_float4(o[e], o[e + 1], o[e + 2], o[e + 3]);
         }
       }
-      if (qi >= 0 && qi < p.Sq) *(float2*)(p.part_ml + prow * 2) = make_float2(m_ref, m_ref != FA_NEG_INF ? l : 0.f);
+      if (qi < p.Sq) *(float2*)(p.part_ml + prow * 2) = make_float2(m_ref, m_ref != FA_NEG_INF ? l : 0.f);
     }
 #else
     if (ok) {

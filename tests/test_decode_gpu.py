@@ -72,24 +72,25 @@ def test_decode_benchmark_shape():
     oracle; all rows against a run with a different split count (the result may not depend
     on how the key range is cut)."""
     B, Hq, Skv, D = 32, 8, 16384, 64
-    for Sq in (1, 16, 64):
+    for Sq in (1, 16, 32, 64):
         s, m = _mods(Hq, Sq, Skv, "offset")
         q, k, v = qkv(B, Hq, Hq, Sq, Skv, D, dtype=torch.float16)
         out, lse = _decode(q, k, v, s, m, 0)
         ref, ref_lse = flax_attention_oracle_chunked(q[:1, :2], k[:1, :2], v[:1, :2], s, m, chunk_bh=1)
         assert max_abs(out[:1, :2], ref) <= 2e-2
         assert max_abs(lse[:1, :2], ref_lse) <= 2e-2 * max(1.0, ref_lse.abs().max().item())
-        out2, lse2 = _decode(q, k, v, s, m, 6 if Sq > 32 else 5)
+        out2, lse2 = _decode(q, k, v, s, m, 12 if Sq > 32 else 5)
         assert max_abs(out, out2) <= 2e-3 and max_abs(lse, lse2) <= 1e-3 * max(1.0, lse.abs().max().item())
 
 
 @pytest.mark.parametrize("dt", ["f16", "bf16"])
-@pytest.mark.parametrize("Sq,splits", [(33, 2), (48, 4), (64, 6), (64, 3), (40, 0)])
+@pytest.mark.parametrize("Sq,splits", [(17, 4), (24, 0), (32, 8), (33, 4), (48, 8), (64, 12), (64, 3), (40, 0), (64, 24)])
 def test_tcgen05_decode_and_general_decode_agree_with_the_oracle(Sq, splits, dt):
-    """33..64 query rows with an even split count run on the split-KV variant of the tcgen05
-    kernel (two partial results per CTA), an odd count or the `general` option on the general
-    decode kernel: both within tolerance of the oracle and close to each other, and the status
-    word of the tcgen05 kernel (bounded waits) stays 0."""
+    """17..64 query rows with a split count that is a multiple of four run on the split-KV variant
+    of the tcgen05 kernel (four partial results per CTA: two warpgroups x two column halves), any
+    other count or the `general` option on the general decode kernel: both within tolerance of the
+    oracle and close to each other, and the status word of the tcgen05 kernel (bounded waits)
+    stays 0."""
     import flaxattention_b200 as fa
 
     B, Hq, Hkv, Skv, D = 2, 4, 4, 3000, 64      # ragged last tile, 24 kv tiles

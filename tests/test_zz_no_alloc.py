@@ -58,7 +58,7 @@ def test_static_scratch_decode_equals_workspace_decode_twice():
     # then the 33..64-row case, where a different kernel (the tcgen05 split-KV variant) writes the
     # scratch, in bf16, again followed by a smaller problem
     cases = ((0, (2, 4, 16, 4096, 64), 6, torch.float16), (1, (1, 4, 1, 2048, 64), 3, torch.float16),
-             (0, (2, 4, 48, 4096, 64), 4, torch.bfloat16), (1, (1, 2, 64, 2048, 64), 2, torch.bfloat16))
+             (0, (2, 4, 48, 4096, 64), 8, torch.bfloat16), (1, (1, 2, 64, 2048, 64), 4, torch.bfloat16))
     for shift, shape, splits, dtype in cases:
         call, q, k, v = _problem(shift, *shape, dtype)
         (o_ws, l_ws), (o_st, l_st) = _run_both(call, q, k, v, splits)
