@@ -937,8 +937,8 @@ int get_fwd_tc_kernel(fa_module* m, int dtype, int D, int flags, Kernel** k, boo
   return get_kernel(m, "fa_fwd_tc.cuh", d, "fa_fwd_tc_kernel", smem, k);
 }
 
-// Shapes the split-KV variant of the tcgen05 kernel covers (`num_splits` partial results per row,
-// four per CTA: two warpgroups x two column halves); everything else runs on the general decode kernel.
+// Shapes the split-KV variant of the tcgen05 kernel covers (`num_splits` CTAs per (batch, head), one
+// partial result per CTA and row); everything else runs on the general decode kernel.
 bool tc_decode_eligible(const fa_attn_params* p) {
   if (p->flags & FA_FLAG_GENERAL_KERNELS) return false;
   if (p->dtype == FA_F32) return false;
@@ -963,7 +963,7 @@ int launch_decode_tc(fa_module* m, const fa_attn_params* p, const FaParams& kp, 
   if (int rc = make_map(&tp.tq, p->dtype, p->q, p->D, p->Sq, p->Hq, p->B, 64)) return rc;  // the queries go into a tile twice
   if (int rc = make_map(&tp.tk, p->dtype, p->k, p->D, p->Skv, p->Hkv, p->B)) return rc;
   if (int rc = make_map(&tp.tv, p->dtype, p->v, p->Dv, p->Skv, p->Hkv, p->B)) return rc;
-  return launch(k, dim3(num_splits / 4, p->Hq, p->B), dim3(384), &tp, stream);
+  return launch(k, dim3(num_splits, p->Hq, p->B), dim3(384), &tp, stream);
 }
 
 int launch_fwd_tc(fa_module* m, const fa_attn_params* p, const FaParams& kp, void* stream) {
@@ -1222,9 +1222,11 @@ int fa_decode_num_splits(const fa_attn_params* p, int sm_count) {
   const long long bh = (long long)p->B * (pack ? p->Hkv : p->Hq);
   const int tiles = (p->Skv + 127) / 128;
   if (!pack && tc_decode_eligible(p)) {
-    // tcgen05 kernel: one CTA per SM, four partial results per CTA, at least eight kv tiles per CTA
+    // tcgen05 kernel: one CTA per SM and split, at least eight kv tiles per CTA; its partial results
+    // always go through the combine kernel, so there are at least two splits
     const int cmax = tiles / 8 > 1 ? (tiles / 8 < 64 ? tiles / 8 : 64) : 1;
-    return 4 * fill_waves(bh, cmax, sm_count);
+    const int c = fill_waves(bh, cmax, sm_count);
+    return c < 2 ? 2 : c;
   }
   // general kernel: as many CTAs per SM as its shared memory allows (at most four by registers),
   // at least four kv tiles per CTA.  A grid that ends in a part-filled wave costs more than a few
@@ -1254,7 +1256,7 @@ int fa_decode(fa_module* m, const fa_attn_params* p, int num_splits, void* works
   FaParams kp;
   fill_params(p, kp);
   const bool pack = decode_packs_heads(p);
-  const bool tc = !pack && tc_decode_eligible(p) && num_splits >= 4 && num_splits % 4 == 0;
+  const bool tc = !pack && tc_decode_eligible(p) && num_splits >= 2;
   DecCfg c;
   if (!tc)
     if (int rc = pick_decode(p->dtype, p->D, p->Dv, pack ? p->Sq * (p->Hq / p->Hkv) : p->Sq, &kp.t, c)) return rc;
@@ -1268,7 +1270,7 @@ int fa_decode(fa_module* m, const fa_attn_params* p, int num_splits, void* works
     kp.part_ml = (float*)((char*)workspace + (rows * p->Dv * sizeof(float) + 255) / 256 * 256);
   }
   if (tc) {
-    // tcgen05 kernel: num_splits / 4 CTAs per (batch, head), each writing four partial results
+    // tcgen05 kernel: num_splits CTAs per (batch, head), each writing one partial result per row
     if (int rc = launch_decode_tc(m, p, kp, num_splits, stream)) return rc;
   } else {
     Kernel* k = nullptr;

@@ -51,9 +51,10 @@ constexpr int ATOM_BYTES = 128 * 128;    // 128 rows x 128 bytes
 // online softmax over its half tiles (own running maximum and sum) and writes P for its columns
 // only; the other 64 columns of its lane are zero, so the P.V product gives every lane the
 // partial output of its own columns.  No thread sits on a padding row while there are at least
-// 33 queries, and a thread's serial work per kv tile is half that of the forward.  Every thread
-// writes an un-normalised partial result (running maximum, sum, O): four per CTA and row, merged
-// by the combine kernel.  More stages, since the kv stream is all there is.
+// 33 queries, and a thread's serial work per kv tile is half that of the forward.  At the end the
+// four partial results of a row (running maximum, sum, O of two warpgroups x two halves) are
+// merged through shared memory and the CTA writes one un-normalised partial result per row for
+// the combine kernel.  More stages, since the kv stream is all there is.
 #ifndef FA_TC_DECODE
 #define FA_TC_DECODE 0
 #endif
@@ -722,27 +723,69 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
     // ---- epilogue: O / l and the logsumexp of this thread's row ---------------------------
     if (ok && cnt > 0) ok = fa_mbar_wait_warp(bar_addr(sb, BAR_O + i), (cnt - 1) & 1u, abort_flag);
 #if FA_TC_DECODE
-    if (ok) {
-      // un-normalised partial result of this thread's columns: number 4 * share + 2 * i + half of the row
-      fa_tc_fence_after();
-      const long long prow = (((long long)b * p.Hq + h) * p.num_splits + 4 * split + 2 * i + half) * p.Sq + qi;
+    // The four partial results of a query row (two warpgroups x two column halves) are merged
+    // inside the CTA: every thread puts its (O, maximum, sum) into shared memory, over the K / V
+    // ring, which nothing reads or writes any more once both warpgroups have seen their last
+    // product complete; then the 256 threads merge 64 rows x 64 columns and the CTA writes ONE
+    // un-normalised partial result per row for the combine kernel.  All 256 softmax threads reach
+    // both barriers, whatever happened before (every earlier wait is bounded).
+    {
+      constexpr int MP = D + 4;  // floats per scratch row: O[D], maximum, sum, pad (16-byte rows)
+      float* scratch = (float*)(sm + OFF_K);
+      static_assert(2 * 128 * MP * 4 <= 2 * NSTAGE * KV_STAGE, "merge scratch fits the K / V ring");
+      asm volatile("bar.sync 2, 256;" ::: "memory");
+      const bool good = ok && *abort_flag == 0;
+      if (good && warp_active) {
+        fa_tc_fence_after();
+        float* row = scratch + (i * 128 + r) * MP;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        float o[32];
-        if (cnt > 0) {
-          fa_tmem_ld32(t_o + c * 32, o);
-          fa_tmem_wait_ld();
-        } else {
+        for (int c = 0; c < D / 32; ++c) {
+          float o[32];
+          if (cnt > 0) {
+            fa_tmem_ld32(t_o + c * 32, o);
+            fa_tmem_wait_ld();
+          } else {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) o[e] = 0.f;
+            for (int e = 0; e < 32; ++e) o[e] = 0.f;
+          }
+#pragma unroll
+          for (int e = 0; e < 32; e += 4) *(float4*)(row + c * 32 + e) = make_float4(o[e], o[e + 1], o[e + 2], o[e + 3]);
         }
-        if (qi < p.Sq) {
+        *(float2*)(row + D) = make_float2(m_ref, m_ref != FA_NEG_INF ? l : 0.f);
+      }
+      asm volatile("bar.sync 2, 256;" ::: "memory");
+      if (*abort_flag == 0) {
+        const int mt = tid;                     // 0 .. 255
+        const int mrow = mt >> 2, c0 = (mt & 3) * 16;  // query row, first of this thread's 16 columns
+        if (mrow < p.Sq) {
+          const float* src[4];
+          float mm[4], mstar = FA_NEG_INF;
 #pragma unroll
-          for (int e = 0; e < 32; e += 4)
-            *(float4*)(p.part_o + prow * D + c * 32 + e) = make_float4(o[e], o[e + 1], o[e + 2], o[e + 3]);
+          for (int k = 0; k < 4; ++k) {
+            src[k] = scratch + ((k >> 1) * 128 + (k & 1) * 64 + mrow) * MP;
+            mm[k] = src[k][D];
+            mstar = fmaxf(mstar, mm[k]);
+          }
+          float acc[16], lsum = 0.f;
+#pragma unroll
+          for (int e = 0; e < 16; ++e) acc[e] = 0.f;
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const float w = mm[k] == FA_NEG_INF ? 0.f : fa_ex2(mm[k] - mstar);
+            lsum += w * src[k][D + 1];
+#pragma unroll
+            for (int e = 0; e < 16; e += 4) {
+              const float4 v4 = *(const float4*)(src[k] + c0 + e);
+              acc[e] += w * v4.x; acc[e + 1] += w * v4.y; acc[e + 2] += w * v4.z; acc[e + 3] += w * v4.w;
+            }
+          }
+          const long long prow = (((long long)b * p.Hq + h) * p.num_splits + split) * p.Sq + mrow;
+#pragma unroll
+          for (int e = 0; e < 16; e += 4)
+            *(float4*)(p.part_o + prow * D + c0 + e) = make_float4(acc[e], acc[e + 1], acc[e + 2], acc[e + 3]);
+          if ((mt & 3) == 0) *(float2*)(p.part_ml + prow * 2) = make_float2(mstar, lsum);
         }
       }
-      if (qi < p.Sq) *(float2*)(p.part_ml + prow * 2) = make_float2(m_ref, m_ref != FA_NEG_INF ? l : 0.f);
     }
 #else
     if (ok) {
