@@ -134,7 +134,8 @@ size_t fa_bwd_workspace_bytes(const fa_attn_params* p);
 int fa_bwd(fa_module* m, const fa_attn_params* p, const fa_tensor* dout, const fa_tensor* dq,
            const fa_tensor* dk, const fa_tensor* dv, void* workspace, size_t workspace_bytes, void* stream);
 
-/* Split-KV decode for Sq <= 64.  num_splits <= 0 lets the library choose.
+/* Split-KV decode for Sq <= 64.  num_splits <= 0 lets the library choose; num_splits is the number of
+ * partial results per row that the combine pass merges (one per CTA of a (batch, head)).
  * Grouped-query attention (Hq = G * Hkv, validated by the reference at
  * flaxattention/core/attention.py:258-265): when G * Sq <= 64 and the BlockMask tables do not
  * depend on the head (no tables, or mask_H == 1) the G query heads of a kv head are packed into
