@@ -289,19 +289,32 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
     if (p.t.kv_num == nullptr || p.t.q_num == nullptr) {
       for (int t = tid; t < n_ctiles; t += NT) cls[t] = FA_HAS_MASK_MOD ? 1 : 2;
     } else {
+      // both counts and, speculatively, this thread's entry of both index lists are read before any
+      // of them is used: one round trip to memory instead of four dependent ones
       const int bm = p.t.mB == 1 ? 0 : b, hm = p.t.mH == 1 ? 0 : h;
       const int kvblk = min(n0 / p.t.KVB, p.t.nKV - 1);
       const long long row = ((long long)bm * p.t.mH + hm) * p.t.nKV + kvblk;
       const int tpb = p.t.nQ == 1 ? n_ctiles : p.t.QB / 128;
+      const int bi0 = tid / tpb, ti0 = tid - bi0 * tpb;
+      int num[2], blk[2];
+#pragma unroll
       for (int which = 0; which < 2; ++which) {
         const int* nump = which ? p.t.full_q_num : p.t.q_num;
         const int* idxp = which ? p.t.full_q_idx : p.t.q_idx;
-        if (nump == nullptr) continue;
-        const int num = min(max(nump[row], 0), p.t.nQ);
-        for (int e = tid; e < num * tpb; e += NT) {
+        num[which] = nump != nullptr ? nump[row] : 0;
+        blk[which] = (nump != nullptr && bi0 < p.t.nQ) ? idxp[row * p.t.nQ + bi0] : 0;
+      }
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        const int* idxp = which ? p.t.full_q_idx : p.t.q_idx;
+        const int n = min(max(num[which], 0), p.t.nQ) * tpb;
+        if (tid < n) {
+          const int t = min(max(blk[which], 0), p.t.nQ - 1) * tpb + ti0;
+          if (t < n_ctiles) cls[t] = (unsigned char)(which ? 2 : 1);
+        }
+        for (int e = tid + NT; e < n; e += NT) {  // (more list entries than threads)
           const int bi = e / tpb, ti = e - bi * tpb;
-          const int blk = min(max(idxp[row * p.t.nQ + bi], 0), p.t.nQ - 1);
-          const int t = blk * tpb + ti;
+          const int t = min(max(idxp[row * p.t.nQ + bi], 0), p.t.nQ - 1) * tpb + ti;
           if (t < n_ctiles) cls[t] = (unsigned char)(which ? 2 : 1);
         }
       }

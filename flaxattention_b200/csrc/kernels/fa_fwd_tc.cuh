@@ -413,26 +413,51 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
   for (int i = tid; i < 2 * MAXT; i += NT) cls[i] = 0;
   if (warp == WARP_MMA) fa_tmem_alloc(sb + OFF_MISC, TMEM_COLS);
   __syncthreads();
-  // class of every kv tile for both query tiles: 0 skip, 1 apply mask_mod, 2 full
-  for (int i = 0; i < (DECODE ? 1 : 2); ++i) {
-    const int mi = m0 + i * BM;
-    if (mi >= p.Sq) continue;
-    if (p.t.kv_num == nullptr) {
-      for (int t = tid; t < ntiles; t += NT) cls[i * MAXT + t] = FA_HAS_MASK_MOD ? 1 : 2;
-    } else {
+  // class of every kv tile for both query tiles: 0 skip, 1 apply mask_mod, 2 full.  Every table read
+  // of the CTA (the two counts and, speculatively, this thread's entry of the two index lists, for
+  // both query tiles) is issued before any of them is used: one round trip to memory instead of
+  // a chain of four dependent ones.
+  {
+    constexpr int NI = DECODE ? 1 : 2;
+    const bool tables = p.t.kv_num != nullptr;
+    const int tpb = tables ? (p.t.nKV == 1 ? ntiles : p.t.KVB / BN) : 1;
+    const int bi0 = tid / tpb, ti0 = tid - bi0 * tpb;
+    long long rows[NI];
+    int num[NI][2], blk[NI][2];
+#pragma unroll
+    for (int i = 0; i < NI; ++i) {
+      const int mi = m0 + i * BM;
       const int bm = p.t.mB == 1 ? 0 : b, hm = p.t.mH == 1 ? 0 : h;
-      const int qblk = min(mi / p.t.QB, p.t.nQ - 1);
-      const long long row = ((long long)bm * p.t.mH + hm) * p.t.nQ + qblk;
-      const int tpb = p.t.nKV == 1 ? ntiles : p.t.KVB / BN;
+      const int qblk = tables ? min(mi / p.t.QB, p.t.nQ - 1) : 0;
+      rows[i] = ((long long)bm * p.t.mH + hm) * p.t.nQ + qblk;
+#pragma unroll
       for (int which = 0; which < 2; ++which) {
         const int* nump = which ? p.t.full_kv_num : p.t.kv_num;
         const int* idxp = which ? p.t.full_kv_idx : p.t.kv_idx;
-        if (nump == nullptr) continue;
-        const int num = min(max(nump[row], 0), p.t.nKV);
-        for (int e = tid; e < num * tpb; e += NT) {
+        const bool have = tables && nump != nullptr && mi < p.Sq;
+        num[i][which] = have ? nump[rows[i]] : 0;
+        blk[i][which] = (have && bi0 < p.t.nKV) ? idxp[rows[i] * p.t.nKV + bi0] : 0;
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < NI; ++i) {
+      const int mi = m0 + i * BM;
+      if (mi >= p.Sq) continue;
+      if (!tables) {
+        for (int t = tid; t < ntiles; t += NT) cls[i * MAXT + t] = FA_HAS_MASK_MOD ? 1 : 2;
+        continue;
+      }
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        const int* idxp = which ? p.t.full_kv_idx : p.t.kv_idx;
+        const int n = min(max(num[i][which], 0), p.t.nKV) * tpb;
+        if (tid < n) {
+          const int t = min(max(blk[i][which], 0), p.t.nKV - 1) * tpb + ti0;
+          if (t < ntiles) cls[i * MAXT + t] = (unsigned char)(which ? 2 : 1);
+        }
+        for (int e = tid + NT; e < n; e += NT) {  // (more list entries than threads)
           const int bi = e / tpb, ti = e - bi * tpb;
-          const int blk = min(max(idxp[row * p.t.nKV + bi], 0), p.t.nKV - 1);
-          const int t = blk * tpb + ti;
+          const int t = min(max(idxp[rows[i] * p.t.nKV + bi], 0), p.t.nKV - 1) * tpb + ti;
           if (t < ntiles) cls[i * MAXT + t] = (unsigned char)(which ? 2 : 1);
         }
       }
