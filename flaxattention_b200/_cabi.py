@@ -64,7 +64,7 @@ EXPORTS = [
     "fa_module_set_buffers", "fa_module_destroy", "fa_module_prepare", "fa_compile_count", "fa_fwd", "fa_bwd_workspace_bytes",
     "fa_bwd", "fa_decode_num_splits", "fa_decode_workspace_bytes", "fa_decode",
     "fa_block_mask_workspace_bytes", "fa_block_mask", "fa_decode_static_capacity", "fa_decode_static",
-    "fa_profile_enable", "fa_profile_read", "fa_decode_packs_heads",
+    "fa_profile_enable", "fa_profile_read", "fa_decode_packs_heads", "fa_selftest_bounded_wait",
 ]
 
 
@@ -112,6 +112,7 @@ def lib() -> C.CDLL:
         L.fa_decode_static.argtypes = [C.c_void_p, C.POINTER(FaAttnParams), C.c_int, C.c_void_p]
     L.fa_profile_enable.argtypes = [C.c_int]
     L.fa_profile_read.argtypes = [C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_char_p)]
+    L.fa_selftest_bounded_wait.argtypes = [C.c_ulonglong, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
     L.fa_set_kernel_dir(os.path.join(_HERE, "csrc", "kernels").encode())
     cache = os.environ.get("FLAXATTN_CACHE_DIR")
     if cache is None:
@@ -162,6 +163,12 @@ class Module:
 def profile_enable(on: bool) -> None:
     """Switches the per-kernel event timing of fa_fwd / fa_bwd / fa_decode on or off."""
     check(lib().fa_profile_enable(1 if on else 0))
+
+
+def selftest_bounded_wait(limit_ns: int, status_ptr: int, gave_up_ptr: int, waited_ns_ptr: int, stream: int = 0) -> None:
+    """Launches the kernel whose only job is to let a bounded mbarrier wait run out (see
+    include/flaxattn.h); the three pointers are device-accessible, zeroed words."""
+    check(lib().fa_selftest_bounded_wait(limit_ns, status_ptr, gave_up_ptr, waited_ns_ptr, stream))
 
 
 def profile_read(max_kernels: int = 16):

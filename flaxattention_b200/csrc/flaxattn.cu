@@ -15,6 +15,7 @@
 #include <sys/stat.h>
 #include <unistd.h>
 
+#include <algorithm>
 #include <atomic>
 #include <cstdio>
 #include <cstdlib>
@@ -108,7 +109,7 @@ std::string cache_dir() {
 }
 
 const char* const kTemplateFiles[] = {"fa_params.h", "fa_common.cuh", "fa_fwd.cuh", "fa_bwd.cuh",
-                                      "fa_decode.cuh", "fa_blockmask.cuh", "fa_sm100.cuh", "fa_fwd_tc.cuh", "fa_bwd_tc.cuh"};
+                                      "fa_decode.cuh", "fa_blockmask.cuh", "fa_sm100.cuh", "fa_fwd_tc.cuh", "fa_bwd_tc.cuh", "fa_selftest.cuh"};
 std::string g_templates_hash;
 int templates_hash(std::string& out) {
   if (g_templates_hash.empty()) {
@@ -805,6 +806,25 @@ int fa_profile_read(int max_kernels, float* ms, const char** names) {
   return n;
 }
 
+int fa_selftest_bounded_wait(unsigned long long limit_ns, int* status, int* gave_up, unsigned long long* waited_ns,
+                             void* stream) {
+  if (!status || !gave_up || !waited_ns) return fail(FA_EINVAL, "status, gave_up and waited_ns are required");
+  if (limit_ns < 1000ull || limit_ns > 100000000ull) return fail(FA_EINVAL, "limit between 1 us and 100 ms");
+  static fa_module* mod = nullptr;  // owns the compiled self-test kernels (one per limit)
+  {
+    std::lock_guard<std::mutex> lk(g_mu);
+    if (!mod) {
+      mod = new fa_module();
+      mod->mod_source = kDefaultMods;
+    }
+  }
+  Kernel* k = nullptr;
+  const std::string defs = "#define FA_WAIT_LIMIT_NS " + std::to_string(limit_ns) + "ull\n";
+  if (int rc = get_kernel(mod, "fa_selftest.cuh", defs, "fa_wait_selftest_kernel", 0, &k)) return rc;
+  struct { int* status; int* gave_up; unsigned long long* waited_ns; } prm = {status, gave_up, waited_ns};
+  return launch(k, dim3(1), dim3(64), &prm, stream);
+}
+
 int fa_module_create(const char* mod_source, fa_module** out) {
   if (!out) return fail(FA_EINVAL, "out is null");
   fa_module* m = new fa_module();
@@ -989,15 +1009,47 @@ struct FaBwdTcParamsHost {
   const float* ndelta;
 };
 
+// SMs of the current device (148 on a B200; asked once per device)
+int device_sm_count() {
+  static std::atomic<int> cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n > 0) return n;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  cached[dev].store(n, std::memory_order_relaxed);
+  return n;
+}
+
+// limits of the pair lists of fa_bwd_tc.cuh (fa_btc::MAXP, MAXI, MAXU)
+int bwd_tc_max_pairs(int D) { return D == 64 ? 2048 : 4096; }
+constexpr int kBwdTcMaxItems = 64, kBwdTcMaxUnits = 256;
+
+// CTAs of the persistent backward: whole waves of one CTA per SM, as few as keep every CTA's pair
+// lists inside their limits when every q tile of every item is listed (the host cannot see how
+// sparse the tables are).
+int bwd_tc_grid(const fa_attn_params* p, int sm_count) {
+  const int G = p->Hq / p->Hkv;
+  const long long n_items = (long long)p->Hkv * p->B * ((p->Skv + 127) / 128);
+  const long long worst = (long long)((p->Sq + 127) / 128) * (p->D / 64) * G;  // pairs of one item
+  long long ipc = std::min<long long>(kBwdTcMaxItems, std::min<long long>(kBwdTcMaxUnits / G, bwd_tc_max_pairs(p->D) / worst));
+  if (ipc < 1) ipc = 1;
+  const long long per_wave = (long long)sm_count * ipc;
+  const long long waves = (n_items + per_wave - 1) / per_wave;
+  return (int)std::min<long long>(n_items, waves * sm_count);
+}
+
 bool tc_bwd_eligible(const fa_attn_params* p) {
   if (p->flags & FA_FLAG_GENERAL_KERNELS) return false;
   if (p->dtype == FA_F32) return false;
   if (p->D != p->Dv || !(p->D == 64 || p->D == 128)) return false;
   if (p->Sq < 128 || p->Skv < 128) return false;
-  // a CTA lists its (query head, q tile) pairs in shared memory: at most 256 q tiles of 128 rows
-  // per head and 1024 pairs (a pair is 128 q rows with D = 64, 64 with D = 128)
+  // a CTA lists the (query head, q tile) pairs of its items in shared memory: at most 256 q tiles
+  // of 128 rows per head, and the pairs of one item must fit the list (a pair is 128 q rows with
+  // D = 64, 64 with D = 128)
   const int n_qtiles = (p->Sq + 127) / 128;
-  if (n_qtiles > 256 || (long long)n_qtiles * (p->D / 64) * (p->Hq / p->Hkv) > 1024) return false;
+  if (n_qtiles > 256 || p->Hq / p->Hkv > kBwdTcMaxUnits) return false;
+  if ((long long)n_qtiles * (p->D / 64) * (p->Hq / p->Hkv) > bwd_tc_max_pairs(p->D)) return false;
   const fa_block_tables& t = p->tables;
   if (t.kv_num_blocks) {
     if (!(t.num_q_blocks == 1 || t.q_block_size % 128 == 0)) return false;
@@ -1020,7 +1072,7 @@ int get_bwd_tc_kernel(fa_module* m, int dtype, int D, int flags, Kernel** k) {
   const int nstage = D == 64 ? 4 : 3, bq = D == 64 ? 128 : 64;
   const int kv_bytes = (D / 64) * 16384, q_bytes = 16384, ds_bytes = (bq / 64) * 16384;
   const int smem = 2 * kv_bytes + 2 * nstage * q_bytes + ds_bytes + 128 * 32 * 4 + nstage * 2 * bq * 4 +
-                   (1 + 3 * nstage + 7) * 8 + 16 + 1024 * 4 + 256 + 1024;
+                   (1 + 3 * nstage + 7) * 8 + 16 + bwd_tc_max_pairs(D) * 4 + (kBwdTcMaxItems + 1) * 4 + 1024;
   std::string d = defs({{"FA_DTYPE", dtype}, {"FA_D", D}, {"FA_ROUND_SCORES", round_flag(dtype, flags)}});
   return get_kernel(m, "fa_bwd_tc.cuh", d, "fa_bwd_tc_kernel", smem, k);
 }
@@ -1147,8 +1199,7 @@ int fa_bwd(fa_module* m, const fa_attn_params* p, const fa_tensor* dout, const f
     if (int rc = make_map(&tp.tk, p->dtype, p->k, p->D, p->Skv, p->Hkv, p->B)) return rc;
     if (int rc = make_map(&tp.tv, p->dtype, p->v, p->Dv, p->Skv, p->Hkv, p->B)) return rc;
     if (int rc = make_map(&tp.tdo, p->dtype, *dout, p->Dv, p->Sq, p->Hq, p->B, bq)) return rc;
-    // heads fastest, kv tile slowest: under a causal mask the first kv tiles meet the most q tiles
-    if (int rc = launch(ktc, dim3(p->Hkv, p->B, (p->Skv + 127) / 128), dim3(512), &tp, stream)) return rc;
+    if (int rc = launch(ktc, dim3((unsigned)bwd_tc_grid(p, device_sm_count())), dim3(512), &tp, stream)) return rc;
     {
       // one 16-byte output chunk per thread: D / 8 chunks per row
       const dim3 grid((unsigned)(((long long)sq_pad * (p->D / 8) + 255) / 256), (unsigned)gy, (unsigned)((n_bh + gy - 1) / gy));

@@ -5,8 +5,10 @@
 // (flaxattention/kernel/attention.py:423-553) and fa_bwd.cuh need seven products and two
 // exponentials.
 //
-// One CTA owns a 128-row kv tile of one (batch, kv head) and walks the q tiles of the query
-// heads that share it.  A pair is 128 kv rows x BQ query rows, BQ = 128 with D = 64 and 64 with
+// The unit of work (an item) is a 128-row kv tile of one (batch, kv head) together with the q tiles
+// of the query heads that share it.  The kernel is persistent: the grid is a whole number of
+// waves of CTAs, every CTA works through several items, and TMEM, the barriers and the pair
+// lists are set up once per CTA.  A pair is 128 kv rows x BQ query rows, BQ = 128 with D = 64 and 64 with
 // D = 128 (the 512 TMEM columns hold two D-wide accumulators, dK and dV, next to the pair's
 // score tiles only for the smaller q tile).  Everything is kept transposed so that dK and dV
 // have kv rows (TMEM lanes) and P^T can be fed to the tensor core straight from TMEM:
@@ -64,8 +66,10 @@ constexpr int Q_ATOM_BYTES = BQ * 128;               // BQ rows x 128 bytes
 constexpr int Q_BYTES = DATOMS * Q_ATOM_BYTES;       // one Q or dO tile (16 KB in both configurations)
 constexpr int DS_ATOMS = BQ / 64;                    // dS^T: [128 kv][BQ q] as atoms of 64 q columns
 constexpr int NSTAGE = D == 64 ? 4 : 3;
-constexpr int MAXP = 1024;               // (head, q tile) pairs per CTA
+constexpr int MAXP = D == 64 ? 2048 : 4096;  // (head, q tile) pairs of all the items of a CTA (what shared memory leaves room for)
 constexpr int MAXC = 256;                // 128-row q tiles per head (Sq <= 32768)
+constexpr int MAXI = 64;                 // items (kv tiles) per CTA
+constexpr int MAXU = 256;                // units (item, query head of the group) per CTA
 constexpr int NT = 512;
 constexpr int WARP_PRODUCER = 12, WARP_MMA = 13, WARP_MMA_B = 14, WARP_MMA_C = 15;
 // Register split (setmaxnreg): the kernel starts with 128 registers per thread (65536 / 512).  The
@@ -85,10 +89,12 @@ constexpr int DQ_HALF_BYTES = 128 * 32 * 4;
 constexpr int OFF_ROW = OFF_DQ + DQ_HALF_BYTES;             // NSTAGE x (nlse2[BQ], ndelta[BQ]) floats
 constexpr int OFF_BAR = OFF_ROW + NSTAGE * 2 * BQ * 4;
 constexpr int NBARS = 1 + 3 * NSTAGE + 7;
-constexpr int OFF_MISC = OFF_BAR + NBARS * 8;               // tmem base, abort, npairs, drain flag
+constexpr int OFF_MISC = OFF_BAR + NBARS * 8;               // tmem base, abort, -, drain flag
 constexpr int OFF_PAIR = OFF_MISC + 16;                     // int pair[MAXP]: q tile | mode << 16 | g << 20
-constexpr int OFF_CLS = OFF_PAIR + MAXP * 4;                // uchar cls[MAXC]
-constexpr int SMEM_BYTES = OFF_CLS + MAXC + 1024;
+constexpr int OFF_ITEM = OFF_PAIR + MAXP * 4;               // int item_off[MAXI + 1]
+constexpr int SMEM_BYTES = OFF_ITEM + (MAXI + 1) * 4 + 1024;
+// set-up scratch (tile classes and pair counts of the units) lies over the Q and dO stages
+static_assert(MAXU * MAXC + (MAXU + 1) * 4 <= 2 * NSTAGE * Q_BYTES, "set-up scratch");
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory");
 constexpr int TMEM_COLS = 512;
 constexpr int COL_S = 0, COL_DP = BQ, COL_P = 2 * BQ;
@@ -237,16 +243,32 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
   unsigned char* sm = smem_raw + (sb - raw);
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int kt = blockIdx.z, hk = blockIdx.x, b = blockIdx.y;  // grid: (kv heads, batch, kv tiles)
-  const int n0 = kt * BT;
   const int G = p.Hq / p.Hkv;
-  const int gb = b + p.b_off;
   const int n_ctiles = min((p.Sq + 127) / 128, MAXC);  // 128-row q tiles (the grain of the BlockMask walk)
   const int sq_pad = ((p.Sq + 127) / 128) * 128;
+  const int n_kvt = (p.Skv + BT - 1) / BT;
+  const int n_items = p.Hkv * p.B * n_kvt;
 
-  volatile int* misc = (volatile int*)(sm + OFF_MISC);  // [0] tmem base, [1] abort, [2] npairs, [3] drain warps leave
+  volatile int* misc = (volatile int*)(sm + OFF_MISC);  // [0] tmem base, [1] abort, [2] unused, [3] drain warps leave
   int* pairs = (int*)(sm + OFF_PAIR);
-  unsigned char* cls = sm + OFF_CLS;
+  int* item_off = (int*)(sm + OFF_ITEM);       // first pair of item i (item_off[n] = total)
+  // set-up scratch over the Q / dO stages (nothing is loaded there before the lists are complete)
+  unsigned char* cls_all = sm + OFF_Q;                       // cls[unit][MAXC]: 0 skip, 1 mask, 2 full
+  int* ucnt = (int*)(sm + OFF_Q + MAXU * MAXC);              // pairs of a unit, then their prefix sums
+
+  // ---- the work of this CTA ------------------------------------------------------------------
+  // An item is the 128-row kv tile of one (batch, kv head); items are numbered with the head
+  // fastest and the kv tile slowest (under a causal mask the heaviest come first).  The grid is a
+  // whole number of waves of CTAs; CTA c takes item c of the first round of gridDim.x items,
+  // item gridDim.x - 1 - c of the second, and so on back and forth, which evens out the sums
+  // when the work per item falls along the numbering.  TMEM, barriers and the pair lists are set
+  // up once per CTA, and the loads of an item run under the tail of the one before.
+  const int Gd = (int)gridDim.x, cta = (int)blockIdx.x;
+  auto item_index = [&](int k) { return k * Gd + ((k & 1) ? Gd - 1 - cta : cta); };
+  int nitems = 0;
+  while (nitems < MAXI && item_index(nitems) < n_items) ++nitems;
+  const bool overflow_items = nitems == MAXI && item_index(MAXI) < n_items;
+  const int nunits = nitems * G;  // a unit: one query head of an item
 
   // ---- set-up --------------------------------------------------------------------------------
   if (tid == 0) {
@@ -262,118 +284,174 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
     fa_mbar_init(bar_addr(sb, BAR_PFREE), 2);  // one arrival from each of the issuers of products 3-4 and 5
     fa_mbar_init(bar_addr(sb, BAR_DQFULL), 1);
     fa_mbar_init(bar_addr(sb, BAR_DQFREE), 128);
-    fa_mbar_init(bar_addr(sb, BAR_FINAL), 1);
+    fa_mbar_init(bar_addr(sb, BAR_FINAL), 2);  // products 3-4 and product 5 of an item's last pair
     fa_mbar_init_fence();
     misc[1] = 0;
     misc[2] = 0;
     misc[3] = 0;
-    // K and V of this CTA's tile do not depend on the pair list: their loads start now and run
-    // while the list is being built
     fa_tma_prefetch_desc(&P.tk);
     fa_tma_prefetch_desc(&P.tv);
-    fa_mbar_expect_tx(bar_addr(sb, BAR_KV), 2 * KV_BYTES);
-    for (int a = 0; a < DATOMS; ++a) {
-      fa_tma_load_4d(sb + OFF_K + a * ATOM_BYTES, &P.tk, bar_addr(sb, BAR_KV), a * 64, n0, hk, b);
-      fa_tma_load_4d(sb + OFF_V + a * ATOM_BYTES, &P.tv, bar_addr(sb, BAR_KV), a * 64, n0, hk, b);
+    fa_tma_prefetch_desc(&P.tq);
+    fa_tma_prefetch_desc(&P.tdo);
+  }
+  // (head, q tile) pairs of every item: each warp classifies the 128-row q tiles of its units
+  // (0 skip, 1 apply mask_mod, 2 full) and counts the pairs; after a prefix sum over the units the
+  // same warp writes the unit's pairs where they belong.  Each listed tile gives 128 / BQ pairs.
+  constexpr int PPT = 128 / BQ;
+  if (nunits <= MAXU) {
+    for (int u = warp; u < nunits; u += NT / 32) {
+      const int it = u / G, g = u - it * G;
+      const int idx = item_index(it);
+      const int hk = idx % p.Hkv, b = (idx / p.Hkv) % p.B, kt = idx / (p.Hkv * p.B);
+      const int h = hk * G + g;
+      unsigned char* cl = cls_all + u * MAXC;
+      ((uint2*)cl)[lane] = make_uint2(0u, 0u);  // MAXC = 256 bytes
+      __syncwarp();
+      if (p.t.kv_num == nullptr || p.t.q_num == nullptr) {
+        for (int t = lane; t < n_ctiles; t += 32) cl[t] = FA_HAS_MASK_MOD ? 1 : 2;
+      } else {
+        // both counts are read before either index list (two round trips to memory, not four)
+        const int bm = p.t.mB == 1 ? 0 : b, hm = p.t.mH == 1 ? 0 : h;
+        const int kvblk = min(kt * BT / p.t.KVB, p.t.nKV - 1);
+        const long long row = ((long long)bm * p.t.mH + hm) * p.t.nKV + kvblk;
+        const int tpb = p.t.nQ == 1 ? n_ctiles : p.t.QB / 128;
+        int num[2];
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+          const int* nump = which ? p.t.full_q_num : p.t.q_num;
+          num[which] = nump != nullptr ? min(max(nump[row], 0), p.t.nQ) * tpb : 0;
+        }
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {
+          const int* idxp = which ? p.t.full_q_idx : p.t.q_idx;
+          for (int e = lane; e < num[which]; e += 32) {
+            const int bi = e / tpb, ti = e - bi * tpb;
+            const int t = min(max(idxp[row * p.t.nQ + bi], 0), p.t.nQ - 1) * tpb + ti;
+            if (t < n_ctiles) cl[t] = (unsigned char)(which ? 2 : 1);
+          }
+          __syncwarp();
+        }
+      }
+      __syncwarp();
+      int cnt = 0;
+      for (int t0 = 0; t0 < n_ctiles; t0 += 32) {
+        const int t = t0 + lane;
+        int n_t = 0;
+        if (t < n_ctiles && cl[t] != 0)
+          for (int v = 0; v < PPT; ++v) n_t += (t * PPT + v) * BQ < p.Sq ? 1 : 0;
+        cnt += __reduce_add_sync(0xffffffffu, n_t);
+      }
+      if (lane == 0) ucnt[u] = cnt;
+    }
+  }
+  __syncthreads();
+  if (warp == 0 && nunits <= MAXU) {
+    // exclusive prefix sums over the units, in place; item_off picks out every G-th
+    int running = 0;
+    for (int u0 = 0; u0 < nunits; u0 += 32) {
+      const int u = u0 + lane;
+      const int v = u < nunits ? ucnt[u] : 0;
+      int inc = v;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, inc, d);
+        if (lane >= d) inc += o;
+      }
+      if (u < nunits) {
+        ucnt[u] = running + inc - v;
+        if (u % G == 0) item_off[u / G] = running + inc - v;
+      }
+      running += __shfl_sync(0xffffffffu, inc, 31);
+    }
+    if (lane == 0) item_off[nitems] = running;
+  }
+  __syncthreads();
+  const int total_pairs = nunits <= MAXU ? item_off[nitems] : MAXP + 1;
+  if (total_pairs > MAXP || overflow_items) {
+    // the host sizes the grid so that the lists fit; a launch that breaks the rule is refused
+    if (tid == 0 && p.status != nullptr) atomicOr(p.status, FA_STATUS_BAD_LAUNCH);
+    return;
+  }
+  for (int u = warp; u < nunits; u += NT / 32) {
+    const int g = u % G;
+    const unsigned char* cl = cls_all + u * MAXC;
+    int w = ucnt[u];
+    for (int t0 = 0; t0 < n_ctiles; t0 += 32) {
+      const int t = t0 + lane;
+      const int c = t < n_ctiles ? (int)cl[t] : 0;
+      int n_t = 0;
+      if (c != 0)
+        for (int v = 0; v < PPT; ++v) n_t += (t * PPT + v) * BQ < p.Sq ? 1 : 0;
+      int inc = n_t;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, inc, d);
+        if (lane >= d) inc += o;
+      }
+      for (int v = 0; v < n_t; ++v) pairs[w + inc - n_t + v] = (t * PPT + v) | (c << 16) | (g << 20);
+      w += __shfl_sync(0xffffffffu, inc, 31);
     }
   }
   if (warp == WARP_MMA) fa_tmem_alloc(sb + OFF_MISC, TMEM_COLS);
-  // (head, q tile) pairs of this kv tile: per head, classify the 128-row q tiles (0 skip, 1 mask,
-  // 2 full); each listed tile gives 128 / BQ pairs
-  int npairs = 0;  // meaningful in thread 0 only
-  for (int g = 0; g < G; ++g) {
-    const int h = hk * G + g;
-    __syncthreads();
-    for (int t = tid; t < MAXC; t += NT) cls[t] = 0;
-    __syncthreads();
-    if (p.t.kv_num == nullptr || p.t.q_num == nullptr) {
-      for (int t = tid; t < n_ctiles; t += NT) cls[t] = FA_HAS_MASK_MOD ? 1 : 2;
-    } else {
-      // both counts and, speculatively, this thread's entry of both index lists are read before any
-      // of them is used: one round trip to memory instead of four dependent ones
-      const int bm = p.t.mB == 1 ? 0 : b, hm = p.t.mH == 1 ? 0 : h;
-      const int kvblk = min(n0 / p.t.KVB, p.t.nKV - 1);
-      const long long row = ((long long)bm * p.t.mH + hm) * p.t.nKV + kvblk;
-      const int tpb = p.t.nQ == 1 ? n_ctiles : p.t.QB / 128;
-      const int bi0 = tid / tpb, ti0 = tid - bi0 * tpb;
-      int num[2], blk[2];
-#pragma unroll
-      for (int which = 0; which < 2; ++which) {
-        const int* nump = which ? p.t.full_q_num : p.t.q_num;
-        const int* idxp = which ? p.t.full_q_idx : p.t.q_idx;
-        num[which] = nump != nullptr ? nump[row] : 0;
-        blk[which] = (nump != nullptr && bi0 < p.t.nQ) ? idxp[row * p.t.nQ + bi0] : 0;
-      }
-#pragma unroll
-      for (int which = 0; which < 2; ++which) {
-        const int* idxp = which ? p.t.full_q_idx : p.t.q_idx;
-        const int n = min(max(num[which], 0), p.t.nQ) * tpb;
-        if (tid < n) {
-          const int t = min(max(blk[which], 0), p.t.nQ - 1) * tpb + ti0;
-          if (t < n_ctiles) cls[t] = (unsigned char)(which ? 2 : 1);
-        }
-        for (int e = tid + NT; e < n; e += NT) {  // (more list entries than threads)
-          const int bi = e / tpb, ti = e - bi * tpb;
-          const int t = min(max(idxp[row * p.t.nQ + bi], 0), p.t.nQ - 1) * tpb + ti;
-          if (t < n_ctiles) cls[t] = (unsigned char)(which ? 2 : 1);
-        }
-      }
-    }
-    __syncthreads();
-    if (tid == 0) {
-      for (int t = 0; t < n_ctiles; ++t) {
-        if (!cls[t]) continue;
-#pragma unroll
-        for (int u = 0; u < 128 / BQ; ++u) {
-          const int qt = t * (128 / BQ) + u;  // BQ-row tile
-          if (qt * BQ < p.Sq && npairs < MAXP) pairs[npairs++] = qt | ((int)cls[t] << 16) | (g << 20);
-        }
-      }
-    }
-  }
-  if (tid == 0) misc[2] = npairs;
+  fence_proxy_async();  // the scratch is given over to the TMA loads of the Q tiles
   fa_tc_fence_before();
   __syncthreads();
   fa_tc_fence_after();
   const fa_u32 tmem = (fa_u32)misc[0];
-  npairs = misc[2];
   volatile int* abort_flag = misc + 1;
   // copies the compiler can see are the same in every lane (read through a broadcast)
   const fa_u32 tmem_u = __shfl_sync(0xffffffffu, tmem, 0);
-  const int npairs_u = __shfl_sync(0xffffffffu, npairs, 0);
+  const int nitems_u = __shfl_sync(0xffffffffu, nitems, 0);
 
   if (warp >= 8) fa_setmaxnreg_dec<REGS_OTHER>();
 
+  // Barrier phases: pair-indexed barriers count the pairs of the CTA across its items (gn);
+  // BAR_KV and BAR_FINAL count the items that have pairs (kvc) - an item without pairs loads no
+  // K / V and only writes zeros.
   if (warp == WARP_PRODUCER) {
     // ================================ producer ================================================
     if (lane == 0) {
-      fa_tma_prefetch_desc(&P.tq);
-      fa_tma_prefetch_desc(&P.tdo);
-      // a CTA without pairs still has to see its K / V loads land before it may exit
-      if (npairs == 0) fa_mbar_wait(bar_addr(sb, BAR_KV), 0, abort_flag);
-    }
-    if (lane == 0) {
       bool ok = true;
-      for (int n = 0; n < npairs && ok; ++n) {
-        const int s = n % NSTAGE;
-        const fa_u32 ph = (fa_u32)((n / NSTAGE) & 1);
-        const int pr = pairs[n];
-        const int m0 = (pr & 0xffff) * BQ, h = hk * G + (pr >> 20);
-        if (n >= NSTAGE) ok = fa_mbar_wait(bar_addr(sb, BAR_DOEMPTY + s), ph ^ 1u, abort_flag);
-        if (!ok) break;
-        // Q and dO tiles plus the per-row scalars of the q tile (prepared by fa_bwd_prep_kernel);
-        // one transaction count covers all the copies
-        const long long rbase = ((long long)b * p.Hq + h) * sq_pad + m0;
-        const fa_u32 full = bar_addr(sb, BAR_QFULL + s);
-        fa_mbar_expect_tx(full, 2 * Q_BYTES + 2 * BQ * 4);
-        for (int a = 0; a < DATOMS; ++a)
-          fa_tma_load_4d(sb + OFF_DO + s * Q_BYTES + a * Q_ATOM_BYTES, &P.tdo, full, a * 64, m0, h, b);
-        if (n >= NSTAGE) ok = fa_mbar_wait(bar_addr(sb, BAR_QEMPTY + s), ph ^ 1u, abort_flag);
-        if (!ok) break;
-        for (int a = 0; a < DATOMS; ++a)
-          fa_tma_load_4d(sb + OFF_Q + s * Q_BYTES + a * Q_ATOM_BYTES, &P.tq, full, a * 64, m0, h, b);
-        fa_bulk_load(sb + OFF_ROW + s * 2 * BQ * 4, P.nlse2 + rbase, BQ * 4, full);
-        fa_bulk_load(sb + OFF_ROW + s * 2 * BQ * 4 + BQ * 4, P.ndelta + rbase, BQ * 4, full);
+      int gn = 0, kvc = 0;
+      for (int it = 0; it < nitems && ok; ++it) {
+        const int p0 = item_off[it], np = item_off[it + 1] - p0;
+        if (np == 0) continue;
+        const int idx = item_index(it);
+        const int hk = idx % p.Hkv, b = (idx / p.Hkv) % p.B, n0 = (idx / (p.Hkv * p.B)) * BT;
+        // The K / V buffers are free once the last products of the previous item are complete;
+        // the Q / dO slots of the item's first pairs free up earlier, so those loads go first.
+        const int kvpos = kvc == 0 ? 0 : min(NSTAGE, np) - 1;
+        for (int n = 0; n < np && ok; ++n, ++gn) {
+          if (n == kvpos) {
+            if (kvc > 0) ok = fa_mbar_wait(bar_addr(sb, BAR_FINAL), (fa_u32)((kvc - 1) & 1), abort_flag);
+            if (!ok) break;
+            fa_mbar_expect_tx(bar_addr(sb, BAR_KV), 2 * KV_BYTES);
+            for (int a = 0; a < DATOMS; ++a) {
+              fa_tma_load_4d(sb + OFF_K + a * ATOM_BYTES, &P.tk, bar_addr(sb, BAR_KV), a * 64, n0, hk, b);
+              fa_tma_load_4d(sb + OFF_V + a * ATOM_BYTES, &P.tv, bar_addr(sb, BAR_KV), a * 64, n0, hk, b);
+            }
+          }
+          const int s = gn % NSTAGE;
+          const fa_u32 ph = (fa_u32)((gn / NSTAGE) & 1);
+          const int pr = pairs[p0 + n];
+          const int m0 = (pr & 0xffff) * BQ, h = hk * G + (pr >> 20);
+          if (gn >= NSTAGE) ok = fa_mbar_wait(bar_addr(sb, BAR_DOEMPTY + s), ph ^ 1u, abort_flag);
+          if (!ok) break;
+          // Q and dO tiles plus the per-row scalars of the q tile (prepared by fa_bwd_prep_kernel);
+          // one transaction count covers all the copies
+          const long long rbase = ((long long)b * p.Hq + h) * sq_pad + m0;
+          const fa_u32 full = bar_addr(sb, BAR_QFULL + s);
+          fa_mbar_expect_tx(full, 2 * Q_BYTES + 2 * BQ * 4);
+          for (int a = 0; a < DATOMS; ++a)
+            fa_tma_load_4d(sb + OFF_DO + s * Q_BYTES + a * Q_ATOM_BYTES, &P.tdo, full, a * 64, m0, h, b);
+          if (gn >= NSTAGE) ok = fa_mbar_wait(bar_addr(sb, BAR_QEMPTY + s), ph ^ 1u, abort_flag);
+          if (!ok) break;
+          for (int a = 0; a < DATOMS; ++a)
+            fa_tma_load_4d(sb + OFF_Q + s * Q_BYTES + a * Q_ATOM_BYTES, &P.tq, full, a * 64, m0, h, b);
+          fa_bulk_load(sb + OFF_ROW + s * 2 * BQ * 4, P.nlse2 + rbase, BQ * 4, full);
+          fa_bulk_load(sb + OFF_ROW + s * 2 * BQ * 4 + BQ * 4, P.ndelta + rbase, BQ * 4, full);
+        }
+        ++kvc;
       }
     }
   } else if (warp == WARP_MMA) {
@@ -383,16 +461,20 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
     //  uniform control flow the descriptors live in uniform registers, which makes each
     //  tcgen05.mma cheaper to issue than from a single-lane branch, and the issue rate of this
     //  one thread is what bounds the tensor core here.
-    if (npairs_u > 0) {
-      const bool leader = fa_elect_one();
-      constexpr fa_u32 IDESC_KK = fa_idesc(DT, 128, BQ, 0, 0);  // A, B K-major, N = BQ
-      constexpr fa_u32 HI = fa_desc_hi_sw128();
-      const fa_u32 loK_k = fa_desc_lo(sb + OFF_K, 16), loV_k = fa_desc_lo(sb + OFF_V, 16);
-      bool ok = fa_mbar_wait_all(bar_addr(sb, BAR_KV), 0, abort_flag);
-      for (int n = 0; n < npairs_u && ok; ++n) {
-        const int s = n % NSTAGE;
-        ok = fa_mbar_wait_all(bar_addr(sb, BAR_QFULL + s), (fa_u32)((n / NSTAGE) & 1), abort_flag);
-        if (ok && n > 0) ok = fa_mbar_wait_all(bar_addr(sb, BAR_SFREE), (fa_u32)((n - 1) & 1), abort_flag);
+    const bool leader = fa_elect_one();
+    constexpr fa_u32 IDESC_KK = fa_idesc(DT, 128, BQ, 0, 0);  // A, B K-major, N = BQ
+    constexpr fa_u32 HI = fa_desc_hi_sw128();
+    const fa_u32 loK_k = fa_desc_lo(sb + OFF_K, 16), loV_k = fa_desc_lo(sb + OFF_V, 16);
+    bool ok = true;
+    int gn = 0, kvc = 0;
+    for (int it = 0; it < nitems_u && ok; ++it) {
+      const int np = __shfl_sync(0xffffffffu, item_off[it + 1] - item_off[it], 0);
+      if (np == 0) continue;
+      ok = fa_mbar_wait_all(bar_addr(sb, BAR_KV), (fa_u32)(kvc & 1), abort_flag);
+      for (int n = 0; n < np && ok; ++n, ++gn) {
+        const int s = gn % NSTAGE;
+        ok = fa_mbar_wait_all(bar_addr(sb, BAR_QFULL + s), (fa_u32)((gn / NSTAGE) & 1), abort_flag);
+        if (ok && gn > 0) ok = fa_mbar_wait_all(bar_addr(sb, BAR_SFREE), (fa_u32)((gn - 1) & 1), abort_flag);
         if (!ok) break;
         fa_tc_fence_after();
         const fa_u32 loQ = fa_desc_lo(sb + OFF_Q + s * Q_BYTES, 16), loDO = fa_desc_lo(sb + OFF_DO + s * Q_BYTES, 16);
@@ -412,25 +494,28 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
           fa_mma_commit(bar_addr(sb, BAR_DOEMPTY + s));
         }
       }
+      ++kvc;
     }
   } else if (warp == WARP_MMA_B) {
     // ================================ MMA issuer B: products 3-4 ===============================
-    if (npairs_u > 0) {
-      const bool leader = fa_elect_one();
-      constexpr fa_u32 IDESC_TN = fa_idesc(DT, 128, D, 0, 1);    // A K-major (TMEM or smem), B MN-major, N = D
-      constexpr fa_u32 HI = fa_desc_hi_sw128();
-      const fa_u32 loDS_k = fa_desc_lo(sb + OFF_DS, 16);
-      bool ok = fa_mbar_wait_all(bar_addr(sb, BAR_KV), 0, abort_flag);
-      for (int n = 0; n < npairs_u && ok; ++n) {
-        const int s = n % NSTAGE;
-        ok = fa_mbar_wait_all(bar_addr(sb, BAR_PREADY), (fa_u32)(n & 1), abort_flag);
+    const bool leader = fa_elect_one();
+    constexpr fa_u32 IDESC_TN = fa_idesc(DT, 128, D, 0, 1);    // A K-major (TMEM or smem), B MN-major, N = D
+    constexpr fa_u32 HI = fa_desc_hi_sw128();
+    const fa_u32 loDS_k = fa_desc_lo(sb + OFF_DS, 16);
+    bool ok = true;
+    int gn = 0;
+    for (int it = 0; it < nitems_u && ok; ++it) {
+      const int np = __shfl_sync(0xffffffffu, item_off[it + 1] - item_off[it], 0);
+      for (int n = 0; n < np && ok; ++n, ++gn) {
+        const int s = gn % NSTAGE;
+        ok = fa_mbar_wait_all(bar_addr(sb, BAR_PREADY), (fa_u32)(gn & 1), abort_flag);
         if (!ok) break;
         fa_tc_fence_after();
         // B operands read MN-major: the D columns are 64-element groups Q_ATOM_BYTES apart, a
         // k-step is 16 q rows = 2048 bytes
         const fa_u32 loQ_mn = fa_desc_lo(sb + OFF_Q + s * Q_BYTES, Q_ATOM_BYTES);
         const fa_u32 loDO_mn = fa_desc_lo(sb + OFF_DO + s * Q_BYTES, Q_ATOM_BYTES);
-        const fa_u32 acc = n > 0;
+        const fa_u32 acc = n > 0;  // the first pair of an item starts its dK and dV
         // 3. dV += P^T dO      (K = BQ q values; A from TMEM)
 #pragma unroll
         for (int kk = 0; kk < BQ / 16; ++kk)
@@ -445,7 +530,7 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
         if (leader) {
           fa_mma_commit(bar_addr(sb, BAR_QEMPTY + s));   // second arrival: the Q tile and row scalars are free
           fa_mma_commit(bar_addr(sb, BAR_PFREE));        // one of the two arrivals that free P^T and dS^T
-          if (n + 1 == npairs_u) fa_mma_commit(bar_addr(sb, BAR_FINAL));
+          if (n + 1 == np) fa_mma_commit(bar_addr(sb, BAR_FINAL));
         }
       }
     }
@@ -453,17 +538,21 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
     // ================================ MMA issuer C: product 5 ==================================
     // (a third issuing warp: what bounds the tensor core in this kernel is how fast one thread
     //  can issue, so the instructions of a pair are spread over three threads)
-    if (npairs_u > 0) {
-      const bool leader = fa_elect_one();
-      constexpr fa_u32 IDESC_NN = fa_idesc(DT, 128, 64, 1, 1);    // A, B MN-major, M = 128, N = 64
-      constexpr fa_u32 HI = fa_desc_hi_sw128();
-      const fa_u32 loK_mn = fa_desc_lo(sb + OFF_K, ATOM_BYTES);
-      const fa_u32 loDS_mn = fa_desc_lo(sb + OFF_DS, ATOM_BYTES);
-      bool ok = fa_mbar_wait_all(bar_addr(sb, BAR_KV), 0, abort_flag);
-      for (int n = 0; n < npairs_u && ok; ++n) {
-        ok = fa_mbar_wait_all(bar_addr(sb, BAR_PREADY), (fa_u32)(n & 1), abort_flag);
+    const bool leader = fa_elect_one();
+    constexpr fa_u32 IDESC_NN = fa_idesc(DT, 128, 64, 1, 1);    // A, B MN-major, M = 128, N = 64
+    constexpr fa_u32 HI = fa_desc_hi_sw128();
+    const fa_u32 loK_mn = fa_desc_lo(sb + OFF_K, ATOM_BYTES);
+    const fa_u32 loDS_mn = fa_desc_lo(sb + OFF_DS, ATOM_BYTES);
+    bool ok = true;
+    int gn = 0, kvc = 0;
+    for (int it = 0; it < nitems_u && ok; ++it) {
+      const int np = __shfl_sync(0xffffffffu, item_off[it + 1] - item_off[it], 0);
+      if (np == 0) continue;
+      ok = fa_mbar_wait_all(bar_addr(sb, BAR_KV), (fa_u32)(kvc & 1), abort_flag);
+      for (int n = 0; n < np && ok; ++n, ++gn) {
+        ok = fa_mbar_wait_all(bar_addr(sb, BAR_PREADY), (fa_u32)(gn & 1), abort_flag);
         // the drain warps must have emptied the dQ columns of the previous pair
-        if (ok && n > 0) ok = fa_mbar_wait_all(bar_addr(sb, BAR_DQFREE), (fa_u32)((n - 1) & 1), abort_flag);
+        if (ok && gn > 0) ok = fa_mbar_wait_all(bar_addr(sb, BAR_DQFREE), (fa_u32)((gn - 1) & 1), abort_flag);
         if (!ok) break;
         fa_tc_fence_after();
         // 5. K = 128 kv rows, a k-step is 16 rows = 2048 bytes of either operand.
@@ -480,42 +569,50 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
         if (leader) {
           fa_mma_commit(bar_addr(sb, BAR_PFREE));
           fa_mma_commit(bar_addr(sb, BAR_DQFULL));
+          if (n + 1 == np) fa_mma_commit(bar_addr(sb, BAR_FINAL));  // (this product is the last reader of K)
         }
       }
+      ++kvc;
     }
   } else if (warp < 8) {
     // ================================ compute warps ============================================
     fa_setmaxnreg_inc<REGS_COMPUTE>();
     const int half = warp >> 2;               // q columns CW*half .. +CW-1 of the pair tile
     const int lane_base = (warp & 3) * 32;
-    const int r = lane_base + lane;           // kv row of this thread
-    const int kv = n0 + r;
-    const bool row_ok = kv < p.Skv;
+    const int r = lane_base + lane;           // kv row of this thread inside the tile
     const fa_u32 t_row = tmem + ((fa_u32)lane_base << 16);
     const float sc2 = p.scale * FA_LOG2E;
     bool ok = true;
-    for (int n = 0; n < npairs && ok; ++n) {
-      const int s = n % NSTAGE;
-      const int pr = pairs[n];
-      const int m0 = (pr & 0xffff) * BQ, mode = (pr >> 16) & 0xf, gh = hk * G + (pr >> 20) + p.h_off;
-      ok = fa_mbar_wait_warp(bar_addr(sb, BAR_SFULL), (fa_u32)(n & 1), abort_flag);
-      if (ok) ok = fa_mbar_wait_warp(bar_addr(sb, BAR_QFULL + s), (fa_u32)((n / NSTAGE) & 1), abort_flag);
-      if (!ok) break;
-      fa_tc_fence_after();
-      const float* rowp = (const float*)(sm + OFF_ROW + s * 2 * BQ * 4);
-      fa_u32 pp[CW / 2], ds[CW / 2];
-      // The CW columns of this thread come in steps of 16 (S^T and dP^T), the loads of a step in
-      // flight while the previous one is computed: few values are live at a time, which leaves
-      // the scheduler registers to overlap the latencies of independent elements (with all the
-      // values loaded up front this loop ran at 28 clocks per element).
-      {
-        const fa_u32 tS = t_row + COL_S + half * CW, tD = t_row + COL_DP + half * CW;
-        const int c0 = half * CW;  // first q column of this thread inside the tile
-        float sA[16], dA[16], sB[16], dB[16];
-        fa_u32 p8[8], d8[8];
-        fa_tmem_ld16(tS, sA);
-        fa_tmem_ld16(tD, dA);
-        fa_tmem_wait_ld();
+    int gn = 0, kvc = 0;
+    for (int it = 0; it < nitems && ok; ++it) {
+      const int p0 = item_off[it], np = item_off[it + 1] - p0;
+      const int idx = item_index(it);
+      const int hk = idx % p.Hkv, b = (idx / p.Hkv) % p.B, n0 = (idx / (p.Hkv * p.B)) * BT;
+      const int gb = b + p.b_off;
+      const int kv = n0 + r;
+      const bool row_ok = kv < p.Skv;
+      for (int n = 0; n < np && ok; ++n, ++gn) {
+        const int s = gn % NSTAGE;
+        const int pr = pairs[p0 + n];
+        const int m0 = (pr & 0xffff) * BQ, mode = (pr >> 16) & 0xf, gh = hk * G + (pr >> 20) + p.h_off;
+        ok = fa_mbar_wait_warp(bar_addr(sb, BAR_SFULL), (fa_u32)(gn & 1), abort_flag);
+        if (ok) ok = fa_mbar_wait_warp(bar_addr(sb, BAR_QFULL + s), (fa_u32)((gn / NSTAGE) & 1), abort_flag);
+        if (!ok) break;
+        fa_tc_fence_after();
+        const float* rowp = (const float*)(sm + OFF_ROW + s * 2 * BQ * 4);
+        fa_u32 pp[CW / 2], ds[CW / 2];
+        // The CW columns of this thread come in steps of 16 (S^T and dP^T), the loads of a step in
+        // flight while the previous one is computed: few values are live at a time, which leaves
+        // the scheduler registers to overlap the latencies of independent elements (with all the
+        // values loaded up front this loop ran at 28 clocks per element).
+        {
+          const fa_u32 tS = t_row + COL_S + half * CW, tD = t_row + COL_DP + half * CW;
+          const int c0 = half * CW;  // first q column of this thread inside the tile
+          float sA[16], dA[16], sB[16], dB[16];
+          fa_u32 p8[8], d8[8];
+          fa_tmem_ld16(tS, sA);
+          fa_tmem_ld16(tD, dA);
+          fa_tmem_wait_ld();
 #define FA_STEP(SC, DC, SN, DN, C, LAST)                                                                   \
   if (!(LAST)) {                                                                                           \
     fa_tmem_ld16(tS + (C) + 16, SN);                                                                       \
@@ -535,58 +632,64 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
     ds[(C) / 2 + e] = d8[e];                                                                               \
   }                                                                                                        \
   if (!(LAST)) fa_tmem_wait_ld();
-        if (CW == 64) {
-          FA_STEP(sA, dA, sB, dB, 0, false)
-          FA_STEP(sB, dB, sA, dA, 16, false)
-          FA_STEP(sA, dA, sB, dB, 32 % CW, false)
-          FA_STEP(sB, dB, sA, dA, 48 % CW, true)
-        } else {
-          FA_STEP(sA, dA, sB, dB, 0, false)
-          FA_STEP(sB, dB, sA, dA, 16, true)
-        }
+          if (CW == 64) {
+            FA_STEP(sA, dA, sB, dB, 0, false)
+            FA_STEP(sB, dB, sA, dA, 16, false)
+            FA_STEP(sA, dA, sB, dB, 32 % CW, false)
+            FA_STEP(sB, dB, sA, dA, 48 % CW, true)
+          } else {
+            FA_STEP(sA, dA, sB, dB, 0, false)
+            FA_STEP(sB, dB, sA, dA, 16, true)
+          }
 #undef FA_STEP
-      }
-      // pin the packed results here: without this the compiler sinks part of the math below the
-      // wait that follows, onto the critical path between two groups of products
+        }
+        // pin the packed results here: without this the compiler sinks part of the math below the
+        // wait that follows, onto the critical path between two groups of products
 #pragma unroll
-      for (int e = 0; e < CW / 2; ++e) asm volatile("" : "+r"(pp[e]), "+r"(ds[e]));
-      // products 3-5 of the previous pair must be done with P^T and dS^T
-      if (n > 0) {
-        ok = fa_mbar_wait_warp(bar_addr(sb, BAR_PFREE), (fa_u32)((n - 1) & 1), abort_flag);
+        for (int e = 0; e < CW / 2; ++e) asm volatile("" : "+r"(pp[e]), "+r"(ds[e]));
+        // products 3-5 of the previous pair must be done with P^T and dS^T
+        if (gn > 0) {
+          ok = fa_mbar_wait_warp(bar_addr(sb, BAR_PFREE), (fa_u32)((gn - 1) & 1), abort_flag);
+          if (!ok) break;
+          fa_tc_fence_after();
+        }
+#pragma unroll
+        for (int i = 0; i < CW / 32; ++i)
+          fa_tmem_st16(t_row + COL_P + half * (CW / 2) + 16 * i, *(const fa_u32(*)[16])(pp + 16 * i));
+        {
+          // dS^T row r: this thread's CW columns are CW / 8 sixteen-byte chunks; chunk ck of a 128-byte
+          // atom row goes to position ck ^ (r & 7) (the 128-byte swizzle of the operand layout)
+#pragma unroll
+          for (int c = 0; c < CW / 8; ++c) {
+            const int col = half * CW + 8 * c;
+            unsigned char* dsrow = sm + OFF_DS + (col >> 6) * ATOM_BYTES + r * 128;
+            uint4 w;
+            w.x = ds[4 * c]; w.y = ds[4 * c + 1]; w.z = ds[4 * c + 2]; w.w = ds[4 * c + 3];
+            *(uint4*)(dsrow + ((((col & 63) >> 3) ^ (r & 7)) * 16)) = w;
+          }
+        }
+        fa_tmem_wait_st();
+        fence_proxy_async();
+        fa_tc_fence_before();
+        fa_mbar_arrive(bar_addr(sb, BAR_PREADY));
+      }
+      if (!ok) break;
+      // ---- dK (scaled) by warps 0-3, dV by warps 4-7, once per item.  The accumulators are read
+      // out before this thread arrives at the next pair's P-ready barrier, which is what the
+      // issuer of the next item's first dV / dK products waits for.
+      if (np > 0) {
+        ok = fa_mbar_wait_warp(bar_addr(sb, BAR_FINAL), (fa_u32)(kvc & 1), abort_flag);
         if (!ok) break;
+        ++kvc;
         fa_tc_fence_after();
       }
-#pragma unroll
-      for (int i = 0; i < CW / 32; ++i)
-        fa_tmem_st16(t_row + COL_P + half * (CW / 2) + 16 * i, *(const fa_u32(*)[16])(pp + 16 * i));
-      {
-        // dS^T row r: this thread's CW columns are CW / 8 sixteen-byte chunks; chunk ck of a 128-byte
-        // atom row goes to position ck ^ (r & 7) (the 128-byte swizzle of the operand layout)
-#pragma unroll
-        for (int c = 0; c < CW / 8; ++c) {
-          const int col = half * CW + 8 * c;
-          unsigned char* dsrow = sm + OFF_DS + (col >> 6) * ATOM_BYTES + r * 128;
-          uint4 w;
-          w.x = ds[4 * c]; w.y = ds[4 * c + 1]; w.z = ds[4 * c + 2]; w.w = ds[4 * c + 3];
-          *(uint4*)(dsrow + ((((col & 63) >> 3) ^ (r & 7)) * 16)) = w;
-        }
-      }
-      fa_tmem_wait_st();
-      fence_proxy_async();
-      fa_tc_fence_before();
-      fa_mbar_arrive(bar_addr(sb, BAR_PREADY));
-    }
-    // ---- epilogue: dK (scaled) by warps 0-3, dV by warps 4-7 ----------------------------------
-    if (ok && npairs > 0) ok = fa_mbar_wait_warp(bar_addr(sb, BAR_FINAL), 0, abort_flag);
-    if (ok) {
-      fa_tc_fence_after();
       const FaTensor& dst = half == 0 ? p.dk : p.dv;
       const float mul = half == 0 ? p.scale : 1.f;
       char* og = (char*)dst.ptr + ((long long)b * dst.sb + (long long)hk * dst.sh + (long long)kv * dst.ss) * 2;
 #pragma unroll
       for (int c = 0; c < D / 32; ++c) {
         float o[32];
-        if (npairs > 0) {
+        if (np > 0) {
           fa_tmem_ld32(t_row + (half == 0 ? COL_DK : COL_DV) + c * 32, o);
           fa_tmem_wait_ld();
         } else {
@@ -614,48 +717,54 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
     const int dtid = tid - 256;
     const int n_qtiles = sq_pad / BQ;
     bool ok = true;
-    for (int n = 0; n < npairs && ok; ++n) {
-      const int pr = pairs[n];
-      const int qt = pr & 0xffff, h = hk * G + (pr >> 20);
-      ok = fa_mbar_wait_warp(bar_addr(sb, BAR_DQFULL), (fa_u32)(n & 1), abort_flag);
-      // The four drain warps meet at named barriers below, so they have to leave this loop together:
-      // a warp whose wait failed says so in a flag only the drain warps write, joins the first
-      // barrier of the pair like the others, and all four read the flag behind that barrier.
-      if (!ok) misc[3] = 1;
-      fa_tc_fence_after();
-      // The 128 x 64 fp32 tile leaves in two halves of 32 columns through one 16 KB staging buffer:
-      // each half is one contiguous 16 KB block of the accumulation buffer.  16-byte chunk k of
-      // lane r goes to position k ^ (r & 7), which spreads the rows of a warp over the banks.
-      float* gdst = P.dq_acc + (((long long)b * p.Hq + h) * n_qtiles + qt) * (128 * 64);
-      unsigned char* strow = sm + OFF_DQ + r * 128;
-      float a[32];
-      if (ok) {
-        fa_tmem_ld32(t_dq, a);
-        fa_tmem_wait_ld();
-      }
-#pragma unroll
-      for (int hf = 0; hf < 2; ++hf) {
-        // the previous bulk reduce must have finished reading the staging buffer
-        if (dtid == 0) bulk_wait_read0();
-        named_bar_sync(1, 128);
-        if (hf == 0 && misc[3] != 0) {
-          ok = false;
-          break;
-        }
-#pragma unroll
-        for (int k = 0; k < 8; ++k)
-          *(float4*)(strow + ((k ^ (r & 7)) * 16)) = make_float4(a[4 * k], a[4 * k + 1], a[4 * k + 2], a[4 * k + 3]);
-        if (hf == 0) {
-          fa_tmem_ld32(t_dq + 32, a);
+    int gn = 0;
+    for (int it = 0; it < nitems && ok; ++it) {
+      const int p0 = item_off[it], np = item_off[it + 1] - p0;
+      const int idx = item_index(it);
+      const int hk = idx % p.Hkv, b = (idx / p.Hkv) % p.B;
+      for (int n = 0; n < np && ok; ++n, ++gn) {
+        const int pr = pairs[p0 + n];
+        const int qt = pr & 0xffff, h = hk * G + (pr >> 20);
+        ok = fa_mbar_wait_warp(bar_addr(sb, BAR_DQFULL), (fa_u32)(gn & 1), abort_flag);
+        // The four drain warps meet at named barriers below, so they have to leave this loop together:
+        // a warp whose wait failed says so in a flag only the drain warps write, joins the first
+        // barrier of the pair like the others, and all four read the flag behind that barrier.
+        if (!ok) misc[3] = 1;
+        fa_tc_fence_after();
+        // The 128 x 64 fp32 tile leaves in two halves of 32 columns through one 16 KB staging buffer:
+        // each half is one contiguous 16 KB block of the accumulation buffer.  16-byte chunk k of
+        // lane r goes to position k ^ (r & 7), which spreads the rows of a warp over the banks.
+        float* gdst = P.dq_acc + (((long long)b * p.Hq + h) * n_qtiles + qt) * (128 * 64);
+        unsigned char* strow = sm + OFF_DQ + r * 128;
+        float a[32];
+        if (ok) {
+          fa_tmem_ld32(t_dq, a);
           fa_tmem_wait_ld();
-          fa_tc_fence_before();
-          fa_mbar_arrive(bar_addr(sb, BAR_DQFREE));
         }
-        fence_proxy_async();
-        named_bar_sync(1, 128);
-        if (dtid == 0) {
-          bulk_reduce_add_f32(gdst + hf * (DQ_HALF_BYTES / 4), sb + OFF_DQ, DQ_HALF_BYTES);
-          bulk_commit();
+#pragma unroll
+        for (int hf = 0; hf < 2; ++hf) {
+          // the previous bulk reduce must have finished reading the staging buffer
+          if (dtid == 0) bulk_wait_read0();
+          named_bar_sync(1, 128);
+          if (hf == 0 && misc[3] != 0) {
+            ok = false;
+            break;
+          }
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            *(float4*)(strow + ((k ^ (r & 7)) * 16)) = make_float4(a[4 * k], a[4 * k + 1], a[4 * k + 2], a[4 * k + 3]);
+          if (hf == 0) {
+            fa_tmem_ld32(t_dq + 32, a);
+            fa_tmem_wait_ld();
+            fa_tc_fence_before();
+            fa_mbar_arrive(bar_addr(sb, BAR_DQFREE));
+          }
+          fence_proxy_async();
+          named_bar_sync(1, 128);
+          if (dtid == 0) {
+            bulk_reduce_add_f32(gdst + hf * (DQ_HALF_BYTES / 4), sb + OFF_DQ, DQ_HALF_BYTES);
+            bulk_commit();
+          }
         }
       }
     }

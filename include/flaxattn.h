@@ -117,6 +117,18 @@ int fa_module_prepare(fa_module* m, int kind, int dtype, int D, int Dv, int Sq_h
 /* Number of kernels compiled (not fetched from a cache) since the library was loaded. */
 int fa_compile_count(void);
 
+/* Self test of the bounded waits.  Every mbarrier wait of the tcgen05 kernels gives up after a time
+ * limit, raises the CTA's abort flag and lets the kernel return with FA_STATUS bit 1 set in the
+ * status word (the reference has no such path: its kernels are scheduled by XLA and cannot wait on
+ * one another, flaxattention/kernel/attention.py:166-205).  This entry point launches one CTA of
+ * two warps that wait, through the same helpers, on a barrier nobody arrives at, with the limit
+ * shortened to `limit_ns` (1 us .. 100 ms).  On return (after the stream has been synchronised by
+ * the caller) *status has bit 1 set, gave_up[0] = 64 threads whose wait reported failure,
+ * gave_up[1] = 0, and *waited_ns is the time thread 0 spent waiting.  All three pointers are
+ * device-accessible memory (device or mapped pinned host memory), zeroed by the caller. */
+int fa_selftest_bounded_wait(unsigned long long limit_ns, int* status, int* gave_up, unsigned long long* waited_ns,
+                             void* stream);
+
 /* Per-kernel device times.  While enabled (process-wide switch), fa_fwd, fa_bwd and fa_decode
  * record a pair of CUDA events around every kernel they launch on the caller's stream; results
  * are unaffected.  fa_profile_read waits for the calling thread's most recent such call to finish
