@@ -597,13 +597,14 @@ __global__ void fa_delta_kernel(FaTensor o, FaTensor dout, float* __restrict__ d
 // row, whatever their order inside a tile): one launch and one pass less than a separate memset.
 template <int DT, int LPR>
 __global__ void fa_bwd_prep_kernel(FaTensor o, FaTensor dout, const float* __restrict__ lse, float* __restrict__ nlse2,
-                                   float* __restrict__ ndelta, float* __restrict__ dq_acc, int Hq, int Sq, int sq_pad,
-                                   int Dv, int D, int n_bh) {
+                                   float* __restrict__ ndelta, float* __restrict__ dq_acc, int* __restrict__ work_counter,
+                                   int Hq, int Sq, int sq_pad, int Dv, int D, int n_bh) {
   // grid: x over the padded rows of one (batch, head), LPR lanes per row; (y, z) over the heads
   constexpr int EPC = 8;
   const int bh = blockIdx.y + blockIdx.z * gridDim.y;
   const int gt = blockIdx.x * blockDim.x + threadIdx.x;
   const int q = gt / LPR, sub = gt % LPR;
+  if (work_counter != nullptr && gt == 0 && bh == 0) *work_counter = 0;  // the item counter of the backward kernel
   const bool in_range = bh < n_bh && q < sq_pad;
   const long long row = (long long)bh * sq_pad + q;
   if (dq_acc != nullptr && in_range) {
@@ -1003,10 +1004,11 @@ int launch_fwd_tc(fa_module* m, const fa_attn_params* p, const FaParams& kp, voi
 // ---- tcgen05 backward ----------------------------------------------------------------------
 struct FaBwdTcParamsHost {
   FaParams p;
-  FaTensorMapHost tq, tk, tv, tdo;
+  FaTensorMapHost tq, tk, tv, tdo, tdk, tdv;
   float* dq_acc;
   const float* nlse2;
   const float* ndelta;
+  int* work_counter;
 };
 
 // SMs of the current device (148 on a B200; asked once per device)
@@ -1021,34 +1023,19 @@ int device_sm_count() {
   return n;
 }
 
-// limits of the pair lists of fa_bwd_tc.cuh (fa_btc::MAXP, MAXI, MAXU)
-int bwd_tc_max_pairs(int D) { return D == 64 ? 2048 : 4096; }
-constexpr int kBwdTcMaxItems = 64, kBwdTcMaxUnits = 256;
-
-// CTAs of the persistent backward: whole waves of one CTA per SM, as few as keep every CTA's pair
-// lists inside their limits when every q tile of every item is listed (the host cannot see how
-// sparse the tables are).
-int bwd_tc_grid(const fa_attn_params* p, int sm_count) {
-  const int G = p->Hq / p->Hkv;
-  const long long n_items = (long long)p->Hkv * p->B * ((p->Skv + 127) / 128);
-  const long long worst = (long long)((p->Sq + 127) / 128) * (p->D / 64) * G;  // pairs of one item
-  long long ipc = std::min<long long>(kBwdTcMaxItems, std::min<long long>(kBwdTcMaxUnits / G, bwd_tc_max_pairs(p->D) / worst));
-  if (ipc < 1) ipc = 1;
-  const long long per_wave = (long long)sm_count * ipc;
-  const long long waves = (n_items + per_wave - 1) / per_wave;
-  return (int)std::min<long long>(n_items, waves * sm_count);
-}
+// pairs one item of fa_bwd_tc.cuh may list (fa_btc::MAXPL)
+int bwd_tc_max_pairs(int D) { return D == 64 ? 1024 : 2048; }
 
 bool tc_bwd_eligible(const fa_attn_params* p) {
   if (p->flags & FA_FLAG_GENERAL_KERNELS) return false;
   if (p->dtype == FA_F32) return false;
   if (p->D != p->Dv || !(p->D == 64 || p->D == 128)) return false;
   if (p->Sq < 128 || p->Skv < 128) return false;
-  // a CTA lists the (query head, q tile) pairs of its items in shared memory: at most 256 q tiles
+  // a CTA lists the (query head, q tile) pairs of an item in shared memory: at most 256 q tiles
   // of 128 rows per head, and the pairs of one item must fit the list (a pair is 128 q rows with
   // D = 64, 64 with D = 128)
   const int n_qtiles = (p->Sq + 127) / 128;
-  if (n_qtiles > 256 || p->Hq / p->Hkv > kBwdTcMaxUnits) return false;
+  if (n_qtiles > 256) return false;
   if ((long long)n_qtiles * (p->D / 64) * (p->Hq / p->Hkv) > bwd_tc_max_pairs(p->D)) return false;
   const fa_block_tables& t = p->tables;
   if (t.kv_num_blocks) {
@@ -1072,7 +1059,7 @@ int get_bwd_tc_kernel(fa_module* m, int dtype, int D, int flags, Kernel** k) {
   const int nstage = D == 64 ? 4 : 3, bq = D == 64 ? 128 : 64;
   const int kv_bytes = (D / 64) * 16384, q_bytes = 16384, ds_bytes = (bq / 64) * 16384;
   const int smem = 2 * kv_bytes + 2 * nstage * q_bytes + ds_bytes + 128 * 32 * 4 + nstage * 2 * bq * 4 +
-                   (1 + 3 * nstage + 7) * 8 + 16 + bwd_tc_max_pairs(D) * 4 + (kBwdTcMaxItems + 1) * 4 + 1024;
+                   (1 + 3 * nstage + 12) * 8 + 16 + 16 + 2 * bwd_tc_max_pairs(D) * 4 + 256 + 1024;
   std::string d = defs({{"FA_DTYPE", dtype}, {"FA_D", D}, {"FA_ROUND_SCORES", round_flag(dtype, flags)}});
   return get_kernel(m, "fa_bwd_tc.cuh", d, "fa_bwd_tc_kernel", smem, k);
 }
@@ -1135,7 +1122,7 @@ int fa_fwd(fa_module* m, const fa_attn_params* p, void* stream) {
 
 size_t fa_bwd_workspace_bytes(const fa_attn_params* p) {
   if (!p || p->B <= 0 || p->Hq <= 0 || p->Sq <= 0) return 0;
-  if (p->Hkv > 0 && p->Hq % p->Hkv == 0 && tc_bwd_eligible(p)) return 2 * rows_pad_bytes(p) + dq_acc_bytes(p);
+  if (p->Hkv > 0 && p->Hq % p->Hkv == 0 && tc_bwd_eligible(p)) return 2 * rows_pad_bytes(p) + dq_acc_bytes(p) + 256;
   return delta_bytes(p);
 }
 
@@ -1176,6 +1163,7 @@ int fa_bwd(fa_module* m, const fa_attn_params* p, const fa_tensor* dout, const f
     float* nlse2 = (float*)workspace;
     float* ndelta = (float*)((char*)workspace + rows_pad_bytes(p));
     float* dq_acc = (float*)((char*)workspace + 2 * rows_pad_bytes(p));
+    int* work_counter = (int*)((char*)workspace + 2 * rows_pad_bytes(p) + dq_acc_bytes(p));  // zeroed by the prep kernel
     const int sq_pad = (p->Sq + 127) / 128 * 128;
     const int n_bh = p->B * p->Hq;
     const int gy = n_bh < 32768 ? n_bh : 32768;
@@ -1184,9 +1172,9 @@ int fa_bwd(fa_module* m, const fa_attn_params* p, const fa_tensor* dout, const f
       const dim3 grid((unsigned)((sq_pad * 8 + 255) / 256), (unsigned)gy, (unsigned)((n_bh + gy - 1) / gy));
       ProfScope prof("fa_bwd_prep_kernel", stream);
       if (p->dtype == FA_F16)
-        fa_bwd_prep_kernel<FA_F16, 8><<<grid, 256, 0, st>>>(kp.o, kp.dout, p->lse, nlse2, ndelta, dq_acc, p->Hq, p->Sq, sq_pad, p->Dv, p->D, n_bh);
+        fa_bwd_prep_kernel<FA_F16, 8><<<grid, 256, 0, st>>>(kp.o, kp.dout, p->lse, nlse2, ndelta, dq_acc, work_counter, p->Hq, p->Sq, sq_pad, p->Dv, p->D, n_bh);
       else
-        fa_bwd_prep_kernel<FA_BF16, 8><<<grid, 256, 0, st>>>(kp.o, kp.dout, p->lse, nlse2, ndelta, dq_acc, p->Hq, p->Sq, sq_pad, p->Dv, p->D, n_bh);
+        fa_bwd_prep_kernel<FA_BF16, 8><<<grid, 256, 0, st>>>(kp.o, kp.dout, p->lse, nlse2, ndelta, dq_acc, work_counter, p->Hq, p->Sq, sq_pad, p->Dv, p->D, n_bh);
       FA_CUDA_CHECK(cudaGetLastError());
     }
     FaBwdTcParamsHost tp;
@@ -1194,12 +1182,17 @@ int fa_bwd(fa_module* m, const fa_attn_params* p, const fa_tensor* dout, const f
     tp.dq_acc = dq_acc;
     tp.nlse2 = nlse2;
     tp.ndelta = ndelta;
+    tp.work_counter = work_counter;
     const int bq = p->D == 64 ? 128 : 64;  // q rows of a (kv tile, q tile) pair of the kernel
     if (int rc = make_map(&tp.tq, p->dtype, p->q, p->D, p->Sq, p->Hq, p->B, bq)) return rc;
     if (int rc = make_map(&tp.tk, p->dtype, p->k, p->D, p->Skv, p->Hkv, p->B)) return rc;
     if (int rc = make_map(&tp.tv, p->dtype, p->v, p->Dv, p->Skv, p->Hkv, p->B)) return rc;
     if (int rc = make_map(&tp.tdo, p->dtype, *dout, p->Dv, p->Sq, p->Hq, p->B, bq)) return rc;
-    if (int rc = launch(ktc, dim3((unsigned)bwd_tc_grid(p, device_sm_count())), dim3(512), &tp, stream)) return rc;
+    if (int rc = make_map(&tp.tdk, p->dtype, *dk, p->D, p->Skv, p->Hkv, p->B)) return rc;
+    if (int rc = make_map(&tp.tdv, p->dtype, *dv, p->Dv, p->Skv, p->Hkv, p->B)) return rc;
+    // persistent: one CTA per SM (fewer when there are fewer items), items handed out through the counter
+    const long long n_items = (long long)p->Hkv * p->B * ((p->Skv + 127) / 128);
+    if (int rc = launch(ktc, dim3((unsigned)std::min<long long>(n_items, device_sm_count())), dim3(512), &tp, stream)) return rc;
     {
       // one 16-byte output chunk per thread: D / 8 chunks per row
       const dim3 grid((unsigned)(((long long)sq_pad * (p->D / 8) + 255) / 256), (unsigned)gy, (unsigned)((n_bh + gy - 1) / gy));

@@ -6,9 +6,9 @@
 // exponentials.
 //
 // The unit of work (an item) is a 128-row kv tile of one (batch, kv head) together with the q tiles
-// of the query heads that share it.  The kernel is persistent: the grid is a whole number of
-// waves of CTAs, every CTA works through several items, and TMEM, the barriers and the pair
-// lists are set up once per CTA.  A pair is 128 kv rows x BQ query rows, BQ = 128 with D = 64 and 64 with
+// of the query heads that share it.  The kernel is persistent: one CTA per SM, every CTA works
+// through items it takes from a counter in global memory, and TMEM and the barriers are set up
+// once per CTA.  A pair is 128 kv rows x BQ query rows, BQ = 128 with D = 64 and 64 with
 // D = 128 (the 512 TMEM columns hold two D-wide accumulators, dK and dV, next to the pair's
 // score tiles only for the smaller q tile).  Everything is kept transposed so that dK and dV
 // have kv rows (TMEM lanes) and P^T can be fed to the tensor core straight from TMEM:
@@ -23,10 +23,10 @@
 // Either way the dQ tile of a pair is 128 TMEM lanes x 64 columns of fp32.  It leaves through a
 // staging buffer and two bulk reduce-adds into an fp32 accumulation buffer (summation order
 // over kv tiles is not fixed; a small kernel scales, un-permutes and converts it afterwards).
-// dK and dV are written once at the end.
+// dK and dV are written once per item.
 //
 // Warp roles (16 warps): 0-3 and 4-7 compute (first / second half of the q columns of the pair),
-// 8-11 dQ drain, 12 TMA producer, 13 MMA issuer A (products 1-2, TMEM owner), 14 MMA issuer B
+// 8-11 drain (dQ of every pair, dK / dV of every item), 12 producer (pair lists and TMA loads), 13 MMA issuer A (products 1-2, TMEM owner), 14 MMA issuer B
 // (products 3-4), 15 MMA issuer C (product 5).
 // S^T/dP^T of pair n+1 are issued as soon as the compute warps hold pair n in registers, so
 // the tensor core runs ahead of the element-wise work.
@@ -46,9 +46,11 @@
 struct FaBwdTcParams {
   FaParams p;
   FaTensorMap tq, tk, tv, tdo;  // 4-d maps (D, S, H, B), 128-byte swizzle; box 64 x 128 rows (k, v), 64 x BQ rows (q, do)
+  FaTensorMap tdk, tdv;         // the outputs dK and dV, like tk and tv
   float* dq_acc;                // per (b, h, BQ-row q tile): two [128 lanes][32 columns] fp32 blocks, 16-byte chunks of a row permuted
   const float* nlse2;           // [B, Hq, ceil(Sq/128)*128]: -lse * log2(e); -inf for rows without mass / beyond Sq
   const float* ndelta;          // same shape: -rowsum(O * dO); 0 beyond Sq
+  int* work_counter;            // zero at launch: items beyond the first of every CTA are handed out through it
 };
 
 namespace fa_btc {
@@ -66,10 +68,8 @@ constexpr int Q_ATOM_BYTES = BQ * 128;               // BQ rows x 128 bytes
 constexpr int Q_BYTES = DATOMS * Q_ATOM_BYTES;       // one Q or dO tile (16 KB in both configurations)
 constexpr int DS_ATOMS = BQ / 64;                    // dS^T: [128 kv][BQ q] as atoms of 64 q columns
 constexpr int NSTAGE = D == 64 ? 4 : 3;
-constexpr int MAXP = D == 64 ? 2048 : 4096;  // (head, q tile) pairs of all the items of a CTA (what shared memory leaves room for)
+constexpr int MAXPL = D == 64 ? 1024 : 2048;  // (head, q tile) pairs of one item (two such lists fit in shared memory)
 constexpr int MAXC = 256;                // 128-row q tiles per head (Sq <= 32768)
-constexpr int MAXI = 64;                 // items (kv tiles) per CTA
-constexpr int MAXU = 256;                // units (item, query head of the group) per CTA
 constexpr int NT = 512;
 constexpr int WARP_PRODUCER = 12, WARP_MMA = 13, WARP_MMA_B = 14, WARP_MMA_C = 15;
 // Register split (setmaxnreg): the kernel starts with 128 registers per thread (65536 / 512).  The
@@ -88,13 +88,12 @@ constexpr int OFF_DQ = OFF_DS + DS_ATOMS * ATOM_BYTES;      // fp32 staging 128 
 constexpr int DQ_HALF_BYTES = 128 * 32 * 4;
 constexpr int OFF_ROW = OFF_DQ + DQ_HALF_BYTES;             // NSTAGE x (nlse2[BQ], ndelta[BQ]) floats
 constexpr int OFF_BAR = OFF_ROW + NSTAGE * 2 * BQ * 4;
-constexpr int NBARS = 1 + 3 * NSTAGE + 7;
+constexpr int NBARS = 1 + 3 * NSTAGE + 12;
 constexpr int OFF_MISC = OFF_BAR + NBARS * 8;               // tmem base, abort, -, drain flag
-constexpr int OFF_PAIR = OFF_MISC + 16;                     // int pair[MAXP]: q tile | mode << 16 | g << 20
-constexpr int OFF_ITEM = OFF_PAIR + MAXP * 4;               // int item_off[MAXI + 1]
-constexpr int SMEM_BYTES = OFF_ITEM + (MAXI + 1) * 4 + 1024;
-// set-up scratch (tile classes and pair counts of the units) lies over the Q and dO stages
-static_assert(MAXU * MAXC + (MAXU + 1) * 4 <= 2 * NSTAGE * Q_BYTES, "set-up scratch");
+constexpr int OFF_ITEM = OFF_MISC + 16;                     // int item[2][2]: item number, pairs (-1: no more work)
+constexpr int OFF_PAIR = OFF_ITEM + 16;                     // int pair[2][MAXPL]: q tile | mode << 16 | g << 20
+constexpr int OFF_CLS = OFF_PAIR + 2 * MAXPL * 4;           // uchar cls[MAXC] (scratch of the list builder)
+constexpr int SMEM_BYTES = OFF_CLS + MAXC + 1024;
 static_assert(SMEM_BYTES <= 227 * 1024, "shared memory");
 constexpr int TMEM_COLS = 512;
 constexpr int COL_S = 0, COL_DP = BQ, COL_P = 2 * BQ;
@@ -113,7 +112,11 @@ constexpr int BAR_PREADY = BAR_SFULL + 2;   // P^T in TMEM and dS^T in smem (256
 constexpr int BAR_PFREE = BAR_SFULL + 3;    // products 3-5 of the pair are complete
 constexpr int BAR_DQFULL = BAR_SFULL + 4;   // dQ of the pair is in TMEM
 constexpr int BAR_DQFREE = BAR_SFULL + 5;   // drain warps hold it in registers (128 arrivals)
-constexpr int BAR_FINAL = BAR_SFULL + 6;
+constexpr int BAR_FINAL = BAR_SFULL + 6;    // products 3-5 of an item's last pair are complete
+constexpr int BAR_DKVFREE = BAR_SFULL + 7;  // the drain warps have read dK and dV of an item out of TMEM (128 arrivals)
+constexpr int BAR_LISTFULL = BAR_SFULL + 8; // [2] the producer has published an item and its pair list
+constexpr int BAR_LISTFREE = BAR_SFULL + 10;  // [2] the 15 consumers of a list are done with it
+constexpr int LIST_CONSUMERS = 3 + 8 + 4;   // MMA issuers, compute warps, drain warps (one arrival each)
 
 __device__ __forceinline__ fa_u32 bar_addr(fa_u32 sb, int i) { return sb + OFF_BAR + i * 8; }
 
@@ -128,6 +131,11 @@ __device__ __forceinline__ void bulk_reduce_add_f32(float* gdst, fa_u32 ssrc, fa
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// brings a tile into L2 ahead of the load that will need it
+__device__ __forceinline__ void tma_prefetch_l2_4d(const FaTensorMap* map, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
 
 // byte offset (in 16-byte units) of k-step kk of a K-major operand whose 64-element column groups
 // are `atom_bytes` apart: 32 bytes per step inside a 128-byte row, four steps per group
@@ -226,6 +234,71 @@ __device__ __forceinline__ void chunk(const float (&s)[W], const float (&dp)[W],
 #endif
 }
 
+
+// The (query head, q tile) pairs of one item, written to `pl` by one warp: per head of the group,
+// the 128-row q tiles the BlockMask lists for the item's kv tile (class 1: apply mask_mod, 2: full)
+// in ascending order, each as 128 / BQ pairs.  Without tables every tile is listed.  Returns the
+// number of pairs (the same in every lane).  `cl` is MAXC bytes of scratch.
+__device__ __forceinline__ int build_pair_list(const FaParams& p, int hk, int b, int kt, int G, int n_ctiles,
+                                               unsigned char* cl, int* pl, int lane) {
+  constexpr int PPT = 128 / BQ;
+  const bool tables = p.t.kv_num != nullptr && p.t.q_num != nullptr;
+  int w = 0;
+  for (int g = 0; g < G; ++g) {
+    if (!tables) {
+      const int nq = (p.Sq + BQ - 1) / BQ;
+      const int mode = FA_HAS_MASK_MOD ? 1 : 2;
+      for (int e = lane; e < nq && w + e < MAXPL; e += 32) pl[w + e] = e | (mode << 16) | (g << 20);
+      w += nq;
+      continue;
+    }
+    const int h = hk * G + g;
+    ((uint2*)cl)[lane] = make_uint2(0u, 0u);  // MAXC = 256 bytes
+    __syncwarp();
+    {
+      // both counts are read before either index list (two round trips to memory, not four)
+      const int bm = p.t.mB == 1 ? 0 : b, hm = p.t.mH == 1 ? 0 : h;
+      const int kvblk = min(kt * BT / p.t.KVB, p.t.nKV - 1);
+      const long long row = ((long long)bm * p.t.mH + hm) * p.t.nKV + kvblk;
+      const int tpb = p.t.nQ == 1 ? n_ctiles : p.t.QB / 128;
+      int num[2];
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        const int* nump = which ? p.t.full_q_num : p.t.q_num;
+        num[which] = nump != nullptr ? min(max(nump[row], 0), p.t.nQ) * tpb : 0;
+      }
+#pragma unroll
+      for (int which = 0; which < 2; ++which) {
+        const int* idxp = which ? p.t.full_q_idx : p.t.q_idx;
+        for (int e = lane; e < num[which]; e += 32) {
+          const int bi = e / tpb, ti = e - bi * tpb;
+          const int t = min(max(idxp[row * p.t.nQ + bi], 0), p.t.nQ - 1) * tpb + ti;
+          if (t < n_ctiles) cl[t] = (unsigned char)(which ? 2 : 1);
+        }
+        __syncwarp();
+      }
+    }
+    for (int t0 = 0; t0 < n_ctiles; t0 += 32) {
+      const int t = t0 + lane;
+      const int c = t < n_ctiles ? (int)cl[t] : 0;
+      int n_t = 0;
+      if (c != 0)
+        for (int v = 0; v < PPT; ++v) n_t += (t * PPT + v) * BQ < p.Sq ? 1 : 0;
+      int inc = n_t;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const int o = __shfl_up_sync(0xffffffffu, inc, d);
+        if (lane >= d) inc += o;
+      }
+      for (int v = 0; v < n_t; ++v)
+        if (w + inc - n_t + v < MAXPL) pl[w + inc - n_t + v] = (t * PPT + v) | (c << 16) | (g << 20);
+      w += __shfl_sync(0xffffffffu, inc, 31);
+    }
+    __syncwarp();
+  }
+  return min(w, MAXPL);
+}
+
 }  // namespace fa_btc
 
 extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(const __grid_constant__ FaBwdTcParams P) {
@@ -248,27 +321,19 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
   const int sq_pad = ((p.Sq + 127) / 128) * 128;
   const int n_kvt = (p.Skv + BT - 1) / BT;
   const int n_items = p.Hkv * p.B * n_kvt;
+  const int Gd = (int)gridDim.x, cta = (int)blockIdx.x;
 
   volatile int* misc = (volatile int*)(sm + OFF_MISC);  // [0] tmem base, [1] abort, [2] unused, [3] drain warps leave
-  int* pairs = (int*)(sm + OFF_PAIR);
-  int* item_off = (int*)(sm + OFF_ITEM);       // first pair of item i (item_off[n] = total)
-  // set-up scratch over the Q / dO stages (nothing is loaded there before the lists are complete)
-  unsigned char* cls_all = sm + OFF_Q;                       // cls[unit][MAXC]: 0 skip, 1 mask, 2 full
-  int* ucnt = (int*)(sm + OFF_Q + MAXU * MAXC);              // pairs of a unit, then their prefix sums
+  int* pairs = (int*)(sm + OFF_PAIR);                   // two lists of MAXPL pairs
+  volatile int* item = (volatile int*)(sm + OFF_ITEM);  // per list: item number, pairs
 
-  // ---- the work of this CTA ------------------------------------------------------------------
   // An item is the 128-row kv tile of one (batch, kv head); items are numbered with the head
-  // fastest and the kv tile slowest (under a causal mask the heaviest come first).  The grid is a
-  // whole number of waves of CTAs; CTA c takes item c of the first round of gridDim.x items,
-  // item gridDim.x - 1 - c of the second, and so on back and forth, which evens out the sums
-  // when the work per item falls along the numbering.  TMEM, barriers and the pair lists are set
-  // up once per CTA, and the loads of an item run under the tail of the one before.
-  const int Gd = (int)gridDim.x, cta = (int)blockIdx.x;
-  auto item_index = [&](int k) { return k * Gd + ((k & 1) ? Gd - 1 - cta : cta); };
-  int nitems = 0;
-  while (nitems < MAXI && item_index(nitems) < n_items) ++nitems;
-  const bool overflow_items = nitems == MAXI && item_index(MAXI) < n_items;
-  const int nunits = nitems * G;  // a unit: one query head of an item
+  // fastest and the kv tile slowest (under a causal mask the heaviest come first).  The kernel is
+  // persistent: CTA c starts with item c and takes further items from a counter in global memory,
+  // so TMEM, the barriers and the descriptors are set up once per CTA, the loads of an item run
+  // under the tail of the one before, and the CTAs stay level whatever the mask does to the work
+  // per item.  The producer warp builds the pair list of the next item (two lists in shared
+  // memory) while the others work on the current one.
 
   // ---- set-up --------------------------------------------------------------------------------
   if (tid == 0) {
@@ -285,6 +350,11 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
     fa_mbar_init(bar_addr(sb, BAR_DQFULL), 1);
     fa_mbar_init(bar_addr(sb, BAR_DQFREE), 128);
     fa_mbar_init(bar_addr(sb, BAR_FINAL), 2);  // products 3-4 and product 5 of an item's last pair
+    fa_mbar_init(bar_addr(sb, BAR_DKVFREE), 128);
+    for (int i = 0; i < 2; ++i) {
+      fa_mbar_init(bar_addr(sb, BAR_LISTFULL + i), 1);
+      fa_mbar_init(bar_addr(sb, BAR_LISTFREE + i), LIST_CONSUMERS);
+    }
     fa_mbar_init_fence();
     misc[1] = 0;
     misc[2] = 0;
@@ -294,130 +364,47 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
     fa_tma_prefetch_desc(&P.tq);
     fa_tma_prefetch_desc(&P.tdo);
   }
-  // (head, q tile) pairs of every item: each warp classifies the 128-row q tiles of its units
-  // (0 skip, 1 apply mask_mod, 2 full) and counts the pairs; after a prefix sum over the units the
-  // same warp writes the unit's pairs where they belong.  Each listed tile gives 128 / BQ pairs.
-  constexpr int PPT = 128 / BQ;
-  if (nunits <= MAXU) {
-    for (int u = warp; u < nunits; u += NT / 32) {
-      const int it = u / G, g = u - it * G;
-      const int idx = item_index(it);
-      const int hk = idx % p.Hkv, b = (idx / p.Hkv) % p.B, kt = idx / (p.Hkv * p.B);
-      const int h = hk * G + g;
-      unsigned char* cl = cls_all + u * MAXC;
-      ((uint2*)cl)[lane] = make_uint2(0u, 0u);  // MAXC = 256 bytes
-      __syncwarp();
-      if (p.t.kv_num == nullptr || p.t.q_num == nullptr) {
-        for (int t = lane; t < n_ctiles; t += 32) cl[t] = FA_HAS_MASK_MOD ? 1 : 2;
-      } else {
-        // both counts are read before either index list (two round trips to memory, not four)
-        const int bm = p.t.mB == 1 ? 0 : b, hm = p.t.mH == 1 ? 0 : h;
-        const int kvblk = min(kt * BT / p.t.KVB, p.t.nKV - 1);
-        const long long row = ((long long)bm * p.t.mH + hm) * p.t.nKV + kvblk;
-        const int tpb = p.t.nQ == 1 ? n_ctiles : p.t.QB / 128;
-        int num[2];
-#pragma unroll
-        for (int which = 0; which < 2; ++which) {
-          const int* nump = which ? p.t.full_q_num : p.t.q_num;
-          num[which] = nump != nullptr ? min(max(nump[row], 0), p.t.nQ) * tpb : 0;
-        }
-#pragma unroll
-        for (int which = 0; which < 2; ++which) {
-          const int* idxp = which ? p.t.full_q_idx : p.t.q_idx;
-          for (int e = lane; e < num[which]; e += 32) {
-            const int bi = e / tpb, ti = e - bi * tpb;
-            const int t = min(max(idxp[row * p.t.nQ + bi], 0), p.t.nQ - 1) * tpb + ti;
-            if (t < n_ctiles) cl[t] = (unsigned char)(which ? 2 : 1);
-          }
-          __syncwarp();
-        }
-      }
-      __syncwarp();
-      int cnt = 0;
-      for (int t0 = 0; t0 < n_ctiles; t0 += 32) {
-        const int t = t0 + lane;
-        int n_t = 0;
-        if (t < n_ctiles && cl[t] != 0)
-          for (int v = 0; v < PPT; ++v) n_t += (t * PPT + v) * BQ < p.Sq ? 1 : 0;
-        cnt += __reduce_add_sync(0xffffffffu, n_t);
-      }
-      if (lane == 0) ucnt[u] = cnt;
-    }
-  }
-  __syncthreads();
-  if (warp == 0 && nunits <= MAXU) {
-    // exclusive prefix sums over the units, in place; item_off picks out every G-th
-    int running = 0;
-    for (int u0 = 0; u0 < nunits; u0 += 32) {
-      const int u = u0 + lane;
-      const int v = u < nunits ? ucnt[u] : 0;
-      int inc = v;
-#pragma unroll
-      for (int d = 1; d < 32; d <<= 1) {
-        const int o = __shfl_up_sync(0xffffffffu, inc, d);
-        if (lane >= d) inc += o;
-      }
-      if (u < nunits) {
-        ucnt[u] = running + inc - v;
-        if (u % G == 0) item_off[u / G] = running + inc - v;
-      }
-      running += __shfl_sync(0xffffffffu, inc, 31);
-    }
-    if (lane == 0) item_off[nitems] = running;
-  }
-  __syncthreads();
-  const int total_pairs = nunits <= MAXU ? item_off[nitems] : MAXP + 1;
-  if (total_pairs > MAXP || overflow_items) {
-    // the host sizes the grid so that the lists fit; a launch that breaks the rule is refused
-    if (tid == 0 && p.status != nullptr) atomicOr(p.status, FA_STATUS_BAD_LAUNCH);
-    return;
-  }
-  for (int u = warp; u < nunits; u += NT / 32) {
-    const int g = u % G;
-    const unsigned char* cl = cls_all + u * MAXC;
-    int w = ucnt[u];
-    for (int t0 = 0; t0 < n_ctiles; t0 += 32) {
-      const int t = t0 + lane;
-      const int c = t < n_ctiles ? (int)cl[t] : 0;
-      int n_t = 0;
-      if (c != 0)
-        for (int v = 0; v < PPT; ++v) n_t += (t * PPT + v) * BQ < p.Sq ? 1 : 0;
-      int inc = n_t;
-#pragma unroll
-      for (int d = 1; d < 32; d <<= 1) {
-        const int o = __shfl_up_sync(0xffffffffu, inc, d);
-        if (lane >= d) inc += o;
-      }
-      for (int v = 0; v < n_t; ++v) pairs[w + inc - n_t + v] = (t * PPT + v) | (c << 16) | (g << 20);
-      w += __shfl_sync(0xffffffffu, inc, 31);
-    }
-  }
   if (warp == WARP_MMA) fa_tmem_alloc(sb + OFF_MISC, TMEM_COLS);
-  fence_proxy_async();  // the scratch is given over to the TMA loads of the Q tiles
   fa_tc_fence_before();
   __syncthreads();
   fa_tc_fence_after();
   const fa_u32 tmem = (fa_u32)misc[0];
   volatile int* abort_flag = misc + 1;
-  // copies the compiler can see are the same in every lane (read through a broadcast)
+  // a copy the compiler can see is the same in every lane (read through a broadcast)
   const fa_u32 tmem_u = __shfl_sync(0xffffffffu, tmem, 0);
-  const int nitems_u = __shfl_sync(0xffffffffu, nitems, 0);
 
   if (warp >= 8) fa_setmaxnreg_dec<REGS_OTHER>();
 
-  // Barrier phases: pair-indexed barriers count the pairs of the CTA across its items (gn);
-  // BAR_KV and BAR_FINAL count the items that have pairs (kvc) - an item without pairs loads no
-  // K / V and only writes zeros.
+  // Barrier phases: the pair-indexed barriers count the pairs of the CTA across its items (gn);
+  // BAR_KV, BAR_FINAL and BAR_DKVFREE count the items that have pairs (kvc) - an item without
+  // pairs loads no K / V and only has zeros written; the list barriers count all items (itc).
   if (warp == WARP_PRODUCER) {
     // ================================ producer ================================================
-    if (lane == 0) {
-      bool ok = true;
-      int gn = 0, kvc = 0;
-      for (int it = 0; it < nitems && ok; ++it) {
-        const int p0 = item_off[it], np = item_off[it + 1] - p0;
-        if (np == 0) continue;
-        const int idx = item_index(it);
-        const int hk = idx % p.Hkv, b = (idx / p.Hkv) % p.B, n0 = (idx / (p.Hkv * p.B)) * BT;
+    // The whole warp builds the lists; lane 0 issues the loads.
+    bool ok = true;
+    int gn = 0, kvc = 0;
+    int idx = cta;
+    for (int itc = 0; ok; ++itc) {
+      const int lb = itc & 1;
+      // the consumers of the list that was in this buffer two items ago must be done with it
+      if (itc >= 2) ok = fa_mbar_wait_warp(bar_addr(sb, BAR_LISTFREE + lb), (fa_u32)(((itc >> 1) - 1) & 1), abort_flag);
+      if (!ok) break;
+      int* pl = pairs + lb * MAXPL;
+      const int hk = idx % p.Hkv, b = (idx / p.Hkv) % p.B, kt = idx / (p.Hkv * p.B);
+      int np = -1;
+      if (idx < n_items) np = build_pair_list(p, hk, b, kt, G, n_ctiles, sm + OFF_CLS, pl, lane);
+      if (lane == 0) {
+        item[2 * lb] = idx;
+        item[2 * lb + 1] = np;
+      }
+      __syncwarp();
+      if (lane == 0) fa_mbar_arrive(bar_addr(sb, BAR_LISTFULL + lb));
+      if (np < 0) break;
+      int next = 0;
+      if (lane == 0) {
+        // the next item is asked for now: the answer is not needed before this item's loads are out
+        next = Gd + atomicAdd(P.work_counter, 1);
+        const int n0 = kt * BT;
         // The K / V buffers are free once the last products of the previous item are complete;
         // the Q / dO slots of the item's first pairs free up earlier, so those loads go first.
         const int kvpos = kvc == 0 ? 0 : min(NSTAGE, np) - 1;
@@ -433,7 +420,7 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
           }
           const int s = gn % NSTAGE;
           const fa_u32 ph = (fa_u32)((gn / NSTAGE) & 1);
-          const int pr = pairs[p0 + n];
+          const int pr = pl[n];
           const int m0 = (pr & 0xffff) * BQ, h = hk * G + (pr >> 20);
           if (gn >= NSTAGE) ok = fa_mbar_wait(bar_addr(sb, BAR_DOEMPTY + s), ph ^ 1u, abort_flag);
           if (!ok) break;
@@ -451,8 +438,20 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
           fa_bulk_load(sb + OFF_ROW + s * 2 * BQ * 4, P.nlse2 + rbase, BQ * 4, full);
           fa_bulk_load(sb + OFF_ROW + s * 2 * BQ * 4 + BQ * 4, P.ndelta + rbase, BQ * 4, full);
         }
-        ++kvc;
+        // K and V of the next item are asked into L2 now; their loads can only start when this
+        // item is complete, and then they find the tiles close by
+        if (ok && next < n_items) {
+          const int hk2 = next % p.Hkv, b2 = (next / p.Hkv) % p.B, n2 = (next / (p.Hkv * p.B)) * BT;
+          for (int a = 0; a < DATOMS; ++a) {
+            tma_prefetch_l2_4d(&P.tk, a * 64, n2, hk2, b2);
+            tma_prefetch_l2_4d(&P.tv, a * 64, n2, hk2, b2);
+          }
+        }
       }
+      if (np > 0) ++kvc;
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      gn = __shfl_sync(0xffffffffu, gn, 0);
+      idx = __shfl_sync(0xffffffffu, next, 0);
     }
   } else if (warp == WARP_MMA) {
     // ================================ MMA issuer A: products 1-2 ===============================
@@ -467,8 +466,13 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
     const fa_u32 loK_k = fa_desc_lo(sb + OFF_K, 16), loV_k = fa_desc_lo(sb + OFF_V, 16);
     bool ok = true;
     int gn = 0, kvc = 0;
-    for (int it = 0; it < nitems_u && ok; ++it) {
-      const int np = __shfl_sync(0xffffffffu, item_off[it + 1] - item_off[it], 0);
+    for (int itc = 0; ok; ++itc) {
+      const int lb = itc & 1;
+      ok = fa_mbar_wait_all(bar_addr(sb, BAR_LISTFULL + lb), (fa_u32)((itc >> 1) & 1), abort_flag);
+      if (!ok) break;
+      const int np = __shfl_sync(0xffffffffu, item[2 * lb + 1], 0);
+      if (leader) fa_mbar_arrive(bar_addr(sb, BAR_LISTFREE + lb));  // (the issuers need the count only)
+      if (np < 0) break;
       if (np == 0) continue;
       ok = fa_mbar_wait_all(bar_addr(sb, BAR_KV), (fa_u32)(kvc & 1), abort_flag);
       for (int n = 0; n < np && ok; ++n, ++gn) {
@@ -503,12 +507,21 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
     constexpr fa_u32 HI = fa_desc_hi_sw128();
     const fa_u32 loDS_k = fa_desc_lo(sb + OFF_DS, 16);
     bool ok = true;
-    int gn = 0;
-    for (int it = 0; it < nitems_u && ok; ++it) {
-      const int np = __shfl_sync(0xffffffffu, item_off[it + 1] - item_off[it], 0);
+    int gn = 0, kvc = 0;
+    for (int itc = 0; ok; ++itc) {
+      const int lb = itc & 1;
+      ok = fa_mbar_wait_all(bar_addr(sb, BAR_LISTFULL + lb), (fa_u32)((itc >> 1) & 1), abort_flag);
+      if (!ok) break;
+      const int np = __shfl_sync(0xffffffffu, item[2 * lb + 1], 0);
+      if (leader) fa_mbar_arrive(bar_addr(sb, BAR_LISTFREE + lb));
+      if (np < 0) break;
+      if (np == 0) continue;
       for (int n = 0; n < np && ok; ++n, ++gn) {
         const int s = gn % NSTAGE;
         ok = fa_mbar_wait_all(bar_addr(sb, BAR_PREADY), (fa_u32)(gn & 1), abort_flag);
+        // the first products of an item overwrite dV and dK: the drain warps must have read the
+        // previous item's out of TMEM
+        if (ok && n == 0 && kvc > 0) ok = fa_mbar_wait_all(bar_addr(sb, BAR_DKVFREE), (fa_u32)((kvc - 1) & 1), abort_flag);
         if (!ok) break;
         fa_tc_fence_after();
         // B operands read MN-major: the D columns are 64-element groups Q_ATOM_BYTES apart, a
@@ -533,6 +546,7 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
           if (n + 1 == np) fa_mma_commit(bar_addr(sb, BAR_FINAL));
         }
       }
+      ++kvc;
     }
   } else if (warp == WARP_MMA_C) {
     // ================================ MMA issuer C: product 5 ==================================
@@ -545,8 +559,13 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
     const fa_u32 loDS_mn = fa_desc_lo(sb + OFF_DS, ATOM_BYTES);
     bool ok = true;
     int gn = 0, kvc = 0;
-    for (int it = 0; it < nitems_u && ok; ++it) {
-      const int np = __shfl_sync(0xffffffffu, item_off[it + 1] - item_off[it], 0);
+    for (int itc = 0; ok; ++itc) {
+      const int lb = itc & 1;
+      ok = fa_mbar_wait_all(bar_addr(sb, BAR_LISTFULL + lb), (fa_u32)((itc >> 1) & 1), abort_flag);
+      if (!ok) break;
+      const int np = __shfl_sync(0xffffffffu, item[2 * lb + 1], 0);
+      if (leader) fa_mbar_arrive(bar_addr(sb, BAR_LISTFREE + lb));
+      if (np < 0) break;
       if (np == 0) continue;
       ok = fa_mbar_wait_all(bar_addr(sb, BAR_KV), (fa_u32)(kvc & 1), abort_flag);
       for (int n = 0; n < np && ok; ++n, ++gn) {
@@ -583,17 +602,21 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
     const fa_u32 t_row = tmem + ((fa_u32)lane_base << 16);
     const float sc2 = p.scale * FA_LOG2E;
     bool ok = true;
-    int gn = 0, kvc = 0;
-    for (int it = 0; it < nitems && ok; ++it) {
-      const int p0 = item_off[it], np = item_off[it + 1] - p0;
-      const int idx = item_index(it);
+    int gn = 0;
+    for (int itc = 0; ok; ++itc) {
+      const int lb = itc & 1;
+      ok = fa_mbar_wait_warp(bar_addr(sb, BAR_LISTFULL + lb), (fa_u32)((itc >> 1) & 1), abort_flag);
+      if (!ok) break;
+      const int idx = item[2 * lb], np = item[2 * lb + 1];
+      if (np < 0) break;
+      const int* pl = pairs + lb * MAXPL;
       const int hk = idx % p.Hkv, b = (idx / p.Hkv) % p.B, n0 = (idx / (p.Hkv * p.B)) * BT;
       const int gb = b + p.b_off;
       const int kv = n0 + r;
       const bool row_ok = kv < p.Skv;
       for (int n = 0; n < np && ok; ++n, ++gn) {
         const int s = gn % NSTAGE;
-        const int pr = pairs[p0 + n];
+        const int pr = pl[n];
         const int m0 = (pr & 0xffff) * BQ, mode = (pr >> 16) & 0xf, gh = hk * G + (pr >> 20) + p.h_off;
         ok = fa_mbar_wait_warp(bar_addr(sb, BAR_SFULL), (fa_u32)(gn & 1), abort_flag);
         if (ok) ok = fa_mbar_wait_warp(bar_addr(sb, BAR_QFULL + s), (fa_u32)((gn / NSTAGE) & 1), abort_flag);
@@ -674,62 +697,41 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
         fa_mbar_arrive(bar_addr(sb, BAR_PREADY));
       }
       if (!ok) break;
-      // ---- dK (scaled) by warps 0-3, dV by warps 4-7, once per item.  The accumulators are read
-      // out before this thread arrives at the next pair's P-ready barrier, which is what the
-      // issuer of the next item's first dV / dK products waits for.
-      if (np > 0) {
-        ok = fa_mbar_wait_warp(bar_addr(sb, BAR_FINAL), (fa_u32)(kvc & 1), abort_flag);
-        if (!ok) break;
-        ++kvc;
-        fa_tc_fence_after();
-      }
-      const FaTensor& dst = half == 0 ? p.dk : p.dv;
-      const float mul = half == 0 ? p.scale : 1.f;
-      char* og = (char*)dst.ptr + ((long long)b * dst.sb + (long long)hk * dst.sh + (long long)kv * dst.ss) * 2;
-#pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        float o[32];
-        if (np > 0) {
-          fa_tmem_ld32(t_row + (half == 0 ? COL_DK : COL_DV) + c * 32, o);
-          fa_tmem_wait_ld();
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) o[e] = 0.f;
-        }
-        if (row_ok) {
-#pragma unroll
-          for (int e = 0; e < 32; e += 8) {
-            uint4 w;
-            w.x = fa_pack2<DT>(o[e] * mul, o[e + 1] * mul);
-            w.y = fa_pack2<DT>(o[e + 2] * mul, o[e + 3] * mul);
-            w.z = fa_pack2<DT>(o[e + 4] * mul, o[e + 5] * mul);
-            w.w = fa_pack2<DT>(o[e + 6] * mul, o[e + 7] * mul);
-            *(uint4*)(og + (c * 32 + e) * 2) = w;
-          }
-        }
-      }
+      // every lane has read its last list entry: the list may be overwritten
+      __syncwarp();
+      if (lane == 0) fa_mbar_arrive(bar_addr(sb, BAR_LISTFREE + lb));
     }
   } else if (warp < 12) {
-    // ================================ dQ drain warps ===========================================
+    // ================================ drain warps: dQ of every pair, dK / dV of every item =======
     const int lane_base = (warp & 3) * 32;
-    const int r = lane_base + lane;  // TMEM lane: q row of the pair (D = 64) or head-dim index (D = 128)
-    const fa_u32 t_dq = tmem + ((fa_u32)lane_base << 16) + COL_DQ;
+    const int r = lane_base + lane;  // TMEM lane: q row of the pair (D = 64) or head-dim index (D = 128); kv row for dK / dV
+    const fa_u32 t_lane = tmem + ((fa_u32)lane_base << 16);
+    const fa_u32 t_dq = t_lane + COL_DQ;
     const int dtid = tid - 256;
     const int n_qtiles = sq_pad / BQ;
     bool ok = true;
-    int gn = 0;
-    for (int it = 0; it < nitems && ok; ++it) {
-      const int p0 = item_off[it], np = item_off[it + 1] - p0;
-      const int idx = item_index(it);
-      const int hk = idx % p.Hkv, b = (idx / p.Hkv) % p.B;
+    int gn = 0, kvc = 0;
+    for (int itc = 0; ok; ++itc) {
+      const int lb = itc & 1;
+      // The four drain warps meet at named barriers, so they have to leave their loops together: a
+      // warp whose wait failed says so in a flag only the drain warps write, joins the next named
+      // barrier like the others, and all four read the flag behind that barrier.
+      ok = fa_mbar_wait_warp(bar_addr(sb, BAR_LISTFULL + lb), (fa_u32)((itc >> 1) & 1), abort_flag);
+      if (!ok) misc[3] = 1;
+      named_bar_sync(1, 128);
+      if (misc[3] != 0) {
+        ok = false;
+        break;
+      }
+      const int idx = item[2 * lb], np = item[2 * lb + 1];
+      if (np < 0) break;  // (the same in all four warps)
+      const int* pl = pairs + lb * MAXPL;
+      const int hk = idx % p.Hkv, b = (idx / p.Hkv) % p.B, n0 = (idx / (p.Hkv * p.B)) * BT;
       for (int n = 0; n < np && ok; ++n, ++gn) {
-        const int pr = pairs[p0 + n];
+        const int pr = pl[n];
         const int qt = pr & 0xffff, h = hk * G + (pr >> 20);
         ok = fa_mbar_wait_warp(bar_addr(sb, BAR_DQFULL), (fa_u32)(gn & 1), abort_flag);
-        // The four drain warps meet at named barriers below, so they have to leave this loop together:
-        // a warp whose wait failed says so in a flag only the drain warps write, joins the first
-        // barrier of the pair like the others, and all four read the flag behind that barrier.
-        if (!ok) misc[3] = 1;
+        if (!ok) misc[3] = 1;  // (read by all four warps behind the first barrier of the pair)
         fa_tc_fence_after();
         // The 128 x 64 fp32 tile leaves in two halves of 32 columns through one 16 KB staging buffer:
         // each half is one contiguous 16 KB block of the accumulation buffer.  16-byte chunk k of
@@ -767,6 +769,68 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
           }
         }
       }
+      if (!ok) break;
+      // ---- dK (scaled) and dV of the item.  A thread owns one kv row (TMEM lane); 64 columns at a
+      // time are converted into the staging buffer in the layout of a K tile (128-byte rows, 16-byte
+      // chunk k of row r at k ^ (r & 7)) and leave through one tensor-map store, which writes whole
+      // lines and clips the rows beyond Skv.  (Each thread storing its own row straight to global
+      // memory took several thousand cycles per item: 32 different lines per instruction.)
+      // An item without pairs has zeros written.
+      if (np > 0) {
+        ok = fa_mbar_wait_warp(bar_addr(sb, BAR_FINAL), (fa_u32)(kvc & 1), abort_flag);
+        if (!ok) misc[3] = 1;
+        named_bar_sync(1, 128);
+        if (misc[3] != 0) {
+          ok = false;
+          break;
+        }
+        fa_tc_fence_after();
+      }
+      {
+        unsigned char* strow = sm + OFF_DQ + r * 128;
+#pragma unroll 1
+        for (int part = 0; part < 2 * DATOMS; ++part) {
+          const int which = part / DATOMS, a = part - which * DATOMS;  // dK atoms first, then dV
+          const float mul = which == 0 ? p.scale : 1.f;
+          // the previous bulk operation must have finished reading the staging buffer
+          if (dtid == 0) bulk_wait_read0();
+          named_bar_sync(1, 128);
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            float o[16];
+            if (np > 0) {
+              fa_tmem_ld16(t_lane + (which == 0 ? COL_DK : COL_DV) + a * 64 + c * 16, o);
+              fa_tmem_wait_ld();
+            } else {
+#pragma unroll
+              for (int e = 0; e < 16; ++e) o[e] = 0.f;
+            }
+#pragma unroll
+            for (int e = 0; e < 16; e += 8) {
+              uint4 w;
+              w.x = fa_pack2<DT>(o[e] * mul, o[e + 1] * mul);
+              w.y = fa_pack2<DT>(o[e + 2] * mul, o[e + 3] * mul);
+              w.z = fa_pack2<DT>(o[e + 4] * mul, o[e + 5] * mul);
+              w.w = fa_pack2<DT>(o[e + 6] * mul, o[e + 7] * mul);
+              *(uint4*)(strow + (((2 * c + (e >> 3)) ^ (r & 7)) * 16)) = w;
+            }
+          }
+          if (part == 2 * DATOMS - 1 && np > 0) {
+            // dK and dV are out of TMEM: the next item's first products may overwrite them
+            fa_tc_fence_before();
+            fa_mbar_arrive(bar_addr(sb, BAR_DKVFREE));
+          }
+          fence_proxy_async();
+          named_bar_sync(1, 128);
+          if (dtid == 0) {
+            fa_tma_store_4d(which == 0 ? &P.tdk : &P.tdv, sb + OFF_DQ, a * 64, n0, hk, b);
+            bulk_commit();
+          }
+        }
+      }
+      if (np > 0) ++kvc;
+      __syncwarp();
+      if (lane == 0) fa_mbar_arrive(bar_addr(sb, BAR_LISTFREE + lb));
     }
     if (dtid == 0) bulk_wait0();
   }

@@ -121,6 +121,12 @@ __device__ __forceinline__ void fa_bulk_load(fa_u32 dst, const void* src, fa_u32
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
 }
+// tile store shared -> global (bulk async-group completion; rows beyond the tensor are clipped)
+__device__ __forceinline__ void fa_tma_store_4d(const FaTensorMap* map, fa_u32 src, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               ::"l"(map), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
 __device__ __forceinline__ void fa_tma_prefetch_desc(const FaTensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
