@@ -896,7 +896,7 @@ struct alignas(64) FaTensorMapHost {
 static_assert(sizeof(FaTensorMapHost) == sizeof(CUtensorMap), "tensor map size");
 struct FaTcParamsHost {
   FaParams p;
-  FaTensorMapHost tq, tk, tv;
+  FaTensorMapHost tq, tk, tv, to;
 };
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -984,6 +984,7 @@ int launch_decode_tc(fa_module* m, const fa_attn_params* p, const FaParams& kp, 
   if (int rc = make_map(&tp.tq, p->dtype, p->q, p->D, p->Sq, p->Hq, p->B, 64)) return rc;  // the queries go into a tile twice
   if (int rc = make_map(&tp.tk, p->dtype, p->k, p->D, p->Skv, p->Hkv, p->B)) return rc;
   if (int rc = make_map(&tp.tv, p->dtype, p->v, p->Dv, p->Skv, p->Hkv, p->B)) return rc;
+  memset(&tp.to, 0, sizeof(tp.to));  // (the decode variant writes partial results, not the output)
   return launch(k, dim3(num_splits, p->Hq, p->B), dim3(384), &tp, stream);
 }
 
@@ -995,6 +996,7 @@ int launch_fwd_tc(fa_module* m, const fa_attn_params* p, const FaParams& kp, voi
   if (int rc = make_map(&tp.tq, p->dtype, p->q, p->D, p->Sq, p->Hq, p->B)) return rc;
   if (int rc = make_map(&tp.tk, p->dtype, p->k, p->D, p->Skv, p->Hkv, p->B)) return rc;
   if (int rc = make_map(&tp.tv, p->dtype, p->v, p->Dv, p->Skv, p->Hkv, p->B)) return rc;
+  if (int rc = make_map(&tp.to, p->dtype, p->o, p->Dv, p->Sq, p->Hq, p->B)) return rc;
   // Heads vary fastest and the query tile pair slowest (the kernel walks the pairs from the last one
   // down), so that under a causal mask the CTAs with the most kv tiles are dispatched first for
   // all heads: longest-first order keeps the tail of the grid short.

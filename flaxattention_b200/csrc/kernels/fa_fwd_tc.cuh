@@ -34,6 +34,7 @@
 struct FaTcParams {
   FaParams p;
   FaTensorMap tq, tk, tv;  // 4-d maps (D, S, H, B), box 64 x 128 x 1 x 1, 128-byte swizzle
+  FaTensorMap to;          // the output, like tq (unused by the decode variant, which writes partial results)
 };
 
 namespace fa_tc {
@@ -813,23 +814,32 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
       }
     }
 #else
-    if (ok) {
-      fa_tc_fence_after();
-      // a row that never saw an unmasked key has no mass (its sum may hold the tiny values the
-      // polynomial exponential returns for -inf): its output is 0
-      const float inv = (l > 0.f && m_ref != FA_NEG_INF) ? 1.f / l : 0.f;
-      char* og = (char*)p.o.ptr + ((long long)b * p.o.sb + (long long)h * p.o.sh + (long long)qi * p.o.ss) * 2;
+    {
+      // The output tile leaves through the shared memory of this warpgroup's query tile, which
+      // nothing reads any more (every S product of the tile is complete): each thread converts its
+      // row into the layout of the tile (128-byte rows, 16-byte chunk k of row r at k ^ (r & 7)) and
+      // one tensor-map store per 64 columns writes whole lines and clips the rows beyond Sq.  (Each
+      // thread storing its own row to global memory costs 32 different lines per instruction.)
+      // All four warps of the warpgroup reach the barrier below, whatever happened before: every
+      // earlier wait is bounded.
+      // (a tile without kv steps: nothing has waited for the load of the query tile yet)
+      if (ok && cnt == 0) ok = fa_mbar_wait_warp(bar_addr(sb, BAR_Q), 0, abort_flag);
+      if (ok) {
+        fa_tc_fence_after();
+        // a row that never saw an unmasked key has no mass (its sum may hold the tiny values the
+        // polynomial exponential returns for -inf): its output is 0
+        const float inv = (l > 0.f && m_ref != FA_NEG_INF) ? 1.f / l : 0.f;
 #pragma unroll
-      for (int c = 0; c < D / 32; ++c) {
-        float o[32];
-        if (cnt > 0) {
-          fa_tmem_ld32(t_o + c * 32, o);
-          fa_tmem_wait_ld();
-        } else {
+        for (int c = 0; c < D / 32; ++c) {
+          float o[32];
+          if (cnt > 0) {
+            fa_tmem_ld32(t_o + c * 32, o);
+            fa_tmem_wait_ld();
+          } else {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) o[e] = 0.f;
-        }
-        if (qi < p.Sq) {
+            for (int e = 0; e < 32; ++e) o[e] = 0.f;
+          }
+          unsigned char* strow = sm + (i * ATOMS + (c >> 1)) * ATOM_BYTES + r * 128;
 #pragma unroll
           for (int e = 0; e < 32; e += 8) {
             uint4 w;
@@ -837,12 +847,19 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
             w.y = fa_pack2<DT>(o[e + 2] * inv, o[e + 3] * inv);
             w.z = fa_pack2<DT>(o[e + 4] * inv, o[e + 5] * inv);
             w.w = fa_pack2<DT>(o[e + 6] * inv, o[e + 7] * inv);
-            *(uint4*)(og + (c * 32 + e) * 2) = w;
+            *(uint4*)(strow + ((((c & 1) * 4 + (e >> 3)) ^ (r & 7)) * 16)) = w;
           }
         }
+        if (p.lse != nullptr && qi < p.Sq)
+          p.lse[((long long)b * p.Hq + h) * p.Sq + qi] = (l > 0.f && m_ref != FA_NEG_INF) ? (m_ref + fa_lg2(l)) * FA_LN2 : FA_NEG_INF;
       }
-      if (p.lse != nullptr && qi < p.Sq)
-        p.lse[((long long)b * p.Hq + h) * p.Sq + qi] = (l > 0.f && m_ref != FA_NEG_INF) ? (m_ref + fa_lg2(l)) * FA_LN2 : FA_NEG_INF;
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      asm volatile("bar.sync %0, 128;" ::"r"(3 + i) : "memory");
+      if ((warp & 3) == 0 && lane == 0 && *abort_flag == 0 && m0 + i * BM < p.Sq) {
+        for (int a = 0; a < ATOMS; ++a) fa_tma_store_4d(&P.to, sb + (i * ATOMS + a) * ATOM_BYTES, a * 64, m0 + i * BM, h, b);
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");  // the tile must outlive the reads of the store
+      }
     }
 #endif
   }
