@@ -520,7 +520,7 @@ def bench_strong(bench, fa, shard_for, rank, world, dev, pk, steps):
         bench.barrier()
         if name == "cfg2":
             ent["note"] = (f"a shard is B={nb} x H={nh}: {nb * nh * (w['Sq'] // 256)} forward CTAs and "
-                           f"{nb * nh * (w['Skv'] // 128)} backward CTAs for 148 SMs")
+                           f"{nb * nh * (w['Skv'] // 128)} backward items (kv tiles) for 148 SMs")
         out[name] = ent
     return out
 
