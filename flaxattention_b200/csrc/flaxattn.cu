@@ -599,28 +599,47 @@ template <int DT, int LPR>
 __global__ void fa_bwd_prep_kernel(FaTensor o, FaTensor dout, const float* __restrict__ lse, float* __restrict__ nlse2,
                                    float* __restrict__ ndelta, float* __restrict__ dq_acc, int* __restrict__ work_counter,
                                    int Hq, int Sq, int sq_pad, int Dv, int D, int n_bh) {
-  // grid: x over the padded rows of one (batch, head), LPR lanes per row; (y, z) over the heads
-  constexpr int EPC = 8;
+  // grid: x over groups of R * (256 / LPR) padded rows of one (batch, head), LPR lanes per row; (y, z) over the heads.
+  // A thread works on R rows, 256 / LPR apart, and has the loads of all of them in flight before it uses the first
+  // (Dv <= 128: at most two 16-byte pieces of O and of dO per lane and row).
+  constexpr int R = 4, ROWS = 256 / LPR;
   const int bh = blockIdx.y + blockIdx.z * gridDim.y;
-  const int gt = blockIdx.x * blockDim.x + threadIdx.x;
-  const int q = gt / LPR, sub = gt % LPR;
-  if (work_counter != nullptr && gt == 0 && bh == 0) *work_counter = 0;  // the item counter of the backward kernel
-  const bool in_range = bh < n_bh && q < sq_pad;
-  const long long row = (long long)bh * sq_pad + q;
-  if (dq_acc != nullptr && in_range) {
-    float4* z = (float4*)(dq_acc + row * D);
-    for (int i = sub; i < D / 4; i += LPR) z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
-  }
-  float acc = 0.f;
-  const bool valid = in_range && q < Sq;
-  if (valid) {
-    const int b = bh / Hq, h = bh - b * Hq;
+  const int rloc = threadIdx.x / LPR, sub = threadIdx.x % LPR;
+  const int q0 = blockIdx.x * (R * ROWS) + rloc;
+  if (work_counter != nullptr && blockIdx.x == 0 && threadIdx.x == 0 && bh == 0) *work_counter = 0;  // the item counter of the backward kernel
+  if (bh >= n_bh) return;
+  const int b = bh / Hq, h = bh - b * Hq;
+  const int nc = Dv / 8;  // 16-byte pieces per row
+  uint4 a[R][2], d[R][2];
+  float l[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int q = q0 + r * ROWS;
+    const bool valid = q < Sq;
     const char* po = (const char*)o.ptr + ((long long)b * o.sb + (long long)h * o.sh + (long long)q * o.ss) * 2;
     const char* pd = (const char*)dout.ptr + ((long long)b * dout.sb + (long long)h * dout.sh + (long long)q * dout.ss) * 2;
-    for (int c = sub; c * EPC < Dv; c += LPR) {
-      const uint4 a = *(const uint4*)(po + c * 16);
-      const uint4 d = *(const uint4*)(pd + c * 16);
-      const unsigned aw[4] = {a.x, a.y, a.z, a.w}, dw[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const int c = sub + k * LPR;
+      const bool have = valid && c < nc;
+      a[r][k] = have ? *(const uint4*)(po + c * 16) : make_uint4(0u, 0u, 0u, 0u);
+      d[r][k] = have ? *(const uint4*)(pd + c * 16) : make_uint4(0u, 0u, 0u, 0u);
+    }
+    l[r] = (valid && sub == 0) ? lse[(long long)bh * Sq + q] : 0.f;
+  }
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int q = q0 + r * ROWS;
+    if (q >= sq_pad) continue;  // (whole lanes groups of a row leave together)
+    const long long row = (long long)bh * sq_pad + q;
+    if (dq_acc != nullptr) {
+      float4* z = (float4*)(dq_acc + row * D);
+      for (int i = sub; i < D / 4; i += LPR) z[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float acc = 0.f;
+#pragma unroll
+    for (int k = 0; k < 2; ++k) {
+      const unsigned aw[4] = {a[r][k].x, a[r][k].y, a[r][k].z, a[r][k].w}, dw[4] = {d[r][k].x, d[r][k].y, d[r][k].z, d[r][k].w};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         if (DT == FA_F16) {
@@ -633,17 +652,13 @@ __global__ void fa_bwd_prep_kernel(FaTensor o, FaTensor dout, const float* __res
         }
       }
     }
-  }
 #pragma unroll
-  for (int off = LPR / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-  if (in_range && sub == 0) {
-    float nl = -INFINITY;
-    if (valid) {
-      const float l = lse[(long long)bh * Sq + q];
-      nl = (l == -INFINITY) ? -INFINITY : -l * 1.4426950408889634f;
+    for (int off = LPR / 2; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    if (sub == 0) {
+      const bool valid = q < Sq;
+      nlse2[row] = (valid && l[r] != -INFINITY) ? -l[r] * 1.4426950408889634f : -INFINITY;
+      ndelta[row] = valid ? -acc : 0.f;
     }
-    nlse2[row] = nl;
-    ndelta[row] = valid ? -acc : 0.f;
   }
 }
 
@@ -1171,7 +1186,8 @@ int fa_bwd(fa_module* m, const fa_attn_params* p, const fa_tensor* dout, const f
     const int gy = n_bh < 32768 ? n_bh : 32768;
     {
       // row scalars; the same pass clears the dQ accumulator
-      const dim3 grid((unsigned)((sq_pad * 8 + 255) / 256), (unsigned)gy, (unsigned)((n_bh + gy - 1) / gy));
+      // 8 lanes per row, 4 rows per thread: 128 rows per block (sq_pad is a multiple of 128)
+      const dim3 grid((unsigned)(sq_pad / 128), (unsigned)gy, (unsigned)((n_bh + gy - 1) / gy));
       ProfScope prof("fa_bwd_prep_kernel", stream);
       if (p->dtype == FA_F16)
         fa_bwd_prep_kernel<FA_F16, 8><<<grid, 256, 0, st>>>(kp.o, kp.dout, p->lse, nlse2, ndelta, dq_acc, work_counter, p->Hq, p->Sq, sq_pad, p->Dv, p->D, n_bh);

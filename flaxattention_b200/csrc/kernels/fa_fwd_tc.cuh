@@ -160,18 +160,38 @@ __device__ __forceinline__ void mod_chunk(float (&v)[32], int n0, int qi, int gb
   }
 }
 // mask_mod (on tiles the BlockMask lists as partial) and the end of the sequence (ragged last
-// tile): masked scores become -inf.  Only the few tiles that need it come here.
-template <int C0>
-__device__ __forceinline__ void mask_chunk(float (&v)[32], bool use_mask, int n0, int qi, int gb, int gh, int Skv) {
+// tile): masked scores become -inf.  Only the few tiles that need it come here, so the code is
+// kept small rather than fast: a rolled loop evaluates the mask of this thread's columns into
+// one word per 32 columns, and the words are applied to the registers.  (A second copy of the whole step with the
+// mask evaluated in line, per element and fully unrolled, made a masked step take 12-15k clocks
+// against 3.5k for a plain one: the step no longer fitted the instruction cache.)
+template <int NW>
+__device__ __forceinline__ void mask_bits(fa_u32 (&w)[NW], bool use_mask, int kv0, int qi, int gb, int gh, int Skv) {
+  // the end of the sequence alone needs no loop: word c covers keys kv0 + 32 c .. + 31
 #pragma unroll
-  for (int e = 0; e < 32; ++e) {
-    const int kv = n0 | (C0 + e);
-    bool keep = kv < Skv;
-#if FA_HAS_MASK_MOD
-    if (use_mask) keep = keep && fa_mask_mod(gb, gh, qi, kv);
-#endif
-    v[e] = keep ? v[e] : FA_NEG_INF;
+  for (int c = 0; c < NW; ++c) {
+    const int left = Skv - (kv0 + 32 * c);
+    w[c] = left >= 32 ? 0xffffffffu : (left <= 0 ? 0u : ((1u << left) - 1u));
   }
+#if FA_HAS_MASK_MOD
+  if (use_mask) {
+    // one rolled loop, the NW words side by side (independent evaluations in every iteration)
+    fa_u32 m[NW];
+#pragma unroll
+    for (int c = 0; c < NW; ++c) m[c] = 0u;
+#pragma unroll 2
+    for (int e = 0; e < 32; ++e) {
+#pragma unroll
+      for (int c = 0; c < NW; ++c) m[c] |= (fa_mask_mod(gb, gh, qi, kv0 + 32 * c + e) ? 1u : 0u) << e;
+    }
+#pragma unroll
+    for (int c = 0; c < NW; ++c) w[c] &= m[c];
+  }
+#endif
+}
+__device__ __forceinline__ void mask_apply(float (&v)[32], fa_u32 bits) {
+#pragma unroll
+  for (int e = 0; e < 32; ++e) v[e] = ((bits >> e) & 1u) ? v[e] : FA_NEG_INF;
 }
 
 // Pass-2 work on one chunk: p = 2^(x * cmul - m), packed to 16 bits, and the row-sum chains.
@@ -215,11 +235,9 @@ struct SoftmaxCtx {
   fa_u32 cnt;
 };
 
-// One kv step of this warpgroup's tile.  MASKED (compile time) selects the version for the few
-// tiles that need mask_mod or end beyond the sequence; the common version carries no mask code,
-// and keeping the two apart keeps the 128 score registers of each out of local memory.
-template <bool MASKED>
-__device__ __forceinline__ bool softmax_step(SoftmaxCtx& c, const int j, const int mode) {
+// One kv step of this warpgroup's tile.  `masked` marks the few tiles that need mask_mod or end
+// beyond the sequence: they take one extra block after the scores are in registers.
+__device__ __forceinline__ bool softmax_step(SoftmaxCtx& c, const int j, const int mode, const bool masked) {
   const FaParams& p = c.p;
   const fa_u32 sb = c.sb, t_s = c.t_s, t_o = c.t_o, t_p = c.t_p;
   const int i = c.i, warp = c.warp, qi = c.qi, gb = c.gb, gh = c.gh;
@@ -246,7 +264,6 @@ __device__ __forceinline__ bool softmax_step(SoftmaxCtx& c, const int j, const i
   const bool use_mask = FA_HAS_MASK_MOD && mode == 1;
 #define FA_P1(V, C0)                                                          \
   if (in_place) mod_chunk<C0>(V, n0, qi, gb, gh, p.scale, sc2);                \
-  if (MASKED) mask_chunk<C0>(V, use_mask, n0, qi, gb, gh, p.Skv);              \
   max_chunk(V, rm);
   fa_tmem_ld32(t_sh, s0);
   fa_tmem_wait_ld();
@@ -272,6 +289,22 @@ __device__ __forceinline__ bool softmax_step(SoftmaxCtx& c, const int j, const i
     FA_P1(s3, 96)
   }
 #undef FA_P1
+  if (masked) {
+    // (the row maximum taken on the way is of the unmasked scores: it is taken again)
+    fa_u32 keep[DECODE ? 2 : 4];
+    mask_bits(keep, use_mask, n0, qi, gb, gh, p.Skv);
+    mask_apply(s0, keep[0]);
+    mask_apply(s1, keep[1]);
+    rm = {FA_NEG_INF, FA_NEG_INF, FA_NEG_INF, FA_NEG_INF};
+    max_chunk(s0, rm);
+    max_chunk(s1, rm);
+    if (!DECODE) {
+      mask_apply(s2, keep[DECODE ? 0 : 2]);
+      mask_apply(s3, keep[DECODE ? 1 : 3]);
+      max_chunk(s2, rm);
+      max_chunk(s3, rm);
+    }
+  }
   float mx = fmaxf(fmaxf(rm.a, rm.b), fmaxf(rm.c, rm.d));
   if (!in_place) mx *= sc2;
   // running maximum, raised lazily
@@ -742,7 +775,7 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
         continue;
       }
       const bool masked = (FA_HAS_MASK_MOD && mode == 1) || (int)sched_tile[DECODE ? 2 * j + i : j] * BN + BN > p.Skv;
-      ok = masked ? softmax_step<true>(c, j, mode) : softmax_step<false>(c, j, mode);
+      ok = softmax_step(c, j, mode, masked);
     }
     const float m_ref = c.m_ref, l = c.l;
     const fa_u32 cnt = warp_active ? c.cnt : idle_cnt;
