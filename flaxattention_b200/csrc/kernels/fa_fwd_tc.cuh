@@ -235,9 +235,15 @@ struct SoftmaxCtx {
   fa_u32 cnt;
 };
 
-// One kv step of this warpgroup's tile.  `masked` marks the few tiles that need mask_mod or end
-// beyond the sequence: they take one extra block after the scores are in registers.
-__device__ __forceinline__ bool softmax_step(SoftmaxCtx& c, const int j, const int mode, const bool masked) {
+// One kv step of this warpgroup's tile.  The few tiles that need mask_mod or end beyond the
+// sequence take one extra block after the scores are in registers.  VARIANT 2: one copy of the
+// step, the block behind a run-time flag (head dim 64, where a second copy of the step costs more
+// in the instruction cache than the branch: causal forward 100 against 108 us).  VARIANT 0 / 1: a
+// copy without and a copy with the block (head dim 128, where the run-time flag made the common,
+// unmasked steps 16 % slower).
+template <int VARIANT>
+__device__ __forceinline__ bool softmax_step(SoftmaxCtx& c, const int j, const int mode, const bool masked_rt) {
+  const bool masked = VARIANT == 2 ? masked_rt : VARIANT == 1;
   const FaParams& p = c.p;
   const fa_u32 sb = c.sb, t_s = c.t_s, t_o = c.t_o, t_p = c.t_p;
   const int i = c.i, warp = c.warp, qi = c.qi, gb = c.gb, gh = c.gh;
@@ -775,7 +781,8 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
         continue;
       }
       const bool masked = (FA_HAS_MASK_MOD && mode == 1) || (int)sched_tile[DECODE ? 2 * j + i : j] * BN + BN > p.Skv;
-      ok = softmax_step(c, j, mode, masked);
+      if (D == 64) ok = softmax_step<2>(c, j, mode, masked);
+      else ok = masked ? softmax_step<1>(c, j, mode, true) : softmax_step<0>(c, j, mode, false);
     }
     const float m_ref = c.m_ref, l = c.l;
     const fa_u32 cnt = warp_active ? c.cnt : idle_cnt;
