@@ -32,6 +32,8 @@ class FaBlockTables(C.Structure):
         ("mask_B", C.c_int32), ("mask_H", C.c_int32),
         ("num_q_blocks", C.c_int32), ("num_kv_blocks", C.c_int32),
         ("q_block_size", C.c_int32), ("kv_block_size", C.c_int32),
+        ("mask_bits", C.c_void_p), ("mask_bits_stride", C.c_int64), ("mask_bits_rows", C.c_int32),
+        ("mask_bits_B", C.c_int32), ("mask_bits_H", C.c_int32),
     ]
 
 
@@ -65,6 +67,7 @@ EXPORTS = [
     "fa_bwd", "fa_decode_num_splits", "fa_decode_workspace_bytes", "fa_decode",
     "fa_block_mask_workspace_bytes", "fa_block_mask", "fa_decode_static_capacity", "fa_decode_static",
     "fa_profile_enable", "fa_profile_read", "fa_decode_packs_heads", "fa_selftest_bounded_wait",
+    "fa_mask_bits_row_words", "fa_mask_bits",
 ]
 
 
@@ -113,6 +116,9 @@ def lib() -> C.CDLL:
     L.fa_profile_enable.argtypes = [C.c_int]
     L.fa_profile_read.argtypes = [C.c_int, C.POINTER(C.c_float), C.POINTER(C.c_char_p)]
     L.fa_selftest_bounded_wait.argtypes = [C.c_ulonglong, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p]
+    L.fa_mask_bits_row_words.restype = C.c_int64
+    L.fa_mask_bits_row_words.argtypes = [C.c_int]
+    L.fa_mask_bits.argtypes = [C.c_void_p] + [C.c_int] * 6 + [C.c_void_p, C.c_void_p]
     L.fa_set_kernel_dir(os.path.join(_HERE, "csrc", "kernels").encode())
     cache = os.environ.get("FLAXATTN_CACHE_DIR")
     if cache is None:

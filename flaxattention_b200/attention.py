@@ -168,6 +168,13 @@ class _Call:
             t.mask_B, t.mask_H = bm.kv_indices.shape[0], bm.kv_indices.shape[1]
             t.num_q_blocks, t.num_kv_blocks = bm.kv_indices.shape[2], bm.kv_indices.shape[3]
             t.q_block_size, t.kv_block_size = bm.BLOCK_SIZE
+            mb = getattr(bm, "mask_bits", None)
+            if mb is not None and self.mask_mod is bm.mask_mod and mb.device == q.device and mb.shape[2] >= self.Sq \
+                    and mb.shape[3] * 32 >= self.Skv and mb.shape[0] in (1, self.B) and mb.shape[1] in (1, self.Hq):
+                if mb.dtype != torch.int32 or not mb.is_contiguous():
+                    raise ValueError("BlockMask.mask_bits must be a contiguous int32 tensor")
+                t.mask_bits, t.mask_bits_stride, t.mask_bits_rows = mb.data_ptr(), mb.shape[3], mb.shape[2]
+                t.mask_bits_B, t.mask_bits_H = mb.shape[0], mb.shape[1]
             for x in (bm.kv_num_blocks, bm.kv_indices, bm.full_kv_num_blocks, bm.full_kv_indices, bm.q_num_blocks,
                       bm.q_indices, bm.full_q_num_blocks, bm.full_q_indices):
                 if x is not None and (x.dtype != torch.int32 or not x.is_contiguous()):

@@ -110,9 +110,13 @@ class BlockMask:
     full_q_indices: Optional[torch.Tensor]
     BLOCK_SIZE: Tuple[int, int]
     mask_mod: Callable
+    # mask_mod of every position as a bit matrix [1 or B, 1 or H, Q_LEN, words] (int32), or None;
+    # not part of the reference's BlockMask: the kernels read it on partial tiles instead of
+    # evaluating mask_mod there
+    mask_bits: Optional[torch.Tensor] = None
 
     def __init__(self, kv_num_blocks, kv_indices, full_kv_num_blocks, full_kv_indices, q_num_blocks, q_indices,
-                 full_q_num_blocks, full_q_indices, BLOCK_SIZE, mask_mod):
+                 full_q_num_blocks, full_q_indices, BLOCK_SIZE, mask_mod, mask_bits=None):
         if kv_indices.ndim < 2:
             raise RuntimeError("BlockMask must have at least 2 dimensions")
         assert kv_num_blocks is not None, "kv_num_blocks must be provided"
@@ -135,6 +139,7 @@ class BlockMask:
         self.full_q_indices = full_q_indices
         self.BLOCK_SIZE = BLOCK_SIZE
         self.mask_mod = mask_mod
+        self.mask_bits = mask_bits
 
     @classmethod
     def from_kv_blocks(cls, kv_num_blocks, kv_indices, full_kv_num_blocks=None, full_kv_indices=None,
@@ -201,7 +206,8 @@ class BlockMask:
         mv = lambda t: None if t is None else t.to(device)  # noqa: E731
         return BlockMask(mv(self.kv_num_blocks), mv(self.kv_indices), mv(self.full_kv_num_blocks),
                          mv(self.full_kv_indices), mv(self.q_num_blocks), mv(self.q_indices),
-                         mv(self.full_q_num_blocks), mv(self.full_q_indices), self.BLOCK_SIZE, self.mask_mod)
+                         mv(self.full_q_num_blocks), mv(self.full_q_indices), self.BLOCK_SIZE, self.mask_mod,
+                         mv(self.mask_bits))
 
     def shard(self, b_slice: slice, h_slice: slice) -> "BlockMask":
         """Tables of one batch x heads shard (broadcast axes are kept whole)."""
@@ -213,7 +219,8 @@ class BlockMask:
             return t[bs, hs].contiguous()
         return BlockMask(cut(self.kv_num_blocks), cut(self.kv_indices), cut(self.full_kv_num_blocks),
                          cut(self.full_kv_indices), cut(self.q_num_blocks), cut(self.q_indices),
-                         cut(self.full_q_num_blocks), cut(self.full_q_indices), self.BLOCK_SIZE, self.mask_mod)
+                         cut(self.full_q_num_blocks), cut(self.full_q_indices), self.BLOCK_SIZE, self.mask_mod,
+                         cut(self.mask_bits))
 
     def __repr__(self):
         def shape_or_none(x):
@@ -316,6 +323,35 @@ def _require_cuda(device) -> torch.device:
     return dev
 
 
+_MASK_BITS_MAX_BYTES = 64 << 20
+
+
+def _build_mask_bits(module, mask_mod, B, H, Q_LEN, KV_LEN, b_offset, h_offset, dev, force):
+    """The bit matrix of ``mask_mod`` (see create_block_mask), or None.  Called with ``dev`` current
+    and the module's captured buffers bound."""
+    if force is False or mask_mod is noop_mask:
+        return None
+    ms = lower_mods(None, mask_mod)
+    if ms.buffers and force is not True:
+        return None
+    # a mask whose device code never names b (h) is the same for every batch entry (head)
+    import re
+    m = re.search(r"fa_mask_mod\(int b, int h, int q, int kv\) \{(.*?)\n\}", ms.source, re.S)
+    body = m.group(1) if m else "b h"
+    nb = B if re.search(r"\bb\b", body) else 1
+    nh = H if re.search(r"\bh\b", body) else 1
+    L = _cabi.lib()
+    words = int(L.fa_mask_bits_row_words(KV_LEN))
+    if force is not True and nb * nh * Q_LEN * words * 4 > _MASK_BITS_MAX_BYTES:
+        return None
+    if nb * nh > 65535 or Q_LEN > 65535:
+        return None
+    bits = torch.empty(nb, nh, Q_LEN, words, dtype=torch.int32, device=dev)
+    _cabi.check(L.fa_mask_bits(module.handle, nb, nh, Q_LEN, KV_LEN, b_offset if nb > 1 else 0,
+                               h_offset if nh > 1 else 0, bits.data_ptr(), torch.cuda.current_stream(dev).cuda_stream))
+    return bits
+
+
 def create_block_mask(
     mask_mod: Callable,
     B: Optional[int],
@@ -327,6 +363,7 @@ def create_block_mask(
     device=None,
     b_offset: int = 0,
     h_offset: int = 0,
+    _mask_bits: Optional[bool] = None,
 ) -> BlockMask:
     """Builds the BlockMask of ``mask_mod`` on the GPU.
 
@@ -338,6 +375,13 @@ def create_block_mask(
     change between calls).  ``b_offset`` / ``h_offset`` give the global index of the first batch
     / head when the tables of one batch x heads shard are built.  A 5-argument function is
     treated as a score_mod whose ``-inf`` results mark masked positions.
+
+    Next to the tables the mask itself is kept as a bit matrix (``BlockMask.mask_bits``, 1 bit per
+    position where the reference's ``create_mask`` materialises a boolean,
+    flaxattention/core/blockmask.py:277-322), one entry along batch / heads when ``mask_mod`` does
+    not read ``b`` / ``h``: on the partial tiles the attention kernels read a row's words instead of
+    evaluating ``mask_mod`` 128 times per row.  It is built when it takes at most 64 MiB and the mask
+    reads no captured tensor (``_mask_bits=True`` / ``False`` forces it on or off).
     """
     if mod_arity(mask_mod) not in (4, 5):
         raise AssertionError("mask_mod must take (b, h, q_idx, kv_idx) or (score, b, h, q_idx, kv_idx)")
@@ -366,7 +410,7 @@ def create_block_mask(
             hit = _TABLE_CACHE.get(cache_key)
             if hit is not None:
                 _TABLE_CACHE.move_to_end(cache_key)
-                return BlockMask(*hit, (Q_BLOCK_SIZE, KV_BLOCK_SIZE), mask_mod)
+                return BlockMask(*hit[:8], (Q_BLOCK_SIZE, KV_BLOCK_SIZE), mask_mod, hit[8])
     L = _cabi.lib()
     with torch.cuda.device(dev):
         mk = lambda *s: torch.empty(*s, dtype=torch.int32, device=dev)  # noqa: E731
@@ -382,9 +426,10 @@ def create_block_mask(
             kv_num.data_ptr(), kv_idx.data_ptr(), fkv_num.data_ptr(), fkv_idx.data_ptr(),
             q_num.data_ptr(), q_idx.data_ptr(), fq_num.data_ptr(), fq_idx.data_ptr(),
             ws.data_ptr(), ws_bytes, torch.cuda.current_stream(dev).cuda_stream))
+        bits = _build_mask_bits(module, mask_mod, B, H, Q_LEN, KV_LEN, b_offset, h_offset, dev, _mask_bits)
     if cache_key is not None:
-        _TABLE_CACHE[cache_key] = (kv_num, kv_idx, fkv_num, fkv_idx, q_num, q_idx, fq_num, fq_idx)
+        _TABLE_CACHE[cache_key] = (kv_num, kv_idx, fkv_num, fkv_idx, q_num, q_idx, fq_num, fq_idx, bits)
         while len(_TABLE_CACHE) > _TABLE_CACHE_MAX:
             _TABLE_CACHE.popitem(last=False)
     return BlockMask(kv_num, kv_idx, fkv_num, fkv_idx, q_num, q_idx, fq_num, fq_idx,
-                     (Q_BLOCK_SIZE, KV_BLOCK_SIZE), mask_mod)
+                     (Q_BLOCK_SIZE, KV_BLOCK_SIZE), mask_mod, bits)

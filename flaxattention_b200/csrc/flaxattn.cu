@@ -483,6 +483,13 @@ int check_common(fa_module* m, const fa_attn_params* p) {
     if ((long long)t.num_q_blocks * t.q_block_size < p->Sq || (long long)t.num_kv_blocks * t.kv_block_size < p->Skv)
       return fail(FA_EINVAL, "BlockMask does not cover the sequence lengths");
   }
+  if (t.mask_bits) {
+    if (!t.kv_num_blocks) return fail(FA_EINVAL, "mask_bits come with the BlockMask tables they were built beside");
+    if (((uintptr_t)t.mask_bits & 15) || t.mask_bits_stride % 4 || t.mask_bits_stride * 32 < p->Skv || t.mask_bits_rows < p->Sq)
+      return fail(FA_EINVAL, "mask_bits: 16-byte aligned, rows of a multiple of 4 words that cover Skv, at least Sq rows");
+    if (!(t.mask_bits_B == 1 || t.mask_bits_B == p->B) || !(t.mask_bits_H == 1 || t.mask_bits_H == p->Hq))
+      return fail(FA_EINVAL, "mask_bits batch/head dims must be 1 or match B/Hq");
+  }
   return FA_OK;
 }
 
@@ -494,6 +501,8 @@ FaTables cvt_tables(const fa_block_tables& t) {
   r.full_q_num = t.full_q_num_blocks; r.full_q_idx = t.full_q_indices;
   r.mB = t.mask_B; r.mH = t.mask_H; r.nQ = t.num_q_blocks; r.nKV = t.num_kv_blocks;
   r.QB = t.q_block_size; r.KVB = t.kv_block_size;
+  r.mask_bits = t.mask_bits; r.mask_stride = t.mask_bits_stride; r.mask_rows = t.mask_bits_rows;
+  r.mask_B = t.mask_bits_B; r.mask_H = t.mask_bits_H;
   return r;
 }
 
@@ -1081,6 +1090,10 @@ int get_bwd_tc_kernel(fa_module* m, int dtype, int D, int flags, Kernel** k) {
   return get_kernel(m, "fa_bwd_tc.cuh", d, "fa_bwd_tc_kernel", smem, k);
 }
 
+int get_mask_bits_kernel(fa_module* m, Kernel** k) {
+  return get_kernel(m, "fa_blockmask.cuh", "", "fa_mask_bits_kernel", 0, k);
+}
+
 int get_blockmask_kernel(fa_module* m, Kernel** k) {
   return get_kernel(m, "fa_blockmask.cuh", "", "fa_blockmask_classify_kernel", 0, k);
 }
@@ -1357,6 +1370,24 @@ size_t fa_block_mask_workspace_bytes(int B, int H, int Q_LEN, int KV_LEN, int q_
   if (B <= 0 || H <= 0 || Q_LEN <= 0 || KV_LEN <= 0 || q_block <= 0 || kv_block <= 0) return 0;
   const long long nQ = (Q_LEN + q_block - 1) / q_block, nKV = (KV_LEN + kv_block - 1) / kv_block;
   return (size_t)((long long)B * H * nQ * nKV);
+}
+
+int64_t fa_mask_bits_row_words(int KV_LEN) { return KV_LEN <= 0 ? 0 : (int64_t)((KV_LEN + 127) / 128) * 4; }
+
+int fa_mask_bits(fa_module* m, int B, int H, int Q_LEN, int KV_LEN, int b_offset, int h_offset, uint32_t* bits,
+                 void* stream) {
+  if (!m) return fail(FA_EINVAL, "module is null");
+  if (B <= 0 || H <= 0 || Q_LEN <= 0 || KV_LEN <= 0) return fail(FA_EINVAL, "B, H, Q_LEN and KV_LEN must be positive");
+  if (!bits || ((uintptr_t)bits & 15)) return fail(FA_EINVAL, "bits must be a 16-byte aligned device pointer");
+  if ((long long)B * H > 65535 || Q_LEN > 65535) return fail(FA_EUNSUPPORTED, "B*H and Q_LEN must not exceed 65535");
+  Kernel* k = nullptr;
+  if (int rc = get_mask_bits_kernel(m, &k)) return rc;
+  FaMaskBitsParams mp;
+  mp.bits = bits;
+  mp.stride = fa_mask_bits_row_words(KV_LEN);
+  mp.B = B; mp.H = H; mp.Q_LEN = Q_LEN; mp.KV_LEN = KV_LEN;
+  mp.b_off = b_offset; mp.h_off = h_offset;
+  return launch(k, dim3((unsigned)((mp.stride + 255) / 256), (unsigned)Q_LEN, (unsigned)(B * H)), dim3(256), &mp, stream);
 }
 
 int fa_block_mask(fa_module* m, int B, int H, int Q_LEN, int KV_LEN, int q_block, int kv_block, int b_offset,

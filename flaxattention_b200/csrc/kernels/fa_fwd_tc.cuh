@@ -166,7 +166,8 @@ __device__ __forceinline__ void mod_chunk(float (&v)[32], int n0, int qi, int gb
 // mask evaluated in line, per element and fully unrolled, made a masked step take 12-15k clocks
 // against 3.5k for a plain one: the step no longer fitted the instruction cache.)
 template <int NW>
-__device__ __forceinline__ void mask_bits(fa_u32 (&w)[NW], bool use_mask, int kv0, int qi, int gb, int gh, int Skv) {
+__device__ __forceinline__ void mask_bits(fa_u32 (&w)[NW], bool use_mask, int kv0, int qi, int gb, int gh, int Skv,
+                                          const unsigned* rowbits) {
   // the end of the sequence alone needs no loop: word c covers keys kv0 + 32 c .. + 31
 #pragma unroll
   for (int c = 0; c < NW; ++c) {
@@ -174,7 +175,16 @@ __device__ __forceinline__ void mask_bits(fa_u32 (&w)[NW], bool use_mask, int kv
     w[c] = left >= 32 ? 0xffffffffu : (left <= 0 ? 0u : ((1u << left) - 1u));
   }
 #if FA_HAS_MASK_MOD
-  if (use_mask) {
+  if (use_mask && rowbits != nullptr) {
+    // mask_mod was evaluated once for all positions (FaTables::mask_bits): this row's words of the tile
+    if (NW == 4) {
+      const uint4 m = *(const uint4*)(rowbits + (kv0 >> 5));
+      w[0] &= m.x; w[1] &= m.y; w[NW > 2 ? 2 : 0] &= m.z; w[NW > 2 ? 3 : 0] &= m.w;
+    } else {
+      const uint2 m = *(const uint2*)(rowbits + (kv0 >> 5));
+      w[0] &= m.x; w[1] &= m.y;
+    }
+  } else if (use_mask) {
     // one rolled loop, the NW words side by side (independent evaluations in every iteration)
     fa_u32 m[NW];
 #pragma unroll
@@ -233,6 +243,7 @@ struct SoftmaxCtx {
   const short* sched_tile;
   float m_ref, l;
   fa_u32 cnt;
+  const unsigned* rowbits;  // this query row of the mask bit matrix, or null
 };
 
 // One kv step of this warpgroup's tile.  The few tiles that need mask_mod or end beyond the
@@ -298,7 +309,7 @@ __device__ __forceinline__ bool softmax_step(SoftmaxCtx& c, const int j, const i
   if (masked) {
     // (the row maximum taken on the way is of the unmasked scores: it is taken again)
     fa_u32 keep[DECODE ? 2 : 4];
-    mask_bits(keep, use_mask, n0, qi, gb, gh, p.Skv);
+    mask_bits(keep, use_mask, n0, qi, gb, gh, p.Skv, c.rowbits);
     mask_apply(s0, keep[0]);
     mask_apply(s1, keep[1]);
     rm = {FA_NEG_INF, FA_NEG_INF, FA_NEG_INF, FA_NEG_INF};
@@ -752,7 +763,11 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
     const fa_u32 t_o = tmem + ((fa_u32)lane_base << 16) + COL_O + i * D;
     const fa_u32 t_p = SEP_P ? tmem + ((fa_u32)lane_base << 16) + COL_P + i * 64 : t_s;
     bool ok = true;
-    SoftmaxCtx c = {p, sb, t_s, t_o, t_p, i, warp, qi, gb, gh, half, p.scale * FA_LOG2E, abort_flag, sched_tile, FA_NEG_INF, 0.f, 0u};
+    // (rows beyond Sq have no row in the bit matrix: their scores are never stored, the mask is evaluated)
+    const unsigned* rowbits = (p.t.mask_bits != nullptr && qi < p.Sq)
+        ? p.t.mask_bits + (((long long)(p.t.mask_B == 1 ? 0 : b) * p.t.mask_H + (p.t.mask_H == 1 ? 0 : h)) * p.t.mask_rows + qi) * p.t.mask_stride
+        : nullptr;
+    SoftmaxCtx c = {p, sb, t_s, t_o, t_p, i, warp, qi, gb, gh, half, p.scale * FA_LOG2E, abort_flag, sched_tile, FA_NEG_INF, 0.f, 0u, rowbits};
     if (DECODE) {
       // the P columns of the other half of this lane's kv columns are never written again
       fa_u32 z[16];

@@ -23,6 +23,14 @@ struct FaTables {
   int mB, mH;    // 1 = broadcast over batch / head
   int nQ, nKV;   // number of q / kv blocks
   int QB, KVB;   // block sizes in tokens
+  // optional: mask_mod evaluated once for all positions.  Bit (kv % 32) of word
+  // [((bb * mask_H + hb) * mask_rows + q) * mask_stride + kv / 32] is mask_mod(b, h, q, kv), with
+  // bb = b (hb = h) or 0 where the matrix is broadcast over the batch (heads).
+  // Null: the kernels evaluate mask_mod themselves on partial tiles.
+  const unsigned* mask_bits;
+  long long mask_stride;  // words per row (a multiple of 4: rows start on 16-byte boundaries)
+  int mask_rows;          // rows per (batch, head) entry
+  int mask_B, mask_H;     // entries of the matrix along batch / heads (1 = broadcast)
 };
 
 struct FaParams {
@@ -45,5 +53,12 @@ struct FaParams {
 struct FaMaskParams {
   signed char* cls;  // [B,H,nQ,nKV]: 0 empty, 1 partial, 2 full
   int B, H, nQ, nKV, QB, KVB;
+  int b_off, h_off;
+};
+
+struct FaMaskBitsParams {
+  unsigned* bits;      // [B,H,Q_LEN,stride] words
+  long long stride;    // words per row
+  int B, H, Q_LEN, KV_LEN;
   int b_off, h_off;
 };

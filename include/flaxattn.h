@@ -76,6 +76,16 @@ typedef struct fa_block_tables {
   int32_t mask_B, mask_H;            /* 1 = broadcast over batch / heads */
   int32_t num_q_blocks, num_kv_blocks;
   int32_t q_block_size, kv_block_size;
+  /* Optional bit matrix of mask_mod (fa_mask_bits): bit (kv % 32) of word
+   * [((bb * mask_bits_H + hb) * mask_bits_rows + q) * mask_bits_stride + kv / 32], with bb / hb = 0
+   * where the matrix is broadcast (mask_bits_B / mask_bits_H = 1: a mask that does not read b / h needs
+   * one entry).  The kernels then read a row's words on partial tiles instead of evaluating mask_mod
+   * there; results are the same.  NULL: mask_mod is evaluated in the kernels.  The matrix belongs to
+   * the same mask_mod, offsets and captured buffers as the tables. */
+  const uint32_t* mask_bits;
+  int64_t mask_bits_stride; /* words per row, fa_mask_bits_row_words(KV_LEN) */
+  int32_t mask_bits_rows;   /* rows per (batch, head) entry (Q_LEN) */
+  int32_t mask_bits_B, mask_bits_H; /* 1 or B / Hq */
 } fa_block_tables;
 
 typedef struct fa_attn_params {
@@ -195,6 +205,14 @@ int fa_block_mask(fa_module* m, int B, int H, int Q_LEN, int KV_LEN, int q_block
                   int32_t* q_num_blocks, int32_t* q_indices,
                   int32_t* full_q_num_blocks, int32_t* full_q_indices,
                   void* workspace, size_t workspace_bytes, void* stream);
+
+/* mask_mod of every position as a bit matrix [B, H, Q_LEN, fa_mask_bits_row_words(KV_LEN)] (uint32,
+ * device, 16-byte aligned) for fa_block_tables::mask_bits.  The reference materialises the boolean
+ * mask itself (create_mask, flaxattention/core/blockmask.py:277-322); this is its 1-bit form and is
+ * optional: it saves the kernels the evaluation of mask_mod on partial tiles. */
+int64_t fa_mask_bits_row_words(int KV_LEN);
+int fa_mask_bits(fa_module* m, int B, int H, int Q_LEN, int KV_LEN, int b_offset, int h_offset, uint32_t* bits,
+                 void* stream);
 
 #ifdef __cplusplus
 }

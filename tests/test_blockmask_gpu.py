@@ -105,3 +105,63 @@ def test_determinism():
     _, b = _gpu_tables(generate_attention_sink(1024, 4), 2, 2, 4096, 4096, 128)
     for k in TABLE_KEYS:
         assert np.array_equal(a[k], b[k])
+
+
+# ---- the mask as a bit matrix (BlockMask.mask_bits) --------------------------------------------
+def _unpack_bits(bits, kv_len):
+    """[.., Q, words] int32 -> [.., Q, kv_len] bool."""
+    w = bits.cpu().numpy().view(np.uint32)
+    cols = np.arange(kv_len)
+    return ((w[..., cols // 32] >> (cols % 32).astype(np.uint32)) & 1).astype(bool)
+
+
+def test_mask_bits_equal_the_mask_of_the_oracle():
+    from flaxattention_b200 import create_block_mask
+    from flaxattention_b200.masks import causal_mask, generate_attention_sink
+    from oracle.blockmask_oracle import create_mask as create_mask_oracle
+
+    for mask, Q, KV in ((causal_mask, 256, 384), (generate_attention_sink(100, 4), 512, 512)):
+        bm = create_block_mask(mask, 2, 3, Q, KV)
+        assert bm.mask_bits is not None and tuple(bm.mask_bits.shape[:3]) == (1, 1, Q), "one entry: the mask reads neither b nor h"
+        got = _unpack_bits(bm.mask_bits, KV)[0, 0]
+        want = create_mask_oracle(mask, 1, 1, Q, KV)[0, 0]
+        assert np.array_equal(got, want)
+    # a mask that reads the head index keeps one entry per head; offsets are the global indices
+    def per_head(b, h, q_idx, kv_idx):
+        return (q_idx >= kv_idx) & ((kv_idx + h) % 3 != 0)
+    bm = create_block_mask(per_head, 1, 4, 128, 200, h_offset=2)
+    assert tuple(bm.mask_bits.shape[:2]) == (1, 4)
+    # (KV_LEN is rounded up to whole blocks, as for the tables: 256 keys)
+    want = create_mask_oracle(per_head, 1, 4, 128, 256, h_offset=2)[0]
+    assert np.array_equal(_unpack_bits(bm.mask_bits, 256)[0], want)
+
+
+@pytest.mark.parametrize("D,dtype", [(64, torch.float16), (128, torch.bfloat16)])
+def test_attention_is_the_same_with_and_without_mask_bits(D, dtype):
+    """The kernels read the bit matrix on partial tiles instead of evaluating mask_mod: forward and
+    gradients must not change by a bit (decode variant included)."""
+    import flaxattention_b200 as fa
+    from flaxattention_b200.masks import generate_attention_sink, generate_causal_offset
+
+    torch.manual_seed(3)
+    dev = torch.device("cuda", 0)
+    mask = generate_attention_sink(200, 4)
+    B, H, S = 2, 4, 640
+    q, k, v = (torch.randn(B, H, S, D, device=dev, dtype=dtype, requires_grad=True) for _ in range(3))
+    res = []
+    for use in (True, False):
+        bm = fa.create_block_mask(mask, B, H, S, S, _mask_bits=use)
+        assert (bm.mask_bits is not None) == use
+        out = fa.flax_attention(q, k, v, block_mask=bm)
+        g = torch.autograd.grad(out.float().square().sum(), (q, k, v))
+        res.append((out, *g))
+    for a, b in zip(*res):
+        assert torch.equal(a, b)
+    if D == 64:
+        sq = 48
+        kk, vv = k.detach()[:, :, :, :].repeat(1, 1, 2, 1), v.detach().repeat(1, 1, 2, 1)  # Skv = 1280
+        qq = q.detach()[:, :, :sq]
+        m2 = generate_causal_offset(kk.shape[2] - sq)
+        outs = [fa.flax_attention(qq, kk, vv, block_mask=fa.create_block_mask(m2, B, H, sq, kk.shape[2], _mask_bits=u))
+                for u in (True, False)]
+        assert torch.equal(outs[0], outs[1])
