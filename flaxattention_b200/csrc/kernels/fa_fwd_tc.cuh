@@ -425,6 +425,33 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
   unsigned char* sched_mode = sm + OFF_MODE;
   unsigned char* cls = sm + OFF_CLS;
 
+  // The BlockMask table reads of this CTA go out first: the two counts and, speculatively, this
+  // thread's entry of the two index lists, for both query tiles.  They are all issued before any is
+  // used (one round trip to memory instead of a chain of four dependent ones) and they are in flight
+  // while the barriers are set up and TMEM is allocated.
+  constexpr int NI = DECODE ? 1 : 2;
+  const int ntiles = min((p.Skv + BN - 1) / BN, MAXT);
+  const bool tables = p.t.kv_num != nullptr;
+  const int tpb = tables ? (p.t.nKV == 1 ? ntiles : p.t.KVB / BN) : 1;
+  const int bi0 = tid / tpb, ti0 = tid - bi0 * tpb;
+  long long rows[NI];
+  int num[NI][2], blk[NI][2];
+#pragma unroll
+  for (int i = 0; i < NI; ++i) {
+    const int mi = m0 + i * BM;
+    const int bm = p.t.mB == 1 ? 0 : b, hm = p.t.mH == 1 ? 0 : h;
+    const int qblk = tables ? min(mi / p.t.QB, p.t.nQ - 1) : 0;
+    rows[i] = ((long long)bm * p.t.mH + hm) * p.t.nQ + qblk;
+#pragma unroll
+    for (int which = 0; which < 2; ++which) {
+      const int* nump = which ? p.t.full_kv_num : p.t.kv_num;
+      const int* idxp = which ? p.t.full_kv_idx : p.t.kv_idx;
+      const bool have = tables && nump != nullptr && mi < p.Sq;
+      num[i][which] = have ? nump[rows[i]] : 0;
+      blk[i][which] = (have && bi0 < p.t.nKV) ? idxp[rows[i] * p.t.nKV + bi0] : 0;
+    }
+  }
+
   // ---- set-up: barriers, TMEM, kv schedule ---------------------------------------------
   if (tid == 0) {
     fa_mbar_init(bar_addr(sb, BAR_Q), 1);
@@ -460,36 +487,12 @@ extern "C" __global__ void __launch_bounds__(fa_tc::NT, 1) fa_fwd_tc_kernel(cons
         }
       }
   }
-  const int ntiles = min((p.Skv + BN - 1) / BN, MAXT);
   for (int i = tid; i < 2 * MAXT; i += NT) cls[i] = 0;
   if (warp == WARP_MMA) fa_tmem_alloc(sb + OFF_MISC, TMEM_COLS);
   __syncthreads();
-  // class of every kv tile for both query tiles: 0 skip, 1 apply mask_mod, 2 full.  Every table read
-  // of the CTA (the two counts and, speculatively, this thread's entry of the two index lists, for
-  // both query tiles) is issued before any of them is used: one round trip to memory instead of
-  // a chain of four dependent ones.
+  // class of every kv tile for both query tiles: 0 skip, 1 apply mask_mod, 2 full (from the table
+  // entries read at the top of the kernel)
   {
-    constexpr int NI = DECODE ? 1 : 2;
-    const bool tables = p.t.kv_num != nullptr;
-    const int tpb = tables ? (p.t.nKV == 1 ? ntiles : p.t.KVB / BN) : 1;
-    const int bi0 = tid / tpb, ti0 = tid - bi0 * tpb;
-    long long rows[NI];
-    int num[NI][2], blk[NI][2];
-#pragma unroll
-    for (int i = 0; i < NI; ++i) {
-      const int mi = m0 + i * BM;
-      const int bm = p.t.mB == 1 ? 0 : b, hm = p.t.mH == 1 ? 0 : h;
-      const int qblk = tables ? min(mi / p.t.QB, p.t.nQ - 1) : 0;
-      rows[i] = ((long long)bm * p.t.mH + hm) * p.t.nQ + qblk;
-#pragma unroll
-      for (int which = 0; which < 2; ++which) {
-        const int* nump = which ? p.t.full_kv_num : p.t.kv_num;
-        const int* idxp = which ? p.t.full_kv_idx : p.t.kv_idx;
-        const bool have = tables && nump != nullptr && mi < p.Sq;
-        num[i][which] = have ? nump[rows[i]] : 0;
-        blk[i][which] = (have && bi0 < p.t.nKV) ? idxp[rows[i] * p.t.nKV + bi0] : 0;
-      }
-    }
 #pragma unroll
     for (int i = 0; i < NI; ++i) {
       const int mi = m0 + i * BM;
