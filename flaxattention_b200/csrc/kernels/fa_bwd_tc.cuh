@@ -155,6 +155,14 @@ __device__ __forceinline__ void chunk(const float (&s)[W], const float (&dp)[W],
 #if !FA_ROUND_SCORES && (!FA_HAS_SCORE_MOD || defined(FA_SCORE_AFFINE))
   // no score_mod, or an affine one: two elements per instruction (packed fp32) wherever the
   // hardware has the form; only the exponentials and the mask are per element
+#if FA_HAS_SCORE_MOD && defined(FA_SCORE_LINEAR_Q)
+  // the multiplier does not read q and the bias is linear in it (relative-position biases such as
+  // ALiBi): both are taken once, at the first column of the chunk, and column e adds e times the slope
+  const float lin_g = fa_score_mul(0.f, gb, gh, q0, kv);
+  const fa_u64 lin_g2 = fa_f2(lin_g, lin_g), lin_gs2 = fa_f2(lin_g * sc2, lin_g * sc2);
+  const float lin_base = fa_score_add2(0.f, gb, gh, q0, kv), lin_dq = fa_score_add2_dq(0.f, gb, gh, q0, kv);
+  const fa_u64 lin_b2 = fa_f2(lin_base, lin_base), lin_d2 = fa_f2(lin_dq, lin_dq);
+#endif
 #pragma unroll
   for (int e = 0; e < W; e += 4) {
     const float4 nl = *(const float4*)(nlse2 + e);
@@ -165,7 +173,11 @@ __device__ __forceinline__ void chunk(const float (&s)[W], const float (&dp)[W],
       const fa_u64 nl2 = u == 0 ? fa_f2(nl.x, nl.y) : fa_f2(nl.z, nl.w);
       const fa_u64 nd2 = u == 0 ? fa_f2(nd.x, nd.y) : fa_f2(nd.z, nd.w);
       const fa_u64 s2 = fa_f2(s[e + u], s[e + u + 1]);
-#if FA_HAS_SCORE_MOD
+#if FA_HAS_SCORE_MOD && defined(FA_SCORE_LINEAR_Q)
+      const fa_u64 g2 = lin_g2;
+      const fa_u64 b2 = fa_add2(fa_fma2(fa_f2((float)(e + u), (float)(e + u + 1)), lin_d2, lin_b2), nl2);
+      const fa_u64 x2 = fa_fma2(s2, lin_gs2, b2);
+#elif FA_HAS_SCORE_MOD
       const fa_u64 g2 = fa_f2(fa_score_mul(0.f, gb, gh, qi0, kv), fa_score_mul(0.f, gb, gh, qi1, kv));
       const fa_u64 b2 = fa_add2(fa_f2(fa_score_add2(0.f, gb, gh, qi0, kv), fa_score_add2(0.f, gb, gh, qi1, kv)), nl2);
       const fa_u64 x2 = fa_fma2(s2, fa_mul2(g2, fa_f2(sc2, sc2)), b2);

@@ -137,6 +137,30 @@ __device__ __forceinline__ void max_chunk(const float (&v)[32], RowMax& mx) {
 // absorb the scale and log2(e).
 template <int C0>
 __device__ __forceinline__ void mod_chunk(float (&v)[32], int n0, int qi, int gb, int gh, float scale, float sc2) {
+#if FA_HAS_SCORE_MOD && defined(FA_SCORE_AFFINE) && defined(FA_SCORE_LINEAR_KV)
+  // The multiplier does not read kv and the bias is linear in it (relative-position biases such as
+  // ALiBi): both are taken once, at the first column of the chunk, and column e adds e times the
+  // slope - two packed FMAs per pair instead of an integer subtraction, an int-to-float conversion
+  // (which shares the SFU with the exponentials) and a multiplication per element.
+  {
+    const int kv0 = n0 | C0;
+    const float mulsc = fa_score_mul(0.f, gb, gh, qi, kv0) * sc2;
+    const float base = fa_score_add2(0.f, gb, gh, qi, kv0);
+    const float dkv = fa_score_add2_dkv(0.f, gb, gh, qi, kv0);
+    const fa_u64 m2 = fa_f2(mulsc, mulsc), b2 = fa_f2(base, base), d2 = fa_f2(dkv, dkv);
+#pragma unroll
+    for (int e = 0; e < 32; e += 2) {
+      float x0 = v[e], x1 = v[e + 1];
+#if FA_ROUND_SCORES
+      fa_round2<DT>(x0, x1);
+#endif
+      fa_f2_unpack(fa_fma2(fa_f2(x0, x1), m2, fa_fma2(fa_f2((float)e, (float)(e + 1)), d2, b2)), x0, x1);
+      v[e] = x0;
+      v[e + 1] = x1;
+    }
+    return;
+  }
+#endif
 #pragma unroll
   for (int e = 0; e < 32; e += 2) {
     float x0 = v[e], x1 = v[e + 1];

@@ -1025,6 +1025,97 @@ def affine_parts(mod: TracedMod):
 
 
 # --------------------------------------------------------------------------------------
+# index-linear biases:  B(b,h,q,kv) == B(.., x0) + (x - x0) * S(b,h,other index)   for x in {q, kv}
+# --------------------------------------------------------------------------------------
+def _depends_on(e: Expr, leaf: str, memo) -> bool:
+    r = memo.get(id(e))
+    if r is None:
+        r = e.op == leaf or any(_depends_on(a, leaf, memo) for a in e.args)
+        memo[id(e)] = r
+    return r
+
+
+def _int_bound(e: Expr, memo) -> float:
+    """Upper bound of |value| of an integer expression made of indices (below 2^16 each), constants,
+    +, - and *; infinity for anything else."""
+    got = memo.get(id(e))
+    if got is not None:
+        return got
+    if e.op in ("b", "h", "q", "kv"):
+        r = float(1 << 16)
+    elif e.op == "const" and e.dtype == I32:
+        r = float(abs(int(e.value)))
+    elif e.op in ("add", "sub") and e.dtype == I32:
+        r = _int_bound(e.args[0], memo) + _int_bound(e.args[1], memo)
+    elif e.op == "neg" and e.dtype == I32:
+        r = _int_bound(e.args[0], memo)
+    elif e.op == "mul" and e.dtype == I32:
+        r = _int_bound(e.args[0], memo) * _int_bound(e.args[1], memo)
+    else:
+        r = float("inf")
+    memo[id(e)] = r
+    return r
+
+
+def linear_slope(root: Expr, leaf: str) -> Optional[Expr]:
+    """If the float expression ``root`` is linear in the index ``leaf`` ('q' or 'kv') - relative-position
+    biases such as ALiBi are - returns its slope, an expression that does not read ``leaf``; else None.
+    A kernel that walks along that index then evaluates the bias once per tile and adds multiples of
+    the slope, instead of an integer subtraction, an int-to-float conversion (which shares the
+    special-function unit with the exponentials) and a multiplication per element.
+    Integer sub-expressions must stay below 2^24 in magnitude so that their conversion to float is
+    exact term by term."""
+    dep: Dict[int, bool] = {}
+    bounds: Dict[int, float] = {}
+    memo: Dict[int, object] = {}
+    fail = object()
+
+    def go(e: Expr):
+        """slope of e (Expr of e's dtype, independent of leaf), or None when e is not linear in leaf"""
+        if not _depends_on(e, leaf, dep):
+            return _B.const(0, I32) if e.dtype == I32 else _B.const(0.0, F32)
+        got = memo.get(id(e), fail)
+        if got is not fail:
+            return got
+        op, a, r = e.op, e.args, None
+        if e.dtype not in (I32, F32):
+            r = None
+        elif op == leaf:
+            r = _B.const(1, I32)
+        elif op in ("add", "sub"):
+            x, y = go(a[0]), go(a[1])
+            if x is not None and y is not None:
+                r = binary(op, cast(x, e.dtype), cast(y, e.dtype))
+        elif op == "neg":
+            x = go(a[0])
+            if x is not None:
+                r = unary("neg", x)
+        elif op == "mul":
+            for u, v in ((a[0], a[1]), (a[1], a[0])):
+                if not _depends_on(v, leaf, dep):
+                    x = go(u)
+                    if x is not None:
+                        r = binary("mul", cast(x, e.dtype), v)
+                    break
+        elif op == "div" and e.dtype == F32:
+            if not _depends_on(a[1], leaf, dep):
+                x = go(a[0])
+                if x is not None:
+                    r = binary("div", cast(x, F32), a[1])
+        elif op == "cast_f32" and a[0].dtype == I32:
+            x = go(a[0])
+            if x is not None and _int_bound(a[0], bounds) < float(1 << 24):
+                r = cast(x, F32)
+        memo[id(e)] = r
+        return r
+
+    res = go(root)
+    if res is None:
+        return None
+    return cast(res, F32)
+
+
+# --------------------------------------------------------------------------------------
 # back ends
 # --------------------------------------------------------------------------------------
 def _topo(root: Expr) -> List[Expr]:
@@ -1396,6 +1487,15 @@ class ModSet:
                 # B already multiplied by log2(e), with the constant folded into row-invariant factors
                 b2 = TracedMod("score", binary("mul", self.affine[1].root, _B.const(math.log2(math.e), F32)), self.affine[1].buffers)
                 parts.append(to_cuda(b2, "fa_score_add2"))
+                # A bias that is linear in kv (q) under a multiplier that does not read kv (q): the kernels
+                # take the bias at the first column of a chunk and add multiples of the slope
+                self.linear = {}
+                for leaf, tag in (("kv", "KV"), ("q", "Q")):
+                    slope = linear_slope(b2.root, leaf)
+                    if slope is not None and not _depends_on(self.affine[0].root, leaf, {}):
+                        self.linear[leaf] = slope
+                        parts.append(f"#define FA_SCORE_LINEAR_{tag} 1\n")
+                        parts.append(to_cuda(TracedMod("score", slope, b2.buffers), f"fa_score_add2_d{leaf}"))
         else:
             self.grad = None
             parts.append(

@@ -284,3 +284,36 @@ def test_jnp_mods_go_through_the_jaxpr_front_end():
     got = modtrace.evaluate(tm, s, b, h, q, kv)
     want = np.asarray(generate_alibi_bias(8)(s, b, h, q, kv), dtype=np.float32)
     np.testing.assert_allclose(np.broadcast_to(got, want.shape), want, rtol=2e-6, atol=2e-6)
+
+
+def test_bias_that_is_linear_in_an_index_gets_a_slope():
+    """Relative-position biases (ALiBi) are linear in q and in kv: the lowering emits the slope so
+    that the kernels add multiples of it along a tile instead of converting an integer per element.
+    Mods that are not linear, or whose integer part could leave the range where the conversion to
+    float is exact, get none."""
+    from flaxattention_b200 import modtrace as mt
+    from flaxattention_b200.mods import generate_alibi_bias
+
+    ms = mt.lower_mods(generate_alibi_bias(8), None)
+    assert "FA_SCORE_LINEAR_KV" in ms.source and "FA_SCORE_LINEAR_Q" in ms.source
+    # slope along kv = -slope along q = -(2 ** -(h + 1)) * log2(e), whatever q and kv are
+    import math
+    for leaf, sign in (("kv", -1.0), ("q", 1.0)):
+        root = ms.linear[leaf]
+        for h in (0, 3, 7):
+            got = float(mt.evaluate(mt.TracedMod("score", root, []), 0.0, 0, h, 5, 9))
+            assert abs(got - sign * 2.0 ** -(h + 1) * math.log2(math.e)) < 1e-6
+
+    def checkerboard(score, b, h, q_idx, kv_idx):
+        return mt.where((q_idx - kv_idx) % 2 == 0, score * 0.5, score * 2.0)
+
+    def quadratic(score, b, h, q_idx, kv_idx):
+        d = mt.float32(q_idx - kv_idx)
+        return score + d * d
+
+    def huge(score, b, h, q_idx, kv_idx):
+        return score + mt.float32(kv_idx * 1000000 + q_idx)
+
+    for fn in (checkerboard, quadratic, huge):
+        src = mt.lower_mods(fn, None).source
+        assert "FA_SCORE_LINEAR_KV" not in src, fn.__name__
