@@ -67,8 +67,8 @@ MIN_LEG_SECONDS = 0.5
 # scaled to its full batch (x4 for B=8, x2 for B=4): the traffic grows with the batch.  Workloads and
 # kernels without a capture are absent.
 NCU_TRAFFIC = {
-    "cfg2": {"fa_fwd_tc_kernel": 4 * 12.67e6, "fa_bwd_tc_kernel": 4 * 25.59e6},
-    "cfg4": {"fa_fwd_tc_kernel": 2 * (240.8e6 + 48.2e6), "fa_bwd_tc_kernel": 2 * (653.2e6 + 362.0e6)},
+    "cfg2": {"fa_fwd_tc_kernel": 4 * 12.65e6, "fa_bwd_tc_kernel": 4 * 25.58e6},
+    "cfg4": {"fa_fwd_tc_kernel": 2 * (248.4e6 + 49.8e6), "fa_bwd_tc_kernel": 2 * (649.6e6 + 360.2e6)},
 }
 
 # S x S x D products per computed block pair that count as algorithmic work of each kernel: the
