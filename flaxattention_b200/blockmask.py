@@ -338,8 +338,9 @@ def _build_mask_bits(module, mask_mod, B, H, Q_LEN, KV_LEN, b_offset, h_offset, 
     import re
     m = re.search(r"fa_mask_mod\(int b, int h, int q, int kv\) \{(.*?)\n\}", ms.source, re.S)
     body = m.group(1) if m else "b h"
-    nb = B if re.search(r"\bb\b", body) else 1
-    nh = H if re.search(r"\bh\b", body) else 1
+    reads_b, reads_h = re.search(r"\bb\b", body) is not None, re.search(r"\bh\b", body) is not None
+    nb = B if reads_b else 1
+    nh = H if reads_h else 1
     L = _cabi.lib()
     words = int(L.fa_mask_bits_row_words(KV_LEN))
     if force is not True and nb * nh * Q_LEN * words * 4 > _MASK_BITS_MAX_BYTES:
@@ -347,8 +348,8 @@ def _build_mask_bits(module, mask_mod, B, H, Q_LEN, KV_LEN, b_offset, h_offset, 
     if nb * nh > 65535 or Q_LEN > 65535:
         return None
     bits = torch.empty(nb, nh, Q_LEN, words, dtype=torch.int32, device=dev)
-    _cabi.check(L.fa_mask_bits(module.handle, nb, nh, Q_LEN, KV_LEN, b_offset if nb > 1 else 0,
-                               h_offset if nh > 1 else 0, bits.data_ptr(), torch.cuda.current_stream(dev).cuda_stream))
+    _cabi.check(L.fa_mask_bits(module.handle, nb, nh, Q_LEN, KV_LEN, b_offset if reads_b else 0,
+                               h_offset if reads_h else 0, bits.data_ptr(), torch.cuda.current_stream(dev).cuda_stream))
     return bits
 
 

@@ -134,6 +134,12 @@ def test_mask_bits_equal_the_mask_of_the_oracle():
     # (KV_LEN is rounded up to whole blocks, as for the tables: 256 keys)
     want = create_mask_oracle(per_head, 1, 4, 128, 256, h_offset=2)[0]
     assert np.array_equal(_unpack_bits(bm.mask_bits, 256)[0], want)
+    # a one-entry shard of a mask that reads b still sees its global batch index
+    def per_batch(b, h, q_idx, kv_idx):
+        return kv_idx <= q_idx + 32 * b
+    bm = create_block_mask(per_batch, 1, 2, 128, 256, b_offset=3)
+    want = create_mask_oracle(per_batch, 1, 1, 128, 256, b_offset=3)[0, 0]
+    assert tuple(bm.mask_bits.shape[:2]) == (1, 1) and np.array_equal(_unpack_bits(bm.mask_bits, 256)[0, 0], want)
 
 
 @pytest.mark.parametrize("D,dtype", [(64, torch.float16), (128, torch.bfloat16)])
