@@ -281,7 +281,7 @@ __device__ __forceinline__ bool softmax_step(SoftmaxCtx& c, const int j, const i
   const bool masked = VARIANT == 2 ? masked_rt : VARIANT == 1;
   const FaParams& p = c.p;
   const fa_u32 sb = c.sb, t_s = c.t_s, t_o = c.t_o, t_p = c.t_p;
-  const int i = c.i, warp = c.warp, qi = c.qi, gb = c.gb, gh = c.gh;
+  const int i = c.i, qi = c.qi, gb = c.gb, gh = c.gh;
   const float sc2 = c.sc2;
   volatile int* abort_flag = c.abort_flag;
   float& m_ref = c.m_ref;
