@@ -1130,6 +1130,7 @@ int fa_module_prepare(fa_module* m, int kind, int dtype, int D, int Dv, int Sq_h
       return get_decode_kernel(m, dtype, D, Dv, 0, c, false, &k);
     }
     case FA_KIND_BLOCKMASK:
+      if (int rc = get_mask_bits_kernel(m, &k)) return rc;
       return get_blockmask_kernel(m, &k);
     default:
       return fail(FA_EUNSUPPORTED, "fa_module_prepare: unknown kind");
