@@ -989,9 +989,11 @@ bool tc_decode_eligible(const fa_attn_params* p) {
   if (p->dtype == FA_F32) return false;
   if (p->D != 64 || p->Dv != 64) return false;
   // The kernel gives every query row two threads (64 kv columns of a tile each), whatever Sq is:
-  // measured on B32 H8 Skv16384 against the general decode kernel it takes 0.23 ms at 64 rows
-  // (general: 0.55) and wins from 17 rows up (general: 0.36 at 32 rows, 0.22 at 16).
-  if (p->Sq < 17 || p->Sq > 64 || p->Skv < 1024 || p->Skv > 32768) return false;
+  // measured on B32 H8 Skv16384 against the general decode kernel it takes 0.225 ms at 64 rows
+  // (general: 0.55), 0.209 at 16 (general: 0.231), 0.209 at 2 and 0.208 at 1 (general: 0.206): it
+  // streams K / V through TMA and a five-stage ring at the same rate whatever the row count, so it
+  // takes everything from two rows up.
+  if (p->Sq < 2 || p->Sq > 64 || p->Skv < 1024 || p->Skv > 32768) return false;
   if (!(p->scale > 0.f)) return false;
   const fa_block_tables& t = p->tables;
   if (t.kv_num_blocks) {
@@ -1125,7 +1127,7 @@ int fa_module_prepare(fa_module* m, int kind, int dtype, int D, int Dv, int Sq_h
     case FA_KIND_DECODE: {
       DecCfg c;
       if (int rc = pick_decode(dtype, D, Dv, Sq_hint, nullptr, c)) return rc;
-      if (dtype != FA_F32 && D == 64 && Dv == 64 && Sq_hint >= 17)
+      if (dtype != FA_F32 && D == 64 && Dv == 64 && Sq_hint >= 2)
         if (int rc = get_fwd_tc_kernel(m, dtype, D, 0, &k, true)) return rc;
       return get_decode_kernel(m, dtype, D, Dv, 0, c, false, &k);
     }

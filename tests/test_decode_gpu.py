@@ -84,9 +84,9 @@ def test_decode_benchmark_shape():
 
 
 @pytest.mark.parametrize("dt", ["f16", "bf16"])
-@pytest.mark.parametrize("Sq,splits", [(17, 4), (24, 0), (32, 8), (33, 4), (48, 8), (64, 12), (64, 3), (40, 0), (64, 24)])
+@pytest.mark.parametrize("Sq,splits", [(2, 4), (5, 0), (16, 8), (17, 4), (24, 0), (32, 8), (33, 4), (48, 8), (64, 12), (64, 3), (40, 0), (64, 24)])
 def test_tcgen05_decode_and_general_decode_agree_with_the_oracle(Sq, splits, dt):
-    """17..64 query rows with a split count that is a multiple of four run on the split-KV variant
+    """2..64 query rows with a split count that is a multiple of four run on the split-KV variant
     of the tcgen05 kernel (four partial results per CTA: two warpgroups x two column halves), any
     other count or the `general` option on the general decode kernel: both within tolerance of the
     oracle and close to each other, and the status word of the tcgen05 kernel (bounded waits)
