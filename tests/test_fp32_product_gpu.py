@@ -30,7 +30,17 @@ def _mods(score, mask, Hq):
     def softcap(s, b, h, q, kv):
         return 20.0 * fnp.tanh(s / 20.0)
 
-    s = {None: None, "alibi": generate_alibi_bias(Hq), "checker": checkerboard, "softcap": softcap}[score]
+    def relbias(s, b, h, q, kv):
+        # multiplier without indices, bias linear in q and in kv with a slope per (batch, head): the kernels
+        # take the bias once per chunk and add multiples of the slope
+        return s * 1.5 + fnp.float32(kv - 2 * q) * (0.002 * fnp.float32(h + 1 + b))
+
+    def halfbias(s, b, h, q, kv):
+        # linear in kv only (the bias is quadratic in q): the forward uses the slope, the backward does not
+        return s + fnp.float32(q) * fnp.float32(q) * 1e-5 - 0.01 * fnp.float32(kv)
+
+    s = {None: None, "alibi": generate_alibi_bias(Hq), "checker": checkerboard, "softcap": softcap,
+         "relbias": relbias, "halfbias": halfbias}[score]
     m = {None: None, "causal": causal_mask, "sink": generate_attention_sink(200, 4),
          "window": generate_sliding_window(100)}[mask]
     return s, m
@@ -61,6 +71,9 @@ CASES = [
     (1, 2, 2, 512, 512, 128, "bf16", None, "sink", True),
     (1, 2, 2, 256, 640, 128, "f16", "checker", None, False),
     (1, 2, 2, 384, 384, 128, "bf16", "alibi", "causal", False),
+    (2, 2, 2, 384, 512, 64, "bf16", "relbias", "causal", True),   # index-linear bias: slope path in both kernels
+    (1, 2, 2, 256, 384, 128, "f16", "relbias", None, False),
+    (1, 2, 2, 384, 384, 64, "f16", "halfbias", "window", True),   # linear in kv only
 ]
 
 
