@@ -73,9 +73,13 @@ constexpr int MAXC = 256;                // 128-row q tiles per head (Sq <= 3276
 constexpr int NT = 512;
 constexpr int WARP_PRODUCER = 12, WARP_MMA = 13, WARP_MMA_B = 14, WARP_MMA_C = 15;
 // Register split (setmaxnreg): the kernel starts with 128 registers per thread (65536 / 512).  The
-// eight warps that are not compute warps give up 72 each and the eight compute warps take 72 each;
-// an increase that asked for more than the decrease releases would wait forever.
-constexpr int REGS_COMPUTE = 200, REGS_OTHER = 56;
+// eight warps that are not compute warps give up 32 each and the eight compute warps take 32 each;
+// an increase that asked for more than the decrease releases would wait forever.  The compute warps
+// need no more than 160 (their 16-column steps keep few values live); with 200 / 56 the producer,
+// drain and issuing warps spilled, and the kernel was 4-5 % slower (dense backward 218 against 205 us,
+// attention sink 934 against 895; 192 / 64, 176 / 80, 168 / 88, 152 / 104 and 144 / 112 all lie within
+// 1 % of 160 / 96, 184 / 72 was as slow as 200 / 56).
+constexpr int REGS_COMPUTE = 160, REGS_OTHER = 96;
 static_assert(256 * (REGS_COMPUTE - 128) <= 256 * (128 - REGS_OTHER), "setmaxnreg.inc would wait forever");
 
 // shared memory map (from a 1024-byte aligned base)
