@@ -85,15 +85,11 @@ constexpr int COL_P = 384;
 #define FA_TC_HALF_EXP 0
 #endif
 // One pair of exponentials in FA_TC_POLY_EVERY goes to the FMA pipe (a cubic, see fa_ex2_poly2).
-// Measured: with no score_mod, every fourth pair takes the forward from 0.118 to 0.114 ms (B8 H8
-// S2048 D64); with a score_mod in the loop the issue slots are already the scarcer resource and
-// nothing is gained, so it is off there.
+// Measured (B8 H8 S2048 D64): every fourth pair takes the forward without a score_mod from 0.118 to
+// 0.114 ms, with the checkerboard mod from 0.133 to 0.129 and causal + ALiBi from 0.088 to 0.085;
+// every eighth is about the same, every third and every second are slower again (the issue slots).
 #ifndef FA_TC_POLY_EVERY
-#if FA_HAS_SCORE_MOD
-#define FA_TC_POLY_EVERY 0
-#else
 #define FA_TC_POLY_EVERY 4
-#endif
 #endif
 constexpr int NT = 384;
 // Register split (setmaxnreg): the kernel starts with 168 registers per thread (65536 / 384, rounded
