@@ -1082,14 +1082,23 @@ size_t dq_acc_bytes(const fa_attn_params* p) {
   return (size_t)p->B * p->Hq * sq_pad * p->D * sizeof(float);
 }
 
-int get_bwd_tc_kernel(fa_module* m, int dtype, int D, int flags, Kernel** k) {
+// kv2: two K / V buffers with a three-stage Q / dO ring instead of one with four (head dim 64)
+int get_bwd_tc_kernel(fa_module* m, int dtype, int D, int flags, bool kv2, Kernel** k) {
   // must match the shared-memory map of fa_bwd_tc.cuh (fa_btc::SMEM_BYTES)
-  const int nstage = D == 64 ? 4 : 3, bq = D == 64 ? 128 : 64;
+  const int bq = D == 64 ? 128 : 64, kvbuf = (D == 64 && kv2) ? 2 : 1, nstage = (D == 64 && kvbuf == 1) ? 4 : 3;
   const int kv_bytes = (D / 64) * 16384, q_bytes = 16384, ds_bytes = (bq / 64) * 16384;
-  const int smem = 2 * kv_bytes + 2 * nstage * q_bytes + ds_bytes + 128 * 32 * 4 + nstage * 2 * bq * 4 +
-                   (1 + 3 * nstage + 12) * 8 + 16 + 16 + 2 * bwd_tc_max_pairs(D) * 4 + 256 + 1024;
-  std::string d = defs({{"FA_DTYPE", dtype}, {"FA_D", D}, {"FA_ROUND_SCORES", round_flag(dtype, flags)}});
+  const int smem = 2 * kvbuf * kv_bytes + 2 * nstage * q_bytes + ds_bytes + 128 * 32 * 4 + nstage * 2 * bq * 4 +
+                   (2 + 3 * nstage + 15) * 8 + 16 + 16 + 2 * bwd_tc_max_pairs(D) * 4 + 256 + 1024;
+  std::string d = defs({{"FA_DTYPE", dtype}, {"FA_D", D}, {"FA_ROUND_SCORES", round_flag(dtype, flags)},
+                        {"FA_BWD_KV2", kvbuf == 2 ? 1 : 0}});
   return get_kernel(m, "fa_bwd_tc.cuh", d, "fa_bwd_tc_kernel", smem, k);
+}
+
+// Short items (a BlockMask that leaves a kv tile at most 32 pairs, 16 on average under a causal mask)
+// take the variant with two K / V buffers; long ones the four-stage ring.
+bool bwd_tc_kv2(const fa_attn_params* p) {
+  if (p->D != 64 || !p->tables.kv_num_blocks) return false;
+  return (long long)((p->Sq + 127) / 128) * (p->Hq / p->Hkv) <= 32;
 }
 
 int get_mask_bits_kernel(fa_module* m, Kernel** k) {
@@ -1120,7 +1129,9 @@ int fa_module_prepare(fa_module* m, int kind, int dtype, int D, int Dv, int Sq_h
       BwdCfg c;
       if (int rc = pick_bwd(dtype, D, Dv, nullptr, c)) return rc;
       if (dtype != FA_F32 && D == Dv && (D == 64 || D == 128) && Sq_hint >= 128)
-        if (int rc = get_bwd_tc_kernel(m, dtype, D, 0, &k)) return rc;
+        if (int rc = get_bwd_tc_kernel(m, dtype, D, 0, false, &k)) return rc;
+        if (D == 64)
+          if (int rc = get_bwd_tc_kernel(m, dtype, D, 0, true, &k)) return rc;
       if (int rc = get_bwd_kernel(m, dtype, D, Dv, 0, c, true, &k)) return rc;
       return get_bwd_kernel(m, dtype, D, Dv, 0, c, false, &k);
     }
@@ -1184,7 +1195,7 @@ int fa_bwd(fa_module* m, const fa_attn_params* p, const fa_tensor* dout, const f
   BwdCfg c{};
   Kernel *kdq = nullptr, *kdkdv = nullptr, *ktc = nullptr;
   if (use_tc) {
-    if (int rc = get_bwd_tc_kernel(m, p->dtype, p->D, p->flags, &ktc)) return rc;
+    if (int rc = get_bwd_tc_kernel(m, p->dtype, p->D, p->flags, bwd_tc_kv2(p), &ktc)) return rc;
   } else {
     if (int rc = pick_bwd(p->dtype, p->D, p->Dv, &kp.t, c)) return rc;
     if (int rc = get_bwd_kernel(m, p->dtype, p->D, p->Dv, p->flags, c, true, &kdq)) return rc;

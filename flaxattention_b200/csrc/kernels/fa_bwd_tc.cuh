@@ -35,7 +35,8 @@
 //                      D = 128: S^T 0-63, dP^T 64-127, P^T 128-159, dQ^T 192-255, dV 256-383, dK 384-511
 // Every mbarrier wait is bounded (see fa_sm100.cuh).
 //
-// Compile-time parameters (macros): FA_DTYPE (0 fp16, 1 bf16), FA_D (64 or 128; Dv = D).
+// Compile-time parameters (macros): FA_DTYPE (0 fp16, 1 bf16), FA_D (64 or 128; Dv = D), FA_BWD_KV2
+// (two K / V buffers and a three-stage ring, head dim 64 only).
 #pragma once
 #include "fa_sm100.cuh"
 
@@ -67,7 +68,17 @@ constexpr int KV_BYTES = DATOMS * ATOM_BYTES;        // one K or V tile
 constexpr int Q_ATOM_BYTES = BQ * 128;               // BQ rows x 128 bytes
 constexpr int Q_BYTES = DATOMS * Q_ATOM_BYTES;       // one Q or dO tile (16 KB in both configurations)
 constexpr int DS_ATOMS = BQ / 64;                    // dS^T: [128 kv][BQ q] as atoms of 64 q columns
-constexpr int NSTAGE = D == 64 ? 4 : 3;
+// K / V buffers and Q / dO ring depth.  With D = 64 shared memory holds either one K / V buffer and a
+// ring of four stages, or two K / V buffers and a ring of three (FA_BWD_KV2): with two, K and V of the
+// next item are loaded while the current one is computed and nothing waits at the change of items,
+// which pays when items are short (causal S=2048, 8.5 pairs per item on average: 150 against 158 us)
+// and costs when they are long (dense S=2048, 16 pairs: 215 against 206 us - the fourth stage matters
+// more than the bubble).  The host picks.  With D = 128 there is one buffer and three stages.
+#ifndef FA_BWD_KV2
+#define FA_BWD_KV2 0
+#endif
+constexpr int KVBUF = (D == 64 && FA_BWD_KV2) ? 2 : 1;
+constexpr int NSTAGE = (D == 64 && KVBUF == 1) ? 4 : 3;
 constexpr int MAXPL = D == 64 ? 1024 : 2048;  // (head, q tile) pairs of one item (two such lists fit in shared memory)
 constexpr int MAXC = 256;                // 128-row q tiles per head (Sq <= 32768)
 constexpr int NT = 512;
@@ -84,15 +95,15 @@ static_assert(256 * (REGS_COMPUTE - 128) <= 256 * (128 - REGS_OTHER), "setmaxnre
 
 // shared memory map (from a 1024-byte aligned base)
 constexpr int OFF_K = 0;
-constexpr int OFF_V = OFF_K + KV_BYTES;
-constexpr int OFF_Q = OFF_V + KV_BYTES;                     // NSTAGE tiles
+constexpr int OFF_V = OFF_K + KVBUF * KV_BYTES;
+constexpr int OFF_Q = OFF_V + KVBUF * KV_BYTES;             // NSTAGE tiles
 constexpr int OFF_DO = OFF_Q + NSTAGE * Q_BYTES;            // NSTAGE tiles
 constexpr int OFF_DS = OFF_DO + NSTAGE * Q_BYTES;           // dS^T
 constexpr int OFF_DQ = OFF_DS + DS_ATOMS * ATOM_BYTES;      // fp32 staging 128 x 32 (half of the dQ tile at a time)
 constexpr int DQ_HALF_BYTES = 128 * 32 * 4;
 constexpr int OFF_ROW = OFF_DQ + DQ_HALF_BYTES;             // NSTAGE x (nlse2[BQ], ndelta[BQ]) floats
 constexpr int OFF_BAR = OFF_ROW + NSTAGE * 2 * BQ * 4;
-constexpr int NBARS = 1 + 3 * NSTAGE + 12;
+constexpr int NBARS = 2 + 3 * NSTAGE + 15;
 constexpr int OFF_MISC = OFF_BAR + NBARS * 8;               // tmem base, abort, -, drain flag
 constexpr int OFF_ITEM = OFF_MISC + 16;                     // int item[2][2]: item number, pairs (-1: no more work)
 constexpr int OFF_PAIR = OFF_ITEM + 16;                     // int pair[2][MAXPL]: q tile | mode << 16 | g << 20
@@ -106,20 +117,21 @@ constexpr int COL_DV = D == 64 ? 320 : 256;
 constexpr int COL_DK = D == 64 ? 384 : 384;
 static_assert(COL_P + BQ / 2 <= (D == 64 ? COL_DV : COL_DQ), "TMEM map");
 
-constexpr int BAR_KV = 0;
+constexpr int BAR_KV = 0;                   // [2] K and V of an item have landed in buffer kb
 // A stage's Q tile (with the row scalars) and dO tile are released separately: dO is last read by
 // product 3, Q by product 4, and the sooner a slot is free the further ahead the producer runs.
-constexpr int BAR_QFULL = 1, BAR_QEMPTY = 1 + NSTAGE, BAR_DOEMPTY = 1 + 2 * NSTAGE;
-constexpr int BAR_SFULL = 1 + 3 * NSTAGE;   // S^T and dP^T of a pair are in TMEM
+constexpr int BAR_QFULL = 2, BAR_QEMPTY = 2 + NSTAGE, BAR_DOEMPTY = 2 + 2 * NSTAGE;
+constexpr int BAR_SFULL = 2 + 3 * NSTAGE;   // S^T and dP^T of a pair are in TMEM
 constexpr int BAR_SFREE = BAR_SFULL + 1;    // compute warps hold them in registers (256 arrivals)
 constexpr int BAR_PREADY = BAR_SFULL + 2;   // P^T in TMEM and dS^T in smem (256 arrivals)
 constexpr int BAR_PFREE = BAR_SFULL + 3;    // products 3-5 of the pair are complete
 constexpr int BAR_DQFULL = BAR_SFULL + 4;   // dQ of the pair is in TMEM
 constexpr int BAR_DQFREE = BAR_SFULL + 5;   // drain warps hold it in registers (128 arrivals)
-constexpr int BAR_FINAL = BAR_SFULL + 6;    // products 3-5 of an item's last pair are complete
-constexpr int BAR_DKVFREE = BAR_SFULL + 7;  // the drain warps have read dK and dV of an item out of TMEM (128 arrivals)
-constexpr int BAR_LISTFULL = BAR_SFULL + 8; // [2] the producer has published an item and its pair list
-constexpr int BAR_LISTFREE = BAR_SFULL + 10;  // [2] the 15 consumers of a list are done with it
+constexpr int BAR_FINAL = BAR_SFULL + 6;    // [2] products 3-5 of the last pair of the item in buffer kb are complete
+constexpr int BAR_DKVFREE = BAR_SFULL + 8;  // the drain warps have read dK and dV of an item out of TMEM (128 arrivals)
+constexpr int BAR_LISTFULL = BAR_SFULL + 9; // [2] the producer has published an item and its pair list
+constexpr int BAR_LISTFREE = BAR_SFULL + 11;  // [2] the 15 consumers of a list are done with it
+constexpr int BAR_KVFREE = BAR_SFULL + 13;  // [2] (two K / V buffers) the stores of dK / dV staged in buffer kb have read it
 constexpr int LIST_CONSUMERS = 3 + 8 + 4;   // MMA issuers, compute warps, drain warps (one arrival each)
 
 __device__ __forceinline__ fa_u32 bar_addr(fa_u32 sb, int i) { return sb + OFF_BAR + i * 8; }
@@ -353,7 +365,11 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
 
   // ---- set-up --------------------------------------------------------------------------------
   if (tid == 0) {
-    fa_mbar_init(bar_addr(sb, BAR_KV), 1);
+    for (int i = 0; i < 2; ++i) {
+      fa_mbar_init(bar_addr(sb, BAR_KV + i), 1);
+      fa_mbar_init(bar_addr(sb, BAR_FINAL + i), 2);  // products 3-4 and product 5 of an item's last pair
+      fa_mbar_init(bar_addr(sb, BAR_KVFREE + i), 1);
+    }
     for (int s = 0; s < NSTAGE; ++s) {
       fa_mbar_init(bar_addr(sb, BAR_QFULL + s), 1);
       fa_mbar_init(bar_addr(sb, BAR_QEMPTY + s), 2);  // one arrival from each MMA issuer
@@ -365,7 +381,6 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
     fa_mbar_init(bar_addr(sb, BAR_PFREE), 2);  // one arrival from each of the issuers of products 3-4 and 5
     fa_mbar_init(bar_addr(sb, BAR_DQFULL), 1);
     fa_mbar_init(bar_addr(sb, BAR_DQFREE), 128);
-    fa_mbar_init(bar_addr(sb, BAR_FINAL), 2);  // products 3-4 and product 5 of an item's last pair
     fa_mbar_init(bar_addr(sb, BAR_DKVFREE), 128);
     for (int i = 0; i < 2; ++i) {
       fa_mbar_init(bar_addr(sb, BAR_LISTFULL + i), 1);
@@ -423,15 +438,17 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
         const int n0 = kt * BT;
         // The K / V buffers are free once the last products of the previous item are complete;
         // the Q / dO slots of the item's first pairs free up earlier, so those loads go first.
-        const int kvpos = kvc == 0 ? 0 : min(NSTAGE, np) - 1;
+        const int kb = kvc % KVBUF, use = kvc / KVBUF;
+        const int kvpos = (KVBUF == 2 || kvc == 0) ? 0 : min(NSTAGE, np) - 1;
         for (int n = 0; n < np && ok; ++n, ++gn) {
           if (n == kvpos) {
-            if (kvc > 0) ok = fa_mbar_wait(bar_addr(sb, BAR_FINAL), (fa_u32)((kvc - 1) & 1), abort_flag);
+            if (use > 0) ok = fa_mbar_wait(bar_addr(sb, (KVBUF == 2 ? BAR_KVFREE : BAR_FINAL) + kb), (fa_u32)((use - 1) & 1), abort_flag);
             if (!ok) break;
-            fa_mbar_expect_tx(bar_addr(sb, BAR_KV), 2 * KV_BYTES);
+            const fa_u32 full = bar_addr(sb, BAR_KV + kb);
+            fa_mbar_expect_tx(full, 2 * KV_BYTES);
             for (int a = 0; a < DATOMS; ++a) {
-              fa_tma_load_4d(sb + OFF_K + a * ATOM_BYTES, &P.tk, bar_addr(sb, BAR_KV), a * 64, n0, hk, b);
-              fa_tma_load_4d(sb + OFF_V + a * ATOM_BYTES, &P.tv, bar_addr(sb, BAR_KV), a * 64, n0, hk, b);
+              fa_tma_load_4d(sb + OFF_K + kb * KV_BYTES + a * ATOM_BYTES, &P.tk, full, a * 64, n0, hk, b);
+              fa_tma_load_4d(sb + OFF_V + kb * KV_BYTES + a * ATOM_BYTES, &P.tv, full, a * 64, n0, hk, b);
             }
           }
           const int s = gn % NSTAGE;
@@ -456,7 +473,7 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
         }
         // K and V of the next item are asked into L2 now; their loads can only start when this
         // item is complete, and then they find the tiles close by
-        if (ok && next < n_items) {
+        if (KVBUF == 1 && ok && next < n_items) {
           const int hk2 = next % p.Hkv, b2 = (next / p.Hkv) % p.B, n2 = (next / (p.Hkv * p.B)) * BT;
           for (int a = 0; a < DATOMS; ++a) {
             tma_prefetch_l2_4d(&P.tk, a * 64, n2, hk2, b2);
@@ -479,7 +496,6 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
     const bool leader = fa_elect_one();
     constexpr fa_u32 IDESC_KK = fa_idesc(DT, 128, BQ, 0, 0);  // A, B K-major, N = BQ
     constexpr fa_u32 HI = fa_desc_hi_sw128();
-    const fa_u32 loK_k = fa_desc_lo(sb + OFF_K, 16), loV_k = fa_desc_lo(sb + OFF_V, 16);
     bool ok = true;
     int gn = 0, kvc = 0;
     for (int itc = 0; ok; ++itc) {
@@ -490,7 +506,9 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
       if (leader) fa_mbar_arrive(bar_addr(sb, BAR_LISTFREE + lb));  // (the issuers need the count only)
       if (np < 0) break;
       if (np == 0) continue;
-      ok = fa_mbar_wait_all(bar_addr(sb, BAR_KV), (fa_u32)(kvc & 1), abort_flag);
+      const int kb = kvc % KVBUF;
+      const fa_u32 loK_k = fa_desc_lo(sb + OFF_K + kb * KV_BYTES, 16), loV_k = fa_desc_lo(sb + OFF_V + kb * KV_BYTES, 16);
+      ok = fa_mbar_wait_all(bar_addr(sb, BAR_KV + kb), (fa_u32)((kvc / KVBUF) & 1), abort_flag);
       for (int n = 0; n < np && ok; ++n, ++gn) {
         const int s = gn % NSTAGE;
         ok = fa_mbar_wait_all(bar_addr(sb, BAR_QFULL + s), (fa_u32)((gn / NSTAGE) & 1), abort_flag);
@@ -559,7 +577,7 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
         if (leader) {
           fa_mma_commit(bar_addr(sb, BAR_QEMPTY + s));   // second arrival: the Q tile and row scalars are free
           fa_mma_commit(bar_addr(sb, BAR_PFREE));        // one of the two arrivals that free P^T and dS^T
-          if (n + 1 == np) fa_mma_commit(bar_addr(sb, BAR_FINAL));
+          if (n + 1 == np) fa_mma_commit(bar_addr(sb, BAR_FINAL + kvc % KVBUF));
         }
       }
       ++kvc;
@@ -571,7 +589,6 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
     const bool leader = fa_elect_one();
     constexpr fa_u32 IDESC_NN = fa_idesc(DT, 128, 64, 1, 1);    // A, B MN-major, M = 128, N = 64
     constexpr fa_u32 HI = fa_desc_hi_sw128();
-    const fa_u32 loK_mn = fa_desc_lo(sb + OFF_K, ATOM_BYTES);
     const fa_u32 loDS_mn = fa_desc_lo(sb + OFF_DS, ATOM_BYTES);
     bool ok = true;
     int gn = 0, kvc = 0;
@@ -583,7 +600,9 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
       if (leader) fa_mbar_arrive(bar_addr(sb, BAR_LISTFREE + lb));
       if (np < 0) break;
       if (np == 0) continue;
-      ok = fa_mbar_wait_all(bar_addr(sb, BAR_KV), (fa_u32)(kvc & 1), abort_flag);
+      const int kb = kvc % KVBUF;
+      const fa_u32 loK_mn = fa_desc_lo(sb + OFF_K + kb * KV_BYTES, ATOM_BYTES);
+      ok = fa_mbar_wait_all(bar_addr(sb, BAR_KV + kb), (fa_u32)((kvc / KVBUF) & 1), abort_flag);
       for (int n = 0; n < np && ok; ++n, ++gn) {
         ok = fa_mbar_wait_all(bar_addr(sb, BAR_PREADY), (fa_u32)(gn & 1), abort_flag);
         // the drain warps must have emptied the dQ columns of the previous pair
@@ -604,7 +623,7 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
         if (leader) {
           fa_mma_commit(bar_addr(sb, BAR_PFREE));
           fa_mma_commit(bar_addr(sb, BAR_DQFULL));
-          if (n + 1 == np) fa_mma_commit(bar_addr(sb, BAR_FINAL));  // (this product is the last reader of K)
+          if (n + 1 == np) fa_mma_commit(bar_addr(sb, BAR_FINAL + kb));  // (this product is the last reader of K)
         }
       }
       ++kvc;
@@ -793,7 +812,8 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
       // memory took several thousand cycles per item: 32 different lines per instruction.)
       // An item without pairs has zeros written.
       if (np > 0) {
-        ok = fa_mbar_wait_warp(bar_addr(sb, BAR_FINAL), (fa_u32)(kvc & 1), abort_flag);
+        const int kb = kvc % KVBUF;
+        ok = fa_mbar_wait_warp(bar_addr(sb, BAR_FINAL + kb), (fa_u32)((kvc / KVBUF) & 1), abort_flag);
         if (!ok) misc[3] = 1;
         named_bar_sync(1, 128);
         if (misc[3] != 0) {
@@ -801,26 +821,24 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
           break;
         }
         fa_tc_fence_after();
-      }
-      {
-        unsigned char* strow = sm + OFF_DQ + r * 128;
 #pragma unroll 1
         for (int part = 0; part < 2 * DATOMS; ++part) {
           const int which = part / DATOMS, a = part - which * DATOMS;  // dK atoms first, then dV
           const float mul = which == 0 ? p.scale : 1.f;
-          // the previous bulk operation must have finished reading the staging buffer
-          if (dtid == 0) bulk_wait_read0();
-          named_bar_sync(1, 128);
+          // two K / V buffers: the staging buffers are the item's own K and V tiles, which nothing reads
+          // any more; one: the parts go through the dQ staging buffer one after the other
+          const int st_off = KVBUF == 2 ? (which == 0 ? OFF_K : OFF_V) + kb * KV_BYTES + a * ATOM_BYTES : OFF_DQ;
+          unsigned char* strow = sm + st_off + r * 128;
+          if (KVBUF == 1) {
+            // the previous bulk operation must have finished reading the staging buffer
+            if (dtid == 0) bulk_wait_read0();
+            named_bar_sync(1, 128);
+          }
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
             float o[16];
-            if (np > 0) {
-              fa_tmem_ld16(t_lane + (which == 0 ? COL_DK : COL_DV) + a * 64 + c * 16, o);
-              fa_tmem_wait_ld();
-            } else {
-#pragma unroll
-              for (int e = 0; e < 16; ++e) o[e] = 0.f;
-            }
+            fa_tmem_ld16(t_lane + (which == 0 ? COL_DK : COL_DV) + a * 64 + c * 16, o);
+            fa_tmem_wait_ld();
 #pragma unroll
             for (int e = 0; e < 16; e += 8) {
               uint4 w;
@@ -831,16 +849,39 @@ extern "C" __global__ void __launch_bounds__(fa_btc::NT, 1) fa_bwd_tc_kernel(con
               *(uint4*)(strow + (((2 * c + (e >> 3)) ^ (r & 7)) * 16)) = w;
             }
           }
-          if (part == 2 * DATOMS - 1 && np > 0) {
+          if (part == 2 * DATOMS - 1) {
             // dK and dV are out of TMEM: the next item's first products may overwrite them
             fa_tc_fence_before();
             fa_mbar_arrive(bar_addr(sb, BAR_DKVFREE));
           }
-          fence_proxy_async();
-          named_bar_sync(1, 128);
+          if (KVBUF == 1 || part == 2 * DATOMS - 1) {
+            fence_proxy_async();
+            named_bar_sync(1, 128);
+          }
           if (dtid == 0) {
-            fa_tma_store_4d(which == 0 ? &P.tdk : &P.tdv, sb + OFF_DQ, a * 64, n0, hk, b);
-            bulk_commit();
+            if (KVBUF == 1) {
+              fa_tma_store_4d(which == 0 ? &P.tdk : &P.tdv, sb + OFF_DQ, a * 64, n0, hk, b);
+              bulk_commit();
+            } else if (part == 2 * DATOMS - 1) {
+              for (int a2 = 0; a2 < DATOMS; ++a2) {
+                fa_tma_store_4d(&P.tdk, sb + OFF_K + kb * KV_BYTES + a2 * ATOM_BYTES, a2 * 64, n0, hk, b);
+                fa_tma_store_4d(&P.tdv, sb + OFF_V + kb * KV_BYTES + a2 * ATOM_BYTES, a2 * 64, n0, hk, b);
+              }
+              bulk_commit();
+              bulk_wait_read0();
+              fa_mbar_arrive(bar_addr(sb, BAR_KVFREE + kb));
+            }
+          }
+        }
+      } else {
+        // an item without pairs: zeros, straight from the registers (rare; a row per thread)
+        const int kv = n0 + r;
+        if (kv < p.Skv) {
+#pragma unroll
+          for (int which = 0; which < 2; ++which) {
+            const FaTensor& dst = which == 0 ? p.dk : p.dv;
+            char* og = (char*)dst.ptr + ((long long)b * dst.sb + (long long)hk * dst.sh + (long long)kv * dst.ss) * 2;
+            for (int c = 0; c < D / 8; ++c) *(uint4*)(og + c * 16) = make_uint4(0u, 0u, 0u, 0u);
           }
         }
       }
