@@ -1094,12 +1094,13 @@ int get_bwd_tc_kernel(fa_module* m, int dtype, int D, int flags, bool kv2, Kerne
   return get_kernel(m, "fa_bwd_tc.cuh", d, "fa_bwd_tc_kernel", smem, k);
 }
 
-// Short items (a BlockMask that leaves a kv tile at most 24 pairs, 12 on average under a causal mask)
-// take the variant with two K / V buffers; long ones the four-stage ring (measured: 8.5 pairs on
-// average gain 5 %, 16 pairs lose 4 %).
+// With a BlockMask the items are short or uneven and the variant with two K / V buffers wins: under a
+// causal mask 97 against 103 us at S=1024 (B16 H8), 150 / 160 at 2048, 197 / 209 at 3072, 263 / 283
+// at 4096, 289 / 303 at 6144 (48 q tiles, 24 pairs per item on average).  Without one every item
+// has all the q tiles and the four-stage ring wins (S=2048, 16 pairs per item: 206 against 215 us).
 bool bwd_tc_kv2(const fa_attn_params* p) {
   if (p->D != 64 || !p->tables.kv_num_blocks) return false;
-  return (long long)((p->Sq + 127) / 128) * (p->Hq / p->Hkv) <= 24;
+  return (long long)((p->Sq + 127) / 128) * (p->Hq / p->Hkv) <= 64;
 }
 
 int get_mask_bits_kernel(fa_module* m, Kernel** k) {
