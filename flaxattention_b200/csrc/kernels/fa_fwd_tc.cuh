@@ -81,9 +81,6 @@ constexpr int COL_S = 0, COL_O = 256;
 // 512 columns are taken by S and O, and P overwrites the S columns it was computed from.
 constexpr bool SEP_P = D == 64;
 constexpr int COL_P = 384;
-#ifndef FA_TC_HALF_EXP
-#define FA_TC_HALF_EXP 0
-#endif
 // One pair of exponentials in FA_TC_POLY_EVERY goes to the FMA pipe (a cubic, see fa_ex2_poly2).
 // Measured (B8 H8 S2048 D64): every fourth pair takes the forward without a score_mod from 0.118 to
 // 0.114 ms, with the checkerboard mod from 0.133 to 0.129 and causal + ALiBi from 0.088 to 0.085;
@@ -231,10 +228,6 @@ __device__ __forceinline__ void pass2_chunk(const float (&v)[32], fa_u32 (&pk)[1
   for (int e = 0; e < 16; ++e) {
     float a0, a1;
     fa_f2_unpack(fa_fma2(fa_f2(v[2 * e], v[2 * e + 1]), cmul, negm), a0, a1);
-#if FA_TC_HALF_EXP
-    pk[e] = fa_ex2_h2<DT>(fa_pack2<DT>(a0, a1));
-    const fa_u64 pf = fa_h2_to_f2<DT>(pk[e]);
-#else
     // one pair in FA_TC_POLY_EVERY takes its exponentials on the FMA pipe: the SFU (16 per clock
     // and SM) is what bounds this loop
     float p0, p1;
@@ -246,7 +239,6 @@ __device__ __forceinline__ void pass2_chunk(const float (&v)[32], fa_u32 (&pk)[1
     }
     pk[e] = fa_pack2<DT>(p0, p1);
     const fa_u64 pf = fa_f2(p0, p1);
-#endif
     if (e & 1) sum_b = fa_add2(sum_b, pf);
     else sum_a = fa_add2(sum_a, pf);
   }
@@ -376,9 +368,8 @@ __device__ __forceinline__ bool softmax_step(SoftmaxCtx& c, const int j, const i
   }
   // ---- pass 2: p = 2^(x * cmul - m) and the row sum; P goes to TMEM as 16-bit pairs (its own
   // columns with D = 64, over the first 64 score columns otherwise).
-  // With FA_TC_HALF_EXP the exponent is rounded to the 16-bit input type first and one SFU
-  // operation yields both values of a pair already in the format the second product needs;
-  // the row sum is then taken over exactly the values that product sees.
+  // (Packed 16-bit exponentials - ex2.approx.f16x2, one SFU operation per pair - were measured
+  // slower: 143 against 131 us, the conversions around them cost more than the SFU time they save.)
   const float m_use = (m_ref == FA_NEG_INF) ? 0.f : m_ref;
   const fa_u64 negm = fa_f2(-m_use, -m_use);
   const float cm = in_place ? 1.f : sc2;

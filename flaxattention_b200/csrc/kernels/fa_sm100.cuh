@@ -316,25 +316,3 @@ __device__ __forceinline__ void fa_tmem_st16f(fa_u32 taddr, const float (&v)[16]
   fa_tmem_st16(taddr, r);
 }
 
-// exp2 of two 16-bit values at once (one SFU operation for the pair); DT selects f16 / bf16
-template <int DT>
-__device__ __forceinline__ fa_u32 fa_ex2_h2(fa_u32 x) {
-  fa_u32 r;
-  if (DT == FA_DT_F16) asm("ex2.approx.f16x2 %0, %1;" : "=r"(r) : "r"(x));
-  else asm("ex2.approx.ftz.bf16x2 %0, %1;" : "=r"(r) : "r"(x));
-  return r;
-}
-// widen a packed 16-bit pair to a packed fp32 pair
-template <int DT>
-__device__ __forceinline__ fa_u64 fa_h2_to_f2(fa_u32 x) {
-  if (DT == FA_DT_F16) {
-    fa_u16 lo, hi;
-    float a, b;
-    asm("mov.b32 {%0, %1}, %2;" : "=h"(lo), "=h"(hi) : "r"(x));
-    asm("cvt.f32.f16 %0, %1;" : "=f"(a) : "h"(lo));
-    asm("cvt.f32.f16 %0, %1;" : "=f"(b) : "h"(hi));
-    return fa_f2(a, b);
-  } else {
-    return fa_f2(__uint_as_float(x << 16), __uint_as_float(x & 0xffff0000u));
-  }
-}
